@@ -1,0 +1,442 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 Gated DeltaNet-2 kernels.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One "step" = one forward + backward pass of ``chunk_gdn2`` over one batch of synthetic
+input with the training configuration of the benchmark specification (per GPU: B=4,
+T=8192, H=32, D=128, bf16 q/k/v/beta/w, fp32 g and state, loss = mean(o^2)+mean(S_T^2)).
+With N > 1 (launched by ``torch.distributed.run``) every rank processes its own batch
+shard of the same size -- (batch, head) pairs are independent, there is no collective on
+the compute path -- and the value is all ranks' tokens over the slowest rank's time.
+
+Rank 0 prints ONE JSON line: tokens/s with inputs resident in HBM (``value``), the same
+through the public API from pinned host buffers (``e2e``), the live-timed dominant kernel
+against the HBM roofline (``roofline``), the CPU port timed on the host (``cpu_baseline``),
+decode figures (``decode``) and the GPU clocks seen while timing (``clocks``).
+
+``--impl reference`` times the reference project's own algorithm for this path -- its
+PyTorch recurrence plus autograd, restated in oracle/gdn2_oracle.py -- on the host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "chunk_gdn2 fwd+bwd tokens/s at T=8192 (H=32, D=128)"
+UNIT = "tokens/s"
+# algorithmic bytes per token-head (bf16 sequence tensors, fp32 g), K = V = 128
+FWD_BYTES = 5 * 256 + 512 + 256                 # read q k v beta w + g, write o
+BWD_BYTES = (5 * 256 + 512 + 256) + (5 * 256 + 512)  # read inputs + dO, write 6 grads
+DECODE_BYTES_PER_HEAD = 2 * 65536 + 1792 + 256
+T1_ZERO_BYTES_PER_HEAD = 65536 + 1280
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("b200", "reference"), default="b200")
+    ap.add_argument("--batch", type=int, default=4, help="per-GPU batch")
+    ap.add_argument("--time", type=int, default=8192)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--skip-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-decode", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true")
+    return ap.parse_args()
+
+
+# --------------------------------------------------------------------------------------
+# CPU arm: the reference's PyTorch path (port), all host threads
+# --------------------------------------------------------------------------------------
+def cpu_fwd_bwd_once(inputs):
+    """fwd+bwd of the reference's fp32 PyTorch recurrence (reference.py:47-99) via autograd."""
+
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import gdn2_oracle as oracle
+
+    leaves = [t.detach().clone().requires_grad_(True) for t in inputs[:6]]
+    s0 = inputs[6].detach().clone().requires_grad_(True)
+    out, fin = oracle.recurrence(*leaves, s0, dtype=torch.float32)
+    loss = out.square().mean() + fin.square().mean()
+    torch.autograd.grad(loss, leaves + [s0])
+    return float(loss.detach())
+
+
+def cpu_sample_inputs(heads, sample_tokens):
+    sys.path.insert(0, str(ROOT / "oracle"))
+    import gdn2_oracle as oracle
+
+    return oracle.make_inputs(1, sample_tokens, heads, seed=0)
+
+
+def run_cpu_baseline(heads, budget_s=12.0):
+    """Time the CPU port on a bounded sample (first tokens of one batch row, all heads)."""
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    cores = torch.get_num_threads()
+    sample_tokens = 64
+    inputs = cpu_sample_inputs(heads, sample_tokens)
+    cpu_fwd_bwd_once(inputs)  # warm-up
+    t0 = time.perf_counter()
+    cpu_fwd_bwd_once(inputs)
+    once = time.perf_counter() - t0
+    reps = max(1, min(20, int(budget_s / max(once, 1e-3))))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        cpu_fwd_bwd_once(inputs)
+    elapsed = (time.perf_counter() - t0) / reps
+    return {
+        "value": sample_tokens / elapsed,
+        "unit": UNIT,
+        "cores": cores,
+        "kind": "port",
+        "sample": f"B=1, T={sample_tokens}, H={heads} slice of the workload, fp32 torch recurrence + autograd, "
+                  f"mean of {reps} runs",
+    }
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    sample_tokens = 64
+    inputs = cpu_sample_inputs(args.heads, sample_tokens)
+    for _ in range(max(1, min(args.warmup, 3))):
+        cpu_fwd_bwd_once(inputs)
+    steps = max(1, args.steps)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_fwd_bwd_once(inputs)
+    ms = (time.perf_counter() - t0) * 1e3 / steps
+    value = sample_tokens / (ms * 1e-3)
+    line = {
+        "impl": "reference",
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 inputs, fp32 state", "data": "synthetic",
+        "config": {"workload": f"train fwd+bwd B={args.batch} T={args.time} H={args.heads} D=128 per GPU",
+                   "sample_per_step": f"B=1, T={sample_tokens}, H={args.heads}"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"B=1, T={sample_tokens}, H={args.heads} per step"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------
+def device_inputs(batch, time_, heads, device, seed):
+    """Benchmark distributions drawn on the device (seeded CUDA generator)."""
+
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    shape = (batch, time_, heads, 128)
+
+    def normal(*size):
+        return torch.randn(*size, generator=gen, device=device, dtype=torch.float32)
+
+    q = torch.nn.functional.normalize(normal(*shape), dim=-1).bfloat16()
+    k = torch.nn.functional.normalize(normal(*shape), dim=-1).bfloat16()
+    v = normal(*shape).bfloat16()
+    beta = torch.sigmoid(normal(*shape)).bfloat16()
+    w = torch.sigmoid(normal(*shape)).bfloat16()
+    g = -torch.clamp(torch.nn.functional.softplus(normal(*shape) - 2.0), max=5.0)
+    s0 = 0.02 * normal(batch, heads, 128, 128)
+    return [q, k, v, g, beta, w, s0]
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, maxes, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        try:
+            for row in open(self.path):
+                cells = [c.strip() for c in row.split(",")]
+                if len(cells) < 9:
+                    continue
+                try:
+                    clocks.append(float(cells[1]))
+                    maxes.append(float(cells[2]))
+                except ValueError:
+                    continue
+                for name, cell in zip(names, cells[5:9]):
+                    if cell.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        return {
+            "sm_mhz": statistics.median(clocks) if clocks else None,
+            "sm_max_mhz": max(maxes) if maxes else None,
+            "samples": len(clocks),
+            "reasons": sorted(reasons),
+        }
+
+
+def measured_peak_hbm():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except (KeyError, ValueError):
+            pass
+    return 6650.0, "fallback"
+
+
+def train_step(pkg, leaves, s0):
+    out, fin = pkg.chunk_gdn2(*leaves, s0, output_final_state=True)
+    loss = out.float().square().mean() + fin.square().mean()
+    grads = torch.autograd.grad(loss, (*leaves, s0))
+    return loss, grads
+
+
+def run_gpu_arm(args):
+    import torch.distributed as dist
+
+    import gdn2_sm120_b200 as pkg
+    from gdn2_sm120_b200 import _lib, shard
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} does not match WORLD_SIZE {world}")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    _lib.lib()  # fail loudly if the CUDA library is missing
+
+    B, T, H = args.batch, args.time, args.heads
+    # weak scaling: every rank owns one batch shard of the per-GPU size
+    inputs = device_inputs(B, T, H, device, seed=1000 * 0 + rank)
+    leaves = [t.requires_grad_(True) for t in inputs[:6]]
+    s0 = inputs[6].requires_grad_(True)
+    tokens_per_rank = B * T
+    token_heads = B * T * H
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing -----------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        train_step(pkg, leaves, s0)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches_before = _lib.LAUNCHES[0]
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    begin.record()
+    for _ in range(args.steps):
+        loss, grads = train_step(pkg, leaves, s0)
+    end.record()
+    barrier()
+    launches = _lib.LAUNCHES[0] - launches_before
+    clocks = sampler.stop() if rank == 0 else None
+    ms_local = begin.elapsed_time(end) / args.steps
+    ms = shard.max_over_ranks(ms_local, device)
+    value = world * tokens_per_rank / (ms * 1e-3)
+    del grads
+
+    # ---- live per-kernel timing (dominant kernel -> roofline) ------------------------------
+    _lib.KERNEL_EVENTS = {}
+    for _ in range(3):
+        train_step(pkg, leaves, s0)
+    torch.cuda.synchronize()
+    kernel_ms = {name: statistics.mean(b.elapsed_time(e) for b, e in pairs)
+                 for name, pairs in _lib.KERNEL_EVENTS.items()}
+    _lib.KERNEL_EVENTS = None
+    kernel_bytes = {
+        "gdn2_token_forward": FWD_BYTES * token_heads,
+        "gdn2_chunk_forward": FWD_BYTES * token_heads,
+        "gdn2_token_chunk_vjp": BWD_BYTES * token_heads,
+        "gdn2_chunk_backward": BWD_BYTES * token_heads,
+        # the cotangent scan re-reads q, k, g, beta, dO: overhead traffic, its own compulsory bytes
+        "gdn2_token_dstate_scan": (3 * 256 + 512 + 256) * token_heads,
+    }
+    peak, peak_kind = measured_peak_hbm()
+    dominant = max(kernel_ms, key=kernel_ms.get) if kernel_ms else None
+    roofline = None
+    if dominant is not None:
+        achieved = kernel_bytes.get(dominant, 0) / (kernel_ms[dominant] * 1e-3) / 1e9
+        roofline = {
+            "bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak,
+            "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+            "kernel_ms": kernel_ms,
+            "step_algorithmic_gbs": (FWD_BYTES + BWD_BYTES) * token_heads / (ms_local * 1e-3) / 1e9,
+        }
+
+    # ---- end to end: pinned host inputs copied in every step, loss read back ----------------
+    e2e = None
+    if not args.skip_e2e:
+        host = [t.detach().cpu().pin_memory() for t in inputs]
+        h2d_bytes = sum(t.numel() * t.element_size() for t in host)
+        staging = [torch.empty_like(t.detach()) for t in inputs]
+
+        def e2e_step():
+            for dst, src in zip(staging, host):
+                dst.copy_(src, non_blocking=True)
+            lv = [t.requires_grad_(True) for t in staging[:6]]
+            st = staging[6].requires_grad_(True)
+            loss_, grads_ = train_step(pkg, lv, st)
+            value_ = loss_.item()  # device -> host read of the step's result
+            for t in staging:
+                t.requires_grad_(False)
+            return value_
+
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        b2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b2.record()
+        for _ in range(args.steps):
+            e2e_step()
+        e2.record()
+        barrier()
+        e2e_ms = shard.max_over_ranks(b2.elapsed_time(e2) / args.steps, device)
+        e2e = {"value": world * tokens_per_rank / (e2e_ms * 1e-3), "unit": UNIT,
+               "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms}
+        del host, staging
+
+    # ---- decode figures (rank-local, reported by rank 0) -------------------------------------
+    decode = None
+    if not args.skip_decode and rank == 0:
+        decode = run_decode(pkg, device, peak)
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.skip_cpu_baseline:
+        cpu_baseline = run_cpu_baseline(H)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16 inputs, fp32 state", "data": "synthetic",
+            "config": {"workload": f"train fwd+bwd B={B} T={T} H={H} D=128 per GPU, loss=mean(o^2)+mean(S_T^2)",
+                       "global_batch": B * world, "seq_len": T, "heads": H, "parallelism": f"dp{world} over batch",
+                       "l2": "inputs (1.8 GB/step) exceed the 126 MB L2"},
+            "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
+            "cpu_baseline": cpu_baseline, "decode": decode,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_decode(pkg, device, peak):
+    """Decode configuration (B=64, H=32, T=1, in-place state) and zero-state closed form
+    (B=256, H=32).  States rotate through buffers larger than L2."""
+
+    from gdn2_sm120_b200 import _lib
+
+    results = {}
+    B, H = 64, 32
+    inp = device_inputs(B, 1, H, device, seed=7)
+    states = [inp[6].clone() for _ in range(4)]  # 4 x 128 MiB > L2
+    out = torch.empty_like(inp[0])
+    reps = 40
+
+    def step(i):
+        pkg.recurrent_gdn2(*inp[:6], states[i % 4], out=out, inplace_final_state=True)
+
+    for i in range(8):
+        step(i)
+    torch.cuda.synchronize()
+    b, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    b.record()
+    for i in range(reps):
+        step(i)
+    e.record()
+    torch.cuda.synchronize()
+    api_us = b.elapsed_time(e) * 1e3 / reps
+    _lib.KERNEL_EVENTS = {}
+    for i in range(reps):
+        step(i)
+    torch.cuda.synchronize()
+    pairs = _lib.KERNEL_EVENTS["gdn2_token_forward"]
+    _lib.KERNEL_EVENTS = None
+    kern_us = statistics.median(x.elapsed_time(y) for x, y in pairs) * 1e3
+    gbs = DECODE_BYTES_PER_HEAD * B * H / (kern_us * 1e-6) / 1e9
+    results["in_place_B64_H32"] = {
+        "us_per_step_api": api_us, "us_per_step_kernel": kern_us, "hbm_gbs": gbs,
+        "frac_of_measured_peak": gbs / peak, "frac_of_8TBs": gbs / 8000.0}
+
+    B = 256
+    inp = device_inputs(B, 1, H, device, seed=8)
+    finals = [torch.empty((B, H, 128, 128), device=device) for _ in range(2)]
+    out = torch.empty_like(inp[0])
+    for i in range(4):
+        pkg.recurrent_gdn2(*inp[:6], out=out, final_state_out=finals[i % 2])
+    torch.cuda.synchronize()
+    _lib.KERNEL_EVENTS = {}
+    for i in range(20):
+        pkg.recurrent_gdn2(*inp[:6], out=out, final_state_out=finals[i % 2])
+    torch.cuda.synchronize()
+    pairs = _lib.KERNEL_EVENTS["gdn2_token_forward_t1_zero"]
+    _lib.KERNEL_EVENTS = None
+    kern_us = statistics.median(x.elapsed_time(y) for x, y in pairs) * 1e3
+    gbs = T1_ZERO_BYTES_PER_HEAD * B * H / (kern_us * 1e-6) / 1e9
+    results["zero_state_B256_H32"] = {"us_per_step_kernel": kern_us, "hbm_gbs": gbs,
+                                      "frac_of_measured_peak": gbs / peak, "frac_of_8TBs": gbs / 8000.0}
+    return results
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

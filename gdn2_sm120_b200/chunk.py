@@ -1,0 +1,147 @@
+"""Chunkwise forward: host wrapper.
+
+Mirrors ``chunk_forward`` / ``ChunkForwardAux`` of the reference
+(src/gdn2_sm120/chunk.py:1056-1075, 1160-1419): same signature, validation, ``out`` /
+``final_state_out`` rules (``final_state_out`` may alias ``initial_state`` exactly,
+never partially) and the ``return_aux`` contract used by the autograd wrapper.
+
+A sequence is split into ``full_tokens = 64 * (T // 64)`` tokens that the tensor-core
+chunk kernels process and a ragged tail of ``T - full_tokens < 64`` tokens that the
+exact fp32 token kernels process on the same buffers (the reference does the same with
+its scalar tail scan, chunk.py:1021-1053).  When the chunk kernels are not enabled for
+a call, ``full_tokens`` is 0 and the token kernels cover the whole sequence.
+
+Activation checkpoints for backward are the fp32 states at chunk / span starts only;
+every WY factor is recomputed in backward instead of being written to HBM, because the
+path is HBM-bound on B200.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib, _validate
+from .recurrent import _byte_span, _launch_token_forward, _spans_overlap
+
+_DIM = _validate.DIM
+_CHUNK = 64           # tokens per tensor-core chunk
+_TOKEN_INTERVAL = 16  # tokens between two token-path boundary slots
+
+
+@dataclass(frozen=True)
+class ChunkForwardAux:
+    """State checkpoints consumed by the checkpointed backward.
+
+    ``chunk_boundaries``  fp32 ``[B, full_tokens/64 + 1, H, 128, 128]``: state before every
+                          64-token chunk and after the last one, or ``None``.
+    ``tail_boundaries``   fp32 ``[B, ceil(tail/16) + 1, H, 128, 128]``: state before every
+                          16-token span of the tail ``[full_tokens, T)`` and after it, or
+                          ``None`` when there is no tail.
+    ``full_tokens``       number of leading tokens covered by ``chunk_boundaries``.
+    """
+
+    chunk_boundaries: torch.Tensor | None
+    tail_boundaries: torch.Tensor | None
+    full_tokens: int
+
+
+def _token_slots(tokens: int) -> int:
+    return -(-tokens // _TOKEN_INTERVAL) + 1
+
+
+def _chunk_kernel_tokens(time: int) -> int:
+    """Leading tokens handed to the tensor-core chunk kernels for a call."""
+
+    from . import chunk_kernels
+
+    return chunk_kernels.supported_tokens(time)
+
+
+def chunk_forward(
+    q,
+    k,
+    v,
+    g,
+    beta,
+    w,
+    initial_state=None,
+    *,
+    scale: float | None = None,
+    return_aux: bool = False,
+    out=None,
+    final_state_out=None,
+):
+    """Run the chunkwise forward; returns ``(output, final_state[, aux])``."""
+
+    batch, time, heads = _validate.sequence_inputs(
+        q, k, v, g, beta, w, dim_error=NotImplementedError, need_tokens=True, need_alignment=True
+    )
+    if initial_state is not None:
+        _validate.state("initial_state", initial_state, batch, heads, q.device, need_alignment=True)
+    output_scale = _validate.float32_scale(scale)
+    if return_aux and (out is not None or final_state_out is not None):
+        raise ValueError("preallocated outputs are supported only when return_aux=False")
+
+    state_shape = (batch, heads, _DIM, _DIM)
+    if out is None:
+        output = torch.empty_like(v)
+    else:
+        _validate.buffer("out", out, v.shape, v.dtype, q.device, need_alignment=True)
+        output = out
+    if final_state_out is None:
+        final_state = torch.empty(state_shape, device=q.device, dtype=torch.float32)
+    else:
+        _validate.buffer("final_state_out", final_state_out, state_shape, torch.float32, q.device,
+                         need_alignment=True)
+        final_state = final_state_out
+
+    if out is not None or final_state_out is not None:
+        seq_spans = [_byte_span(t) for t in (q, k, v, g, beta, w)]
+        init_span = _byte_span(initial_state) if initial_state is not None else None
+        out_span, final_span = _byte_span(output), _byte_span(final_state)
+        if out is not None:
+            if any(_spans_overlap(out_span, s) for s in seq_spans) or (
+                init_span is not None and _spans_overlap(out_span, init_span)
+            ):
+                raise ValueError("out must not overlap an input tensor")
+            if _spans_overlap(out_span, final_span):
+                raise ValueError("out and final_state_out must not overlap")
+        if final_state_out is not None:
+            if any(_spans_overlap(final_span, s) for s in seq_spans):
+                raise ValueError("final_state_out must not overlap a sequence input")
+            if init_span is not None and final_span != init_span and _spans_overlap(final_span, init_span):
+                raise ValueError(
+                    "final_state_out may exactly alias initial_state but must not partially overlap it"
+                )
+
+    full_tokens = _chunk_kernel_tokens(time)
+    tail = time - full_tokens
+    chunk_boundaries = tail_boundaries = None
+    if return_aux:
+        if full_tokens:
+            chunk_boundaries = torch.empty(
+                (batch, full_tokens // _CHUNK + 1, heads, _DIM, _DIM), device=q.device, dtype=torch.float32
+            )
+        if tail:
+            tail_boundaries = torch.empty(
+                (batch, _token_slots(tail), heads, _DIM, _DIM), device=q.device, dtype=torch.float32
+            )
+
+    state = initial_state
+    if full_tokens:
+        from . import chunk_kernels
+
+        chunk_kernels.forward(q, k, v, g, beta, w, state, output, final_state, chunk_boundaries,
+                              batch, time, heads, full_tokens, output_scale)
+        state = final_state
+    if tail:
+        _launch_token_forward(q, k, v, g, beta, w, state, output, final_state, tail_boundaries,
+                              batch, time, heads, full_tokens, time, output_scale)
+    if not return_aux:
+        return output, final_state
+    return output, final_state, ChunkForwardAux(chunk_boundaries, tail_boundaries, full_tokens)
+
+
+__all__ = ["ChunkForwardAux", "chunk_forward"]

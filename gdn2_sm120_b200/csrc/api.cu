@@ -1,0 +1,167 @@
+// extern "C" entry points of libgdn2_b200.so: argument validation + kernel launches.
+// No allocation, no synchronisation, no exceptions cross this boundary.
+
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace gdn2 {
+
+// launchers defined next to their kernels
+int launch_token_forward(const void*, const void*, const void*, const void*, const void*,
+                         const void*, const float*, void*, float*, float*, int64_t, int64_t,
+                         int64_t, int64_t, int64_t, int, int, float, cudaStream_t);
+int launch_token_t1_zero(const void*, const void*, const void*, const void*, void*, float*,
+                         int64_t, int64_t, int, float, cudaStream_t);
+int launch_token_dstate_scan(const void*, const void*, const void*, const void*, const void*,
+                             const float*, float*, float*, int64_t, int64_t, int64_t, int64_t,
+                             int64_t, int, int, float, cudaStream_t);
+int launch_token_chunk_vjp(const void*, const void*, const void*, const void*, const void*,
+                           const void*, const void*, const float*, const float*, void*, void*,
+                           void*, void*, void*, void*, int64_t, int64_t, int64_t, int64_t,
+                           int64_t, int, int, float, cudaStream_t);
+
+namespace {
+thread_local char g_cuda_error[256] = {0};
+}
+
+void record_cuda_error(cudaError_t err) {
+  std::snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s", cudaGetErrorName(err),
+                cudaGetErrorString(err));
+}
+
+int check_launch() {
+  const cudaError_t err = cudaGetLastError();
+  if (err == cudaSuccess) return GDN2_OK;
+  record_cuda_error(err);
+  return GDN2_ERR_LAUNCH;
+}
+
+namespace {
+
+inline bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+int check_shape(int64_t B, int64_t T, int64_t H) {
+  if (B <= 0 || H <= 0 || T < 0) return GDN2_ERR_BAD_SHAPE;
+  // element offsets are 64-bit, but keep every product representable
+  const int64_t limit = int64_t(1) << 46;
+  if (B > limit || H > limit || T > limit) return GDN2_ERR_TOO_LARGE;
+  if (B * H > limit || (T > 0 && B * H > limit / T)) return GDN2_ERR_TOO_LARGE;
+  return GDN2_OK;
+}
+
+int check_range(int64_t T, int64_t t_begin, int64_t t_end) {
+  if (t_begin < 0 || t_end < t_begin || t_end > T) return GDN2_ERR_BAD_RANGE;
+  return GDN2_OK;
+}
+
+int check_types(int dtype, int g_dtype) {
+  if (!valid_seq_dtype(dtype) || !valid_gate_dtype(g_dtype, dtype)) return GDN2_ERR_BAD_DTYPE;
+  return GDN2_OK;
+}
+
+}  // namespace
+}  // namespace gdn2
+
+using namespace gdn2;
+
+extern "C" {
+
+int gdn2_version(void) { return 100; /* 0.1.0 */ }
+
+const char* gdn2_status_string(int status) {
+  switch (status) {
+    case GDN2_OK: return "ok";
+    case GDN2_ERR_NULL_POINTER: return "a required pointer is NULL";
+    case GDN2_ERR_BAD_SHAPE: return "batch and heads must be positive and time non-negative";
+    case GDN2_ERR_BAD_DTYPE: return "unsupported dtype code (q/k/v/beta/w: bf16 or fp16; g: same or fp32)";
+    case GDN2_ERR_BAD_RANGE: return "token range must satisfy 0 <= t_begin <= t_end <= T";
+    case GDN2_ERR_ALIGNMENT: return "a pointer does not satisfy the required alignment";
+    case GDN2_ERR_UNSUPPORTED: return "shape or option not supported by this entry point";
+    case GDN2_ERR_LAUNCH: return "CUDA reported an error at launch (see gdn2_last_cuda_error)";
+    case GDN2_ERR_DEVICE: return "the current device is not a compute-capability 10.x GPU";
+    case GDN2_ERR_TOO_LARGE: return "problem size exceeds the launch grid or 64-bit index budget";
+    default: return "unknown status";
+  }
+}
+
+const char* gdn2_last_cuda_error(void) { return g_cuda_error; }
+
+int gdn2_device_supported(void) {
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
+  int major = 0;
+  err = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
+  return major == 10 ? 1 : 0;
+}
+
+int gdn2_token_forward(const void* q, const void* k, const void* v, const void* g,
+                       const void* beta, const void* w, const float* initial_state, void* out,
+                       float* final_state, float* boundaries, int64_t batch, int64_t time,
+                       int64_t heads, int64_t t_begin, int64_t t_end, int dtype, int g_dtype,
+                       float scale, void* stream) {
+  if (!q || !k || !v || !g || !beta || !w || !out) return GDN2_ERR_NULL_POINTER;
+  int st = check_shape(batch, time, heads);
+  if (st != GDN2_OK) return st;
+  if ((st = check_range(time, t_begin, t_end)) != GDN2_OK) return st;
+  if ((st = check_types(dtype, g_dtype)) != GDN2_OK) return st;
+  if (!aligned(initial_state, 4) || !aligned(final_state, 4) || !aligned(boundaries, 4))
+    return GDN2_ERR_ALIGNMENT;
+  return launch_token_forward(q, k, v, g, beta, w, initial_state, out, final_state, boundaries,
+                              batch, time, heads, t_begin, t_end, dtype, g_dtype, scale,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int gdn2_token_forward_t1_zero(const void* q, const void* k, const void* v, const void* w,
+                               void* out, float* final_state, int64_t batch, int64_t heads,
+                               int dtype, float scale, void* stream) {
+  if (!q || !k || !v || !w || !out || !final_state) return GDN2_ERR_NULL_POINTER;
+  int st = check_shape(batch, 1, heads);
+  if (st != GDN2_OK) return st;
+  if (!valid_seq_dtype(dtype)) return GDN2_ERR_BAD_DTYPE;
+  if (!aligned(final_state, 4)) return GDN2_ERR_ALIGNMENT;
+  return launch_token_t1_zero(q, k, v, w, out, final_state, batch, heads, dtype, scale,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int gdn2_token_dstate_scan(const void* q, const void* k, const void* g, const void* beta,
+                           const void* d_out, const float* d_final_state, float* d_boundaries,
+                           float* d_initial_state, int64_t batch, int64_t time, int64_t heads,
+                           int64_t t_begin, int64_t t_end, int dtype, int g_dtype, float scale,
+                           void* stream) {
+  if (!q || !k || !g || !beta || !d_out || !d_boundaries) return GDN2_ERR_NULL_POINTER;
+  int st = check_shape(batch, time, heads);
+  if (st != GDN2_OK) return st;
+  if ((st = check_range(time, t_begin, t_end)) != GDN2_OK) return st;
+  if ((st = check_types(dtype, g_dtype)) != GDN2_OK) return st;
+  if (!aligned(d_final_state, 4) || !aligned(d_boundaries, 4) || !aligned(d_initial_state, 4))
+    return GDN2_ERR_ALIGNMENT;
+  return launch_token_dstate_scan(q, k, g, beta, d_out, d_final_state, d_boundaries,
+                                  d_initial_state, batch, time, heads, t_begin, t_end, dtype,
+                                  g_dtype, scale, static_cast<cudaStream_t>(stream));
+}
+
+int gdn2_token_chunk_vjp(const void* q, const void* k, const void* v, const void* g,
+                         const void* beta, const void* w, const void* d_out,
+                         const float* boundaries, const float* d_boundaries, void* dq, void* dk,
+                         void* dv, void* dg, void* dbeta, void* dw, int64_t batch, int64_t time,
+                         int64_t heads, int64_t t_begin, int64_t t_end, int dtype, int g_dtype,
+                         float scale, void* stream) {
+  if (!q || !k || !v || !g || !beta || !w || !d_out || !boundaries || !d_boundaries || !dq ||
+      !dk || !dv || !dg || !dbeta || !dw)
+    return GDN2_ERR_NULL_POINTER;
+  int st = check_shape(batch, time, heads);
+  if (st != GDN2_OK) return st;
+  if ((st = check_range(time, t_begin, t_end)) != GDN2_OK) return st;
+  if ((st = check_types(dtype, g_dtype)) != GDN2_OK) return st;
+  if (!aligned(boundaries, 16) || !aligned(d_boundaries, 16)) return GDN2_ERR_ALIGNMENT;
+  if (t_begin == t_end) return GDN2_OK;
+  return launch_token_chunk_vjp(q, k, v, g, beta, w, d_out, boundaries, d_boundaries, dq, dk, dv,
+                                dg, dbeta, dw, batch, time, heads, t_begin, t_end, dtype,
+                                g_dtype, scale, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,577 @@
+// Token-path kernels: exact fp32 recurrence, one token at a time.
+//
+//   token_forward_kernel      decode / short-sequence forward, optional boundary stack
+//   token_t1_zero_kernel      T == 1, zero initial state closed form (write-only state)
+//   token_dstate_scan_kernel  reverse scan of the state cotangent
+//   token_chunk_vjp_kernel    per-16-token-span recompute + reverse sweep -> all gradients
+//
+// These serve decode (the HBM-bound serving path), every sequence shorter than one
+// tensor-core chunk, and the ragged tail after the last full chunk.  They follow the
+// recurrence of src/gdn2_sm120/reference.py:80-93 of the reference literally; the
+// thread mapping is this library's own (the reference's token kernel is
+// src/gdn2_sm120/recurrent.py:108-243).
+//
+// State tile ownership in the forward / scan kernels: one CTA = (batch, head,
+// 32 value columns), 128 threads.  Thread `tid` owns the float4 column group
+// cg = tid & 7 of the key rows rg + 16*i, rg = tid >> 3, i = 0..7, so one warp
+// touches four 128-byte row segments per i: fully coalesced 128-bit state I/O, 32
+// fp32 state registers per thread, and every state element is read and written by
+// exactly one thread (which is why an exact in-place state update is race-free).
+
+#include "common.cuh"
+
+namespace gdn2 {
+
+namespace {
+
+constexpr int kTokThreads = 128;
+constexpr int kTokVT = 32;                     // value columns per CTA
+constexpr int kTokTiles = kDim / kTokVT;       // 4 CTAs per (batch, head)
+constexpr int kRowsPerThread = 8;              // 128 rows / 16 row groups
+constexpr int64_t kStateElems = int64_t(kDim) * kDim;
+
+struct TokenFwdParams {
+  const void *q, *k, *v, *g, *beta, *w;
+  const float* s_in;
+  void* out;
+  float* s_out;
+  float* bnd;
+  int64_t T, H, t_begin, t_end, n_slots;
+  float scale;
+};
+
+__device__ __forceinline__ float4 ld_red4(const float (*red)[kTokVT], int col) {
+  // sum of the four per-warp partial rows
+  float4 s = *reinterpret_cast<const float4*>(&red[0][col]);
+#pragma unroll
+  for (int wv = 1; wv < 4; ++wv) {
+    const float4 t = *reinterpret_cast<const float4*>(&red[wv][col]);
+    s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+  }
+  return s;
+}
+
+template <typename T, typename G>
+__global__ void __launch_bounds__(kTokThreads) token_forward_kernel(const TokenFwdParams p) {
+  __shared__ float s_a[2][kDim], s_e[2][kDim], s_k[2][kDim], s_q[2][kDim];
+  __shared__ float s_z[2][kTokVT];
+  __shared__ __align__(16) float s_red[2][2][4][kTokVT];  // [buffer][erase|output][warp][column]
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int cg = tid & 7, rg = tid >> 3;
+  const int vt = int(blockIdx.x % kTokTiles);
+  const int64_t bh = blockIdx.x / kTokTiles;
+  const int64_t b = bh / p.H, h = bh % p.H;
+  const int col0 = vt * kTokVT + cg * 4;
+
+  auto stage = [&](int64_t t, int buf) {
+    const int64_t idx = ((b * p.T + t) * p.H + h) * kDim;
+    const float kv = ldf<T>(p.k, idx + tid);
+    s_a[buf][tid] = expf(ldf<G>(p.g, idx + tid));
+    s_e[buf][tid] = ldf<T>(p.beta, idx + tid) * kv;
+    s_k[buf][tid] = kv;
+    s_q[buf][tid] = p.scale * ldf<T>(p.q, idx + tid);
+    if (tid < kTokVT) {
+      s_z[buf][tid] = ldf<T>(p.w, idx + vt * kTokVT + tid) * ldf<T>(p.v, idx + vt * kTokVT + tid);
+    }
+  };
+
+  float S[kRowsPerThread][4];
+  if (p.s_in != nullptr) {
+    const float* src = p.s_in + bh * kStateElems;
+    const bool vec = (reinterpret_cast<uintptr_t>(p.s_in) & 15) == 0;
+#pragma unroll
+    for (int i = 0; i < kRowsPerThread; ++i) load4(src + (rg + 16 * i) * kDim + col0, vec, S[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < kRowsPerThread; ++i) S[i][0] = S[i][1] = S[i][2] = S[i][3] = 0.f;
+  }
+
+  auto store_tile = [&](float* base) {
+    const bool vec = (reinterpret_cast<uintptr_t>(base) & 15) == 0;
+#pragma unroll
+    for (int i = 0; i < kRowsPerThread; ++i) store4(base + (rg + 16 * i) * kDim + col0, vec, S[i]);
+  };
+
+  if (p.t_begin < p.t_end) {
+    stage(p.t_begin, 0);
+  }
+  __syncthreads();
+
+  for (int64_t t = p.t_begin; t < p.t_end; ++t) {
+    const int64_t rel = t - p.t_begin;
+    const int buf = int(rel & 1);
+    if (p.bnd != nullptr && (rel % kTokenInterval) == 0) {
+      store_tile(p.bnd + ((b * p.n_slots + rel / kTokenInterval) * p.H + h) * kStateElems);
+    }
+    // X = a * S ; partial r = X^T e over this thread's rows
+    float r[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < kRowsPerThread; ++i) {
+      const float a = s_a[buf][rg + 16 * i], e = s_e[buf][rg + 16 * i];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        S[i][c] *= a;
+        r[c] = fmaf(S[i][c], e, r[c]);
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      r[c] += __shfl_xor_sync(0xffffffffu, r[c], 8);
+      r[c] += __shfl_xor_sync(0xffffffffu, r[c], 16);
+    }
+    if (lane < 8) {
+      *reinterpret_cast<float4*>(&s_red[buf][0][warp][cg * 4]) = make_float4(r[0], r[1], r[2], r[3]);
+    }
+    if (t + 1 < p.t_end) stage(t + 1, buf ^ 1);
+    __syncthreads();
+
+    const float4 rs = ld_red4(s_red[buf][0], cg * 4);
+    const float u[4] = {s_z[buf][cg * 4 + 0] - rs.x, s_z[buf][cg * 4 + 1] - rs.y,
+                        s_z[buf][cg * 4 + 2] - rs.z, s_z[buf][cg * 4 + 3] - rs.w};
+    // S = X + k u^T ; partial o = S^T (scale q)
+    float o[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < kRowsPerThread; ++i) {
+      const float kv = s_k[buf][rg + 16 * i], qv = s_q[buf][rg + 16 * i];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        S[i][c] = fmaf(kv, u[c], S[i][c]);
+        o[c] = fmaf(S[i][c], qv, o[c]);
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      o[c] += __shfl_xor_sync(0xffffffffu, o[c], 8);
+      o[c] += __shfl_xor_sync(0xffffffffu, o[c], 16);
+    }
+    if (lane < 8) {
+      *reinterpret_cast<float4*>(&s_red[buf][1][warp][cg * 4]) = make_float4(o[0], o[1], o[2], o[3]);
+    }
+    __syncthreads();
+    if (tid < kTokVT) {
+      const float ov = s_red[buf][1][0][tid] + s_red[buf][1][1][tid] + s_red[buf][1][2][tid] +
+                       s_red[buf][1][3][tid];
+      stf<T>(p.out, ((b * p.T + t) * p.H + h) * kDim + vt * kTokVT + tid, ov);
+    }
+  }
+
+  if (p.bnd != nullptr) {
+    store_tile(p.bnd + ((b * p.n_slots + (p.n_slots - 1)) * p.H + h) * kStateElems);
+  }
+  if (p.s_out != nullptr) {
+    store_tile(p.s_out + bh * kStateElems);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+struct T1ZeroParams {
+  const void *q, *k, *v, *w;
+  void* out;
+  float* s_out;
+  int64_t H;
+  float scale;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kTokThreads) token_t1_zero_kernel(const T1ZeroParams p) {
+  __shared__ float s_k[kDim];
+  __shared__ float s_z[kTokVT];
+  __shared__ float s_part[4];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int cg = tid & 7, rg = tid >> 3;
+  const int vt = int(blockIdx.x % kTokTiles);
+  const int64_t bh = blockIdx.x / kTokTiles;
+  const int64_t idx = bh * kDim;  // T == 1: [B, 1, H, 128]
+
+  const float kv = ldf<T>(p.k, idx + tid);
+  s_k[tid] = kv;
+  float qk = p.scale * ldf<T>(p.q, idx + tid) * kv;
+  if (tid < kTokVT) {
+    s_z[tid] = ldf<T>(p.w, idx + vt * kTokVT + tid) * ldf<T>(p.v, idx + vt * kTokVT + tid);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) qk += __shfl_xor_sync(0xffffffffu, qk, off);
+  if (lane == 0) s_part[warp] = qk;
+  __syncthreads();
+  qk = s_part[0] + s_part[1] + s_part[2] + s_part[3];
+
+  float z[4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) z[c] = s_z[cg * 4 + c];
+  float* dst = p.s_out + bh * kStateElems + vt * kTokVT + cg * 4;
+  const bool vec = (reinterpret_cast<uintptr_t>(p.s_out) & 15) == 0;
+#pragma unroll
+  for (int i = 0; i < kRowsPerThread; ++i) {
+    const float kr = s_k[rg + 16 * i];
+    const float row[4] = {kr * z[0], kr * z[1], kr * z[2], kr * z[3]};
+    store4(dst + (rg + 16 * i) * kDim, vec, row);
+  }
+  if (tid < kTokVT) stf<T>(p.out, idx + vt * kTokVT + tid, qk * s_z[tid]);
+}
+
+// ---------------------------------------------------------------------------------
+struct DstateScanParams {
+  const void *q, *k, *g, *beta, *d_out;
+  const float* ds_final;
+  float* d_bnd;
+  float* ds_init;
+  int64_t T, H, t_begin, t_end, n_slots;
+  float scale;
+};
+
+template <typename T, typename G>
+__global__ void __launch_bounds__(kTokThreads) token_dstate_scan_kernel(const DstateScanParams p) {
+  __shared__ float s_a[2][kDim], s_e[2][kDim], s_k[2][kDim], s_q[2][kDim];
+  __shared__ float s_do[2][kTokVT];
+  __shared__ __align__(16) float s_red[2][4][kTokVT];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int cg = tid & 7, rg = tid >> 3;
+  const int vt = int(blockIdx.x % kTokTiles);
+  const int64_t bh = blockIdx.x / kTokTiles;
+  const int64_t b = bh / p.H, h = bh % p.H;
+  const int col0 = vt * kTokVT + cg * 4;
+
+  auto stage = [&](int64_t t, int buf) {
+    const int64_t idx = ((b * p.T + t) * p.H + h) * kDim;
+    const float kv = ldf<T>(p.k, idx + tid);
+    s_a[buf][tid] = expf(ldf<G>(p.g, idx + tid));
+    s_e[buf][tid] = ldf<T>(p.beta, idx + tid) * kv;
+    s_k[buf][tid] = kv;
+    s_q[buf][tid] = p.scale * ldf<T>(p.q, idx + tid);
+    if (tid < kTokVT) s_do[buf][tid] = ldf<T>(p.d_out, idx + vt * kTokVT + tid);
+  };
+
+  float dS[kRowsPerThread][4];
+  if (p.ds_final != nullptr) {
+    const float* src = p.ds_final + bh * kStateElems;
+    const bool vec = (reinterpret_cast<uintptr_t>(p.ds_final) & 15) == 0;
+#pragma unroll
+    for (int i = 0; i < kRowsPerThread; ++i) load4(src + (rg + 16 * i) * kDim + col0, vec, dS[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < kRowsPerThread; ++i) dS[i][0] = dS[i][1] = dS[i][2] = dS[i][3] = 0.f;
+  }
+  auto store_tile = [&](float* base) {
+    const bool vec = (reinterpret_cast<uintptr_t>(base) & 15) == 0;
+#pragma unroll
+    for (int i = 0; i < kRowsPerThread; ++i) store4(base + (rg + 16 * i) * kDim + col0, vec, dS[i]);
+  };
+
+  store_tile(p.d_bnd + ((b * p.n_slots + (p.n_slots - 1)) * p.H + h) * kStateElems);
+  if (p.t_begin < p.t_end) stage(p.t_end - 1, 0);
+  __syncthreads();
+
+  int buf = 0;
+  for (int64_t t = p.t_end - 1; t >= p.t_begin; --t, buf ^= 1) {
+    // dS' = dS + (scale q) do^T ; partial du = dS'^T k
+    float du[4] = {0.f, 0.f, 0.f, 0.f};
+    float dov[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) dov[c] = s_do[buf][cg * 4 + c];
+#pragma unroll
+    for (int i = 0; i < kRowsPerThread; ++i) {
+      const float kv = s_k[buf][rg + 16 * i], qv = s_q[buf][rg + 16 * i];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        dS[i][c] = fmaf(qv, dov[c], dS[i][c]);
+        du[c] = fmaf(dS[i][c], kv, du[c]);
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      du[c] += __shfl_xor_sync(0xffffffffu, du[c], 8);
+      du[c] += __shfl_xor_sync(0xffffffffu, du[c], 16);
+    }
+    if (lane < 8) {
+      *reinterpret_cast<float4*>(&s_red[buf][warp][cg * 4]) = make_float4(du[0], du[1], du[2], du[3]);
+    }
+    if (t - 1 >= p.t_begin) stage(t - 1, buf ^ 1);
+    __syncthreads();
+    const float4 ds = ld_red4(s_red[buf], cg * 4);
+    const float dus[4] = {ds.x, ds.y, ds.z, ds.w};
+    // dS <- a * (dS' - e du^T)
+#pragma unroll
+    for (int i = 0; i < kRowsPerThread; ++i) {
+      const float a = s_a[buf][rg + 16 * i], e = s_e[buf][rg + 16 * i];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) dS[i][c] = a * fmaf(-e, dus[c], dS[i][c]);
+    }
+    const int64_t rel = t - p.t_begin;
+    if ((rel % kTokenInterval) == 0) {
+      store_tile(p.d_bnd + ((b * p.n_slots + rel / kTokenInterval) * p.H + h) * kStateElems);
+    }
+  }
+  if (p.ds_init != nullptr) store_tile(p.ds_init + bh * kStateElems);
+}
+
+// ---------------------------------------------------------------------------------
+// Chunk-local VJP.  One CTA = (batch, 16-token span, head), 128 threads, thread = key
+// row.  The span is swept in 16 passes of 8 value columns: forward from the saved
+// boundary keeping every decayed state X_t of the pass in shared memory (private to
+// the owning thread), then in reverse with the cotangent tile in registers.  Sums over
+// the value axis (dq, dk, d(beta k), dg) stay inside the thread and are accumulated
+// across passes in registers, so no partial buffers, atomics or second kernel exist.
+constexpr int kVjpThreads = 128;
+constexpr int kVjpVT = 8;
+constexpr int kVjpPasses = kDim / kVjpVT;
+
+template <typename T>
+struct VjpSmem {
+  float hist[kTokenInterval][kVjpVT][kDim];  // X_t of the current pass      64 KiB
+  float a[kTokenInterval][kDim];             // exp(g)                        8 KiB
+  float du[kTokenInterval][kDim];            // d(u) for all value columns    8 KiB
+  T q[kTokenInterval][kDim], k[kTokenInterval][kDim], beta[kTokenInterval][kDim];
+  T v[kTokenInterval][kDim], w[kTokenInterval][kDim], dout[kTokenInterval][kDim];  // 24 KiB
+  float u[kTokenInterval][kVjpVT];
+  float red[2][4][kVjpVT];
+};
+
+struct ChunkVjpParams {
+  const void *q, *k, *v, *g, *beta, *w, *d_out;
+  const float *bnd, *d_bnd;
+  void *dq, *dk, *dv, *dg, *dbeta, *dw;
+  int64_t T, H, t_begin, t_end, n_slots;
+  float scale;
+};
+
+// Sum eight per-thread values over the 128 threads of the CTA; every thread gets all
+// eight totals.  Halving butterfly: 9 shuffles instead of 40.
+__device__ __forceinline__ void block_sum8(float (&x)[8], float (*red)[4][kVjpVT], int& rb,
+                                           int lane, int warp) {
+  const bool h16 = (lane & 16) != 0, h8 = (lane & 8) != 0, h4 = (lane & 4) != 0;
+  float y[4], z[2];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float recv = __shfl_xor_sync(0xffffffffu, h16 ? x[j] : x[j + 4], 16);
+    y[j] = (h16 ? x[j + 4] : x[j]) + recv;  // column j + 4*h16
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const float recv = __shfl_xor_sync(0xffffffffu, h8 ? y[j] : y[j + 2], 8);
+    z[j] = (h8 ? y[j + 2] : y[j]) + recv;  // column j + 2*h8 + 4*h16
+  }
+  float s;
+  {
+    const float recv = __shfl_xor_sync(0xffffffffu, h4 ? z[0] : z[1], 4);
+    s = (h4 ? z[1] : z[0]) + recv;  // column h4 + 2*h8 + 4*h16 == lane >> 2
+  }
+  s += __shfl_xor_sync(0xffffffffu, s, 2);
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  if ((lane & 3) == 0) red[rb][warp][lane >> 2] = s;
+  __syncthreads();
+#pragma unroll
+  for (int c = 0; c < 8; ++c) x[c] = red[rb][0][c] + red[rb][1][c] + red[rb][2][c] + red[rb][3][c];
+  rb ^= 1;
+}
+
+template <typename T, typename G>
+__global__ void __launch_bounds__(kVjpThreads) token_chunk_vjp_kernel(const ChunkVjpParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  VjpSmem<T>& sm = *reinterpret_cast<VjpSmem<T>*>(smem_raw);
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t n_spans = p.n_slots - 1;
+  const int64_t h = blockIdx.x % p.H;
+  const int64_t j = (blockIdx.x / p.H) % n_spans;
+  const int64_t b = blockIdx.x / (p.H * n_spans);
+  const int64_t t0 = p.t_begin + j * kTokenInterval;
+  const int n = int(min(int64_t(kTokenInterval), p.t_end - t0));
+
+  for (int t = 0; t < n; ++t) {
+    const int64_t idx = ((b * p.T + t0 + t) * p.H + h) * kDim + tid;
+    sm.q[t][tid] = static_cast<const T*>(p.q)[idx];
+    sm.k[t][tid] = static_cast<const T*>(p.k)[idx];
+    sm.beta[t][tid] = static_cast<const T*>(p.beta)[idx];
+    sm.v[t][tid] = static_cast<const T*>(p.v)[idx];
+    sm.w[t][tid] = static_cast<const T*>(p.w)[idx];
+    sm.dout[t][tid] = static_cast<const T*>(p.d_out)[idx];
+    sm.a[t][tid] = expf(ldf<G>(p.g, idx));
+  }
+  __syncthreads();
+
+  float adq[kTokenInterval], adk[kTokenInterval], ade[kTokenInterval], adg[kTokenInterval];
+#pragma unroll
+  for (int t = 0; t < kTokenInterval; ++t) adq[t] = adk[t] = ade[t] = adg[t] = 0.f;
+
+  const float* s_src = p.bnd + ((b * p.n_slots + j) * p.H + h) * kStateElems + tid * kDim;
+  const float* ds_src = p.d_bnd + ((b * p.n_slots + j + 1) * p.H + h) * kStateElems + tid * kDim;
+  int rb = 0;
+
+  for (int pass = 0; pass < kVjpPasses; ++pass) {
+    const int cb = pass * kVjpVT;
+    float S[kVjpVT];
+    {
+      const float4 lo = *reinterpret_cast<const float4*>(s_src + cb);
+      const float4 hi = *reinterpret_cast<const float4*>(s_src + cb + 4);
+      S[0] = lo.x; S[1] = lo.y; S[2] = lo.z; S[3] = lo.w;
+      S[4] = hi.x; S[5] = hi.y; S[6] = hi.z; S[7] = hi.w;
+    }
+    // ---- forward recompute, keeping X_t ----
+#pragma unroll
+    for (int t = 0; t < kTokenInterval; ++t) {
+      if (t < n) {
+        const float a = sm.a[t][tid];
+        const float kv = to_float(sm.k[t][tid]);
+        const float e = to_float(sm.beta[t][tid]) * kv;
+        float r[kVjpVT];
+#pragma unroll
+        for (int c = 0; c < kVjpVT; ++c) {
+          S[c] *= a;
+          sm.hist[t][c][tid] = S[c];
+          r[c] = S[c] * e;
+        }
+        block_sum8(r, sm.red, rb, lane, warp);
+#pragma unroll
+        for (int c = 0; c < kVjpVT; ++c) {
+          const float u = to_float(sm.w[t][cb + c]) * to_float(sm.v[t][cb + c]) - r[c];
+          S[c] = fmaf(kv, u, S[c]);
+          if (tid == c) sm.u[t][c] = u;
+        }
+      }
+    }
+    __syncthreads();  // sm.u of the last token visible to everyone
+
+    float dS[kVjpVT];
+    {
+      const float4 lo = *reinterpret_cast<const float4*>(ds_src + cb);
+      const float4 hi = *reinterpret_cast<const float4*>(ds_src + cb + 4);
+      dS[0] = lo.x; dS[1] = lo.y; dS[2] = lo.z; dS[3] = lo.w;
+      dS[4] = hi.x; dS[5] = hi.y; dS[6] = hi.z; dS[7] = hi.w;
+    }
+    // ---- reverse sweep ----
+#pragma unroll
+    for (int t = kTokenInterval - 1; t >= 0; --t) {
+      if (t < n) {
+        const float a = sm.a[t][tid];
+        const float kv = to_float(sm.k[t][tid]);
+        const float e = to_float(sm.beta[t][tid]) * kv;
+        const float qs = p.scale * to_float(sm.q[t][tid]);
+        float X[kVjpVT], du[kVjpVT];
+        float acc_q = 0.f, acc_k = 0.f;
+#pragma unroll
+        for (int c = 0; c < kVjpVT; ++c) {
+          X[c] = sm.hist[t][c][tid];
+          const float u = sm.u[t][c];
+          const float st = fmaf(kv, u, X[c]);            // S_t
+          const float dov = to_float(sm.dout[t][cb + c]);
+          acc_q = fmaf(st, dov, acc_q);
+          dS[c] = fmaf(qs, dov, dS[c]);                  // dS'
+          acc_k = fmaf(dS[c], u, acc_k);
+          du[c] = dS[c] * kv;
+        }
+        adq[t] += acc_q;
+        adk[t] += acc_k;
+        block_sum8(du, sm.red, rb, lane, warp);
+        float acc_e = 0.f, acc_g = 0.f;
+#pragma unroll
+        for (int c = 0; c < kVjpVT; ++c) {
+          acc_e = fmaf(X[c], du[c], acc_e);
+          const float dx = fmaf(-e, du[c], dS[c]);
+          acc_g = fmaf(dx, X[c], acc_g);
+          dS[c] = a * dx;
+          if (tid == c) sm.du[t][cb + c] = du[c];
+        }
+        ade[t] -= acc_e;
+        adg[t] += acc_g;
+      }
+    }
+  }
+  __syncthreads();  // sm.du complete
+
+#pragma unroll
+  for (int t = 0; t < kTokenInterval; ++t) {
+    if (t < n) {
+      const int64_t idx = ((b * p.T + t0 + t) * p.H + h) * kDim + tid;
+      const float kv = to_float(sm.k[t][tid]);
+      const float bv = to_float(sm.beta[t][tid]);
+      stf<T>(p.dq, idx, p.scale * adq[t]);
+      stf<T>(p.dk, idx, fmaf(ade[t], bv, adk[t]));
+      stf<T>(p.dbeta, idx, ade[t] * kv);
+      stf<G>(p.dg, idx, adg[t]);
+      const float duv = sm.du[t][tid];
+      stf<T>(p.dv, idx, duv * to_float(sm.w[t][tid]));
+      stf<T>(p.dw, idx, duv * to_float(sm.v[t][tid]));
+    }
+  }
+}
+
+inline int64_t slots_for(int64_t t_begin, int64_t t_end) {
+  return (t_end - t_begin + kTokenInterval - 1) / kTokenInterval + 1;
+}
+
+inline bool grid_fits(int64_t blocks) { return blocks > 0 && blocks <= int64_t(0x7fffffff); }
+
+}  // namespace
+
+// ---- launchers (called from api.cu) --------------------------------------------------
+int launch_token_forward(const void* q, const void* k, const void* v, const void* g,
+                         const void* beta, const void* w, const float* s_in, void* out,
+                         float* s_out, float* bnd, int64_t B, int64_t T, int64_t H,
+                         int64_t t_begin, int64_t t_end, int dtype, int g_dtype, float scale,
+                         cudaStream_t stream) {
+  const int64_t blocks = B * H * kTokTiles;
+  if (!grid_fits(blocks)) return GDN2_ERR_TOO_LARGE;
+  TokenFwdParams p{q, k, v, g, beta, w, s_in, out, s_out, bnd,
+                   T, H, t_begin, t_end, slots_for(t_begin, t_end), scale};
+  GDN2_DISPATCH_TYPES(dtype, g_dtype,
+                      (token_forward_kernel<T, G><<<unsigned(blocks), kTokThreads, 0, stream>>>(p)));
+  return check_launch();
+}
+
+int launch_token_t1_zero(const void* q, const void* k, const void* v, const void* w, void* out,
+                         float* s_out, int64_t B, int64_t H, int dtype, float scale,
+                         cudaStream_t stream) {
+  const int64_t blocks = B * H * kTokTiles;
+  if (!grid_fits(blocks)) return GDN2_ERR_TOO_LARGE;
+  T1ZeroParams p{q, k, v, w, out, s_out, H, scale};
+  if (dtype == GDN2_BF16) {
+    token_t1_zero_kernel<__nv_bfloat16><<<unsigned(blocks), kTokThreads, 0, stream>>>(p);
+  } else {
+    token_t1_zero_kernel<__half><<<unsigned(blocks), kTokThreads, 0, stream>>>(p);
+  }
+  return check_launch();
+}
+
+int launch_token_dstate_scan(const void* q, const void* k, const void* g, const void* beta,
+                             const void* d_out, const float* ds_final, float* d_bnd,
+                             float* ds_init, int64_t B, int64_t T, int64_t H, int64_t t_begin,
+                             int64_t t_end, int dtype, int g_dtype, float scale,
+                             cudaStream_t stream) {
+  const int64_t blocks = B * H * kTokTiles;
+  if (!grid_fits(blocks)) return GDN2_ERR_TOO_LARGE;
+  DstateScanParams p{q, k, g, beta, d_out, ds_final, d_bnd, ds_init,
+                     T, H, t_begin, t_end, slots_for(t_begin, t_end), scale};
+  GDN2_DISPATCH_TYPES(
+      dtype, g_dtype,
+      (token_dstate_scan_kernel<T, G><<<unsigned(blocks), kTokThreads, 0, stream>>>(p)));
+  return check_launch();
+}
+
+int launch_token_chunk_vjp(const void* q, const void* k, const void* v, const void* g,
+                           const void* beta, const void* w, const void* d_out, const float* bnd,
+                           const float* d_bnd, void* dq, void* dk, void* dv, void* dg,
+                           void* dbeta, void* dw, int64_t B, int64_t T, int64_t H,
+                           int64_t t_begin, int64_t t_end, int dtype, int g_dtype, float scale,
+                           cudaStream_t stream) {
+  const int64_t n_slots = slots_for(t_begin, t_end);
+  const int64_t blocks = B * (n_slots - 1) * H;
+  if (!grid_fits(blocks)) return GDN2_ERR_TOO_LARGE;
+  ChunkVjpParams p{q, k, v, g, beta, w, d_out, bnd, d_bnd, dq, dk, dv, dg, dbeta, dw,
+                   T, H, t_begin, t_end, n_slots, scale};
+  GDN2_DISPATCH_TYPES(dtype, g_dtype, {
+    auto kernel = token_chunk_vjp_kernel<T, G>;
+    const int smem = int(sizeof(VjpSmem<T>));
+    cudaError_t err =
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) {
+      record_cuda_error(err);
+      return GDN2_ERR_LAUNCH;
+    }
+    kernel<<<unsigned(blocks), kVjpThreads, smem, stream>>>(p);
+  });
+  return check_launch();
+}
+
+}  // namespace gdn2

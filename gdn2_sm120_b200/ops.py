@@ -1,0 +1,175 @@
+"""Public PyTorch operators: ``chunk_gdn2`` and ``recurrent_gdn2``.
+
+Drop-in for src/gdn2_sm120/ops.py:224-327 of the reference: identical signatures,
+defaults, return conventions, grad-mode detection (inference bypasses the
+``autograd.Function``), hidden-final-state handling (no zero cotangent is materialised
+when the loss ignores ``S_T``) and T == 0 behaviour.  Device work goes through the C ABI
+on the current PyTorch stream of the tensors' device.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _validate
+from .backward import backward_from_aux
+from .chunk import ChunkForwardAux, _token_slots, chunk_forward
+from .recurrent import _launch_token_forward, _use_recurrent_kernel, token_forward
+
+_DIM = 128
+_CHUNK_SIZE = 64
+_PARALLEL_BACKWARD_MIN_TOKENS = 64
+
+
+def _use_compact_wy_backward(batch: int, time: int, heads: int) -> bool:
+    """True when backward runs the tensor-core compact-WY chunk VJP for the leading
+    full chunks (reference selector: src/gdn2_sm120/ops.py:22-28).
+
+    The reference needs T >= 128, or T == 64 on a grid large enough to fill its GPU,
+    because its VJP is a 10-12 launch graph.  The B200 VJP is a fused kernel per
+    direction, so one full 64-token chunk is enough regardless of the grid.
+    """
+
+    del batch, heads
+    return time >= _PARALLEL_BACKWARD_MIN_TOKENS
+
+
+class _ChunkGDN2(torch.autograd.Function):
+    """Connects the forward kernels, their state checkpoints and the backward kernels."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, w, initial_state, scale: float, prepare_backward: bool):
+        seq = tuple(_validate.detached(x) for x in (q, k, v, g, beta, w))
+        state = _validate.detached(initial_state)
+        batch, time, heads = q.shape[0], q.shape[1], q.shape[2]
+        aux = None
+        if _use_recurrent_kernel(batch, time, heads, chunk_api=True):
+            if prepare_backward and time > 0:
+                # token path with fp32 checkpoints every 16 tokens
+                batch, time, heads = _validate.sequence_inputs(*seq)
+                if state is not None:
+                    _validate.state("initial_state", state, batch, heads, q.device)
+                output = torch.empty_like(seq[2])
+                final_state = torch.empty((batch, heads, _DIM, _DIM), device=q.device,
+                                          dtype=torch.float32)
+                boundaries = torch.empty((batch, _token_slots(time), heads, _DIM, _DIM),
+                                         device=q.device, dtype=torch.float32)
+                _launch_token_forward(*seq, state, output, final_state, boundaries, batch, time,
+                                      heads, 0, time, _validate.float32_scale(scale))
+                aux = ChunkForwardAux(None, boundaries, 0)
+            else:
+                output, final_state = token_forward(*seq, state, scale=scale)
+        elif prepare_backward:
+            output, final_state, aux = chunk_forward(*seq, state, scale=scale, return_aux=True)
+        else:
+            output, final_state = chunk_forward(*seq, state, scale=scale)
+        saved = [q, k, v, g, beta, w]
+        ctx.n_chunk_boundaries = ctx.n_tail_boundaries = 0
+        ctx.full_tokens = 0
+        if aux is not None:
+            ctx.full_tokens = aux.full_tokens
+            if aux.chunk_boundaries is not None:
+                saved.append(aux.chunk_boundaries)
+                ctx.n_chunk_boundaries = 1
+            if aux.tail_boundaries is not None:
+                saved.append(aux.tail_boundaries)
+                ctx.n_tail_boundaries = 1
+        ctx.save_for_backward(*saved)
+        ctx.set_materialize_grads(False)
+        ctx.has_initial_state = initial_state is not None
+        ctx.scale = scale
+        return output, final_state
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, d_output, d_final_state):
+        q, k, v, g, beta, w, *saved = ctx.saved_tensors
+        if q.shape[1] == 0:
+            empty = tuple(torch.empty_like(x) for x in (q, k, v, g, beta, w))
+            d_state = None
+            if ctx.has_initial_state:
+                d_state = (
+                    torch.zeros((q.shape[0], q.shape[2], _DIM, _DIM), device=q.device,
+                                dtype=torch.float32)
+                    if d_final_state is None
+                    else d_final_state.contiguous().clone()
+                )
+            return (*empty, d_state, None, None)
+        if d_output is None:
+            d_output = torch.zeros_like(v)
+        elif not d_output.is_contiguous():
+            d_output = d_output.contiguous()
+        if d_final_state is not None and not d_final_state.is_contiguous():
+            d_final_state = d_final_state.contiguous()
+        chunk_boundaries = saved.pop(0) if ctx.n_chunk_boundaries else None
+        tail_boundaries = saved.pop(0) if ctx.n_tail_boundaries else None
+        aux = ChunkForwardAux(chunk_boundaries, tail_boundaries, ctx.full_tokens)
+        seq = tuple(_validate.detached(x) for x in (q, k, v, g, beta, w))
+        *sequence_grads, d_initial_state = backward_from_aux(
+            *seq, aux, d_output, d_final_state, _validate.float32_scale(ctx.scale)
+        )
+        return (*sequence_grads, d_initial_state if ctx.has_initial_state else None, None, None)
+
+
+def chunk_gdn2(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    g: torch.Tensor,
+    beta: torch.Tensor,
+    w: torch.Tensor,
+    initial_state: torch.Tensor | None = None,
+    *,
+    scale: float | None = None,
+    output_final_state: bool = False,
+) -> tuple[torch.Tensor, torch.Tensor | None]:
+    """Gated DeltaNet-2 with shape-dispatched forward and native backward.
+
+    Sequence tensors are contiguous ``[B, T, H, 128]``; q/k/v/beta/w fp16 or bf16, ``g``
+    additionally fp32; states fp32 ``[B, H, 128, 128]``.  Gate activations and q/k
+    normalisation stay with the caller.  ``g`` must be finite and non-positive with every
+    16-token prefix sum above ln(FLT_MIN).  Returns ``(o, S_T)`` or ``(o, None)``.
+    """
+
+    output_scale = float(scale) if scale is not None else 1.0 / math.sqrt(_DIM)
+    if not math.isfinite(output_scale):
+        raise ValueError("scale must be finite")
+    wants_grad = torch.is_grad_enabled() and any(
+        isinstance(t, torch.Tensor) and t.requires_grad for t in (q, k, v, g, beta, w, initial_state)
+    )
+    if wants_grad:
+        output, final_state = _ChunkGDN2.apply(q, k, v, g, beta, w, initial_state, output_scale, True)
+        return output, final_state if output_final_state else None
+
+    seq = tuple(_validate.detached(x) for x in (q, k, v, g, beta, w))
+    state = _validate.detached(initial_state)
+    if _use_recurrent_kernel(q.shape[0], q.shape[1], q.shape[2], chunk_api=True):
+        output, final_state = token_forward(*seq, state, scale=output_scale)
+    else:
+        output, final_state = chunk_forward(*seq, state, scale=output_scale, return_aux=False)
+    return output, final_state if output_final_state else None
+
+
+def recurrent_gdn2(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    g: torch.Tensor,
+    beta: torch.Tensor,
+    w: torch.Tensor,
+    initial_state: torch.Tensor | None = None,
+    *,
+    scale: float | None = None,
+    out: torch.Tensor | None = None,
+    final_state_out: torch.Tensor | None = None,
+    inplace_final_state: bool = False,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """Forward-only GDN2 for serving, with the recurrent/chunk crossover."""
+
+    return token_forward(q, k, v, g, beta, w, initial_state, scale=scale, out=out,
+                         final_state_out=final_state_out, inplace_final_state=inplace_final_state)
+
+
+__all__ = ["chunk_gdn2", "recurrent_gdn2"]

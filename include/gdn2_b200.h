@@ -1,0 +1,147 @@
+/*
+ * gdn2_b200 -- C ABI of the B200 (sm_100a) Gated DeltaNet-2 kernels.
+ *
+ * This header is the drop-in boundary: these are the calls a host binding
+ * makes in place of the reference project's cached TVM-FFI executors
+ * (`compiled(*tensors, scalars, stream)`).  Every entry point
+ *
+ *   - takes raw device pointers, 64-bit sizes, a dtype code, a float scale and
+ *     the CUDA stream to launch on (the caller makes the owning device
+ *     current first);
+ *   - never allocates, frees, synchronises or throws; outputs and scratch are
+ *     caller-owned;
+ *   - returns GDN2_OK or a negative gdn2_status, after validating its
+ *     arguments on the host and checking cudaGetLastError() after launch.
+ *
+ * Layouts (identical to the reference, README.md:48-54 of the reference):
+ *   sequence tensors  [B, T, H, 128] contiguous, q/k/v/beta/w in `dtype`
+ *                     (bf16 or fp16), g in `g_dtype` (same as dtype, or fp32);
+ *   states            [B, H, 128, 128] fp32, key-major rows, value contiguous;
+ *   boundary stacks   [B, n_slots, H, 128, 128] fp32, slot j = state (or state
+ *                     cotangent) before token t_begin + j*GDN2_TOKEN_INTERVAL,
+ *                     last slot = after token t_end-1,
+ *                     n_slots = ceil((t_end - t_begin)/GDN2_TOKEN_INTERVAL) + 1.
+ *
+ * Token sub-ranges: the token-path calls work on tokens [t_begin, t_end) of a
+ * [B, T, H, 128] tensor, so that a ragged tail after the last full chunk runs
+ * on the same buffers without copies.
+ */
+#ifndef GDN2_B200_H_
+#define GDN2_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GDN2_DIM 128            /* K == V == 128 */
+#define GDN2_TOKEN_INTERVAL 16  /* tokens between two token-path boundary slots */
+#define GDN2_CHUNK 64           /* tokens per chunk of the tensor-core chunk path */
+
+typedef enum gdn2_dtype {
+  GDN2_BF16 = 0,
+  GDN2_FP16 = 1,
+  GDN2_FP32 = 2 /* only valid for g_dtype */
+} gdn2_dtype;
+
+typedef enum gdn2_status {
+  GDN2_OK = 0,
+  GDN2_ERR_NULL_POINTER = -1,
+  GDN2_ERR_BAD_SHAPE = -2,
+  GDN2_ERR_BAD_DTYPE = -3,
+  GDN2_ERR_BAD_RANGE = -4,
+  GDN2_ERR_ALIGNMENT = -5,
+  GDN2_ERR_UNSUPPORTED = -6,
+  GDN2_ERR_LAUNCH = -7,
+  GDN2_ERR_DEVICE = -8,
+  GDN2_ERR_TOO_LARGE = -9
+} gdn2_status;
+
+/* Library/ABI version (major*10000 + minor*100 + patch). */
+int gdn2_version(void);
+
+/* Human-readable text for a gdn2_status (static storage). */
+const char* gdn2_status_string(int status);
+
+/* Text of the last CUDA error seen by the calling thread's most recent failed
+ * entry point (static thread-local storage; empty when none). */
+const char* gdn2_last_cuda_error(void);
+
+/* 1 when the current device is compute capability 10.x, else 0 (negative
+ * status on a CUDA error).  Replaces the reference's capability gate
+ * (src/gdn2_sm120/recurrent.py:412-418, chunk.py:1210-1213). */
+int gdn2_device_supported(void);
+
+/*
+ * Recurrent / decode forward over tokens [t_begin, t_end).
+ * Replaces _token_forward_kernel and its launcher
+ * (src/gdn2_sm120/recurrent.py:108-243, 306-340, 576-648).
+ *
+ *   initial_state  may be NULL (recurrence starts from zero)
+ *   out            [B, T, H, 128] in `dtype`; rows [t_begin, t_end) are written
+ *   final_state    fp32 state after token t_end-1; may equal initial_state
+ *                  exactly (in-place update); may be NULL if not wanted
+ *   boundaries     optional boundary stack (see header comment), or NULL
+ * State pointers need only 4-byte alignment; 16-byte aligned ones use 128-bit
+ * transfers.
+ */
+int gdn2_token_forward(const void* q, const void* k, const void* v, const void* g,
+                       const void* beta, const void* w, const float* initial_state,
+                       void* out, float* final_state, float* boundaries,
+                       int64_t batch, int64_t time, int64_t heads,
+                       int64_t t_begin, int64_t t_end,
+                       int dtype, int g_dtype, float scale, void* stream);
+
+/*
+ * T == 1 closed form for a zero initial state: S = k (w*v)^T,
+ * o = scale (q.k) (w*v).  Reads neither g nor beta.
+ * Replaces _token_forward_t1_zero_kernel (src/gdn2_sm120/recurrent.py:246-303,
+ * 343-371, 651-701).
+ */
+int gdn2_token_forward_t1_zero(const void* q, const void* k, const void* v, const void* w,
+                               void* out, float* final_state,
+                               int64_t batch, int64_t heads,
+                               int dtype, float scale, void* stream);
+
+/*
+ * Reverse scan of the state cotangent over tokens [t_begin, t_end):
+ *   dS' = dS + (scale q) do^T ; du = dS'^T k ; dS <- exp(g) * (dS' - (beta k) du^T).
+ * Writes every boundary slot of `d_boundaries` (required) and, when non-NULL,
+ * the cotangent of the state before t_begin into `d_initial_state`.
+ * d_final_state may be NULL (zero terminal cotangent).
+ * Replaces the scalar boundary scan _wy_boundary_dstate_kernel
+ * (src/gdn2_sm120/backward_parallel.py:625-718) and its host wrapper
+ * wy_boundary_dstate (:1997-2190) for the token path.
+ */
+int gdn2_token_dstate_scan(const void* q, const void* k, const void* g, const void* beta,
+                           const void* d_out, const float* d_final_state,
+                           float* d_boundaries, float* d_initial_state,
+                           int64_t batch, int64_t time, int64_t heads,
+                           int64_t t_begin, int64_t t_end,
+                           int dtype, int g_dtype, float scale, void* stream);
+
+/*
+ * Chunk-local token VJP over tokens [t_begin, t_end): from the forward state
+ * boundaries (written by gdn2_token_forward) and the cotangent boundaries
+ * (written by gdn2_token_dstate_scan) recompute each 16-token span forward in
+ * fp32 and sweep it in reverse.  Writes rows [t_begin, t_end) of
+ * dq, dk, dv, dbeta, dw (`dtype`) and dg (`g_dtype`).
+ * Replaces _parallel_chunk_vjp_kernel / _parallel_chunk_vjp_full_kernel and
+ * their reduction (src/gdn2_sm120/backward_parallel.py:1052-1421) and the short
+ * final-state-only backward kernels (src/gdn2_sm120/backward.py:378-797); unlike
+ * those it never reconstructs earlier states by inverting the recurrence.
+ */
+int gdn2_token_chunk_vjp(const void* q, const void* k, const void* v, const void* g,
+                         const void* beta, const void* w, const void* d_out,
+                         const float* boundaries, const float* d_boundaries,
+                         void* dq, void* dk, void* dv, void* dg, void* dbeta, void* dw,
+                         int64_t batch, int64_t time, int64_t heads,
+                         int64_t t_begin, int64_t t_end,
+                         int dtype, int g_dtype, float scale, void* stream);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#endif /* GDN2_B200_H_ */

@@ -1,0 +1,151 @@
+"""CPU tests of the oracle: pinned to the reference-generated golden vectors, plus the
+self-consistency identities the reference checks (tests/test_reference.py:11-113 there)."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import gdn2_oracle as oracle
+from conftest import load_golden
+
+GOLDEN_CASES = [
+    "config0_b1_t64_h2",
+    "decode_b1_t5_h2_bf16",
+    "decode_b1_t5_h2_fp16_lowg",
+    "decode_b2_t1_h3_zero",
+    "short_b2_t19_h3",
+    "chunk_b1_t129_h2_nostate",
+]
+
+
+def _inputs(rec):
+    return (rec["q"], rec["k"], rec["v"], rec["g"], rec["beta"], rec["w"], rec.get("initial_state"))
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_fp32_oracle_reproduces_reference_forward_bit_exactly(name):
+    """Same op order in float32 => identical bits to reference.py:47-99."""
+
+    torch.set_num_threads(1)
+    rec = load_golden(name)
+    q, k, v, g, beta, w, s0 = _inputs(rec)
+    o, s = oracle.recurrence(q, k, v, g, beta, w, s0, scale=rec["scale"], dtype=torch.float32)
+    assert torch.equal(o.to(rec["dtype"]).view(torch.int16), rec["out"].view(torch.int16))
+    torch.testing.assert_close(s, rec["final_state"], rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_fp64_oracle_agrees_with_reference_within_fp32_rounding(name):
+    rec = load_golden(name)
+    q, k, v, g, beta, w, s0 = _inputs(rec)
+    o, s = oracle.recurrence(q, k, v, g, beta, w, s0, scale=rec["scale"])
+    assert oracle.rel_l2(s, rec["final_state"]) < 2e-6
+    torch.testing.assert_close(o.to(rec["dtype"]).float(), rec["out"].float(), rtol=2e-2, atol=1e-3)
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_chunkwise_restatement_matches_reference_chunk16(name):
+    rec = load_golden(name)
+    q, k, v, g, beta, w, s0 = _inputs(rec)
+    o, s = oracle.chunkwise(q, k, v, g, beta, w, s0, scale=rec["scale"], chunk_size=16)
+    assert oracle.rel_l2(s, rec["final_state_chunk16"]) < 5e-6
+    assert oracle.rel_l2(o, rec["out_chunk16"].double()) < 6e-3  # reference output is 16-bit
+
+
+@pytest.mark.parametrize("name", [n for n in GOLDEN_CASES if n != "decode_b1_t5_h2_fp16_lowg"])
+def test_gradients_match_reference_autograd(name):
+    """Reference gradients are fp32 autograd results rounded to the leaf dtypes."""
+
+    rec = load_golden(name)
+    q, k, v, g, beta, w, s0 = _inputs(rec)
+    o, s = oracle.recurrence(q, k, v, g, beta, w, s0, scale=rec["scale"])
+    # the reference loss squares the *rounded* output and autograd carries the cotangent
+    # back through the cast in the 16-bit type: d/do = round(2*round(o)/n)
+    o_rounded = o.to(rec["dtype"]).float()
+    d_out = (2.0 * o_rounded / o.numel()).to(rec["dtype"]).double()
+    d_state = 2.0 * s / s.numel()
+    grads = oracle.token_vjp(q, k, v, g, beta, w, s0, d_out, d_state, scale=rec["scale"])
+    for label, grad in zip(("dq", "dk", "dv", "dg", "dbeta", "dw"), grads):
+        tol = 6e-3 if rec[label].dtype != torch.float32 else 2e-5
+        assert oracle.rel_l2(grad, rec[label].double()) < tol, label
+    if s0 is not None:
+        assert oracle.rel_l2(grads[6], rec["dS0"]) < 2e-5
+
+
+@pytest.mark.parametrize("time", [1, 3, 4, 5, 9])
+@pytest.mark.parametrize("chunk", [1, 2, 4])
+def test_chunkwise_equals_recurrence_small_dims(time, chunk):
+    gen = torch.Generator().manual_seed(17)
+    shape_k, shape_v = (2, time, 3, 4), (2, time, 3, 5)
+    q, k, beta = (torch.randn(shape_k, generator=gen, dtype=torch.float64) for _ in range(3))
+    v, w = (torch.randn(shape_v, generator=gen, dtype=torch.float64) for _ in range(2))
+    g = -torch.rand(shape_k, generator=gen, dtype=torch.float64)
+    s0 = torch.randn((2, 3, 4, 5), generator=gen, dtype=torch.float64)
+    o_r, s_r = oracle.recurrence(q, k, v, g, beta, w, s0)
+    o_c, s_c = oracle.chunkwise(q, k, v, g, beta, w, s0, chunk_size=chunk)
+    torch.testing.assert_close(o_c, o_r, rtol=1e-10, atol=1e-10)
+    torch.testing.assert_close(s_c, s_r, rtol=1e-10, atol=1e-10)
+
+
+@pytest.mark.parametrize("with_state", [True, False])
+@pytest.mark.parametrize("with_final_grad", [True, False])
+def test_token_vjp_equals_autograd(with_state, with_final_grad):
+    gen = torch.Generator().manual_seed(23)
+    shape_k, shape_v = (2, 5, 2, 7), (2, 5, 2, 5)
+    q, k, beta = (torch.randn(shape_k, generator=gen, dtype=torch.float64) for _ in range(3))
+    v, w = (torch.randn(shape_v, generator=gen, dtype=torch.float64) for _ in range(2))
+    g = -torch.rand(shape_k, generator=gen, dtype=torch.float64)
+    s0 = torch.randn((2, 2, 7, 5), generator=gen, dtype=torch.float64) if with_state else None
+    d_out = torch.randn(shape_v, generator=gen, dtype=torch.float64)
+    d_fin = torch.randn((2, 2, 7, 5), generator=gen, dtype=torch.float64) if with_final_grad else None
+    _, _, auto = oracle.recurrence_grads(q, k, v, g, beta, w, s0, d_out, d_fin)
+    manual = oracle.token_vjp(q, k, v, g, beta, w, s0, d_out, d_fin)
+    for a, m in zip(auto, manual):
+        if a is None:
+            assert m is None
+        else:
+            torch.testing.assert_close(m, a, rtol=1e-10, atol=1e-12)
+
+
+def test_zero_key_known_answer():
+    """k = 0 => o = 0 and S_T = S_0 * exp(sum g) (reference tests/test_reference.py:11-24)."""
+
+    gen = torch.Generator().manual_seed(3)
+    shape = (1, 6, 2, 4)
+    q, v, beta, w = (torch.randn(shape, generator=gen, dtype=torch.float64) for _ in range(4))
+    k = torch.zeros(shape, dtype=torch.float64)
+    g = -torch.rand(shape, generator=gen, dtype=torch.float64)
+    s0 = torch.randn((1, 2, 4, 4), generator=gen, dtype=torch.float64)
+    o, s = oracle.recurrence(q, k, v, g, beta, w, s0)
+    expected = s0 * g.sum(dim=1).exp().unsqueeze(-1)
+    torch.testing.assert_close(s, expected, rtol=1e-12, atol=1e-12)
+    # with k == 0 nothing is written, the output only reads the decayed initial state
+    decayed = s0.clone()
+    for t in range(6):
+        decayed = g[:, t].exp().unsqueeze(-1) * decayed
+        ref = torch.einsum("bhk,bhkv->bhv", q[:, t] * 0.5, decayed)
+        torch.testing.assert_close(o[:, t], ref, rtol=1e-12, atol=1e-12)
+
+
+def test_t1_zero_state_closed_form():
+    q, k, v, g, beta, w, _ = oracle.make_inputs(2, 1, 3, seed=611, with_state=False)
+    o, s = oracle.recurrence(q, k, v, g, beta, w, None, scale=0.0625)
+    o_cf, s_cf = oracle.t1_zero_closed_form(q, k, v, w, scale=0.0625)
+    torch.testing.assert_close(o_cf, o, rtol=1e-12, atol=1e-14)
+    torch.testing.assert_close(s_cf, s, rtol=1e-12, atol=1e-14)
+
+
+def test_empty_sequence():
+    q, k, v, g, beta, w, s0 = oracle.make_inputs(1, 0, 2)
+    o, s = oracle.recurrence(q, k, v, g, beta, w, s0)
+    assert o.shape == (1, 0, 2, 128)
+    torch.testing.assert_close(s, s0.double(), rtol=0, atol=0)
+
+
+def test_input_distribution_respects_decay_contract():
+    *_, g, _, _, _ = oracle.make_inputs(1, 256, 2, seed=0)[:4] + (None, None, None)
+    g = oracle.make_inputs(1, 256, 2, seed=0)[3]
+    assert g.max() <= 0 and g.min() >= -5.0
+    windows = g.unfold(1, 16, 16).sum(-1)
+    assert windows.min() > -87.0

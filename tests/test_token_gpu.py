@@ -1,0 +1,249 @@
+"""GPU parity tests of the token path (decode / short sequences / serving options).
+
+Every kernel call goes through the C ABI (ctypes) via the public Python API and is
+compared with the CPU oracle on identical seeded inputs.  Tolerances: output
+rtol = atol = 2e-3 and state rtol = atol = 1e-5 (the reference's own token-path
+tolerances, tests/test_recurrent.py:195-226 there) -- far inside the 2e-2 / 1e-2 and
+1e-3 relative bounds of the benchmark specification.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import pytest
+import torch
+
+import gdn2_oracle as oracle
+from conftest import load_golden
+from gdn2_sm120_b200 import _lib, chunk_gdn2, recurrent_gdn2, token_forward
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def dev(*tensors):
+    return tuple(None if t is None else t.to(DEV) for t in tensors)
+
+
+def check_forward(out, state, ref_out, ref_state, dtype):
+    torch.testing.assert_close(out.float().cpu(), ref_out.to(dtype).float(), rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(state.cpu().double(), ref_state, rtol=1e-5, atol=1e-5)
+    assert oracle.rel_l2(state, ref_state) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("low_g", [False, True])
+@pytest.mark.parametrize("with_state", [True, False])
+def test_decode_shapes_match_oracle(dtype, low_g, with_state):
+    g_dtype = dtype if low_g else torch.float32
+    cpu = oracle.make_inputs(1, 5, 2, seed=1234, dtype=dtype, g_dtype=g_dtype, with_state=with_state)
+    ref_out, ref_state = oracle.recurrence(*cpu, scale=0.125)
+    out, state = recurrent_gdn2(*dev(*cpu), scale=0.125)
+    assert out.dtype == dtype and state.dtype == torch.float32
+    check_forward(out, state, ref_out, ref_state, dtype)
+
+
+@pytest.mark.parametrize("name", ["config0_b1_t64_h2", "decode_b1_t5_h2_bf16", "decode_b1_t5_h2_fp16_lowg",
+                                  "decode_b2_t1_h3_zero", "short_b2_t19_h3"])
+def test_token_forward_matches_reference_golden_vectors(name):
+    rec = load_golden(name)
+    args = dev(rec["q"], rec["k"], rec["v"], rec["g"], rec["beta"], rec["w"], rec.get("initial_state"))
+    out, state = token_forward(*args, scale=rec["scale"])
+    torch.testing.assert_close(out.float().cpu(), rec["out"].float(), rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(state.cpu(), rec["final_state"], rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_t1_zero_state_closed_form(dtype):
+    q, k, v, g, beta, w, _ = oracle.make_inputs(2, 1, 3, seed=611, dtype=dtype, with_state=False)
+    ref_out, ref_state = oracle.t1_zero_closed_form(q, k, v, w, scale=0.0625)
+    dq, dk, dv, dg, dbeta, dw = dev(q, k, v, g, beta, w)
+    out, state = token_forward(dq, dk, dv, dg, dbeta, dw, scale=0.0625)
+    check_forward(out, state, ref_out, ref_state, dtype)
+    # the closed form reads neither g nor beta: changing them must not change a bit
+    out2, state2 = token_forward(dq, dk, dv, dg.to(dtype), torch.zeros_like(dbeta), dw, scale=0.0625)
+    assert torch.equal(state, state2) and torch.equal(out, out2)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        out3, state3 = token_forward(dq, dk, dv, dg, dbeta, dw, scale=0.0625)
+    side.synchronize()
+    assert torch.equal(state, state3) and torch.equal(out, out3)
+    out4, _ = token_forward(dq, dk, dv, dg, dbeta, dw, scale=0.25)
+    torch.testing.assert_close(out4.float(), 4 * out.float(), rtol=2e-2, atol=1e-4)
+
+
+def test_serving_buffers_are_returned_by_identity():
+    cpu = oracle.make_inputs(2, 3, 4, seed=77)
+    ref_out, ref_state = oracle.recurrence(*cpu)
+    q, k, v, g, beta, w, s0 = dev(*cpu)
+    out_buf = torch.empty_like(q)
+    fin_buf = torch.empty_like(s0)
+    out, fin = recurrent_gdn2(q, k, v, g, beta, w, s0, out=out_buf, final_state_out=fin_buf)
+    assert out is out_buf and fin is fin_buf
+    check_forward(out, fin, ref_out, ref_state, q.dtype)
+    s0_before = s0.clone()
+    out, fin = recurrent_gdn2(q, k, v, g, beta, w, s0)  # default: fresh tensors, inputs untouched
+    assert torch.equal(s0, s0_before) and fin.data_ptr() != s0.data_ptr()
+    out, fin = recurrent_gdn2(q, k, v, g, beta, w, s0, inplace_final_state=True)
+    assert fin is s0
+    check_forward(out, s0, ref_out, ref_state, q.dtype)
+
+
+def test_serving_option_rejections():
+    q, k, v, g, beta, w, s0 = dev(*oracle.make_inputs(1, 2, 2, seed=5))
+    with pytest.raises(ValueError, match="requires initial_state"):
+        recurrent_gdn2(q, k, v, g, beta, w, inplace_final_state=True)
+    with pytest.raises(ValueError, match="cannot be used with inplace_final_state"):
+        recurrent_gdn2(q, k, v, g, beta, w, s0, final_state_out=torch.empty_like(s0), inplace_final_state=True)
+    with pytest.raises(ValueError, match="out must not overlap"):
+        recurrent_gdn2(q, k, v, g, beta, w, s0, out=q)
+    shared = torch.empty(s0.numel() + q.numel(), device=DEV)
+    with pytest.raises(ValueError, match="out must not overlap"):
+        recurrent_gdn2(q, k, v, g, beta, w, s0, out=s0.view(torch.bfloat16)[0, 0, :2].reshape(1, 2, 2, 128))
+    with pytest.raises(ValueError, match="final_state_out must not overlap"):
+        recurrent_gdn2(q, k, v, g, beta, w, s0, final_state_out=s0)
+    with pytest.raises(TypeError, match="final_state_out must use"):
+        recurrent_gdn2(q, k, v, g, beta, w, s0, final_state_out=torch.empty_like(s0, dtype=torch.float64))
+    with pytest.raises(ValueError, match="out must have shape"):
+        recurrent_gdn2(q, k, v, g, beta, w, s0, out=torch.empty(1, 3, 2, 128, device=DEV, dtype=q.dtype))
+    with pytest.raises(ValueError, match="representable as float32"):
+        recurrent_gdn2(q, k, v, g, beta, w, s0, scale=1e100)
+    del shared
+
+
+def test_unaligned_state_and_output_buffers():
+    """Contiguous but only 4-byte (state) / 2-byte (out) aligned buffers use scalar I/O."""
+
+    cpu = oracle.make_inputs(2, 2, 3, seed=91)
+    ref_out, ref_state = oracle.recurrence(*cpu)
+    q, k, v, g, beta, w, s0 = dev(*cpu)
+    n_state = s0.numel()
+    backing_in = torch.empty(n_state + 1, device=DEV)
+    s_unaligned = backing_in[1:].view_as(s0)
+    s_unaligned.copy_(s0)
+    assert s_unaligned.data_ptr() % 16 != 0
+    backing_out = torch.empty(q.numel() + 1, device=DEV, dtype=q.dtype)
+    out_unaligned = backing_out[1:].view_as(q)
+    backing_fin = torch.empty(n_state + 1, device=DEV)
+    fin_unaligned = backing_fin[1:].view_as(s0)
+    out, fin = recurrent_gdn2(q, k, v, g, beta, w, s_unaligned, out=out_unaligned, final_state_out=fin_unaligned)
+    assert out is out_unaligned and fin is fin_unaligned
+    check_forward(out, fin, ref_out, ref_state, q.dtype)
+    out, fin = recurrent_gdn2(q, k, v, g, beta, w, s_unaligned, inplace_final_state=True)
+    assert fin is s_unaligned
+    check_forward(out, fin, ref_out, ref_state, q.dtype)
+
+
+def test_offset_singleton_slices_and_odd_singleton_strides():
+    torch.manual_seed(831)
+
+    def token_slice(dtype):
+        return torch.randn((1, 8, 1, 128), device=DEV, dtype=dtype)[:, 4:5]
+
+    q, k, v, beta, w = [token_slice(torch.bfloat16) * 0.3 for _ in range(5)]
+    q, k, v, beta, w = [torch.randn((1, 8, 1, 128), device=DEV).mul(0.3).bfloat16()[:, 4:5] for _ in range(5)]
+    g = -torch.rand((1, 8, 1, 128), device=DEV)[:, 4:5] * 0.04
+    s0 = (torch.randn((1, 3, 128, 128), device=DEV) * 0.1)[:, 1:2]
+    out_buf = torch.empty((1, 8, 1, 128), device=DEV, dtype=q.dtype)[:, 4:5]
+    fin_buf = torch.empty((1, 3, 128, 128), device=DEV)[:, 1:2]
+    assert all(t.is_contiguous() for t in (q, k, v, g, beta, w, s0, out_buf, fin_buf))
+    ref_out, ref_state = oracle.recurrence(*(t.cpu() for t in (q, k, v, g, beta, w, s0)), scale=0.0625)
+    out, fin = recurrent_gdn2(q, k, v, g, beta, w, s0, scale=0.0625, out=out_buf, final_state_out=fin_buf)
+    assert out is out_buf and fin is fin_buf
+    check_forward(out, fin, ref_out, ref_state, q.dtype)
+
+    shape, strides = (2, 1, 3, 128), (384, 999, 128, 1)
+    cpu = oracle.make_inputs(2, 1, 3, seed=919)
+    moved = []
+    for t in cpu[:6]:
+        s = torch.empty_strided(shape, strides, device=DEV, dtype=t.dtype)
+        s.copy_(t)
+        moved.append(s)
+    assert moved[0].is_contiguous() and moved[0].stride() == strides
+    ref_out, ref_state = oracle.recurrence(*cpu)
+    out, fin = token_forward(*moved, cpu[6].to(DEV))
+    check_forward(out, fin, ref_out, ref_state, cpu[0].dtype)
+
+
+def test_empty_sequence_semantics():
+    q, k, v, g, beta, w, s0 = dev(*oracle.make_inputs(2, 0, 3, seed=1))
+    out, fin = recurrent_gdn2(q, k, v, g, beta, w, s0)
+    assert out.shape == (2, 0, 3, 128) and torch.equal(fin, s0) and fin is not s0
+    out, fin = recurrent_gdn2(q, k, v, g, beta, w)
+    assert torch.count_nonzero(fin) == 0
+    out, fin = recurrent_gdn2(q, k, v, g, beta, w, s0, inplace_final_state=True)
+    assert fin is s0
+    out, fin = chunk_gdn2(q, k, v, g, beta, w, s0, output_final_state=True)
+    assert torch.equal(fin, s0)
+
+
+@pytest.mark.parametrize("time", [2, 15, 16, 17, 33, 63])
+def test_short_sequences_via_chunk_api(time):
+    cpu = oracle.make_inputs(2, time, 3, seed=2026 + time)
+    ref_out, ref_state = oracle.recurrence(*cpu)
+    out, fin = chunk_gdn2(*dev(*cpu), output_final_state=True)
+    check_forward(out, fin, ref_out, ref_state, cpu[0].dtype)
+    out2, fin2 = chunk_gdn2(*dev(*cpu))
+    assert fin2 is None and torch.equal(out, out2)
+
+
+def test_non_default_stream_and_launch_reuse_across_lengths():
+    side = torch.cuda.Stream()
+    for time, scale in ((1, 0.125), (7, 0.125), (7, 0.3), (40, None)):
+        cpu = oracle.make_inputs(1, time, 2, seed=300 + time)
+        ref_out, ref_state = oracle.recurrence(*cpu, scale=scale)
+        args = dev(*cpu)
+        torch.cuda.synchronize()
+        with torch.cuda.stream(side):
+            out, fin = token_forward(*args, scale=scale)
+        side.synchronize()
+        check_forward(out, fin, ref_out, ref_state, cpu[0].dtype)
+
+
+def test_decode_config_in_place_full_size():
+    """Benchmark decode configuration: B=64, H=32, T=1, in-place fp32 state; then the
+    zero-state closed form at B=256, H=32."""
+
+    cpu = oracle.make_inputs(64, 1, 32, seed=0)
+    ref_out, ref_state = oracle.recurrence(*cpu, dtype=torch.float32)
+    q, k, v, g, beta, w, s0 = dev(*cpu)
+    out = torch.empty_like(q)
+    out_ret, fin = recurrent_gdn2(q, k, v, g, beta, w, s0, out=out, inplace_final_state=True)
+    assert fin is s0 and out_ret is out
+    torch.testing.assert_close(out.float().cpu(), ref_out.to(q.dtype).float(), rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(s0.cpu(), ref_state, rtol=1e-5, atol=1e-5)
+    # a second step continues from the updated state (decode loop)
+    ref_out2, ref_state2 = oracle.recurrence(*cpu[:6], ref_state, dtype=torch.float32)
+    recurrent_gdn2(q, k, v, g, beta, w, s0, out=out, inplace_final_state=True)
+    torch.testing.assert_close(s0.cpu(), ref_state2, rtol=2e-5, atol=2e-5)
+
+    cpu = oracle.make_inputs(256, 1, 32, seed=0, with_state=False)
+    ref_out, ref_state = oracle.t1_zero_closed_form(cpu[0], cpu[1], cpu[2], cpu[5], dtype=torch.float32)
+    out, fin = recurrent_gdn2(*dev(*cpu[:6]))
+    torch.testing.assert_close(fin.cpu(), ref_state, rtol=1e-6, atol=1e-7)
+    torch.testing.assert_close(out.float().cpu(), ref_out.to(out.dtype).float(), rtol=2e-3, atol=2e-3)
+
+
+def test_raw_c_abi_call_with_token_sub_range():
+    """Call the C entry point directly: process tokens [3, 9) of a T=12 tensor and write a
+    boundary stack; rows outside the range of `out` must stay untouched."""
+
+    cpu = oracle.make_inputs(1, 12, 2, seed=44)
+    q, k, v, g, beta, w, s0 = dev(*cpu)
+    out = torch.full_like(q, 7.0)
+    fin = torch.empty_like(s0)
+    bnd = torch.empty((1, 2, 2, 128, 128), device=DEV)
+    handle = _lib.lib()
+    status = handle.gdn2_token_forward(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), w.data_ptr(),
+        s0.data_ptr(), out.data_ptr(), fin.data_ptr(), bnd.data_ptr(), 1, 12, 2, 3, 9,
+        _lib.BF16, _lib.FP32, ctypes.c_float(0.1), torch.cuda.current_stream().cuda_stream)
+    assert status == 0
+    torch.cuda.synchronize()
+    sub = tuple(t[:, 3:9] for t in cpu[:6])
+    ref_out, ref_state = oracle.recurrence(*sub, cpu[6], scale=0.1)
+    torch.testing.assert_close(out[:, 3:9].float().cpu(), ref_out.to(q.dtype).float(), rtol=2e-3, atol=2e-3)
+    assert torch.all(out[:, :3] == 7.0) and torch.all(out[:, 9:] == 7.0)
+    torch.testing.assert_close(fin.cpu().double(), ref_state, rtol=1e-5, atol=1e-5)
+    assert torch.equal(bnd[:, 0], s0) and torch.equal(bnd[:, 1], fin)
