@@ -70,8 +70,8 @@ def backward_from_aux(q, k, v, g, beta, w, aux: ChunkForwardAux, d_out, d_final_
     if full:
         from . import chunk_kernels
 
-        chunk_kernels.backward(q, k, v, g, beta, w, aux.chunk_boundaries, d_out, d_state, grads,
-                               d_initial_state, batch, time, heads, full, scale)
+        chunk_kernels.backward(q, k, v, g, beta, w, aux.workspace, aux.chunk_boundaries, d_out,
+                               d_state, grads, d_initial_state, batch, time, heads, full, scale)
     return (*grads, d_initial_state)
 
 

@@ -40,23 +40,26 @@ class ChunkForwardAux:
                           16-token span of the tail ``[full_tokens, T)`` and after it, or
                           ``None`` when there is no tail.
     ``full_tokens``       number of leading tokens covered by ``chunk_boundaries``.
+    ``workspace``         the chunk kernels' per-chunk WY factors (operand-ready tiles written
+                          by the forward prep kernel and reused by backward), or ``None``.
     """
 
     chunk_boundaries: torch.Tensor | None
     tail_boundaries: torch.Tensor | None
     full_tokens: int
+    workspace: torch.Tensor | None = None
 
 
 def _token_slots(tokens: int) -> int:
     return -(-tokens // _TOKEN_INTERVAL) + 1
 
 
-def _chunk_kernel_tokens(time: int) -> int:
+def _chunk_kernel_tokens(time: int, training: bool) -> int:
     """Leading tokens handed to the tensor-core chunk kernels for a call."""
 
     from . import chunk_kernels
 
-    return chunk_kernels.supported_tokens(time)
+    return chunk_kernels.supported_tokens(time, training=training)
 
 
 def chunk_forward(
@@ -116,7 +119,7 @@ def chunk_forward(
                     "final_state_out may exactly alias initial_state but must not partially overlap it"
                 )
 
-    full_tokens = _chunk_kernel_tokens(time)
+    full_tokens = _chunk_kernel_tokens(time, return_aux)
     tail = time - full_tokens
     chunk_boundaries = tail_boundaries = None
     if return_aux:
@@ -130,18 +133,21 @@ def chunk_forward(
             )
 
     state = initial_state
+    workspace = None
     if full_tokens:
         from . import chunk_kernels
 
-        chunk_kernels.forward(q, k, v, g, beta, w, state, output, final_state, chunk_boundaries,
-                              batch, time, heads, full_tokens, output_scale)
+        workspace = chunk_kernels.forward(q, k, v, g, beta, w, state, output, final_state,
+                                          chunk_boundaries, batch, time, heads, full_tokens,
+                                          output_scale)
         state = final_state
     if tail:
         _launch_token_forward(q, k, v, g, beta, w, state, output, final_state, tail_boundaries,
                               batch, time, heads, full_tokens, time, output_scale)
     if not return_aux:
         return output, final_state
-    return output, final_state, ChunkForwardAux(chunk_boundaries, tail_boundaries, full_tokens)
+    return output, final_state, ChunkForwardAux(chunk_boundaries, tail_boundaries, full_tokens,
+                                                workspace if return_aux else None)
 
 
 __all__ = ["ChunkForwardAux", "chunk_forward"]

@@ -1,0 +1,654 @@
+// Tensor-core chunk forward (64-token chunks, compact-WY form), two kernels:
+//
+//   chunk_prep_kernel   one CTA per (batch, chunk, head), all chunks in parallel.  Builds the WY
+//                       factors of the chunk and writes them as operand-ready blobs:
+//                       cumulative log-decay, block-anchored Gram products on bf16 tcgen05 MMAs,
+//                       blocked inverse of the unit lower-triangular system on CUDA cores (fp32),
+//                       Y = T E and U^T = Z^T T^T on tf32 tcgen05 MMAs.
+//   chunk_scan_kernel   one CTA per (batch, head), chunks in order.  The state lives transposed
+//                       (S^T: value rows x key columns) in TMEM as the fp32 accumulator and is fed
+//                       back as the tf32 A operand of the next MMAs without leaving TMEM:
+//                           R^T  = U^T - S^T Y^T
+//                           O^T  = S^T Qg^T + R^T Aqk^T
+//                           S^T <- S^T diag(d) + R^T Kt
+//                       Operand blobs arrive by 1-D bulk copies on mbarriers.
+//
+// Math per chunk (reference: src/gdn2_sm120/reference.py:149-172, chunk.py:188-331, with the
+// chunk length re-chosen as 64 and the decay normalisation anchored per 16-token block so that
+// every exponent stays inside the contract "16-token prefix sums of g > -87"):
+//   G_i = sum_{t<=i} g_t,  a_I = G at the start of block I = i / 16
+//   L[i][j]   = sum_k beta k_i exp(G_i - a_I) * k_j exp(a_I - G_j)      (j < i)
+//   Aqk[i][j] = sum_k scale q_i exp(G_i - a_I) * k_j exp(a_I - G_j)     (j <= i)
+//   T = (I + L)^-1,  Y = T (beta k exp(G)),  U = T (w v)
+//   Qg = scale q exp(G),  Kt = k exp(G_end - G),  d = exp(G_end)
+
+#include "chunk_common.cuh"
+
+namespace gdn2 {
+
+using namespace tc;
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// prep kernel
+// ---------------------------------------------------------------------------------------------
+constexpr int kPrepThreads = 256;
+constexpr int kLd = 65;  // leading dimension of the fp32 64x64 scratch matrices
+
+struct PrepSmem {
+  // region 1: bf16 Gram A operand [E_anchored ; Q_anchored] (128 x 128), later fp32 L / T / W scratch
+  alignas(128) uint8_t gram_a[32768];
+  // region 2: bf16 Gram B operands K^I, rows j < 16 (I + 1): 4 KiB + 8 KiB + 12 KiB + 16 KiB
+  alignas(128) uint8_t gram_b[40960];
+  alignas(128) uint8_t et[32768];      // E^T  tile X[r = k][c = j], tf32
+  alignas(128) uint8_t zt[32768];      // Z^T  tile X[r = v][c = j], tf32
+  alignas(128) uint8_t tmat[32768];    // T    tile X[r = i][c = j], tf32 (rows 64..127 unused filler)
+  float part[16][kDim];                // per 4-token group partial sums -> exclusive prefixes
+  float gend[kDim];
+  alignas(8) uint64_t bar[2];
+  uint32_t tmem_base;
+};
+
+struct PrepParams {
+  const void *q, *k, *v, *g, *beta, *w;
+  uint8_t* ws;
+  int64_t T, H, n_chunks, n_ch;
+  float scale;
+};
+
+__device__ __forceinline__ int gram_b_offset(int I) { return (I == 0) ? 0 : (I == 1) ? 4096 : (I == 2) ? 12288 : 24576; }
+__device__ __forceinline__ int gram_col(int I) { return (I == 0) ? 0 : (I == 1) ? 16 : (I == 2) ? 48 : 96; }
+
+template <typename T, typename G>
+__global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepParams p) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  PrepSmem& sm = *reinterpret_cast<PrepSmem*>(smem_raw);
+  const WsLayout ws{p.n_ch};
+  int* status = reinterpret_cast<int*>(p.ws + ws.off_status());
+  BoundedWaiter waiter(status);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t ch = blockIdx.x;
+  const int64_t h = ch % p.H;
+  const int64_t c = (ch / p.H) % p.n_chunks;
+  const int64_t b = ch / (p.H * p.n_chunks);
+  const int64_t t0 = c * kChunk;
+
+  if (warp == 0) {
+    tmem_alloc(&sm.tmem_base, 256);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&sm.bar[0], 1);
+    mbar_init(&sm.bar[1], 1);
+    fence_mbar_init();
+  }
+
+  // ---- cumulative log-decay: thread = (4-token group tg, 8-channel group c8) -----------------
+  const int tg = tid >> 4, c8 = tid & 15;
+  float Gc[4][8];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int64_t idx = ((b * p.T + t0 + 4 * tg + e) * p.H + h) * kDim + 8 * c8;
+    float gv[8];
+    load8<G>(p.g, idx, gv);
+#pragma unroll
+    for (int f = 0; f < 8; ++f) Gc[e][f] = (e ? Gc[e - 1][f] : 0.f) + gv[f];
+  }
+#pragma unroll
+  for (int f = 0; f < 8; ++f) sm.part[tg][8 * c8 + f] = Gc[3][f];
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tb = sm.tmem_base;
+  if (tid < kDim) {
+    float run = 0.f;
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      const float x = sm.part[t][tid];
+      sm.part[t][tid] = run;
+      run += x;
+    }
+    sm.gend[tid] = run;
+  }
+  __syncthreads();
+
+  uint8_t* blob_q = p.ws + ws.off_q() + ch * kBlobQ;
+  uint8_t* blob_kt = p.ws + ws.off_kt() + ch * kBlobKt;
+  const int my_block = tg >> 2;
+  float ebar[4][8], ktail[4][8];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int i = 4 * tg + e;
+    const int64_t idx = ((b * p.T + t0 + i) * p.H + h) * kDim + 8 * c8;
+    float kk[8], qq[8], bb[8];
+    load8<T>(p.k, idx, kk);
+    load8<T>(p.q, idx, qq);
+    load8<T>(p.beta, idx, bb);
+    float ea[8], qa[8], qg[8];
+#pragma unroll
+    for (int f = 0; f < 8; ++f) {
+      const int kc = 8 * c8 + f;
+      const float Gi = Gc[e][f] + sm.part[tg][kc];
+      Gc[e][f] = Gi;
+      const float anchored = __expf(Gi - sm.part[4 * my_block][kc]);
+      const float full = __expf(Gi);
+      const float bk = bb[f] * kk[f];
+      ea[f] = bk * anchored;
+      qa[f] = p.scale * qq[f] * anchored;
+      ebar[e][f] = to_tf32(bk * full);
+      qg[f] = to_tf32(p.scale * qq[f] * full);
+      ktail[e][f] = to_tf32(kk[f] * __expf(sm.gend[kc] - Gi));
+    }
+    // Gram A operand rows i (erase) and 64 + i (query), bf16, K-major
+    *reinterpret_cast<uint4*>(sm.gram_a + blk_off<2>(i, 8 * c8, 2048, 128)) =
+        make_uint4(pack_bf16(ea[0], ea[1]), pack_bf16(ea[2], ea[3]), pack_bf16(ea[4], ea[5]), pack_bf16(ea[6], ea[7]));
+    *reinterpret_cast<uint4*>(sm.gram_a + blk_off<2>(64 + i, 8 * c8, 2048, 128)) =
+        make_uint4(pack_bf16(qa[0], qa[1]), pack_bf16(qa[2], qa[3]), pack_bf16(qa[4], qa[5]), pack_bf16(qa[6], qa[7]));
+    // Gram B operands: token i is a column of every row block I >= its own
+#pragma unroll
+    for (int I = 0; I < 4; ++I) {
+      if (I >= my_block) {
+        float kb[8];
+#pragma unroll
+        for (int f = 0; f < 8; ++f) kb[f] = kk[f] * __expf(sm.part[4 * I][8 * c8 + f] - Gc[e][f]);
+        *reinterpret_cast<uint4*>(sm.gram_b + gram_b_offset(I) + blk_off<2>(i, 8 * c8, 2048, 128)) =
+            make_uint4(pack_bf16(kb[0], kb[1]), pack_bf16(kb[2], kb[3]), pack_bf16(kb[4], kb[5]), pack_bf16(kb[6], kb[7]));
+      }
+    }
+    // Q_gamma tile X[r = i][c = k], tf32, straight to the workspace
+    float4* qdst = reinterpret_cast<float4*>(blob_q + blk_off<4>(i, 8 * c8, 4096, 128));
+    qdst[0] = make_float4(qg[0], qg[1], qg[2], qg[3]);
+    qdst[8] = make_float4(qg[4], qg[5], qg[6], qg[7]);  // next 16-byte column chunk: +128 bytes
+  }
+  // transposed tiles X[r = channel][c = token]: the thread's 4 tokens are one 16-byte chunk per channel,
+  // its 8 channels are 8 consecutive rows -> 128 contiguous bytes
+#pragma unroll
+  for (int f = 0; f < 8; ++f) {
+    const uint32_t off = blk_off<4>(8 * c8 + f, 4 * tg, 2048, 128);
+    *reinterpret_cast<float4*>(sm.et + off) = make_float4(ebar[0][f], ebar[1][f], ebar[2][f], ebar[3][f]);
+    *reinterpret_cast<float4*>(blob_kt + off) = make_float4(ktail[0][f], ktail[1][f], ktail[2][f], ktail[3][f]);
+  }
+  {
+    float zz[4][8];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int64_t idx = ((b * p.T + t0 + 4 * tg + e) * p.H + h) * kDim + 8 * c8;
+      float vv[8], ww[8];
+      load8<T>(p.v, idx, vv);
+      load8<T>(p.w, idx, ww);
+#pragma unroll
+      for (int f = 0; f < 8; ++f) zz[e][f] = to_tf32(vv[f] * ww[f]);
+    }
+#pragma unroll
+    for (int f = 0; f < 8; ++f) {
+      *reinterpret_cast<float4*>(sm.zt + blk_off<4>(8 * c8 + f, 4 * tg, 2048, 128)) =
+          make_float4(zz[0][f], zz[1][f], zz[2][f], zz[3][f]);
+    }
+  }
+  if (tid < kDim) {
+    reinterpret_cast<float*>(p.ws + ws.off_d() + ch * kBlobD)[tid] = __expf(sm.gend[tid]);
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+
+  // ---- Gram products on the tensor cores: P_I = [E_a ; Q_a] (K^I)^T -----------------------------
+  if (tid == 0) {
+    tc_fence_after();
+#pragma unroll
+    for (int I = 0; I < 4; ++I) {
+      const uint32_t id = idesc(128, 16 * (I + 1), kFmtBF16, kMajorK, kMajorK);
+      const uint32_t a0 = smem_u32(sm.gram_a), b0 = smem_u32(sm.gram_b + gram_b_offset(I));
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        mma_f16_ss(tb + gram_col(I), smem_desc(a0 + ks * 256, 128, 2048), smem_desc(b0 + ks * 256, 128, 2048), id,
+                   ks > 0 ? 1u : 0u);
+      }
+    }
+    mma_commit(&sm.bar[0]);
+  }
+  waiter.wait(&sm.bar[0], 0);
+  tc_fence_after();
+
+  // ---- pull L (rows 0..63) into fp32 scratch, Aqk (rows 64..127) into the workspace ---------------
+  float* Ln = reinterpret_cast<float*>(sm.gram_a);           // [64][kLd]  16.6 KiB
+  float* Tn = Ln + 64 * kLd;                                  // [64][kLd]  (fits: 2 * 16.6 KiB > 32 KiB? see below)
+  // 2 * 64 * 65 * 4 = 33280 bytes > 32768: Tn spills 512 bytes into gram_b, which is dead by now.
+  float* Wn = reinterpret_cast<float*>(sm.gram_b + 4096);     // [3][16][17] scratch
+  if (warp < 4) {
+    const int r = 32 * warp + lane;       // TMEM lane = row of [E_a ; Q_a]
+    const int i = r & 63;
+    const int I_lo = (warp & 1) * 2;
+    const int my_I = I_lo + (lane >> 4);
+    uint8_t* blob_a = p.ws + ws.off_a() + ch * kBlobA;
+#pragma unroll
+    for (int c0 = 0; c0 < 64; c0 += 16) {
+      uint32_t lo[16], hi[16];
+      const bool need_lo = c0 < 16 * (I_lo + 1), need_hi = c0 < 16 * (I_lo + 2);
+      if (need_lo) tmem_ld16(tmem_addr(tb, 32 * warp, gram_col(I_lo) + c0), lo);
+      if (need_hi) tmem_ld16(tmem_addr(tb, 32 * warp, gram_col(I_lo + 1) + c0), hi);
+      tmem_wait_ld();
+      float vals[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const bool mine_lo = (my_I == I_lo);
+        const float x = mine_lo ? (need_lo ? __uint_as_float(lo[j]) : 0.f) : (need_hi ? __uint_as_float(hi[j]) : 0.f);
+        const int col = c0 + j;
+        vals[j] = (r < 64) ? ((col < i) ? x : 0.f) : ((col <= i) ? to_tf32(x) : 0.f);
+      }
+      if (r < 64) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) Ln[i * kLd + c0 + j] = vals[j];
+      } else {
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+          *reinterpret_cast<float4*>(blob_a + blk_off<4>(i, c0 + 4 * j4, 2048, 128)) =
+              make_float4(vals[4 * j4], vals[4 * j4 + 1], vals[4 * j4 + 2], vals[4 * j4 + 3]);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+
+  // ---- T = (I + L)^-1, blocked: 16x16 diagonal blocks by substitution, the rest by block products --
+  for (int e = tid; e < 64 * 64; e += kPrepThreads) Tn[(e >> 6) * kLd + (e & 63)] = 0.f;
+  __syncthreads();
+  if (tid < 64) {
+    const int I = tid >> 4, cc = tid & 15;
+    float x[16];
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+      float s = (r == cc) ? 1.f : 0.f;
+#pragma unroll
+      for (int m = 0; m < r; ++m) s = fmaf(-Ln[(16 * I + r) * kLd + 16 * I + m], x[m], s);
+      x[r] = s;
+    }
+#pragma unroll
+    for (int r = 0; r < 16; ++r) Tn[(16 * I + r) * kLd + 16 * I + cc] = x[r];
+  }
+  __syncthreads();
+  for (int d = 1; d < 4; ++d) {
+    const int n_pairs = 4 - d;
+    // W = L[I rows, 16J .. 16I) * T[16J .. 16I, J cols]
+    for (int e = tid; e < n_pairs * 256; e += kPrepThreads) {
+      const int pair = e >> 8, r = (e >> 4) & 15, cc = e & 15;
+      const int J = pair, I = pair + d;
+      float s = 0.f;
+      for (int m = 16 * J; m < 16 * I; ++m) s = fmaf(Ln[(16 * I + r) * kLd + m], Tn[m * kLd + 16 * J + cc], s);
+      Wn[(pair * 16 + r) * 17 + cc] = s;
+    }
+    __syncthreads();
+    // T_IJ = -T_II W
+    for (int e = tid; e < n_pairs * 256; e += kPrepThreads) {
+      const int pair = e >> 8, r = (e >> 4) & 15, cc = e & 15;
+      const int J = pair, I = pair + d;
+      float s = 0.f;
+#pragma unroll
+      for (int m = 0; m < 16; ++m) s = fmaf(Tn[(16 * I + r) * kLd + 16 * I + m], Wn[(pair * 16 + m) * 17 + cc], s);
+      Tn[(16 * I + r) * kLd + 16 * J + cc] = -s;
+    }
+    __syncthreads();
+  }
+  // T as tf32 tile X[r = i][c = j] in shared memory (MMA operand) and in the workspace (for backward)
+  {
+    uint8_t* blob_t = p.ws + ws.off_t() + ch * kBlobT;
+    for (int e = tid; e < 64 * 16; e += kPrepThreads) {
+      const int i = e & 63, c4 = e >> 6;  // consecutive threads -> consecutive rows -> contiguous 16-byte chunks
+      const float4 val = make_float4(to_tf32(Tn[i * kLd + 4 * c4]), to_tf32(Tn[i * kLd + 4 * c4 + 1]),
+                                     to_tf32(Tn[i * kLd + 4 * c4 + 2]), to_tf32(Tn[i * kLd + 4 * c4 + 3]));
+      const uint32_t off = blk_off<4>(i, 4 * c4, 2048, 128);
+      *reinterpret_cast<float4*>(sm.tmat + off) = val;
+      *reinterpret_cast<float4*>(blob_t + off) = val;
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+
+  // ---- Y = T E (rows 0..63 of an M = 128 product) and U^T = Z^T T^T --------------------------------
+  if (tid == 0) {
+    tc_fence_after();
+    const uint32_t t0a = smem_u32(sm.tmat), e0 = smem_u32(sm.et), z0 = smem_u32(sm.zt);
+    const uint32_t id_y = idesc(128, 128, kFmtTF32, kMajorK, kMajorK);
+    const uint32_t id_u = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      mma_tf32_ss(tb + 0, smem_desc(t0a + ks * 256, 128, 2048), smem_desc(e0 + ks * 256, 128, 2048), id_y,
+                  ks > 0 ? 1u : 0u);
+    }
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      mma_tf32_ss(tb + 128, smem_desc(z0 + ks * 256, 128, 2048), smem_desc(t0a + ks * 256, 128, 2048), id_u,
+                  ks > 0 ? 1u : 0u);
+    }
+    mma_commit(&sm.bar[1]);
+  }
+  waiter.wait(&sm.bar[1], 0);
+  tc_fence_after();
+  {
+    // Y: lanes 0..63 hold rows i; warps 0,1 take key columns 0..63, warps 4,5 take 64..127
+    const int q4 = warp & 3;
+    if (q4 < 2) {
+      const int i = 32 * q4 + lane;
+      const int cbase = (warp >= 4) ? 64 : 0;
+      uint8_t* blob_y = p.ws + ws.off_y() + ch * kBlobY;
+#pragma unroll
+      for (int c0 = 0; c0 < 64; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld16(tmem_addr(tb, 32 * q4, cbase + c0), r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+          *reinterpret_cast<float4*>(blob_y + blk_off<4>(i, cbase + c0 + 4 * j4, 4096, 128)) =
+              make_float4(to_tf32(__uint_as_float(r[4 * j4])), to_tf32(__uint_as_float(r[4 * j4 + 1])),
+                          to_tf32(__uint_as_float(r[4 * j4 + 2])), to_tf32(__uint_as_float(r[4 * j4 + 3])));
+        }
+      }
+    }
+    // U^T: lane = value row; warps 0..3 take tokens 0..31, warps 4..7 take 32..63 (kept in full fp32)
+    {
+      const int vrow = 32 * q4 + lane;
+      const int ibase = (warp >= 4) ? 32 : 0;
+      uint8_t* blob_ut = p.ws + ws.off_ut() + ch * kBlobUt;
+#pragma unroll
+      for (int c0 = 0; c0 < 32; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld16(tmem_addr(tb, 32 * q4, 128 + ibase + c0), r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+          *reinterpret_cast<float4*>(blob_ut + blk_off<4>(vrow, ibase + c0 + 4 * j4, 2048, 128)) =
+              make_float4(__uint_as_float(r[4 * j4]), __uint_as_float(r[4 * j4 + 1]),
+                          __uint_as_float(r[4 * j4 + 2]), __uint_as_float(r[4 * j4 + 3]));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tb, 256);
+}
+
+// ---------------------------------------------------------------------------------------------
+// scan kernel
+// ---------------------------------------------------------------------------------------------
+constexpr int kScanThreads = 128;
+
+struct ScanSmem {
+  alignas(128) uint8_t y[32768];
+  alignas(128) uint8_t ut[32768];
+  alignas(128) uint8_t q[32768];
+  alignas(128) uint8_t kt[32768];
+  alignas(128) uint8_t a[16384];
+  alignas(16) float d[kDim];
+  alignas(8) uint64_t bar_yqa, bar_ut, bar_kt, bar_mma1, bar_mma2;
+  uint32_t tmem_base;
+};
+
+struct ScanParams {
+  const uint8_t* ws;
+  const float* s_in;   // [B,H,128,128] or null
+  void* out;           // [B,T,H,128]
+  float* s_out;        // [B,H,128,128] or null
+  float* bnd;          // [B, n_chunks+1, H,128,128] or null
+  int* status;
+  int64_t T, H, n_chunks, n_ch;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanParams p) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  ScanSmem& sm = *reinterpret_cast<ScanSmem*>(smem_raw);
+  const WsLayout ws{p.n_ch};
+  BoundedWaiter waiter(p.status);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int64_t bh = blockIdx.x;
+  const int64_t b = bh / p.H, h = bh % p.H;
+  constexpr uint32_t kColS = 0, kColR = 128, kColO = 192;
+
+  if (warp == 0) {
+    tmem_alloc(&sm.tmem_base, 256);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&sm.bar_yqa, 1);
+    mbar_init(&sm.bar_ut, 1);
+    mbar_init(&sm.bar_kt, 1);
+    mbar_init(&sm.bar_mma1, 1);
+    mbar_init(&sm.bar_mma2, 1);
+    fence_mbar_init();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tb = sm.tmem_base;
+  const uint32_t lane_base = 32u * warp;   // this warp's TMEM lane quadrant; thread = lane = value row
+  const int vrow = tid;
+
+  auto ch_of = [&](int64_t c) { return (b * p.n_chunks + c) * p.H + h; };
+  auto load_yqa = [&](int64_t c) {
+    const int64_t ch = ch_of(c);
+    mbar_arrive_expect_tx(&sm.bar_yqa, uint32_t(kBlobY + kBlobQ + kBlobA));
+    bulk_g2s(sm.y, p.ws + ws.off_y() + ch * kBlobY, uint32_t(kBlobY), &sm.bar_yqa);
+    bulk_g2s(sm.q, p.ws + ws.off_q() + ch * kBlobQ, uint32_t(kBlobQ), &sm.bar_yqa);
+    bulk_g2s(sm.a, p.ws + ws.off_a() + ch * kBlobA, uint32_t(kBlobA), &sm.bar_yqa);
+  };
+  auto load_ut = [&](int64_t c) {
+    mbar_arrive_expect_tx(&sm.bar_ut, uint32_t(kBlobUt));
+    bulk_g2s(sm.ut, p.ws + ws.off_ut() + ch_of(c) * kBlobUt, uint32_t(kBlobUt), &sm.bar_ut);
+  };
+  auto load_kt = [&](int64_t c) {
+    const int64_t ch = ch_of(c);
+    mbar_arrive_expect_tx(&sm.bar_kt, uint32_t(kBlobKt + kBlobD));
+    bulk_g2s(sm.kt, p.ws + ws.off_kt() + ch * kBlobKt, uint32_t(kBlobKt), &sm.bar_kt);
+    bulk_g2s(sm.d, p.ws + ws.off_d() + ch * kBlobD, uint32_t(kBlobD), &sm.bar_kt);
+  };
+
+  if (tid == 0) {
+    load_ut(0);
+    load_yqa(0);
+    load_kt(0);
+  }
+
+  // ---- S^T <- S_0^T : thread v gathers column v of the key-major state --------------------------
+  {
+    const float* src = (p.s_in != nullptr) ? p.s_in + bh * int64_t(kDim) * kDim + vrow : nullptr;
+#pragma unroll
+    for (int c0 = 0; c0 < kDim; c0 += 32) {
+      uint32_t r[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[j] = (src != nullptr) ? __float_as_uint(src[(c0 + j) * kDim]) : 0u;
+      tmem_st32(tmem_addr(tb, lane_base, kColS + c0), r);
+    }
+    tmem_wait_st();
+  }
+
+  for (int64_t c = 0; c < p.n_chunks; ++c) {
+    const uint32_t par = uint32_t(c & 1);
+    const int64_t t0 = c * kChunk;
+    if (c > 0) {
+      // the previous state update must have finished reading R^T and the Kt buffer
+      waiter.wait(&sm.bar_mma2, par ^ 1u);
+      tc_fence_after();
+      if (tid == 0) load_kt(c);
+    }
+    // ---- R^T <- U^T (thread v copies row v of the U^T tile into TMEM) ------------------------------
+    waiter.wait(&sm.bar_ut, par);
+    {
+      const uint8_t* row = sm.ut + (vrow >> 3) * 2048 + (vrow & 7) * 16;
+#pragma unroll
+      for (int c0 = 0; c0 < kChunk; c0 += 32) {
+        uint32_t r[32];
+#pragma unroll
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const uint4 x = *reinterpret_cast<const uint4*>(row + (c0 / 4 + c4) * 128);
+          r[4 * c4] = x.x; r[4 * c4 + 1] = x.y; r[4 * c4 + 2] = x.z; r[4 * c4 + 3] = x.w;
+        }
+        tmem_st32(tmem_addr(tb, lane_base, kColR + c0), r);
+      }
+      tmem_wait_st();
+    }
+    waiter.wait(&sm.bar_yqa, par);
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      if (c + 1 < p.n_chunks) load_ut(c + 1);  // every thread has consumed the U^T tile
+      const uint32_t y0 = smem_u32(sm.y), q0 = smem_u32(sm.q), a0 = smem_u32(sm.a);
+      const uint32_t id_neg = idesc(128, 64, kFmtTF32, kMajorK, kMajorK, 1, 0);
+      const uint32_t id_pos = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
+      // R^T -= S^T Y^T   (A = state columns, K = 128 keys)
+#pragma unroll
+      for (int ks = 0; ks < 16; ++ks) {
+        mma_tf32_ts(tb + kColR, tb + kColS + ks * 8, smem_desc(y0 + ks * 256, 128, 4096), id_neg, 1u);
+      }
+      // O^T = S^T Qg^T
+#pragma unroll
+      for (int ks = 0; ks < 16; ++ks) {
+        mma_tf32_ts(tb + kColO, tb + kColS + ks * 8, smem_desc(q0 + ks * 256, 128, 4096), id_pos, ks > 0 ? 1u : 0u);
+      }
+      // O^T += R^T Aqk^T  (A = residual columns, K = 64 tokens)
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        mma_tf32_ts(tb + kColO, tb + kColR + ks * 8, smem_desc(a0 + ks * 256, 128, 2048), id_pos, 1u);
+      }
+      mma_commit(&sm.bar_mma1);
+    }
+    waiter.wait(&sm.bar_mma1, par);
+    tc_fence_after();
+    if (tid == 0 && c + 1 < p.n_chunks) load_yqa(c + 1);  // the three MMAs no longer read Y, Q, A
+
+    // ---- output rows of this chunk: thread v writes o[t0 + i][v] ----------------------------------
+    {
+      T* out = static_cast<T*>(p.out);
+#pragma unroll
+      for (int c0 = 0; c0 < kChunk; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_addr(tb, lane_base, kColO + c0), r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          out[((b * p.T + t0 + c0 + j) * p.H + h) * kDim + vrow] = from_float<T>(__uint_as_float(r[j]));
+        }
+      }
+    }
+    // ---- checkpoint the chunk-start state, then decay the accumulator: S^T <- S^T diag(d) ----------
+    waiter.wait(&sm.bar_kt, par);
+    {
+      float* ck = (p.bnd != nullptr)
+                      ? p.bnd + ((b * (p.n_chunks + 1) + c) * p.H + h) * int64_t(kDim) * kDim + vrow
+                      : nullptr;
+#pragma unroll
+      for (int c0 = 0; c0 < kDim; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_addr(tb, lane_base, kColS + c0), r);
+        tmem_wait_ld();
+        if (ck != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) ck[(c0 + j) * kDim] = __uint_as_float(r[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * sm.d[c0 + j]);
+        tmem_st32(tmem_addr(tb, lane_base, kColS + c0), r);
+      }
+      tmem_wait_st();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t k0 = smem_u32(sm.kt);
+      const uint32_t id_s = idesc(128, 128, kFmtTF32, kMajorK, kMajorK);
+      // S^T += R^T Kt   (B tile X[r = key][c = token])
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        mma_tf32_ts(tb + kColS, tb + kColR + ks * 8, smem_desc(k0 + ks * 256, 128, 2048), id_s, 1u);
+      }
+      mma_commit(&sm.bar_mma2);
+    }
+  }
+
+  // ---- final state ---------------------------------------------------------------------------------
+  if (p.n_chunks > 0) {
+    waiter.wait(&sm.bar_mma2, uint32_t((p.n_chunks - 1) & 1));
+    tc_fence_after();
+  }
+  {
+    float* fin = (p.s_out != nullptr) ? p.s_out + bh * int64_t(kDim) * kDim + vrow : nullptr;
+    float* ck = (p.bnd != nullptr)
+                    ? p.bnd + ((b * (p.n_chunks + 1) + p.n_chunks) * p.H + h) * int64_t(kDim) * kDim + vrow
+                    : nullptr;
+#pragma unroll
+    for (int c0 = 0; c0 < kDim; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld32(tmem_addr(tb, lane_base, kColS + c0), r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (fin != nullptr) fin[(c0 + j) * kDim] = __uint_as_float(r[j]);
+        if (ck != nullptr) ck[(c0 + j) * kDim] = __uint_as_float(r[j]);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tb, 256);
+}
+
+}  // namespace
+
+// ---- launcher ---------------------------------------------------------------------------------
+int64_t chunk_workspace_bytes(int64_t batch, int64_t full_tokens, int64_t heads) {
+  const WsLayout ws{batch * (full_tokens / kChunk) * heads};
+  return ws.total();
+}
+
+int64_t chunk_status_offset(int64_t batch, int64_t full_tokens, int64_t heads) {
+  const WsLayout ws{batch * (full_tokens / kChunk) * heads};
+  return ws.off_status();
+}
+
+int launch_chunk_forward(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                         const void* w, const float* s_in, void* out, float* s_out, float* bnd,
+                         uint8_t* workspace, int64_t B, int64_t T, int64_t H, int64_t full_tokens,
+                         int dtype, int g_dtype, float scale, cudaStream_t stream) {
+  const int64_t n_chunks = full_tokens / kChunk;
+  const int64_t n_ch = B * n_chunks * H;
+  if (n_ch <= 0 || n_ch > int64_t(0x7fffffff)) return GDN2_ERR_TOO_LARGE;
+  const WsLayout ws{n_ch};
+  int* status = reinterpret_cast<int*>(workspace + ws.off_status());
+  cudaError_t err = cudaMemsetAsync(status, 0, 256, stream);
+  if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
+
+  PrepParams pp{q, k, v, g, beta, w, workspace, T, H, n_chunks, n_ch, scale};
+  GDN2_DISPATCH_TYPES(dtype, g_dtype, {
+    auto kernel = chunk_prep_kernel<T, G>;
+    const int smem = int(sizeof(PrepSmem));
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
+    kernel<<<unsigned(n_ch), kPrepThreads, smem, stream>>>(pp);
+  });
+  int st = check_launch();
+  if (st != GDN2_OK) return st;
+
+  ScanParams sp{workspace, s_in, out, s_out, bnd, status, T, H, n_chunks, n_ch};
+  const int smem = int(sizeof(ScanSmem));
+  if (dtype == GDN2_BF16) {
+    auto kernel = chunk_scan_kernel<__nv_bfloat16>;
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
+    kernel<<<unsigned(B * H), kScanThreads, smem, stream>>>(sp);
+  } else {
+    auto kernel = chunk_scan_kernel<__half>;
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
+    kernel<<<unsigned(B * H), kScanThreads, smem, stream>>>(sp);
+  }
+  return check_launch();
+}
+
+}  // namespace gdn2

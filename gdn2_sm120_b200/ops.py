@@ -66,7 +66,7 @@ class _ChunkGDN2(torch.autograd.Function):
         else:
             output, final_state = chunk_forward(*seq, state, scale=scale)
         saved = [q, k, v, g, beta, w]
-        ctx.n_chunk_boundaries = ctx.n_tail_boundaries = 0
+        ctx.n_chunk_boundaries = ctx.n_tail_boundaries = ctx.n_workspace = 0
         ctx.full_tokens = 0
         if aux is not None:
             ctx.full_tokens = aux.full_tokens
@@ -76,6 +76,9 @@ class _ChunkGDN2(torch.autograd.Function):
             if aux.tail_boundaries is not None:
                 saved.append(aux.tail_boundaries)
                 ctx.n_tail_boundaries = 1
+            if aux.workspace is not None:
+                saved.append(aux.workspace)
+                ctx.n_workspace = 1
         ctx.save_for_backward(*saved)
         ctx.set_materialize_grads(False)
         ctx.has_initial_state = initial_state is not None
@@ -105,7 +108,8 @@ class _ChunkGDN2(torch.autograd.Function):
             d_final_state = d_final_state.contiguous()
         chunk_boundaries = saved.pop(0) if ctx.n_chunk_boundaries else None
         tail_boundaries = saved.pop(0) if ctx.n_tail_boundaries else None
-        aux = ChunkForwardAux(chunk_boundaries, tail_boundaries, ctx.full_tokens)
+        workspace = saved.pop(0) if ctx.n_workspace else None
+        aux = ChunkForwardAux(chunk_boundaries, tail_boundaries, ctx.full_tokens, workspace)
         seq = tuple(_validate.detached(x) for x in (q, k, v, g, beta, w))
         *sequence_grads, d_initial_state = backward_from_aux(
             *seq, aux, d_output, d_final_state, _validate.float32_scale(ctx.scale)

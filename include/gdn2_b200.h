@@ -140,6 +140,45 @@ int gdn2_token_chunk_vjp(const void* q, const void* k, const void* v, const void
                          int64_t t_begin, int64_t t_end,
                          int dtype, int g_dtype, float scale, void* stream);
 
+
+/*
+ * ---- tensor-core chunk path (64-token chunks) ---------------------------------------
+ *
+ * Bytes of caller-owned workspace the chunk kernels need for `full_tokens` leading
+ * tokens (a multiple of GDN2_CHUNK) of a [batch, T, heads, 128] problem.  The workspace
+ * holds the per-chunk WY factors (Y, U^T, Q_gamma, K_tail^T, A_qk, (I+L)^-1, gamma_end)
+ * as operand-ready tiles plus a device status word; backward reuses it, so for training
+ * it must stay alive (and unmodified) until gdn2_chunk_backward has run.
+ * Replaces the intermediate allocations of chunk_forward (src/gdn2_sm120/chunk.py:1317-1362).
+ */
+int64_t gdn2_chunk_workspace_bytes(int64_t batch, int64_t full_tokens, int64_t heads);
+
+/*
+ * Chunkwise forward over tokens [0, full_tokens).  Replaces _prepare_wy_kernel and
+ * _inter_chunk_k_split_mma_kernel and their launcher (src/gdn2_sm120/chunk.py:139-331,
+ * 438-856, 859-1053).
+ *   initial_state  fp32 [B,H,128,128] or NULL (zero)
+ *   out            [B,T,H,128] in `dtype`; rows [0, full_tokens) are written
+ *   final_state    fp32 state after token full_tokens-1 (may alias initial_state exactly); or NULL
+ *   chunk_boundaries  NULL, or fp32 [B, full_tokens/64 + 1, H,128,128]: state before every
+ *                  chunk and after the last one (the activation checkpoints of backward)
+ * All sequence pointers, states and the workspace must be 16-byte aligned.
+ */
+int gdn2_chunk_forward(const void* q, const void* k, const void* v, const void* g,
+                       const void* beta, const void* w, const float* initial_state,
+                       void* out, float* final_state, float* chunk_boundaries,
+                       void* workspace, int64_t batch, int64_t time, int64_t heads,
+                       int64_t full_tokens, int dtype, int g_dtype, float scale, void* stream);
+
+/*
+ * Synchronise `stream` and return the device status word of a workspace: 0 = ok,
+ * 1 = a bounded wait inside a kernel expired (results are invalid).  Diagnostic call
+ * for tests and smoke checks; no counterpart in the reference (its kernels have no
+ * asynchronous waits).
+ */
+int gdn2_chunk_read_status(const void* workspace, int64_t batch, int64_t full_tokens,
+                           int64_t heads, void* stream);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif
