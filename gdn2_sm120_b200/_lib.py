@@ -39,8 +39,9 @@ _PROTOTYPES: dict[str, list] = {
     "gdn2_token_forward_t1_zero": [_P] * 6 + [_I64] * 2 + [_INT, _F32, _P],
     "gdn2_token_dstate_scan": [_P] * 8 + [_I64] * 5 + [_INT, _INT, _F32, _P],
     "gdn2_token_chunk_vjp": [_P] * 15 + [_I64] * 5 + [_INT, _INT, _F32, _P],
-    "gdn2_chunk_workspace_bytes": [_I64] * 3,
-    "gdn2_chunk_forward": [_P] * 11 + [_I64] * 4 + [_INT, _INT, _F32, _P],
+    "gdn2_chunk_workspace_bytes": [_I64] * 3 + [_INT],
+    "gdn2_chunk_forward": [_P] * 11 + [_I64] * 4 + [_INT, _INT, _INT, _F32, _P],
+    "gdn2_chunk_backward": [_P] * 18 + [_I64] * 4 + [_INT, _INT, _F32, _P],
     "gdn2_chunk_read_status": [_P] + [_I64] * 3 + [_P],
 }
 _RESTYPES = {"gdn2_status_string": ctypes.c_char_p, "gdn2_last_cuda_error": ctypes.c_char_p,

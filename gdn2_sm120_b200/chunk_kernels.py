@@ -33,8 +33,8 @@ def supported_tokens(time: int, *, training: bool = False) -> int:
     return (time // _CHUNK) * _CHUNK
 
 
-def workspace_bytes(batch: int, full_tokens: int, heads: int) -> int:
-    size = _lib.lib().gdn2_chunk_workspace_bytes(batch, full_tokens, heads)
+def workspace_bytes(batch: int, full_tokens: int, heads: int, training: bool = False) -> int:
+    size = _lib.lib().gdn2_chunk_workspace_bytes(batch, full_tokens, heads, int(training))
     if size <= 0:
         raise RuntimeError(f"gdn2_chunk_workspace_bytes failed with status {size}")
     return int(size)
@@ -44,12 +44,14 @@ def forward(q, k, v, g, beta, w, initial_state, output, final_state, chunk_bound
             batch, time, heads, full_tokens, scale) -> torch.Tensor:
     """Run the chunk forward over tokens [0, full_tokens); returns the workspace."""
 
-    workspace = torch.empty(workspace_bytes(batch, full_tokens, heads), device=q.device, dtype=torch.uint8)
+    training = chunk_boundaries is not None
+    workspace = torch.empty(workspace_bytes(batch, full_tokens, heads, training), device=q.device,
+                            dtype=torch.uint8)
     _lib.call(
         "gdn2_chunk_forward", q.device,
         q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), w.data_ptr(),
         _lib.ptr(initial_state), output.data_ptr(), _lib.ptr(final_state), _lib.ptr(chunk_boundaries),
-        workspace.data_ptr(), batch, time, heads, full_tokens,
+        workspace.data_ptr(), batch, time, heads, full_tokens, int(training),
         _lib.dtype_code(q.dtype), _lib.dtype_code(g.dtype), scale, _lib.stream_ptr(q.device),
     )
     return workspace
@@ -65,4 +67,16 @@ def read_status(workspace: torch.Tensor, batch: int, full_tokens: int, heads: in
 
 def backward(q, k, v, g, beta, w, workspace, chunk_boundaries, d_out, d_final_state, grads,
              d_initial_state, batch, time, heads, full_tokens, scale) -> None:
-    raise RuntimeError("the tensor-core chunk backward is not built into this library")
+    """Chunk backward over tokens [0, full_tokens): fills rows of ``grads`` and ``d_initial_state``."""
+
+    dq, dk, dv, dg, dbeta, dw = grads
+    d_boundaries = torch.empty_like(chunk_boundaries)
+    _lib.call(
+        "gdn2_chunk_backward", q.device,
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), w.data_ptr(),
+        d_out.data_ptr(), _lib.ptr(d_final_state), chunk_boundaries.data_ptr(), d_boundaries.data_ptr(),
+        workspace.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dg.data_ptr(),
+        dbeta.data_ptr(), dw.data_ptr(), _lib.ptr(d_initial_state),
+        batch, time, heads, full_tokens,
+        _lib.dtype_code(q.dtype), _lib.dtype_code(g.dtype), scale, _lib.stream_ptr(q.device),
+    )

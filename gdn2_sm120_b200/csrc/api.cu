@@ -22,11 +22,16 @@ int launch_token_chunk_vjp(const void*, const void*, const void*, const void*, c
                            void*, void*, void*, void*, int64_t, int64_t, int64_t, int64_t,
                            int64_t, int, int, float, cudaStream_t);
 
-int64_t chunk_workspace_bytes(int64_t, int64_t, int64_t);
+int64_t chunk_workspace_bytes(int64_t, int64_t, int64_t, int);
 int64_t chunk_status_offset(int64_t, int64_t, int64_t);
 int launch_chunk_forward(const void*, const void*, const void*, const void*, const void*, const void*,
                          const float*, void*, float*, float*, uint8_t*, int64_t, int64_t, int64_t,
-                         int64_t, int, int, float, cudaStream_t);
+                         int64_t, int, int, int, float, cudaStream_t);
+
+int launch_chunk_backward(const void*, const void*, const void*, const void*, const void*, const void*,
+                          const void*, const float*, const float*, float*, uint8_t*, void*, void*, void*,
+                          void*, void*, void*, float*, int64_t, int64_t, int64_t, int64_t, int, int, float,
+                          cudaStream_t);
 
 namespace {
 thread_local char g_cuda_error[256] = {0};
@@ -170,17 +175,18 @@ int gdn2_token_chunk_vjp(const void* q, const void* k, const void* v, const void
                                 g_dtype, scale, static_cast<cudaStream_t>(stream));
 }
 
-int64_t gdn2_chunk_workspace_bytes(int64_t batch, int64_t full_tokens, int64_t heads) {
+int64_t gdn2_chunk_workspace_bytes(int64_t batch, int64_t full_tokens, int64_t heads, int training) {
   if (batch <= 0 || heads <= 0 || full_tokens <= 0 || full_tokens % GDN2_CHUNK != 0) return GDN2_ERR_BAD_SHAPE;
-  return chunk_workspace_bytes(batch, full_tokens, heads);
+  return chunk_workspace_bytes(batch, full_tokens, heads, training);
 }
 
 int gdn2_chunk_forward(const void* q, const void* k, const void* v, const void* g,
                        const void* beta, const void* w, const float* initial_state, void* out,
                        float* final_state, float* chunk_boundaries, void* workspace,
-                       int64_t batch, int64_t time, int64_t heads, int64_t full_tokens, int dtype,
-                       int g_dtype, float scale, void* stream) {
+                       int64_t batch, int64_t time, int64_t heads, int64_t full_tokens, int training,
+                       int dtype, int g_dtype, float scale, void* stream) {
   if (!q || !k || !v || !g || !beta || !w || !out || !workspace) return GDN2_ERR_NULL_POINTER;
+  if (training && !chunk_boundaries) return GDN2_ERR_NULL_POINTER;
   int st = check_shape(batch, time, heads);
   if (st != GDN2_OK) return st;
   if (full_tokens <= 0 || full_tokens > time || full_tokens % GDN2_CHUNK != 0) return GDN2_ERR_BAD_RANGE;
@@ -190,8 +196,32 @@ int gdn2_chunk_forward(const void* q, const void* k, const void* v, const void* 
     if (!aligned(ptr, 16)) return GDN2_ERR_ALIGNMENT;
   }
   return launch_chunk_forward(q, k, v, g, beta, w, initial_state, out, final_state, chunk_boundaries,
-                              static_cast<uint8_t*>(workspace), batch, time, heads, full_tokens, dtype,
-                              g_dtype, scale, static_cast<cudaStream_t>(stream));
+                              static_cast<uint8_t*>(workspace), batch, time, heads, full_tokens, training,
+                              dtype, g_dtype, scale, static_cast<cudaStream_t>(stream));
+}
+
+int gdn2_chunk_backward(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                        const void* w, const void* d_out, const float* d_final_state,
+                        const float* chunk_boundaries, float* d_boundaries, void* workspace, void* dq,
+                        void* dk, void* dv, void* dg, void* dbeta, void* dw, float* d_initial_state,
+                        int64_t batch, int64_t time, int64_t heads, int64_t full_tokens, int dtype,
+                        int g_dtype, float scale, void* stream) {
+  if (!q || !k || !v || !g || !beta || !w || !d_out || !chunk_boundaries || !d_boundaries || !workspace ||
+      !dq || !dk || !dv || !dg || !dbeta || !dw)
+    return GDN2_ERR_NULL_POINTER;
+  int st = check_shape(batch, time, heads);
+  if (st != GDN2_OK) return st;
+  if (full_tokens <= 0 || full_tokens > time || full_tokens % GDN2_CHUNK != 0) return GDN2_ERR_BAD_RANGE;
+  if ((st = check_types(dtype, g_dtype)) != GDN2_OK) return st;
+  const void* need16[] = {q, k, v, g, beta, w, d_out, d_final_state, chunk_boundaries, d_boundaries, workspace,
+                          dq, dk, dv, dg, dbeta, dw, d_initial_state};
+  for (const void* ptr : need16) {
+    if (!aligned(ptr, 16)) return GDN2_ERR_ALIGNMENT;
+  }
+  return launch_chunk_backward(q, k, v, g, beta, w, d_out, d_final_state, chunk_boundaries, d_boundaries,
+                               static_cast<uint8_t*>(workspace), dq, dk, dv, dg, dbeta, dw, d_initial_state,
+                               batch, time, heads, full_tokens, dtype, g_dtype, scale,
+                               static_cast<cudaStream_t>(stream));
 }
 
 int gdn2_chunk_read_status(const void* workspace, int64_t batch, int64_t full_tokens, int64_t heads,

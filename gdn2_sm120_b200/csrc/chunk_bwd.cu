@@ -1,0 +1,747 @@
+// Tensor-core chunk backward (64-token chunks), two kernels that consume the WY tiles and
+// residuals saved by the forward and the fp32 chunk-start states:
+//
+//   chunk_bwd_scan_kernel  one CTA per (batch, head), chunks in reverse order.  The state
+//                          cotangent lives transposed (dS^T: value rows x key columns) in TMEM:
+//                              dR^T  = dO^T Aqk + dS^T Kt^T
+//                              dS^T <- dS^T diag(d) + dO^T Qg - dR^T Y
+//                          It writes dR^T per chunk and the cotangent at every chunk start.
+//   chunk_bwd_vjp_kernel   one CTA per (batch, chunk, head), all chunks in parallel.  With
+//                          R = T (Z - E S_0) as the parametrisation (no Y / U needed):
+//                              dZ = T^T dR                      dv = dZ w, dw = dZ v
+//                              [-dE ; dQg] = [dZ ; dO] S_0^T    dKt = R dS_1^T
+//                              [-dL ; dA]  = [dZ ; dO] R^T      (strictly lower / lower part)
+//                          then the Gram products' VJP with the same 16-token block anchors as the
+//                          forward, and a per-channel chain (one thread = one key channel) that
+//                          forms dq, dk, dbeta and the reverse cumulative sum for dg.
+//
+// Reference counterparts: boundary scan  src/gdn2_sm120/backward_parallel.py:721-1049,
+// compact-WY VJP  src/gdn2_sm120/backward_wy.py:226-1168 (a 10-12 launch graph there).
+
+#include "chunk_common.cuh"
+
+namespace gdn2 {
+
+using namespace tc;
+
+namespace {
+
+constexpr int64_t kStateElems = int64_t(kDim) * kDim;
+
+// =============================================================================================
+// reverse scan
+// =============================================================================================
+constexpr int kBScanThreads = 128;
+
+struct BScanSmem {
+  alignas(128) uint8_t dot[32768];   // dO^T tile X[r = v][c = i], tf32 (built from dO)
+  alignas(128) uint8_t kn[32768];    // K_tail   X[r = j][c = k]
+  alignas(128) uint8_t qt[32768];    // Qg^T     X[r = k][c = i]
+  alignas(128) uint8_t yt[32768];    // Y^T      X[r = k][c = j]
+  alignas(128) uint8_t at[16384];    // Aqk^T    X[r = j][c = i]
+  alignas(16) float d[kDim];
+  alignas(8) uint64_t bar_ak, bar_qy, bar_mma1, bar_mma2;
+  uint32_t tmem_base;
+};
+
+struct BScanParams {
+  uint8_t* ws;
+  const void* d_out;        // [B,T,H,128]
+  const float* ds_final;    // [B,H,128,128] or null
+  float* d_bnd;             // [B, n_chunks+1, H,128,128]
+  float* ds_init;           // [B,H,128,128] or null
+  int* status;
+  int64_t T, H, n_chunks, n_ch;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const BScanParams p) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  BScanSmem& sm = *reinterpret_cast<BScanSmem*>(smem_raw);
+  const WsLayout ws{p.n_ch, true};
+  BoundedWaiter waiter(p.status);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int64_t bh = blockIdx.x;
+  const int64_t b = bh / p.H, h = bh % p.H;
+  constexpr uint32_t kColS = 0, kColR = 128;
+
+  if (warp == 0) {
+    tmem_alloc(&sm.tmem_base, 256);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&sm.bar_ak, 1);
+    mbar_init(&sm.bar_qy, 1);
+    mbar_init(&sm.bar_mma1, 1);
+    mbar_init(&sm.bar_mma2, 1);
+    fence_mbar_init();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tb = sm.tmem_base;
+  const uint32_t lane_base = 32u * warp;
+  const int vrow = tid;
+
+  auto ch_of = [&](int64_t c) { return (b * p.n_chunks + c) * p.H + h; };
+  auto load_ak = [&](int64_t c) {
+    const int64_t ch = ch_of(c);
+    mbar_arrive_expect_tx(&sm.bar_ak, uint32_t(kBlobAt + kBlobKn));
+    bulk_g2s(sm.at, p.ws + ws.off_at() + ch * kBlobAt, uint32_t(kBlobAt), &sm.bar_ak);
+    bulk_g2s(sm.kn, p.ws + ws.off_kn() + ch * kBlobKn, uint32_t(kBlobKn), &sm.bar_ak);
+  };
+  auto load_qy = [&](int64_t c) {
+    const int64_t ch = ch_of(c);
+    mbar_arrive_expect_tx(&sm.bar_qy, uint32_t(kBlobQt + kBlobYt + kBlobD));
+    bulk_g2s(sm.qt, p.ws + ws.off_qt() + ch * kBlobQt, uint32_t(kBlobQt), &sm.bar_qy);
+    bulk_g2s(sm.yt, p.ws + ws.off_yt() + ch * kBlobYt, uint32_t(kBlobYt), &sm.bar_qy);
+    bulk_g2s(sm.d, p.ws + ws.off_d() + ch * kBlobD, uint32_t(kBlobD), &sm.bar_qy);
+  };
+
+  if (tid == 0 && p.n_chunks > 0) {
+    load_ak(p.n_chunks - 1);
+    load_qy(p.n_chunks - 1);
+  }
+
+  // ---- dS^T <- dS_T^T (thread v gathers column v); also becomes the last boundary slot -----------
+  {
+    const float* src = (p.ds_final != nullptr) ? p.ds_final + bh * kStateElems + vrow : nullptr;
+    float* slot = p.d_bnd + ((b * (p.n_chunks + 1) + p.n_chunks) * p.H + h) * kStateElems + vrow;
+#pragma unroll
+    for (int c0 = 0; c0 < kDim; c0 += 32) {
+      uint32_t r[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float x = (src != nullptr) ? src[(c0 + j) * kDim] : 0.f;
+        slot[(c0 + j) * kDim] = x;
+        r[j] = __float_as_uint(x);
+      }
+      tmem_st32(tmem_addr(tb, lane_base, kColS + c0), r);
+    }
+    tmem_wait_st();
+  }
+
+  // dO^T tile builder: thread = (4-token group tg 0..15, 16-channel group c16 0..7)
+  const int tg = tid >> 3, c16 = tid & 7;
+  uint32_t it = 0;
+  for (int64_t c = p.n_chunks - 1; c >= 0; --c, ++it) {
+    const uint32_t par = it & 1u;
+    const int64_t t0 = c * kChunk;
+    if (it > 0) {
+      // previous iteration's second MMA group read dO^T, Qt, Yt and dR^T
+      waiter.wait(&sm.bar_mma2, par ^ 1u);
+      tc_fence_after();
+      // cotangent at the start of chunk c + 1 (= end of chunk c)
+      float* slot = p.d_bnd + ((b * (p.n_chunks + 1) + c + 1) * p.H + h) * kStateElems + vrow;
+#pragma unroll
+      for (int c0 = 0; c0 < kDim; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_addr(tb, lane_base, kColS + c0), r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) slot[(c0 + j) * kDim] = __uint_as_float(r[j]);
+      }
+      if (tid == 0) load_qy(c);
+    }
+    // ---- dO^T tile -------------------------------------------------------------------------------
+    {
+      float dv[4][16];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int64_t idx = ((b * p.T + t0 + 4 * tg + e) * p.H + h) * kDim + 16 * c16;
+        float lo[8], hi[8];
+        load8<T>(p.d_out, idx, lo);
+        load8<T>(p.d_out, idx + 8, hi);
+#pragma unroll
+        for (int f = 0; f < 8; ++f) { dv[e][f] = lo[f]; dv[e][8 + f] = hi[f]; }
+      }
+#pragma unroll
+      for (int f = 0; f < 16; ++f) {
+        *reinterpret_cast<float4*>(sm.dot + blk_off<4>(16 * c16 + f, 4 * tg, 2048, 128)) =
+            make_float4(dv[0][f], dv[1][f], dv[2][f], dv[3][f]);
+      }
+    }
+    fence_async_smem();
+    waiter.wait(&sm.bar_ak, par);
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t d0 = smem_u32(sm.dot), a0 = smem_u32(sm.at), k0 = smem_u32(sm.kn);
+      const uint32_t id64 = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
+      // dR^T = dO^T Aqk   (A: dO^T [v x i], B: Aqk^T tile X[r = j][c = i])
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        mma_tf32_ss(tb + kColR, smem_desc(d0 + ks * 256, 128, 2048), smem_desc(a0 + ks * 256, 128, 2048), id64,
+                    ks > 0 ? 1u : 0u);
+      }
+      // dR^T += dS^T Kt^T (A: cotangent columns, K = 128 keys; B: K_tail tile X[r = j][c = k])
+#pragma unroll
+      for (int ks = 0; ks < 16; ++ks) {
+        mma_tf32_ts(tb + kColR, tb + kColS + ks * 8, smem_desc(k0 + ks * 256, 128, 4096), id64, 1u);
+      }
+      mma_commit(&sm.bar_mma1);
+    }
+    waiter.wait(&sm.bar_mma1, par);
+    tc_fence_after();
+    if (tid == 0 && c > 0) load_ak(c - 1);  // At / Kn are free again
+
+    // ---- dR^T out (tile X[r = v][c = j]) ------------------------------------------------------------
+    {
+      uint8_t* blob = p.ws + ws.off_drt() + ch_of(c) * kBlobDRt + (vrow >> 3) * 2048 + (vrow & 7) * 16;
+#pragma unroll
+      for (int c0 = 0; c0 < kChunk; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_addr(tb, lane_base, kColR + c0), r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c4 = 0; c4 < 8; ++c4) {
+          *reinterpret_cast<uint4*>(blob + (c0 / 4 + c4) * 128) =
+              make_uint4(r[4 * c4], r[4 * c4 + 1], r[4 * c4 + 2], r[4 * c4 + 3]);
+        }
+      }
+    }
+    // ---- decay: dS^T <- dS^T diag(d) -------------------------------------------------------------------
+    waiter.wait(&sm.bar_qy, par);
+#pragma unroll
+    for (int c0 = 0; c0 < kDim; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld32(tmem_addr(tb, lane_base, kColS + c0), r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * sm.d[c0 + j]);
+      tmem_st32(tmem_addr(tb, lane_base, kColS + c0), r);
+    }
+    tmem_wait_st();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t d0 = smem_u32(sm.dot), q0 = smem_u32(sm.qt), y0 = smem_u32(sm.yt);
+      const uint32_t id_pos = idesc(128, 128, kFmtTF32, kMajorK, kMajorK);
+      const uint32_t id_neg = idesc(128, 128, kFmtTF32, kMajorK, kMajorK, 1, 0);
+      // dS^T += dO^T Qg   (B: Qg^T tile X[r = k][c = i])
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        mma_tf32_ss(tb + kColS, smem_desc(d0 + ks * 256, 128, 2048), smem_desc(q0 + ks * 256, 128, 2048), id_pos, 1u);
+      }
+      // dS^T -= dR^T Y    (A: dR^T columns, K = 64 tokens; B: Y^T tile X[r = k][c = j])
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        mma_tf32_ts(tb + kColS, tb + kColR + ks * 8, smem_desc(y0 + ks * 256, 128, 2048), id_neg, 1u);
+      }
+      mma_commit(&sm.bar_mma2);
+    }
+  }
+
+  // ---- cotangent of the initial state: slot 0 and d_initial_state ------------------------------------
+  if (p.n_chunks > 0) {
+    waiter.wait(&sm.bar_mma2, (it - 1) & 1u);
+    tc_fence_after();
+  }
+  {
+    float* slot = p.d_bnd + ((b * (p.n_chunks + 1)) * p.H + h) * kStateElems + vrow;
+    float* init = (p.ds_init != nullptr) ? p.ds_init + bh * kStateElems + vrow : nullptr;
+#pragma unroll
+    for (int c0 = 0; c0 < kDim; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld32(tmem_addr(tb, lane_base, kColS + c0), r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        slot[(c0 + j) * kDim] = __uint_as_float(r[j]);
+        if (init != nullptr) init[(c0 + j) * kDim] = __uint_as_float(r[j]);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tb, 256);
+}
+
+
+// =============================================================================================
+// chunk VJP
+// =============================================================================================
+constexpr int kVjpThreads = 256;
+
+// dynamic shared memory map (bytes).  Phase B = products with the states, phase C = Gram VJP.
+constexpr int kOffStack = 0;            // B: [dZ ; dO]  X[r = 128][c = v], RS 4096, 64 KiB
+constexpr int kOffRn = 65536;           // B: R          X[r = j][c = v],   RS 4096, 32 KiB
+constexpr int kOffS0 = 98304;           // B: S_0        X[r = k][c = v],   RS 4096, 64 KiB
+constexpr int kOffDrt = 98304;          //    (before S_0 arrives) dR^T X[r = v][c = i], 32 KiB
+constexpr int kOffTt = 131072;          //    (before S_0 arrives) T^T  X[r = j][c = i], 16 KiB
+constexpr int kOffDs1 = 163840;         // B: dS_1 half  X[r = k][c = 64 v], RS 2048, 32 KiB
+constexpr int kOffStack2 = 0;           // C: [dL ; dA]  X[r = 128][c = j], RS 2048, 32 KiB
+constexpr int kOffDLt = 32768;          // C: dL^T       X[r = j][c = i],   16 KiB
+constexpr int kOffDAt = 49152;          // C: dA^T       X[r = j][c = i],   16 KiB
+constexpr int kOffKIt = 65536;          // C: (K^I)^T    X[r = k][c = j < 16(I+1)], 8/16/24/32 KiB
+constexpr int kOffEat = 147456;         // C: E_a^T      X[r = k][c = i],   32 KiB
+constexpr int kOffQat = 180224;         // C: Q_a^T      X[r = k][c = i],   32 KiB
+constexpr int kOffMisc = 212992;
+struct VjpMisc {
+  float part[16][kDim];   // exclusive prefixes of the log-decay per 4-token group
+  float gend[kDim];
+  float dd[kDim];         // sum_v dS_1 * S_0
+  float xe[2][kDim];      // per-half sum_j Kt_j dKt_j
+  float xt[2][kDim];      // per-half sum of dG
+  alignas(8) uint64_t bar_a, bar_r, bar_m;
+  uint32_t tmem_base;
+};
+constexpr int kVjpSmemBytes = kOffMisc + int(sizeof(VjpMisc));
+static_assert(kVjpSmemBytes <= 232448, "VJP kernel exceeds the 227 KiB shared-memory limit");
+
+__device__ __forceinline__ int kit_offset(int I) { return kOffKIt + ((I == 0) ? 0 : (I == 1) ? 8192 : (I == 2) ? 24576 : 49152); }
+__device__ __forceinline__ uint32_t d6_col(int I) { return (I == 3) ? 0u : (I == 2) ? 64u : (I == 1) ? 448u : 480u; }
+
+struct VjpParams {
+  const void *q, *k, *v, *g, *beta, *w, *d_out;
+  const uint8_t* ws;
+  const float* bnd;     // [B, n_chunks+1, H,128,128] forward states
+  const float* d_bnd;   // same shape, cotangents
+  void *dq, *dk, *dv, *dg, *dbeta, *dw;
+  int* status;
+  int64_t T, H, n_chunks, n_ch;
+  float scale;
+};
+
+template <typename T, typename G>
+__global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const VjpParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  VjpMisc& ms = *reinterpret_cast<VjpMisc*>(smem + kOffMisc);
+  const WsLayout ws{p.n_ch, true};
+  BoundedWaiter waiter(p.status);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int q4 = warp & 3, half = warp >> 2;
+  const int64_t ch = blockIdx.x;
+  const int64_t h = ch % p.H;
+  const int64_t c = (ch / p.H) % p.n_chunks;
+  const int64_t b = ch / (p.H * p.n_chunks);
+  const int64_t t0 = c * kChunk;
+  auto seq_idx = [&](int tok) { return ((b * p.T + t0 + tok) * p.H + h) * int64_t(kDim); };
+
+  if (warp == 0) {
+    tmem_alloc(&ms.tmem_base, 512);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    mbar_init(&ms.bar_a, 1);
+    mbar_init(&ms.bar_r, 1);
+    mbar_init(&ms.bar_m, 1);
+    fence_mbar_init();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tb = ms.tmem_base;
+  uint32_t mma_phase = 0;
+  constexpr uint32_t kColDz = 0, kColD2 = 64, kColD3 = 128, kColD4 = 256, kColD5 = 320;
+
+  if (tid == 0) {
+    mbar_arrive_expect_tx(&ms.bar_a, uint32_t(kBlobDRt + kBlobTt));
+    bulk_g2s(smem + kOffDrt, p.ws + ws.off_drt() + ch * kBlobDRt, uint32_t(kBlobDRt), &ms.bar_a);
+    bulk_g2s(smem + kOffTt, p.ws + ws.off_tt() + ch * kBlobTt, uint32_t(kBlobTt), &ms.bar_a);
+    mbar_arrive_expect_tx(&ms.bar_r, uint32_t(kBlobRn));
+    bulk_g2s(smem + kOffRn, p.ws + ws.off_rn() + ch * kBlobRn, uint32_t(kBlobRn), &ms.bar_r);
+  }
+  const int tg = tid >> 4, c8 = tid & 15;
+  // dO rows of the stack (rows 64 + i)
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int i = 4 * tg + e;
+    float dv8[8];
+    load8<T>(p.d_out, seq_idx(i) + 8 * c8, dv8);
+    float4* dst = reinterpret_cast<float4*>(smem + kOffStack + blk_off<4>(64 + i, 8 * c8, 4096, 128));
+    dst[0] = make_float4(dv8[0], dv8[1], dv8[2], dv8[3]);
+    dst[8] = make_float4(dv8[4], dv8[5], dv8[6], dv8[7]);
+  }
+  waiter.wait(&ms.bar_a, 0);
+  tc_fence_before();
+  __syncthreads();
+  // ---- M1: dZ^T = dR^T T  (A: dR^T [v x i]; B: T^T tile X[r = j][c = i]) ---------------------------
+  if (tid == 0) {
+    tc_fence_after();
+    const uint32_t a0 = smem_u32(smem + kOffDrt), b0 = smem_u32(smem + kOffTt);
+    const uint32_t id = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      mma_tf32_ss(tb + kColDz, smem_desc(a0 + ks * 256, 128, 2048), smem_desc(b0 + ks * 256, 128, 2048), id,
+                  ks > 0 ? 1u : 0u);
+    }
+    mma_commit(&ms.bar_m);
+  }
+  waiter.wait(&ms.bar_m, mma_phase & 1u);
+  ++mma_phase;
+  tc_fence_after();
+
+  // ---- bring in S_0 (whole) and the first half of dS_1 with 16-byte async copies ---------------------
+  const float* s0_src = p.bnd + ((b * (p.n_chunks + 1) + c) * p.H + h) * kStateElems;
+  const float* ds1_src = p.d_bnd + ((b * (p.n_chunks + 1) + c + 1) * p.H + h) * kStateElems;
+#pragma unroll
+  for (int x = 0; x < 16; ++x) {
+    const int kr = (tid & 7) + 8 * x, v4 = ((tid >> 3) & 3) + 4 * ((tid >> 5) & 7);
+    cp_async16(smem + kOffS0 + x * 4096 + v4 * 128 + (tid & 7) * 16, s0_src + kr * kDim + 4 * v4);
+  }
+  auto load_ds1_half = [&](int hf) {
+#pragma unroll
+    for (int x = 0; x < 8; ++x) {
+      const int qd = tid + 256 * x;
+      const int kr = (qd & 7) + 8 * (qd >> 7), v4 = ((qd >> 3) & 3) + 4 * ((qd >> 5) & 3);
+      cp_async16(smem + kOffDs1 + (qd >> 7) * 2048 + v4 * 128 + (qd & 7) * 16,
+                 ds1_src + kr * kDim + 64 * hf + 4 * v4);
+    }
+    cp_async_commit();
+  };
+  load_ds1_half(0);
+
+  // ---- dZ: into the stack (rows j), and dv = dZ w, dw = dZ v --------------------------------------------
+  {
+    const int vrow = 32 * q4 + lane;
+    uint32_t r[32];
+    tmem_ld32(tmem_addr(tb, 32 * q4, kColDz + 32 * half), r);
+    tmem_wait_ld();
+#pragma unroll
+    for (int jj = 0; jj < 32; ++jj) {
+      const int j = 32 * half + jj;
+      const float dz = __uint_as_float(r[jj]);
+      *reinterpret_cast<float*>(smem + kOffStack + blk_off<4>(j, vrow, 4096, 128)) = to_tf32(dz);
+      const int64_t idx = seq_idx(j) + vrow;
+      const float wv = ldf<T>(p.w, idx), vv = ldf<T>(p.v, idx);
+      stf<T>(p.dv, idx, dz * wv);
+      stf<T>(p.dw, idx, dz * vv);
+    }
+  }
+  cp_async_wait_all();
+  waiter.wait(&ms.bar_r, 0);
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  // ---- M2 / M3 / M4 (first half) -------------------------------------------------------------------------
+  if (tid == 0) {
+    tc_fence_after();
+    const uint32_t st = smem_u32(smem + kOffStack), rn = smem_u32(smem + kOffRn);
+    const uint32_t s0 = smem_u32(smem + kOffS0), d1 = smem_u32(smem + kOffDs1);
+    const uint32_t id64 = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
+    const uint32_t id128 = idesc(128, 128, kFmtTF32, kMajorK, kMajorK);
+#pragma unroll
+    for (int ks = 0; ks < 16; ++ks) {  // [dZ;dO] R^T
+      mma_tf32_ss(tb + kColD2, smem_desc(st + ks * 256, 128, 4096), smem_desc(rn + ks * 256, 128, 4096), id64,
+                  ks > 0 ? 1u : 0u);
+    }
+#pragma unroll
+    for (int ks = 0; ks < 16; ++ks) {  // S_0 [dZ;dO]^T
+      mma_tf32_ss(tb + kColD3, smem_desc(s0 + ks * 256, 128, 4096), smem_desc(st + ks * 256, 128, 4096), id128,
+                  ks > 0 ? 1u : 0u);
+    }
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {  // dS_1[:, v < 64] R[:, v < 64]^T
+      mma_tf32_ss(tb + kColD4, smem_desc(d1 + ks * 256, 128, 2048), smem_desc(rn + ks * 256, 128, 4096), id64,
+                  ks > 0 ? 1u : 0u);
+    }
+    mma_commit(&ms.bar_m);
+  }
+  // dd partial (thread = key row) over the value half that is resident
+  auto dd_partial = [&](int hf) {
+    float acc = 0.f;
+    const uint8_t* a = smem + kOffDs1 + (tid >> 3) * 2048 + (tid & 7) * 16;
+    const uint8_t* s = smem + kOffS0 + (tid >> 3) * 4096 + (tid & 7) * 16 + hf * 16 * 128;
+#pragma unroll
+    for (int c4 = 0; c4 < 16; ++c4) {
+      const float4 x = *reinterpret_cast<const float4*>(a + c4 * 128);
+      const float4 y = *reinterpret_cast<const float4*>(s + c4 * 128);
+      acc = fmaf(x.x, y.x, acc); acc = fmaf(x.y, y.y, acc); acc = fmaf(x.z, y.z, acc); acc = fmaf(x.w, y.w, acc);
+    }
+    return acc;
+  };
+  float dd_acc = 0.f;
+  if (tid < kDim) dd_acc = dd_partial(0);
+  waiter.wait(&ms.bar_m, mma_phase & 1u);
+  ++mma_phase;
+  tc_fence_after();
+  __syncthreads();  // every dd reader is done with the first half before it is overwritten
+  load_ds1_half(1);
+  cp_async_wait_all();
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0) {
+    tc_fence_after();
+    const uint32_t rn = smem_u32(smem + kOffRn), d1 = smem_u32(smem + kOffDs1);
+    const uint32_t id64 = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {  // dS_1[:, v >= 64] R[:, v >= 64]^T
+      mma_tf32_ss(tb + kColD4, smem_desc(d1 + ks * 256, 128, 2048), smem_desc(rn + (8 + ks) * 256, 128, 4096), id64, 1u);
+    }
+    mma_commit(&ms.bar_m);
+  }
+  if (tid < kDim) ms.dd[tid] = dd_acc + dd_partial(1);
+  waiter.wait(&ms.bar_m, mma_phase & 1u);
+  ++mma_phase;
+  tc_fence_after();
+
+  // ================================ phase C: Gram VJP =============================================
+  // log-decay prefixes, same scheme as the forward prep kernel: thread = (4 tokens, 8 channels)
+  float Gc[4][8];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    float gv[8];
+    load8<G>(p.g, seq_idx(4 * tg + e) + 8 * c8, gv);
+#pragma unroll
+    for (int f = 0; f < 8; ++f) Gc[e][f] = (e ? Gc[e - 1][f] : 0.f) + gv[f];
+  }
+#pragma unroll
+  for (int f = 0; f < 8; ++f) ms.part[tg][8 * c8 + f] = Gc[3][f];
+  __syncthreads();  // also: every thread is past the last phase-B wait, dd readers are done
+  if (tid < kDim) {
+    float run = 0.f;
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      const float x = ms.part[t][tid];
+      ms.part[t][tid] = run;
+      run += x;
+    }
+    ms.gend[tid] = run;
+  }
+  __syncthreads();
+
+  // [-dL_raw ; dA_raw] out of TMEM: masked tiles [dL ; dA] (rows) and their transposes
+  if (warp < 4) {
+    const int r = 32 * warp + lane, i = r & 63;
+    uint8_t* tr_base = smem + ((r < 64) ? kOffDLt : kOffDAt);
+#pragma unroll
+    for (int c0 = 0; c0 < 64; c0 += 16) {
+      uint32_t raw[16];
+      tmem_ld16(tmem_addr(tb, 32 * warp, kColD2 + c0), raw);
+      tmem_wait_ld();
+      float vals[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const int col = c0 + j;
+        const float x = __uint_as_float(raw[j]);
+        vals[j] = to_tf32((r < 64) ? ((col < i) ? -x : 0.f) : ((col <= i) ? x : 0.f));
+        *reinterpret_cast<float*>(tr_base + blk_off<4>(col, i, 2048, 128)) = vals[j];
+      }
+#pragma unroll
+      for (int j4 = 0; j4 < 4; ++j4) {
+        *reinterpret_cast<float4*>(smem + kOffStack2 + blk_off<4>(r, c0 + 4 * j4, 2048, 128)) =
+            make_float4(vals[4 * j4], vals[4 * j4 + 1], vals[4 * j4 + 2], vals[4 * j4 + 3]);
+      }
+    }
+  }
+  // anchored Gram operands, transposed tiles X[r = channel][c = token]
+  {
+    const int my_block = tg >> 2;
+    float kk[4][8], eat[4][8], qat[4][8];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int64_t idx = seq_idx(4 * tg + e) + 8 * c8;
+      float qq[8], bb[8];
+      load8<T>(p.k, idx, kk[e]);
+      load8<T>(p.q, idx, qq);
+      load8<T>(p.beta, idx, bb);
+#pragma unroll
+      for (int f = 0; f < 8; ++f) {
+        const int kc = 8 * c8 + f;
+        const float Gi = Gc[e][f] + ms.part[tg][kc];
+        Gc[e][f] = Gi;
+        const float anchored = __expf(Gi - ms.part[4 * my_block][kc]);
+        eat[e][f] = to_tf32(bb[f] * kk[e][f] * anchored);
+        qat[e][f] = to_tf32(p.scale * qq[f] * anchored);
+      }
+    }
+#pragma unroll
+    for (int f = 0; f < 8; ++f) {
+      const uint32_t off = blk_off<4>(8 * c8 + f, 4 * tg, 2048, 128);
+      *reinterpret_cast<float4*>(smem + kOffEat + off) = make_float4(eat[0][f], eat[1][f], eat[2][f], eat[3][f]);
+      *reinterpret_cast<float4*>(smem + kOffQat + off) = make_float4(qat[0][f], qat[1][f], qat[2][f], qat[3][f]);
+    }
+#pragma unroll
+    for (int I = 0; I < 4; ++I) {
+      if (I >= my_block) {
+#pragma unroll
+        for (int f = 0; f < 8; ++f) {
+          const int kc = 8 * c8 + f;
+          const float aI = ms.part[4 * I][kc];
+          *reinterpret_cast<float4*>(smem + kit_offset(I) + blk_off<4>(kc, 4 * tg, 512 * (I + 1), 128)) =
+              make_float4(to_tf32(kk[0][f] * __expf(aI - Gc[0][f])), to_tf32(kk[1][f] * __expf(aI - Gc[1][f])),
+                          to_tf32(kk[2][f] * __expf(aI - Gc[2][f])), to_tf32(kk[3][f] * __expf(aI - Gc[3][f])));
+        }
+      }
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0) {
+    tc_fence_after();
+    const uint32_t s2 = smem_u32(smem + kOffStack2);
+    const uint32_t dlt = smem_u32(smem + kOffDLt), dat = smem_u32(smem + kOffDAt);
+    const uint32_t eat0 = smem_u32(smem + kOffEat), qat0 = smem_u32(smem + kOffQat);
+    const uint32_t id16 = idesc(128, 16, kFmtTF32, kMajorK, kMajorK);
+    // dEa^T | dQa^T: columns 16 I .. of each 64-column half = (K^I)^T x rows of block I of [dL ; dA]
+#pragma unroll
+    for (int I = 0; I < 4; ++I) {
+      const uint32_t kit = smem_u32(smem + kit_offset(I));
+      const uint32_t rs = 512u * (I + 1);
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        for (int ks = 0; ks < 2 * (I + 1); ++ks) {
+          mma_tf32_ss(tb + kColD5 + part * 64 + 16 * I, smem_desc(kit + ks * 256, 128, rs),
+                      smem_desc(s2 + (part * 8 + 2 * I) * 2048 + ks * 256, 128, 2048), id16, ks > 0 ? 1u : 0u);
+        }
+      }
+    }
+    // (dK^I)^T = Ea^T[:, block I] dL[block I, :] + Qa^T[:, block I] dA[block I, :]
+#pragma unroll
+    for (int I = 0; I < 4; ++I) {
+      const uint32_t idn = idesc(128, 16 * (I + 1), kFmtTF32, kMajorK, kMajorK);
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        const uint32_t a_base = (part ? qat0 : eat0) + 4 * I * 128;
+        const uint32_t b_base = (part ? dat : dlt) + 4 * I * 128;
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+          mma_tf32_ss(tb + d6_col(I), smem_desc(a_base + ks * 256, 128, 2048), smem_desc(b_base + ks * 256, 128, 2048),
+                      idn, (part | ks) ? 1u : 0u);
+        }
+      }
+    }
+    mma_commit(&ms.bar_m);
+  }
+  waiter.wait(&ms.bar_m, mma_phase & 1u);
+  ++mma_phase;
+  tc_fence_after();
+
+  // ================================ per-channel chain ==============================================
+  {
+    const int kc = tid & 127;
+    const float gend = ms.gend[kc];
+    float grun = ms.part[8 * half][kc];
+    float dGv[32];
+    float e_part = 0.f, tot = 0.f;
+#pragma unroll
+    for (int bb = 0; bb < 2; ++bb) {
+      const int Ib = 2 * half + bb, i0 = 16 * Ib;
+      const float a_me = ms.part[4 * Ib][kc];
+      float Gb[16], qv[16], kv[16], bv[16], P3[16];
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        const int64_t idx = seq_idx(i0 + t) + kc;
+        grun += ldf<G>(p.g, idx);
+        Gb[t] = grun;
+        qv[t] = ldf<T>(p.q, idx);
+        kv[t] = ldf<T>(p.k, idx);
+        bv[t] = ldf<T>(p.beta, idx);
+      }
+      uint32_t r[16], r2[16];
+      tmem_ld16(tmem_addr(tb, 32 * q4, kColD4 + i0), r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        const float et = __expf(gend - Gb[t]);
+        const float dkt = __uint_as_float(r[t]);
+        P3[t] = dkt * et;
+        e_part = fmaf(kv[t] * et, dkt, e_part);
+      }
+#pragma unroll
+      for (int I = 0; I < 4; ++I) {
+        if (I >= Ib) {
+          const float aI = ms.part[4 * I][kc];
+          tmem_ld16(tmem_addr(tb, 32 * q4, d6_col(I) + i0), r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int t = 0; t < 16; ++t) P3[t] = fmaf(__uint_as_float(r[t]), __expf(aI - Gb[t]), P3[t]);
+        }
+      }
+      float P2[16];
+      tmem_ld16(tmem_addr(tb, 32 * q4, kColD3 + i0), r);        // -dE (state part)
+      tmem_ld16(tmem_addr(tb, 32 * q4, kColD5 + i0), r2);       // dEa
+      tmem_wait_ld();
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        P2[t] = fmaf(-__uint_as_float(r[t]), __expf(Gb[t]), __uint_as_float(r2[t]) * __expf(Gb[t] - a_me));
+      }
+      tmem_ld16(tmem_addr(tb, 32 * q4, kColD3 + 64 + i0), r);   // dQg (state part)
+      tmem_ld16(tmem_addr(tb, 32 * q4, kColD5 + 64 + i0), r2);  // dQa
+      tmem_wait_ld();
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        const float P1 = fmaf(__uint_as_float(r[t]), __expf(Gb[t]), __uint_as_float(r2[t]) * __expf(Gb[t] - a_me));
+        const float dq = p.scale * P1;
+        const float db = kv[t] * P2[t];
+        const float dk = fmaf(bv[t], P2[t], P3[t]);
+        const float dG = qv[t] * dq + bv[t] * db - kv[t] * P3[t];
+        const int64_t idx = seq_idx(i0 + t) + kc;
+        stf<T>(p.dq, idx, dq);
+        stf<T>(p.dk, idx, dk);
+        stf<T>(p.dbeta, idx, db);
+        dGv[16 * bb + t] = dG;
+        tot += dG;
+      }
+    }
+    ms.xe[half][kc] = e_part;
+    __syncthreads();
+    if (half == 1) {
+      const float end_term = ms.xe[0][kc] + ms.xe[1][kc] + __expf(gend) * ms.dd[kc];
+      dGv[31] += end_term;
+      tot += end_term;
+    }
+    ms.xt[half][kc] = tot;
+    __syncthreads();
+    float run = (half == 0) ? ms.xt[1][kc] : 0.f;
+#pragma unroll
+    for (int t = 31; t >= 0; --t) {
+      run += dGv[t];
+      stf<G>(p.dg, seq_idx(32 * half + t) + kc, run);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tb, 512);
+}
+
+}  // namespace
+
+// ---- launcher ---------------------------------------------------------------------------------------
+int launch_chunk_backward(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                          const void* w, const void* d_out, const float* ds_final, const float* bnd,
+                          float* d_bnd, uint8_t* workspace, void* dq, void* dk, void* dv, void* dg,
+                          void* dbeta, void* dw, float* ds_init, int64_t B, int64_t T, int64_t H,
+                          int64_t full_tokens, int dtype, int g_dtype, float scale, cudaStream_t stream) {
+  const int64_t n_chunks = full_tokens / kChunk;
+  const int64_t n_ch = B * n_chunks * H;
+  if (n_ch <= 0 || n_ch > int64_t(0x7fffffff)) return GDN2_ERR_TOO_LARGE;
+  const WsLayout ws{n_ch, true};
+  int* status = reinterpret_cast<int*>(workspace + ws.off_status());
+  cudaError_t err;
+
+  BScanParams sp{workspace, d_out, ds_final, d_bnd, ds_init, status, T, H, n_chunks, n_ch};
+  const int scan_smem = int(sizeof(BScanSmem));
+  if (dtype == GDN2_BF16) {
+    auto kernel = chunk_bwd_scan_kernel<__nv_bfloat16>;
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, scan_smem);
+    if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
+    kernel<<<unsigned(B * H), kBScanThreads, scan_smem, stream>>>(sp);
+  } else {
+    auto kernel = chunk_bwd_scan_kernel<__half>;
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, scan_smem);
+    if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
+    kernel<<<unsigned(B * H), kBScanThreads, scan_smem, stream>>>(sp);
+  }
+  int st = check_launch();
+  if (st != GDN2_OK) return st;
+
+  VjpParams vp{q, k, v, g, beta, w, d_out, workspace, bnd, d_bnd, dq, dk, dv, dg, dbeta, dw,
+               status, T, H, n_chunks, n_ch, scale};
+  GDN2_DISPATCH_TYPES(dtype, g_dtype, {
+    auto kernel = chunk_bwd_vjp_kernel<T, G>;
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kVjpSmemBytes);
+    if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
+    kernel<<<unsigned(n_ch), kVjpThreads, kVjpSmemBytes, stream>>>(vp);
+  });
+  return check_launch();
+}
+
+}  // namespace gdn2

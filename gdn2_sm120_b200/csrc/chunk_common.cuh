@@ -12,6 +12,14 @@
 //   A    X[r = token i (64)][c = token j (64)]  RS = 2048   16 KiB   tril(Q_gamma Kbar^T)
 //   Tm   X[r = token i (64)][c = token j (64)]  RS = 2048   16 KiB   (I+L)^-1
 //   D    float[128]                                         512 B    gamma_end
+// and, for training calls only (consumed by backward, which contracts over the other index):
+//   Yt   X[r = key k (128)][c = token i (64)]   RS = 2048   32 KiB   Y^T
+//   Qt   X[r = key k (128)][c = token i (64)]   RS = 2048   32 KiB   Q_gamma^T
+//   Kn   X[r = token j (64)][c = key k (128)]   RS = 4096   32 KiB   K_tail
+//   At   X[r = token j (64)][c = token i (64)]  RS = 2048   16 KiB   A_qk^T
+//   Tt   X[r = token j (64)][c = token i (64)]  RS = 2048   16 KiB   ((I+L)^-1)^T
+//   Rn   X[r = token j (64)][c = value v (128)] RS = 4096   32 KiB   R = U - Y S_0 (forward scan)
+//   dRt  X[r = value v (128)][c = token j (64)] RS = 2048   32 KiB   dR^T (backward scan)
 //
 // Arrays are stored one after another (struct of arrays), each n_ch entries long.
 #pragma once
@@ -25,10 +33,13 @@ constexpr int kChunk = GDN2_CHUNK;  // 64
 
 constexpr int64_t kBlobY = 32768, kBlobUt = 32768, kBlobQ = 32768, kBlobKt = 32768;
 constexpr int64_t kBlobA = 16384, kBlobT = 16384, kBlobD = 512;
-constexpr int64_t kBlobTotal = kBlobY + kBlobUt + kBlobQ + kBlobKt + kBlobA + kBlobT + kBlobD;
+constexpr int64_t kBlobFwd = kBlobY + kBlobUt + kBlobQ + kBlobKt + kBlobA + kBlobT + kBlobD;
+constexpr int64_t kBlobYt = 32768, kBlobQt = 32768, kBlobKn = 32768, kBlobAt = 16384, kBlobTt = 16384;
+constexpr int64_t kBlobRn = 32768, kBlobDRt = 32768;
 
 struct WsLayout {
   int64_t n_ch;
+  bool training = false;
   __host__ __device__ int64_t off_y() const { return 0; }
   __host__ __device__ int64_t off_ut() const { return n_ch * kBlobY; }
   __host__ __device__ int64_t off_q() const { return n_ch * (kBlobY + kBlobUt); }
@@ -37,7 +48,17 @@ struct WsLayout {
   __host__ __device__ int64_t off_t() const { return off_a() + n_ch * kBlobA; }
   __host__ __device__ int64_t off_d() const { return off_t() + n_ch * kBlobT; }
   __host__ __device__ int64_t off_status() const { return off_d() + n_ch * kBlobD; }
-  __host__ __device__ int64_t total() const { return off_status() + 256; }
+  // training-only arrays follow the status block
+  __host__ __device__ int64_t off_yt() const { return off_status() + 256; }
+  __host__ __device__ int64_t off_qt() const { return off_yt() + n_ch * kBlobYt; }
+  __host__ __device__ int64_t off_kn() const { return off_qt() + n_ch * kBlobQt; }
+  __host__ __device__ int64_t off_at() const { return off_kn() + n_ch * kBlobKn; }
+  __host__ __device__ int64_t off_tt() const { return off_at() + n_ch * kBlobAt; }
+  __host__ __device__ int64_t off_rn() const { return off_tt() + n_ch * kBlobTt; }
+  __host__ __device__ int64_t off_drt() const { return off_rn() + n_ch * kBlobRn; }
+  __host__ __device__ int64_t total() const {
+    return training ? off_drt() + n_ch * kBlobDRt : off_status() + 256;
+  }
 };
 
 // device status codes written to the workspace status word (0 = ok)

@@ -55,6 +55,7 @@ struct PrepParams {
   uint8_t* ws;
   int64_t T, H, n_chunks, n_ch;
   float scale;
+  int training;  // also write the transposed tiles that backward consumes
 };
 
 __device__ __forceinline__ int gram_b_offset(int I) { return (I == 0) ? 0 : (I == 1) ? 4096 : (I == 2) ? 12288 : 24576; }
@@ -64,9 +65,10 @@ template <typename T, typename G>
 __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   PrepSmem& sm = *reinterpret_cast<PrepSmem*>(smem_raw);
-  const WsLayout ws{p.n_ch};
+  const WsLayout ws{p.n_ch, p.training != 0};
   int* status = reinterpret_cast<int*>(p.ws + ws.off_status());
   BoundedWaiter waiter(status);
+  const bool training = p.training != 0;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int64_t ch = blockIdx.x;
@@ -117,7 +119,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
   uint8_t* blob_q = p.ws + ws.off_q() + ch * kBlobQ;
   uint8_t* blob_kt = p.ws + ws.off_kt() + ch * kBlobKt;
   const int my_block = tg >> 2;
-  float ebar[4][8], ktail[4][8];
+  uint8_t* blob_kn = p.ws + ws.off_kn() + ch * kBlobKn;
+  float ebar[4][8], ktail[4][8], qgam[4][8];
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
     const int i = 4 * tg + e;
@@ -161,6 +164,13 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     float4* qdst = reinterpret_cast<float4*>(blob_q + blk_off<4>(i, 8 * c8, 4096, 128));
     qdst[0] = make_float4(qg[0], qg[1], qg[2], qg[3]);
     qdst[8] = make_float4(qg[4], qg[5], qg[6], qg[7]);  // next 16-byte column chunk: +128 bytes
+#pragma unroll
+    for (int f = 0; f < 8; ++f) qgam[e][f] = qg[f];
+    if (training) {
+      float4* kdst = reinterpret_cast<float4*>(blob_kn + blk_off<4>(i, 8 * c8, 4096, 128));
+      kdst[0] = make_float4(ktail[e][0], ktail[e][1], ktail[e][2], ktail[e][3]);
+      kdst[8] = make_float4(ktail[e][4], ktail[e][5], ktail[e][6], ktail[e][7]);
+    }
   }
   // transposed tiles X[r = channel][c = token]: the thread's 4 tokens are one 16-byte chunk per channel,
   // its 8 channels are 8 consecutive rows -> 128 contiguous bytes
@@ -169,6 +179,10 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     const uint32_t off = blk_off<4>(8 * c8 + f, 4 * tg, 2048, 128);
     *reinterpret_cast<float4*>(sm.et + off) = make_float4(ebar[0][f], ebar[1][f], ebar[2][f], ebar[3][f]);
     *reinterpret_cast<float4*>(blob_kt + off) = make_float4(ktail[0][f], ktail[1][f], ktail[2][f], ktail[3][f]);
+    if (training) {
+      *reinterpret_cast<float4*>(p.ws + ws.off_qt() + ch * kBlobQt + off) =
+          make_float4(qgam[0][f], qgam[1][f], qgam[2][f], qgam[3][f]);
+    }
   }
   {
     float zz[4][8];
@@ -217,6 +231,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
   float* Tn = Ln + 64 * kLd;                                  // [64][kLd]  (fits: 2 * 16.6 KiB > 32 KiB? see below)
   // 2 * 64 * 65 * 4 = 33280 bytes > 32768: Tn spills 512 bytes into gram_b, which is dead by now.
   float* Wn = reinterpret_cast<float*>(sm.gram_b + 4096);     // [3][16][17] scratch
+  float* An = reinterpret_cast<float*>(sm.gram_b + 8192);     // [64][kLd] A_qk, natural (training)
   if (warp < 4) {
     const int r = 32 * warp + lane;       // TMEM lane = row of [E_a ; Q_a]
     const int i = r & 63;
@@ -246,6 +261,10 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
         for (int j4 = 0; j4 < 4; ++j4) {
           *reinterpret_cast<float4*>(blob_a + blk_off<4>(i, c0 + 4 * j4, 2048, 128)) =
               make_float4(vals[4 * j4], vals[4 * j4 + 1], vals[4 * j4 + 2], vals[4 * j4 + 3]);
+        }
+        if (training) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) An[i * kLd + c0 + j] = vals[j];
         }
       }
     }
@@ -302,6 +321,16 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
       const uint32_t off = blk_off<4>(i, 4 * c4, 2048, 128);
       *reinterpret_cast<float4*>(sm.tmat + off) = val;
       *reinterpret_cast<float4*>(blob_t + off) = val;
+      if (training) {
+        // transposed tiles X[r = j][c = i]: here `i` plays the role of the row j, 4*c4.. of the column i
+        const int j = i;
+        *reinterpret_cast<float4*>(p.ws + ws.off_tt() + ch * kBlobTt + off) =
+            make_float4(to_tf32(Tn[(4 * c4) * kLd + j]), to_tf32(Tn[(4 * c4 + 1) * kLd + j]),
+                        to_tf32(Tn[(4 * c4 + 2) * kLd + j]), to_tf32(Tn[(4 * c4 + 3) * kLd + j]));
+        *reinterpret_cast<float4*>(p.ws + ws.off_at() + ch * kBlobAt + off) =
+            make_float4(An[(4 * c4) * kLd + j], An[(4 * c4 + 1) * kLd + j], An[(4 * c4 + 2) * kLd + j],
+                        An[(4 * c4 + 3) * kLd + j]);
+      }
     }
   }
   fence_async_smem();
@@ -323,6 +352,14 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     for (int ks = 0; ks < 8; ++ks) {
       mma_tf32_ss(tb + 128, smem_desc(z0 + ks * 256, 128, 2048), smem_desc(t0a + ks * 256, 128, 2048), id_u,
                   ks > 0 ? 1u : 0u);
+    }
+    if (training) {
+      // Y^T = E^T T^T (lane = key), columns 192..255
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        mma_tf32_ss(tb + 192, smem_desc(e0 + ks * 256, 128, 2048), smem_desc(t0a + ks * 256, 128, 2048), id_u,
+                    ks > 0 ? 1u : 0u);
+      }
     }
     mma_commit(&sm.bar[1]);
   }
@@ -365,6 +402,21 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
                           __uint_as_float(r[4 * j4 + 2]), __uint_as_float(r[4 * j4 + 3]));
         }
       }
+      if (training) {
+        uint8_t* blob_yt = p.ws + ws.off_yt() + ch * kBlobYt;
+#pragma unroll
+        for (int c0 = 0; c0 < 32; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld16(tmem_addr(tb, 32 * q4, 192 + ibase + c0), r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j4 = 0; j4 < 4; ++j4) {
+            *reinterpret_cast<float4*>(blob_yt + blk_off<4>(vrow, ibase + c0 + 4 * j4, 2048, 128)) =
+                make_float4(to_tf32(__uint_as_float(r[4 * j4])), to_tf32(__uint_as_float(r[4 * j4 + 1])),
+                            to_tf32(__uint_as_float(r[4 * j4 + 2])), to_tf32(__uint_as_float(r[4 * j4 + 3])));
+          }
+        }
+      }
     }
   }
   tc_fence_before();
@@ -396,13 +448,15 @@ struct ScanParams {
   float* bnd;          // [B, n_chunks+1, H,128,128] or null
   int* status;
   int64_t T, H, n_chunks, n_ch;
+  uint8_t* ws_out;     // same workspace, writable (training: residual blobs)
+  int training;
 };
 
 template <typename T>
 __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   ScanSmem& sm = *reinterpret_cast<ScanSmem*>(smem_raw);
-  const WsLayout ws{p.n_ch};
+  const WsLayout ws{p.n_ch, p.training != 0};
   BoundedWaiter waiter(p.status);
 
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -522,6 +576,21 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
     tc_fence_after();
     if (tid == 0 && c + 1 < p.n_chunks) load_yqa(c + 1);  // the three MMAs no longer read Y, Q, A
 
+    // ---- training: keep the residual R = U - Y S_0 (natural tile X[r = j][c = v]) for backward ------
+    if (p.training) {
+      uint8_t* blob_rn = p.ws_out + ws.off_rn() + ch_of(c) * kBlobRn + (vrow >> 2) * 128 + (vrow & 3) * 4;
+#pragma unroll
+      for (int c0 = 0; c0 < kChunk; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_addr(tb, lane_base, kColR + c0), r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int tok = c0 + j;
+          *reinterpret_cast<uint32_t*>(blob_rn + (tok >> 3) * 4096 + (tok & 7) * 16) = r[j];
+        }
+      }
+    }
     // ---- output rows of this chunk: thread v writes o[t0 + i][v] ----------------------------------
     {
       T* out = static_cast<T*>(p.out);
@@ -602,8 +671,8 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
 }  // namespace
 
 // ---- launcher ---------------------------------------------------------------------------------
-int64_t chunk_workspace_bytes(int64_t batch, int64_t full_tokens, int64_t heads) {
-  const WsLayout ws{batch * (full_tokens / kChunk) * heads};
+int64_t chunk_workspace_bytes(int64_t batch, int64_t full_tokens, int64_t heads, int training) {
+  const WsLayout ws{batch * (full_tokens / kChunk) * heads, training != 0};
   return ws.total();
 }
 
@@ -615,16 +684,16 @@ int64_t chunk_status_offset(int64_t batch, int64_t full_tokens, int64_t heads) {
 int launch_chunk_forward(const void* q, const void* k, const void* v, const void* g, const void* beta,
                          const void* w, const float* s_in, void* out, float* s_out, float* bnd,
                          uint8_t* workspace, int64_t B, int64_t T, int64_t H, int64_t full_tokens,
-                         int dtype, int g_dtype, float scale, cudaStream_t stream) {
+                         int training, int dtype, int g_dtype, float scale, cudaStream_t stream) {
   const int64_t n_chunks = full_tokens / kChunk;
   const int64_t n_ch = B * n_chunks * H;
   if (n_ch <= 0 || n_ch > int64_t(0x7fffffff)) return GDN2_ERR_TOO_LARGE;
-  const WsLayout ws{n_ch};
+  const WsLayout ws{n_ch, training != 0};
   int* status = reinterpret_cast<int*>(workspace + ws.off_status());
   cudaError_t err = cudaMemsetAsync(status, 0, 256, stream);
   if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
 
-  PrepParams pp{q, k, v, g, beta, w, workspace, T, H, n_chunks, n_ch, scale};
+  PrepParams pp{q, k, v, g, beta, w, workspace, T, H, n_chunks, n_ch, scale, training};
   GDN2_DISPATCH_TYPES(dtype, g_dtype, {
     auto kernel = chunk_prep_kernel<T, G>;
     const int smem = int(sizeof(PrepSmem));
@@ -635,7 +704,7 @@ int launch_chunk_forward(const void* q, const void* k, const void* v, const void
   int st = check_launch();
   if (st != GDN2_OK) return st;
 
-  ScanParams sp{workspace, s_in, out, s_out, bnd, status, T, H, n_chunks, n_ch};
+  ScanParams sp{workspace, s_in, out, s_out, bnd, status, T, H, n_chunks, n_ch, workspace, training};
   const int smem = int(sizeof(ScanSmem));
   if (dtype == GDN2_BF16) {
     auto kernel = chunk_scan_kernel<__nv_bfloat16>;

@@ -147,11 +147,12 @@ int gdn2_token_chunk_vjp(const void* q, const void* k, const void* v, const void
  * Bytes of caller-owned workspace the chunk kernels need for `full_tokens` leading
  * tokens (a multiple of GDN2_CHUNK) of a [batch, T, heads, 128] problem.  The workspace
  * holds the per-chunk WY factors (Y, U^T, Q_gamma, K_tail^T, A_qk, (I+L)^-1, gamma_end)
- * as operand-ready tiles plus a device status word; backward reuses it, so for training
- * it must stay alive (and unmodified) until gdn2_chunk_backward has run.
+ * as operand-ready tiles plus a device status word.  With `training` != 0 it is larger:
+ * it also holds the transposed tiles and the residuals that gdn2_chunk_backward consumes,
+ * and must stay alive (and unmodified) until that call has run.
  * Replaces the intermediate allocations of chunk_forward (src/gdn2_sm120/chunk.py:1317-1362).
  */
-int64_t gdn2_chunk_workspace_bytes(int64_t batch, int64_t full_tokens, int64_t heads);
+int64_t gdn2_chunk_workspace_bytes(int64_t batch, int64_t full_tokens, int64_t heads, int training);
 
 /*
  * Chunkwise forward over tokens [0, full_tokens).  Replaces _prepare_wy_kernel and
@@ -162,13 +163,38 @@ int64_t gdn2_chunk_workspace_bytes(int64_t batch, int64_t full_tokens, int64_t h
  *   final_state    fp32 state after token full_tokens-1 (may alias initial_state exactly); or NULL
  *   chunk_boundaries  NULL, or fp32 [B, full_tokens/64 + 1, H,128,128]: state before every
  *                  chunk and after the last one (the activation checkpoints of backward)
+ *   training       non-zero: workspace was sized with training = 1, chunk_boundaries is
+ *                  required, and everything backward needs is saved
  * All sequence pointers, states and the workspace must be 16-byte aligned.
  */
 int gdn2_chunk_forward(const void* q, const void* k, const void* v, const void* g,
                        const void* beta, const void* w, const float* initial_state,
                        void* out, float* final_state, float* chunk_boundaries,
                        void* workspace, int64_t batch, int64_t time, int64_t heads,
-                       int64_t full_tokens, int dtype, int g_dtype, float scale, void* stream);
+                       int64_t full_tokens, int training, int dtype, int g_dtype, float scale,
+                       void* stream);
+
+/*
+ * Chunkwise backward over tokens [0, full_tokens): reverse scan of the state cotangent plus
+ * the compact-WY chunk VJP, from what gdn2_chunk_forward(training = 1) saved.  Replaces
+ * wy_boundary_dstate and compact_wy_chunk_vjp_cute with their kernels
+ * (src/gdn2_sm120/backward_parallel.py:537-1049, 1997-2190; backward_wy.py:226-1168, 1669-1984).
+ *   d_out            [B,T,H,128] in `dtype` (rows [0, full_tokens) are read)
+ *   d_final_state    cotangent of the state after token full_tokens-1, or NULL (zero)
+ *   chunk_boundaries the forward's fp32 [B, full_tokens/64 + 1, H,128,128] checkpoints
+ *   d_boundaries     caller-owned scratch of the same shape (cotangent at every chunk start)
+ *   workspace        the forward's training workspace (read, and its dR^T slots written)
+ *   dq, dk, dv, dbeta, dw (`dtype`), dg (`g_dtype`): rows [0, full_tokens) are written
+ *   d_initial_state  fp32 [B,H,128,128] or NULL
+ * Every pointer must be 16-byte aligned.
+ */
+int gdn2_chunk_backward(const void* q, const void* k, const void* v, const void* g,
+                        const void* beta, const void* w, const void* d_out,
+                        const float* d_final_state, const float* chunk_boundaries,
+                        float* d_boundaries, void* workspace,
+                        void* dq, void* dk, void* dv, void* dg, void* dbeta, void* dw,
+                        float* d_initial_state, int64_t batch, int64_t time, int64_t heads,
+                        int64_t full_tokens, int dtype, int g_dtype, float scale, void* stream);
 
 /*
  * Synchronise `stream` and return the device status word of a workspace: 0 = ok,
