@@ -197,8 +197,9 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
         tmem_wait_ld();
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
-          *reinterpret_cast<uint4*>(blob + (c0 / 4 + c4) * 128) =
-              make_uint4(r[4 * c4], r[4 * c4 + 1], r[4 * c4 + 2], r[4 * c4 + 3]);
+          *reinterpret_cast<float4*>(blob + (c0 / 4 + c4) * 128) =
+              make_float4(to_tf32(__uint_as_float(r[4 * c4])), to_tf32(__uint_as_float(r[4 * c4 + 1])),
+                          to_tf32(__uint_as_float(r[4 * c4 + 2])), to_tf32(__uint_as_float(r[4 * c4 + 3])));
         }
       }
     }
@@ -376,23 +377,38 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
   ++mma_phase;
   tc_fence_after();
 
-  // ---- bring in S_0 (whole) and the first half of dS_1 with 16-byte async copies ---------------------
+  // ---- bring in S_0 (whole) and the first half of dS_1 -------------------------------------------------
   const float* s0_src = p.bnd + ((b * (p.n_chunks + 1) + c) * p.H + h) * kStateElems;
   const float* ds1_src = p.d_bnd + ((b * (p.n_chunks + 1) + c + 1) * p.H + h) * kStateElems;
+  // (rounded to nearest tf32 on the way: the MMA would otherwise truncate, which biases the products)
+  auto rn4 = [](float4 x) { return make_float4(to_tf32(x.x), to_tf32(x.y), to_tf32(x.z), to_tf32(x.w)); };
+  {
+    float4 buf[16];
 #pragma unroll
-  for (int x = 0; x < 16; ++x) {
-    const int kr = (tid & 7) + 8 * x, v4 = ((tid >> 3) & 3) + 4 * ((tid >> 5) & 7);
-    cp_async16(smem + kOffS0 + x * 4096 + v4 * 128 + (tid & 7) * 16, s0_src + kr * kDim + 4 * v4);
+    for (int x = 0; x < 16; ++x) {
+      const int kr = (tid & 7) + 8 * x, v4 = ((tid >> 3) & 3) + 4 * ((tid >> 5) & 7);
+      buf[x] = *reinterpret_cast<const float4*>(s0_src + kr * kDim + 4 * v4);
+    }
+#pragma unroll
+    for (int x = 0; x < 16; ++x) {
+      const int v4 = ((tid >> 3) & 3) + 4 * ((tid >> 5) & 7);
+      *reinterpret_cast<float4*>(smem + kOffS0 + x * 4096 + v4 * 128 + (tid & 7) * 16) = rn4(buf[x]);
+    }
   }
   auto load_ds1_half = [&](int hf) {
+    float4 buf[8];
 #pragma unroll
     for (int x = 0; x < 8; ++x) {
       const int qd = tid + 256 * x;
       const int kr = (qd & 7) + 8 * (qd >> 7), v4 = ((qd >> 3) & 3) + 4 * ((qd >> 5) & 3);
-      cp_async16(smem + kOffDs1 + (qd >> 7) * 2048 + v4 * 128 + (qd & 7) * 16,
-                 ds1_src + kr * kDim + 64 * hf + 4 * v4);
+      buf[x] = *reinterpret_cast<const float4*>(ds1_src + kr * kDim + 64 * hf + 4 * v4);
     }
-    cp_async_commit();
+#pragma unroll
+    for (int x = 0; x < 8; ++x) {
+      const int qd = tid + 256 * x;
+      const int v4 = ((qd >> 3) & 3) + 4 * ((qd >> 5) & 3);
+      *reinterpret_cast<float4*>(smem + kOffDs1 + (qd >> 7) * 2048 + v4 * 128 + (qd & 7) * 16) = rn4(buf[x]);
+    }
   };
   load_ds1_half(0);
 
@@ -413,7 +429,6 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
       stf<T>(p.dw, idx, dz * vv);
     }
   }
-  cp_async_wait_all();
   waiter.wait(&ms.bar_r, 0);
   fence_async_smem();
   tc_fence_before();
@@ -462,7 +477,6 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
   tc_fence_after();
   __syncthreads();  // every dd reader is done with the first half before it is overwritten
   load_ds1_half(1);
-  cp_async_wait_all();
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
@@ -615,22 +629,26 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
   tc_fence_after();
 
   // ================================ per-channel chain ==============================================
+  // One thread = one key channel over 32 tokens.  The log-decay G and the anchored operands are
+  // re-evaluated with exactly the expressions (and summation order) used when the MMA tiles were
+  // built, so that dG multiplies each Gram cotangent by the very tf32 value the tensor cores saw:
+  // the row and column contributions of the Gram products to dG then cancel as they do exactly.
   {
     const int kc = tid & 127;
     const float gend = ms.gend[kc];
-    float grun = ms.part[8 * half][kc];
     float dGv[32];
     float e_part = 0.f, tot = 0.f;
 #pragma unroll
     for (int bb = 0; bb < 2; ++bb) {
       const int Ib = 2 * half + bb, i0 = 16 * Ib;
       const float a_me = ms.part[4 * Ib][kc];
-      float Gb[16], qv[16], kv[16], bv[16], P3[16];
+      float Gb[16], qv[16], kv[16], bv[16], P3[16], dGa[16];
+      float loc = 0.f;
 #pragma unroll
       for (int t = 0; t < 16; ++t) {
         const int64_t idx = seq_idx(i0 + t) + kc;
-        grun += ldf<G>(p.g, idx);
-        Gb[t] = grun;
+        loc = ((t & 3) ? loc : 0.f) + ldf<G>(p.g, idx);
+        Gb[t] = loc + ms.part[(i0 + t) >> 2][kc];
         qv[t] = ldf<T>(p.q, idx);
         kv[t] = ldf<T>(p.k, idx);
         bv[t] = ldf<T>(p.beta, idx);
@@ -642,8 +660,10 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
       for (int t = 0; t < 16; ++t) {
         const float et = __expf(gend - Gb[t]);
         const float dkt = __uint_as_float(r[t]);
+        const float kt = kv[t] * et;
         P3[t] = dkt * et;
-        e_part = fmaf(kv[t] * et, dkt, e_part);
+        e_part = fmaf(kt, dkt, e_part);
+        dGa[t] = -kt * dkt;
       }
 #pragma unroll
       for (int I = 0; I < 4; ++I) {
@@ -652,7 +672,12 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
           tmem_ld16(tmem_addr(tb, 32 * q4, d6_col(I) + i0), r);
           tmem_wait_ld();
 #pragma unroll
-          for (int t = 0; t < 16; ++t) P3[t] = fmaf(__uint_as_float(r[t]), __expf(aI - Gb[t]), P3[t]);
+          for (int t = 0; t < 16; ++t) {
+            const float ex = __expf(aI - Gb[t]);
+            const float dki = __uint_as_float(r[t]);
+            P3[t] = fmaf(dki, ex, P3[t]);
+            dGa[t] = fmaf(-to_tf32(kv[t] * ex), dki, dGa[t]);
+          }
         }
       }
       float P2[16];
@@ -661,22 +686,27 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
       tmem_wait_ld();
 #pragma unroll
       for (int t = 0; t < 16; ++t) {
-        P2[t] = fmaf(-__uint_as_float(r[t]), __expf(Gb[t]), __uint_as_float(r2[t]) * __expf(Gb[t] - a_me));
+        const float eg = __expf(Gb[t]), ea = __expf(Gb[t] - a_me);
+        const float de = -__uint_as_float(r[t]), dea = __uint_as_float(r2[t]);
+        P2[t] = fmaf(de, eg, dea * ea);
+        const float bk = bv[t] * kv[t];
+        dGa[t] = fmaf(bk * eg, de, dGa[t]);
+        dGa[t] = fmaf(to_tf32(bk * ea), dea, dGa[t]);
       }
       tmem_ld16(tmem_addr(tb, 32 * q4, kColD3 + 64 + i0), r);   // dQg (state part)
       tmem_ld16(tmem_addr(tb, 32 * q4, kColD5 + 64 + i0), r2);  // dQa
       tmem_wait_ld();
 #pragma unroll
       for (int t = 0; t < 16; ++t) {
-        const float P1 = fmaf(__uint_as_float(r[t]), __expf(Gb[t]), __uint_as_float(r2[t]) * __expf(Gb[t] - a_me));
-        const float dq = p.scale * P1;
-        const float db = kv[t] * P2[t];
-        const float dk = fmaf(bv[t], P2[t], P3[t]);
-        const float dG = qv[t] * dq + bv[t] * db - kv[t] * P3[t];
+        const float eg = __expf(Gb[t]), ea = __expf(Gb[t] - a_me);
+        const float dqg = __uint_as_float(r[t]), dqa = __uint_as_float(r2[t]);
+        const float P1 = fmaf(dqg, eg, dqa * ea);
+        const float sq = p.scale * qv[t];
+        const float dG = fmaf(to_tf32(sq * ea), dqa, fmaf(sq * eg, dqg, dGa[t]));
         const int64_t idx = seq_idx(i0 + t) + kc;
-        stf<T>(p.dq, idx, dq);
-        stf<T>(p.dk, idx, dk);
-        stf<T>(p.dbeta, idx, db);
+        stf<T>(p.dq, idx, p.scale * P1);
+        stf<T>(p.dk, idx, fmaf(bv[t], P2[t], P3[t]));
+        stf<T>(p.dbeta, idx, kv[t] * P2[t]);
         dGv[16 * bb + t] = dG;
         tot += dG;
       }

@@ -2,7 +2,7 @@
 //
 //   chunk_prep_kernel   one CTA per (batch, chunk, head), all chunks in parallel.  Builds the WY
 //                       factors of the chunk and writes them as operand-ready blobs:
-//                       cumulative log-decay, block-anchored Gram products on bf16 tcgen05 MMAs,
+//                       cumulative log-decay, block-anchored Gram products on tf32 tcgen05 MMAs,
 //                       blocked inverse of the unit lower-triangular system on CUDA cores (fp32),
 //                       Y = T E and U^T = Z^T T^T on tf32 tcgen05 MMAs.
 //   chunk_scan_kernel   one CTA per (batch, head), chunks in order.  The state lives transposed
@@ -37,12 +37,12 @@ constexpr int kPrepThreads = 256;
 constexpr int kLd = 65;  // leading dimension of the fp32 64x64 scratch matrices
 
 struct PrepSmem {
-  // region 1: bf16 Gram A operand [E_anchored ; Q_anchored] (128 x 128), later fp32 L / T / W scratch
-  alignas(128) uint8_t gram_a[32768];
-  // region 2: bf16 Gram B operands K^I, rows j < 16 (I + 1): 4 KiB + 8 KiB + 12 KiB + 16 KiB
-  alignas(128) uint8_t gram_b[40960];
-  alignas(128) uint8_t et[32768];      // E^T  tile X[r = k][c = j], tf32
-  alignas(128) uint8_t zt[32768];      // Z^T  tile X[r = v][c = j], tf32
+  // region 1: tf32 Gram A operand [E_anchored ; Q_anchored] X[r = 128][c = k], RS 4096;
+  //           after the Gram products: fp32 scratch for L, T, the block products and A_qk
+  alignas(128) uint8_t gram_a[65536];
+  // region 2: tf32 Gram B operands K^I X[r = j < 16 (I + 1)][c = k], RS 4096: 8 + 16 + 24 + 32 KiB;
+  //           after the Gram products: E^T at +0 and Z^T at +32 KiB, tiles X[r = channel][c = j], RS 2048
+  alignas(128) uint8_t gram_b[81920];
   alignas(128) uint8_t tmat[32768];    // T    tile X[r = i][c = j], tf32 (rows 64..127 unused filler)
   float part[16][kDim];                // per 4-token group partial sums -> exclusive prefixes
   float gend[kDim];
@@ -58,7 +58,7 @@ struct PrepParams {
   int training;  // also write the transposed tiles that backward consumes
 };
 
-__device__ __forceinline__ int gram_b_offset(int I) { return (I == 0) ? 0 : (I == 1) ? 4096 : (I == 2) ? 12288 : 24576; }
+__device__ __forceinline__ int gram_b_offset(int I) { return (I == 0) ? 0 : (I == 1) ? 8192 : (I == 2) ? 24576 : 49152; }
 __device__ __forceinline__ int gram_col(int I) { return (I == 0) ? 0 : (I == 1) ? 16 : (I == 2) ? 48 : 96; }
 
 template <typename T, typename G>
@@ -138,26 +138,31 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
       const float anchored = __expf(Gi - sm.part[4 * my_block][kc]);
       const float full = __expf(Gi);
       const float bk = bb[f] * kk[f];
-      ea[f] = bk * anchored;
-      qa[f] = p.scale * qq[f] * anchored;
+      ea[f] = to_tf32(bk * anchored);
+      qa[f] = to_tf32(p.scale * qq[f] * anchored);
       ebar[e][f] = to_tf32(bk * full);
       qg[f] = to_tf32(p.scale * qq[f] * full);
       ktail[e][f] = to_tf32(kk[f] * __expf(sm.gend[kc] - Gi));
     }
-    // Gram A operand rows i (erase) and 64 + i (query), bf16, K-major
-    *reinterpret_cast<uint4*>(sm.gram_a + blk_off<2>(i, 8 * c8, 2048, 128)) =
-        make_uint4(pack_bf16(ea[0], ea[1]), pack_bf16(ea[2], ea[3]), pack_bf16(ea[4], ea[5]), pack_bf16(ea[6], ea[7]));
-    *reinterpret_cast<uint4*>(sm.gram_a + blk_off<2>(64 + i, 8 * c8, 2048, 128)) =
-        make_uint4(pack_bf16(qa[0], qa[1]), pack_bf16(qa[2], qa[3]), pack_bf16(qa[4], qa[5]), pack_bf16(qa[6], qa[7]));
+    // Gram A operand rows i (erase) and 64 + i (query), tf32, K-major
+    {
+      float4* ed = reinterpret_cast<float4*>(sm.gram_a + blk_off<4>(i, 8 * c8, 4096, 128));
+      ed[0] = make_float4(ea[0], ea[1], ea[2], ea[3]);
+      ed[8] = make_float4(ea[4], ea[5], ea[6], ea[7]);
+      float4* qd = reinterpret_cast<float4*>(sm.gram_a + blk_off<4>(64 + i, 8 * c8, 4096, 128));
+      qd[0] = make_float4(qa[0], qa[1], qa[2], qa[3]);
+      qd[8] = make_float4(qa[4], qa[5], qa[6], qa[7]);
+    }
     // Gram B operands: token i is a column of every row block I >= its own
 #pragma unroll
     for (int I = 0; I < 4; ++I) {
       if (I >= my_block) {
         float kb[8];
 #pragma unroll
-        for (int f = 0; f < 8; ++f) kb[f] = kk[f] * __expf(sm.part[4 * I][8 * c8 + f] - Gc[e][f]);
-        *reinterpret_cast<uint4*>(sm.gram_b + gram_b_offset(I) + blk_off<2>(i, 8 * c8, 2048, 128)) =
-            make_uint4(pack_bf16(kb[0], kb[1]), pack_bf16(kb[2], kb[3]), pack_bf16(kb[4], kb[5]), pack_bf16(kb[6], kb[7]));
+        for (int f = 0; f < 8; ++f) kb[f] = to_tf32(kk[f] * __expf(sm.part[4 * I][8 * c8 + f] - Gc[e][f]));
+        float4* kd = reinterpret_cast<float4*>(sm.gram_b + gram_b_offset(I) + blk_off<4>(i, 8 * c8, 4096, 128));
+        kd[0] = make_float4(kb[0], kb[1], kb[2], kb[3]);
+        kd[8] = make_float4(kb[4], kb[5], kb[6], kb[7]);
       }
     }
     // Q_gamma tile X[r = i][c = k], tf32, straight to the workspace
@@ -177,29 +182,21 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
 #pragma unroll
   for (int f = 0; f < 8; ++f) {
     const uint32_t off = blk_off<4>(8 * c8 + f, 4 * tg, 2048, 128);
-    *reinterpret_cast<float4*>(sm.et + off) = make_float4(ebar[0][f], ebar[1][f], ebar[2][f], ebar[3][f]);
     *reinterpret_cast<float4*>(blob_kt + off) = make_float4(ktail[0][f], ktail[1][f], ktail[2][f], ktail[3][f]);
     if (training) {
       *reinterpret_cast<float4*>(p.ws + ws.off_qt() + ch * kBlobQt + off) =
           make_float4(qgam[0][f], qgam[1][f], qgam[2][f], qgam[3][f]);
     }
   }
-  {
-    float zz[4][8];
+  float zz[4][8];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int64_t idx = ((b * p.T + t0 + 4 * tg + e) * p.H + h) * kDim + 8 * c8;
-      float vv[8], ww[8];
-      load8<T>(p.v, idx, vv);
-      load8<T>(p.w, idx, ww);
+  for (int e = 0; e < 4; ++e) {
+    const int64_t idx = ((b * p.T + t0 + 4 * tg + e) * p.H + h) * kDim + 8 * c8;
+    float vv[8], ww[8];
+    load8<T>(p.v, idx, vv);
+    load8<T>(p.w, idx, ww);
 #pragma unroll
-      for (int f = 0; f < 8; ++f) zz[e][f] = to_tf32(vv[f] * ww[f]);
-    }
-#pragma unroll
-    for (int f = 0; f < 8; ++f) {
-      *reinterpret_cast<float4*>(sm.zt + blk_off<4>(8 * c8 + f, 4 * tg, 2048, 128)) =
-          make_float4(zz[0][f], zz[1][f], zz[2][f], zz[3][f]);
-    }
+    for (int f = 0; f < 8; ++f) zz[e][f] = to_tf32(vv[f] * ww[f]);
   }
   if (tid < kDim) {
     reinterpret_cast<float*>(p.ws + ws.off_d() + ch * kBlobD)[tid] = __expf(sm.gend[tid]);
@@ -213,12 +210,12 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     tc_fence_after();
 #pragma unroll
     for (int I = 0; I < 4; ++I) {
-      const uint32_t id = idesc(128, 16 * (I + 1), kFmtBF16, kMajorK, kMajorK);
+      const uint32_t id = idesc(128, 16 * (I + 1), kFmtTF32, kMajorK, kMajorK);
       const uint32_t a0 = smem_u32(sm.gram_a), b0 = smem_u32(sm.gram_b + gram_b_offset(I));
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        mma_f16_ss(tb + gram_col(I), smem_desc(a0 + ks * 256, 128, 2048), smem_desc(b0 + ks * 256, 128, 2048), id,
-                   ks > 0 ? 1u : 0u);
+      for (int ks = 0; ks < 16; ++ks) {
+        mma_tf32_ss(tb + gram_col(I), smem_desc(a0 + ks * 256, 128, 4096), smem_desc(b0 + ks * 256, 128, 4096), id,
+                    ks > 0 ? 1u : 0u);
       }
     }
     mma_commit(&sm.bar[0]);
@@ -227,11 +224,19 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
   tc_fence_after();
 
   // ---- pull L (rows 0..63) into fp32 scratch, Aqk (rows 64..127) into the workspace ---------------
-  float* Ln = reinterpret_cast<float*>(sm.gram_a);           // [64][kLd]  16.6 KiB
-  float* Tn = Ln + 64 * kLd;                                  // [64][kLd]  (fits: 2 * 16.6 KiB > 32 KiB? see below)
-  // 2 * 64 * 65 * 4 = 33280 bytes > 32768: Tn spills 512 bytes into gram_b, which is dead by now.
-  float* Wn = reinterpret_cast<float*>(sm.gram_b + 4096);     // [3][16][17] scratch
-  float* An = reinterpret_cast<float*>(sm.gram_b + 8192);     // [64][kLd] A_qk, natural (training)
+  // the Gram operands are dead: region 1 becomes fp32 scratch, region 2 receives E^T and Z^T
+  float* Ln = reinterpret_cast<float*>(sm.gram_a);           // [64][kLd]   L
+  float* Tn = Ln + 64 * kLd;                                  // [64][kLd]   T
+  float* An = Tn + 64 * kLd;                                  // [64][kLd]   A_qk, natural (training)
+  float* Wn = An + 64 * kLd;                                  // [3][16][17] block products
+  uint8_t* et_tile = sm.gram_b;                               // E^T  X[r = k][c = j], tf32, 32 KiB
+  uint8_t* zt_tile = sm.gram_b + 32768;                       // Z^T  X[r = v][c = j], tf32, 32 KiB
+#pragma unroll
+  for (int f = 0; f < 8; ++f) {
+    const uint32_t off = blk_off<4>(8 * c8 + f, 4 * tg, 2048, 128);
+    *reinterpret_cast<float4*>(et_tile + off) = make_float4(ebar[0][f], ebar[1][f], ebar[2][f], ebar[3][f]);
+    *reinterpret_cast<float4*>(zt_tile + off) = make_float4(zz[0][f], zz[1][f], zz[2][f], zz[3][f]);
+  }
   if (warp < 4) {
     const int r = 32 * warp + lane;       // TMEM lane = row of [E_a ; Q_a]
     const int i = r & 63;
@@ -340,7 +345,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
   // ---- Y = T E (rows 0..63 of an M = 128 product) and U^T = Z^T T^T --------------------------------
   if (tid == 0) {
     tc_fence_after();
-    const uint32_t t0a = smem_u32(sm.tmat), e0 = smem_u32(sm.et), z0 = smem_u32(sm.zt);
+    const uint32_t t0a = smem_u32(sm.tmat), e0 = smem_u32(et_tile), z0 = smem_u32(zt_tile);
     const uint32_t id_y = idesc(128, 128, kFmtTF32, kMajorK, kMajorK);
     const uint32_t id_u = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
 #pragma unroll
@@ -587,7 +592,7 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int tok = c0 + j;
-          *reinterpret_cast<uint32_t*>(blob_rn + (tok >> 3) * 4096 + (tok & 7) * 16) = r[j];
+          *reinterpret_cast<float*>(blob_rn + (tok >> 3) * 4096 + (tok & 7) * 16) = to_tf32(__uint_as_float(r[j]));
         }
       }
     }
