@@ -43,6 +43,7 @@ _PROTOTYPES: dict[str, list] = {
     "gdn2_chunk_forward": [_P] * 11 + [_I64] * 4 + [_INT, _INT, _INT, _F32, _P],
     "gdn2_chunk_backward": [_P] * 18 + [_I64] * 4 + [_INT, _INT, _F32, _P],
     "gdn2_chunk_read_status": [_P] + [_I64] * 3 + [_P],
+    "gdn2_chunk_forward_static": [_P] * 9 + [_I64] * 4 + [_INT, _INT, _F32, _P],
 }
 _RESTYPES = {"gdn2_status_string": ctypes.c_char_p, "gdn2_last_cuda_error": ctypes.c_char_p,
              "gdn2_chunk_workspace_bytes": ctypes.c_int64}

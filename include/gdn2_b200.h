@@ -205,6 +205,30 @@ int gdn2_chunk_backward(const void* q, const void* k, const void* v, const void*
 int gdn2_chunk_read_status(const void* workspace, int64_t batch, int64_t full_tokens,
                            int64_t heads, void* stream);
 
+/*
+ * Chunk forward (inference) for callers that must not allocate.  No counterpart in the
+ * reference: it exists for hosts such as a serving runtime that partitions device memory
+ * once at start-up, or a plugin hook that runs inside another component's memory plan,
+ * where obtaining a workspace per call is not possible.  Same kernels and results as
+ * gdn2_chunk_forward with training = 0 and chunk_boundaries = NULL, but the WY workspace
+ * is a fixed ~10 MiB array inside the library image (held by every GPU that loads the
+ * library, until the process exits).
+ *   limit      batch * (full_tokens / 64) * heads <= GDN2_STATIC_MAX_CHUNK_HEADS, otherwise
+ *              GDN2_ERR_TOO_LARGE
+ *   first call on each device resolves the array's address (one driver query); issue it
+ *              before any stream capture begins
+ *   sharing    every call on a device uses the same array, which keeps the previous call's
+ *              contents; the status word is cleared per call and every tile is rewritten
+ *              before use, but calls whose kernels overlap on the GPU race -- serialise them
+ * Calls no cudaMalloc / cudaFree / allocating library routine.  Pointers 16-byte aligned.
+ */
+#define GDN2_STATIC_MAX_CHUNK_HEADS 64
+int gdn2_chunk_forward_static(const void* q, const void* k, const void* v, const void* g,
+                              const void* beta, const void* w, const float* initial_state,
+                              void* out, float* final_state,
+                              int64_t batch, int64_t time, int64_t heads, int64_t full_tokens,
+                              int dtype, int g_dtype, float scale, void* stream);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif
