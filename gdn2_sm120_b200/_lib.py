@@ -95,7 +95,7 @@ def stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
-# Number of successful kernel-launching entry-point calls (each launches one kernel).
+# Number of kernels launched through successful entry-point calls.
 LAUNCHES = [0]
 # When set to a dict, every call is bracketed by CUDA events on the current stream and
 # the pair is appended under the entry point's name (used by bench.py to time individual
@@ -103,11 +103,15 @@ LAUNCHES = [0]
 KERNEL_EVENTS: dict[str, list] | None = None
 
 
+# kernels launched by one successful call of each entry point (default 1)
+_KERNELS_PER_CALL = {"gdn2_chunk_forward": 2, "gdn2_chunk_backward": 2, "gdn2_chunk_forward_static": 2}
+
+
 def check(status: int, what: str) -> None:
     """Turn a negative gdn2_status into a RuntimeError; count successful launches."""
 
     if status == 0:
-        LAUNCHES[0] += 1
+        LAUNCHES[0] += _KERNELS_PER_CALL.get(what, 1)
         return
     handle = lib()
     text = handle.gdn2_status_string(status).decode()

@@ -11,9 +11,9 @@ exact fp32 token kernels process on the same buffers (the reference does the sam
 its scalar tail scan, chunk.py:1021-1053).  When the chunk kernels are not enabled for
 a call, ``full_tokens`` is 0 and the token kernels cover the whole sequence.
 
-Activation checkpoints for backward are the fp32 states at chunk / span starts only;
-every WY factor is recomputed in backward instead of being written to HBM, because the
-path is HBM-bound on B200.
+Activation checkpoints for backward are the fp32 states at chunk / span starts plus,
+for the chunk kernels, the workspace of per-chunk WY factors that the forward prep kernel
+wrote (the reference saves the same factors, chunk.py:1056-1075).
 """
 
 from __future__ import annotations
