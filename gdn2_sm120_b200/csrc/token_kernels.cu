@@ -19,6 +19,7 @@
 // exactly one thread (which is why an exact in-place state update is race-free).
 
 #include "common.cuh"
+#include "tc05.cuh"
 
 namespace gdn2 {
 
@@ -162,6 +163,146 @@ __global__ void __launch_bounds__(kTokThreads) token_forward_kernel(const TokenF
   if (p.s_out != nullptr) {
     store_tile(p.s_out + bh * kStateElems);
   }
+}
+
+// ---------------------------------------------------------------------------------
+// Decode step (T == 1, 16-byte aligned states, many heads): persistent CTAs, one per SM, each
+// walking over (batch, head) pairs.  A head's whole 64 KiB state travels global -> shared ->
+// global as 1-D bulk asynchronous copies through a three-slot ring, so two loads and one store
+// are in flight per SM while the current head is updated in place in shared memory.
+// Thread = (value column v, key half): the sums over keys stay inside a thread except for one
+// two-way combine, and shared-memory accesses to the state are conflict-free.
+constexpr int kDecThreads = 256;
+constexpr int kDecStages = 3;
+
+struct DecodeSmem {
+  alignas(128) float state[kDecStages][kDim * kDim];
+  alignas(16) float ae[2][kDim], a[2][kDim], kk[2][kDim], qs[2][kDim], z[2][kDim];
+  float red[2][2][kDim];   // [parity][key half][column]  erase partial sums
+  float redo[2][2][kDim];  //                             output partial sums
+  alignas(8) uint64_t full[kDecStages];
+};
+
+struct DecodeParams {
+  const void *q, *k, *v, *g, *beta, *w;
+  const float* s_in;
+  void* out;
+  float* s_out;
+  int64_t n_heads;  // batch * heads; T == 1 so sequence row index == head index
+  float scale;
+};
+
+template <typename T, typename G>
+__global__ void __launch_bounds__(kDecThreads, 1) token_decode_ring_kernel(const DecodeParams p) {
+  extern __shared__ __align__(128) unsigned char dec_smem_raw[];
+  DecodeSmem& sm = *reinterpret_cast<DecodeSmem*>(dec_smem_raw);
+  const int tid = threadIdx.x;
+  const int col = tid & (kDim - 1), kh = tid >> 7;
+  const int64_t first = blockIdx.x, stride = gridDim.x;
+  const int64_t n_mine = (p.n_heads > first) ? (p.n_heads - first + stride - 1) / stride : 0;
+  constexpr uint32_t kStateBytes = kDim * kDim * sizeof(float);
+
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < kDecStages; ++s) tc::mbar_init(&sm.full[s], 1);
+    tc::fence_mbar_init();
+  }
+  __syncthreads();
+
+  auto issue_load = [&](int64_t n) {  // thread 0 only
+    const int s = int(n % kDecStages);
+    tc::mbar_arrive_expect_tx(&sm.full[s], kStateBytes);
+    tc::bulk_g2s(sm.state[s], p.s_in + (first + n * stride) * int64_t(kDim) * kDim, kStateBytes, &sm.full[s]);
+  };
+  // per-head vectors: threads 0..127 own a key channel, threads 128..255 a value channel
+  float va = 0.f, vb = 0.f, vc = 0.f, vd = 0.f;
+  auto fetch_vectors = [&](int64_t n) {
+    const int64_t idx = (first + n * stride) * kDim + col;
+    if (kh == 0) {
+      va = ldf<G>(p.g, idx); vb = ldf<T>(p.beta, idx); vc = ldf<T>(p.k, idx); vd = ldf<T>(p.q, idx);
+    } else {
+      va = ldf<T>(p.w, idx); vb = ldf<T>(p.v, idx);
+    }
+  };
+  auto stage_vectors = [&](int buf) {
+    if (kh == 0) {
+      const float av = expf(va);
+      sm.a[buf][col] = av;
+      sm.ae[buf][col] = av * (vb * vc);
+      sm.kk[buf][col] = vc;
+      sm.qs[buf][col] = p.scale * vd;
+    } else {
+      sm.z[buf][col] = va * vb;
+    }
+  };
+
+  if (n_mine > 0) {
+    if (tid == 0) {
+      issue_load(0);
+      if (n_mine > 1) issue_load(1);
+    }
+    fetch_vectors(0);
+    stage_vectors(0);
+  }
+  __syncthreads();
+
+  bool dead = false;
+  for (int64_t n = 0; n < n_mine; ++n) {
+    const int s = int(n % kDecStages), buf = int(n & 1);
+    const int64_t bh = first + n * stride;
+    if (tid == 0 && n + 2 < n_mine) {
+      // slot of head n + 2 was last used by head n - 1: its store must have finished reading it
+      tc::bulk_wait_read_all();
+      issue_load(n + 2);
+    }
+    if (n + 1 < n_mine) fetch_vectors(n + 1);
+    if (!dead && !tc::mbar_wait(&sm.full[s], uint32_t((n / kDecStages) & 1), 1u << 20)) dead = true;
+
+    float* S = sm.state[s] + col;
+    const int k0 = 64 * kh;
+    // pass 1: r[v] = sum_k S[k][v] * (a[k] e[k])
+    float r = 0.f;
+#pragma unroll 4
+    for (int kq = 0; kq < 64; kq += 4) {
+      const float4 f = *reinterpret_cast<const float4*>(&sm.ae[buf][k0 + kq]);
+      r = fmaf(S[(k0 + kq) * kDim], f.x, r);
+      r = fmaf(S[(k0 + kq + 1) * kDim], f.y, r);
+      r = fmaf(S[(k0 + kq + 2) * kDim], f.z, r);
+      r = fmaf(S[(k0 + kq + 3) * kDim], f.w, r);
+    }
+    sm.red[buf][kh][col] = r;
+    __syncthreads();
+    const float u = sm.z[buf][col] - (sm.red[buf][0][col] + sm.red[buf][1][col]);
+    // pass 2: S <- a S + k u^T ; o[v] = sum_k S[k][v] (scale q[k])
+    float o = 0.f;
+#pragma unroll 4
+    for (int kq = 0; kq < 64; kq += 4) {
+      const float4 fa = *reinterpret_cast<const float4*>(&sm.a[buf][k0 + kq]);
+      const float4 fk = *reinterpret_cast<const float4*>(&sm.kk[buf][k0 + kq]);
+      const float4 fq = *reinterpret_cast<const float4*>(&sm.qs[buf][k0 + kq]);
+      float x0 = fmaf(fk.x, u, fa.x * S[(k0 + kq) * kDim]);
+      float x1 = fmaf(fk.y, u, fa.y * S[(k0 + kq + 1) * kDim]);
+      float x2 = fmaf(fk.z, u, fa.z * S[(k0 + kq + 2) * kDim]);
+      float x3 = fmaf(fk.w, u, fa.w * S[(k0 + kq + 3) * kDim]);
+      S[(k0 + kq) * kDim] = x0; S[(k0 + kq + 1) * kDim] = x1;
+      S[(k0 + kq + 2) * kDim] = x2; S[(k0 + kq + 3) * kDim] = x3;
+      o = fmaf(x0, fq.x, o); o = fmaf(x1, fq.y, o); o = fmaf(x2, fq.z, o); o = fmaf(x3, fq.w, o);
+    }
+    sm.redo[buf][kh][col] = o;
+    if (n + 1 < n_mine) stage_vectors(buf ^ 1);
+    tc::fence_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      tc::bulk_s2g(p.s_out + bh * int64_t(kDim) * kDim, sm.state[s], kStateBytes);
+      tc::bulk_commit();
+    }
+    if (kh == 0) {
+      float ov = sm.redo[buf][0][col] + sm.redo[buf][1][col];
+      if (dead) ov = __int_as_float(0x7fc00000);  // a bulk copy never arrived: make the failure visible
+      stf<T>(p.out, bh * kDim + col, ov);
+    }
+  }
+  if (tid == 0) tc::bulk_wait_all();
 }
 
 // ---------------------------------------------------------------------------------
@@ -513,6 +654,24 @@ int launch_token_forward(const void* q, const void* k, const void* v, const void
                          cudaStream_t stream) {
   const int64_t blocks = B * H * kTokTiles;
   if (!grid_fits(blocks)) return GDN2_ERR_TOO_LARGE;
+  // decode fast path: one token, state in and out, 16-byte aligned, enough heads to fill the GPU
+  if (T == 1 && t_begin == 0 && t_end == 1 && s_in != nullptr && s_out != nullptr && bnd == nullptr &&
+      B * H >= 256 && ((reinterpret_cast<uintptr_t>(s_in) | reinterpret_cast<uintptr_t>(s_out)) & 15) == 0) {
+    int dev = 0, sms = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err == cudaSuccess) err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
+    DecodeParams dp{q, k, v, g, beta, w, s_in, out, s_out, B * H, scale};
+    const int smem = int(sizeof(DecodeSmem));
+    const unsigned grid = unsigned(B * H < sms ? B * H : sms);
+    GDN2_DISPATCH_TYPES(dtype, g_dtype, {
+      auto kernel = token_decode_ring_kernel<T, G>;
+      err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
+      kernel<<<grid, kDecThreads, smem, stream>>>(dp);
+    });
+    return check_launch();
+  }
   TokenFwdParams p{q, k, v, g, beta, w, s_in, out, s_out, bnd,
                    T, H, t_begin, t_end, slots_for(t_begin, t_end), scale};
   GDN2_DISPATCH_TYPES(dtype, g_dtype,

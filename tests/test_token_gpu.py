@@ -253,3 +253,21 @@ def test_raw_c_abi_call_with_token_sub_range():
     assert torch.all(out[:, :3] == 7.0) and torch.all(out[:, 9:] == 7.0)
     torch.testing.assert_close(fin.cpu().double(), ref_state, rtol=1e-5, atol=1e-5)
     assert torch.equal(bnd[:, 0], s0) and torch.equal(bnd[:, 1], fin)
+
+
+@pytest.mark.parametrize("dtype,low_g", [(torch.bfloat16, False), (torch.float16, True)])
+def test_decode_ring_kernel_out_of_place_and_odd_head_count(dtype, low_g):
+    """B*H >= 256 with aligned states takes the persistent bulk-copy decode kernel; 323 heads do not
+    divide evenly over the SMs, and the separate output state must leave the input state untouched."""
+
+    g_dtype = dtype if low_g else torch.float32
+    cpu = oracle.make_inputs(17, 1, 19, seed=4242, dtype=dtype, g_dtype=g_dtype)
+    ref_out, ref_state = oracle.recurrence(*cpu, scale=0.11)
+    q, k, v, g, beta, w, s0 = dev(*cpu)
+    before = s0.clone()
+    fin_buf = torch.empty_like(s0)
+    out, fin = recurrent_gdn2(q, k, v, g, beta, w, s0, scale=0.11, final_state_out=fin_buf)
+    assert fin is fin_buf and torch.equal(s0, before)
+    check_forward(out, fin, ref_out, ref_state, dtype)
+    out2, fin2 = recurrent_gdn2(q, k, v, g, beta, w, s0, scale=0.11)
+    assert torch.equal(out, out2) and torch.equal(fin, fin2)
