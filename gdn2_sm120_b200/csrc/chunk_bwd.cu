@@ -265,35 +265,49 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
 // =============================================================================================
 // chunk VJP
 // =============================================================================================
-constexpr int kVjpThreads = 256;
+// 512 threads.  Elementwise phases: warp = 4-token group tg, lane = 4-channel group c4 (as in the
+// forward prep kernel).  TMEM phases: warp & 3 = lane quadrant, warp >> 2 = share of the columns.
+// Final chain: thread = (key channel, 16-token block).
+constexpr int kVjpThreads = 512;
+constexpr int kCsN = 144;              // natural 128-column tiles: padded chunk stride
+constexpr int kRsN = 32 * kCsN;        // 4608
+constexpr int kRsT = 2064;             // transposed 64-column tiles: padded row-group stride
+constexpr int kCsS = 144;              // 64-column tiles written by scattered 4-byte stores
+constexpr int kRsS = 16 * kCsS;        // 2304
 
 // dynamic shared memory map (bytes).  Phase B = products with the states, phase C = Gram VJP.
-constexpr int kOffStack = 0;            // B: [dZ ; dO]  X[r = 128][c = v], RS 4096, 64 KiB
-constexpr int kOffRn = 65536;           // B: R          X[r = j][c = v],   RS 4096, 32 KiB
-constexpr int kOffS0 = 98304;           // B: S_0        X[r = k][c = v],   RS 4096, 64 KiB
-constexpr int kOffDrt = 98304;          //    (before S_0 arrives) dR^T X[r = v][c = i], 32 KiB
-constexpr int kOffTt = 131072;          //    (before S_0 arrives) T^T  X[r = j][c = i], 16 KiB
-constexpr int kOffDs1 = 163840;         // B: dS_1 half  X[r = k][c = 64 v], RS 2048, 32 KiB
-constexpr int kOffStack2 = 0;           // C: [dL ; dA]  X[r = 128][c = j], RS 2048, 32 KiB
-constexpr int kOffDLt = 32768;          // C: dL^T       X[r = j][c = i],   16 KiB
-constexpr int kOffDAt = 49152;          // C: dA^T       X[r = j][c = i],   16 KiB
-constexpr int kOffKIt = 65536;          // C: (K^I)^T    X[r = k][c = j < 16(I+1)], 8/16/24/32 KiB
-constexpr int kOffEat = 147456;         // C: E_a^T      X[r = k][c = i],   32 KiB
-constexpr int kOffQat = 180224;         // C: Q_a^T      X[r = k][c = i],   32 KiB
-constexpr int kOffMisc = 212992;
+constexpr int kOffStack = 0;                      // B: [dZ ; dO] X[r = 128][c = v], RS kRsN     73728
+constexpr int kOffRn = kOffStack + 16 * kRsN;     // B: R X[r = j][c = v], RS 4096 (bulk copy)   32768
+constexpr int kOffS0 = kOffRn + 32768;            // B: S_0 X[r = k][c = v], RS 4096             65536
+constexpr int kOffDrt = kOffS0;                   //    (before S_0 arrives) dR^T X[r = v][c = i] 32768
+constexpr int kOffTt = kOffS0 + 32768;            //    (before S_0 arrives) T^T  X[r = j][c = i] 16384
+constexpr int kOffDs1 = kOffS0 + 65536;           // B: dS_1 half X[r = k][c = 64 v], RS 2048    32768
+constexpr int kEndB = kOffDs1 + 32768;            // 204800
+constexpr int kOffStack2 = 0;                     // C: [dL ; dA] X[r = 128][c = j], RS 2048     32768
+constexpr int kOffDLt = 32768;                    // C: dL^T X[r = j][c = i], RS kRsS            18432
+constexpr int kOffDAt = kOffDLt + 8 * kRsS;       // C: dA^T                                     18432
+constexpr int kOffKIt = kOffDAt + 8 * kRsS;       // C: (K^I)^T X[r = k][c = j < 16 (I+1)], RS 512 (I+1) + 16
+constexpr int kKItBytes = 16 * (528 + 1040 + 1552 + 2064);  // 82944
+constexpr int kOffEat = kOffKIt + kKItBytes;      // C: E_a^T X[r = k][c = i], RS kRsT           33024
+constexpr int kOffQat = kOffEat + 16 * kRsT;      // C: Q_a^T                                    33024
+constexpr int kEndC = kOffQat + 16 * kRsT;        // 218624
+constexpr int kOffMisc = (kEndB > kEndC ? kEndB : kEndC);
 struct VjpMisc {
   float part[16][kDim];   // exclusive prefixes of the log-decay per 4-token group
   float gend[kDim];
   float dd[kDim];         // sum_v dS_1 * S_0
-  float xe[2][kDim];      // per-half sum_j Kt_j dKt_j
-  float xt[2][kDim];      // per-half sum of dG
+  float xe[4][kDim];      // per-block sum_j Kt_j dKt_j
+  float xt[4][kDim];      // per-block sum of dG
   alignas(8) uint64_t bar_a, bar_r, bar_m;
   uint32_t tmem_base;
 };
 constexpr int kVjpSmemBytes = kOffMisc + int(sizeof(VjpMisc));
 static_assert(kVjpSmemBytes <= 232448, "VJP kernel exceeds the 227 KiB shared-memory limit");
 
-__device__ __forceinline__ int kit_offset(int I) { return kOffKIt + ((I == 0) ? 0 : (I == 1) ? 8192 : (I == 2) ? 24576 : 49152); }
+__device__ __forceinline__ int kit_rs(int I) { return 512 * (I + 1) + 16; }
+__device__ __forceinline__ int kit_offset(int I) {
+  return kOffKIt + 16 * ((I == 0) ? 0 : (I == 1) ? 528 : (I == 2) ? (528 + 1040) : (528 + 1040 + 1552));
+}
 __device__ __forceinline__ uint32_t d6_col(int I) { return (I == 3) ? 0u : (I == 2) ? 64u : (I == 1) ? 448u : 480u; }
 
 struct VjpParams {
@@ -307,6 +321,35 @@ struct VjpParams {
   float scale;
 };
 
+template <typename T>
+__device__ __forceinline__ void load4v(const void* base, int64_t idx, float (&out)[4]);
+template <>
+__device__ __forceinline__ void load4v<__nv_bfloat16>(const void* base, int64_t idx, float (&out)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(base) + idx);
+  out[0] = __uint_as_float(raw.x << 16); out[1] = __uint_as_float(raw.x & 0xffff0000u);
+  out[2] = __uint_as_float(raw.y << 16); out[3] = __uint_as_float(raw.y & 0xffff0000u);
+}
+template <>
+__device__ __forceinline__ void load4v<__half>(const void* base, int64_t idx, float (&out)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __half*>(base) + idx);
+  const __half2* h = reinterpret_cast<const __half2*>(&raw);
+  const float2 a = __half22float2(h[0]), b = __half22float2(h[1]);
+  out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
+}
+template <>
+__device__ __forceinline__ void load4v<float>(const void* base, int64_t idx, float (&out)[4]) {
+  const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(base) + idx);
+  out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+}
+
+__device__ __forceinline__ void tmem_ld8f(uint32_t taddr, float (&x)[8]) {
+  uint32_t r[8];
+  tmem_ld8(taddr, r);
+  tmem_wait_ld();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) x[i] = __uint_as_float(r[i]);
+}
+
 template <typename T, typename G>
 __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const VjpParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
@@ -315,7 +358,8 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
   BoundedWaiter waiter(p.status);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int q4 = warp & 3, half = warp >> 2;
+  const int q4 = warp & 3, part = warp >> 2;
+  const int tg = warp, c4 = lane, kc0 = 4 * lane;
   const int64_t ch = blockIdx.x;
   const int64_t h = ch % p.H;
   const int64_t c = (ch / p.H) % p.n_chunks;
@@ -333,6 +377,7 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
     mbar_init(&ms.bar_m, 1);
     fence_mbar_init();
   }
+  if (tid < kDim) ms.dd[tid] = 0.f;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -347,167 +392,74 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
     mbar_arrive_expect_tx(&ms.bar_r, uint32_t(kBlobRn));
     bulk_g2s(smem + kOffRn, p.ws + ws.off_rn() + ch * kBlobRn, uint32_t(kBlobRn), &ms.bar_r);
   }
-  const int tg = tid >> 4, c8 = tid & 15;
-  // dO rows of the stack (rows 64 + i)
+  const float* s0_src = p.bnd + ((b * (p.n_chunks + 1) + c) * p.H + h) * kStateElems;
+  const float* ds1_src = p.d_bnd + ((b * (p.n_chunks + 1) + c + 1) * p.H + h) * kStateElems;
+  auto rn4 = [](float4 x) { return make_float4(to_tf32(x.x), to_tf32(x.y), to_tf32(x.z), to_tf32(x.w)); };
+  // One half (64 value columns) of dS_1 into shared memory, rounded to nearest tf32, and on the way
+  // its contribution to dd[k] = sum_v dS_1[k][v] S_0[k][v] (S_0 re-read through L2).
+  // chunk id qd = tid + 512 x: key row = (qd & 7) + 8 (qd >> 7), 4-value chunk = ((qd >> 3) & 15)
+  auto load_ds1_half = [&](int hf) {
+    float4 buf[4], sbuf[4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const int qd = tid + 512 * x;
+      const int kr = (qd & 7) + 8 * (qd >> 7), v4 = (qd >> 3) & 15;
+      buf[x] = *reinterpret_cast<const float4*>(ds1_src + kr * kDim + 64 * hf + 4 * v4);
+      sbuf[x] = *reinterpret_cast<const float4*>(s0_src + kr * kDim + 64 * hf + 4 * v4);
+    }
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const int qd = tid + 512 * x;
+      const int v4 = (qd >> 3) & 15;
+      *reinterpret_cast<float4*>(smem + kOffDs1 + (qd >> 7) * 2048 + v4 * 128 + (qd & 7) * 16) = rn4(buf[x]);
+      float acc = buf[x].x * sbuf[x].x + buf[x].y * sbuf[x].y + buf[x].z * sbuf[x].z + buf[x].w * sbuf[x].w;
+      // lanes that differ in bits 3, 4 hold other value chunks of the same key row
+      acc += __shfl_xor_sync(0xffffffffu, acc, 8);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+      if ((lane >> 3) == 0) atomicAdd(&ms.dd[(qd & 7) + 8 * (qd >> 7)], acc);
+    }
+  };
+  load_ds1_half(0);
+
+  // dO rows of the stack (rows 64 + i), natural tile with padded chunk stride
+  float Gc[4][4];
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
     const int i = 4 * tg + e;
-    float dv8[8];
-    load8<T>(p.d_out, seq_idx(i) + 8 * c8, dv8);
-    float4* dst = reinterpret_cast<float4*>(smem + kOffStack + blk_off<4>(64 + i, 8 * c8, 4096, 128));
-    dst[0] = make_float4(dv8[0], dv8[1], dv8[2], dv8[3]);
-    dst[8] = make_float4(dv8[4], dv8[5], dv8[6], dv8[7]);
+    float dv4[4], gv[4];
+    load4v<T>(p.d_out, seq_idx(i) + kc0, dv4);
+    load4v<G>(p.g, seq_idx(i) + kc0, gv);
+    *reinterpret_cast<float4*>(smem + kOffStack + ((64 + i) >> 3) * kRsN + c4 * kCsN + (i & 7) * 16) =
+        make_float4(dv4[0], dv4[1], dv4[2], dv4[3]);
+#pragma unroll
+    for (int f = 0; f < 4; ++f) Gc[e][f] = (e ? Gc[e - 1][f] : 0.f) + gv[f];
   }
+#pragma unroll
+  for (int f = 0; f < 4; ++f) ms.part[tg][kc0 + f] = Gc[3][f];
   waiter.wait(&ms.bar_a, 0);
+  waiter.wait(&ms.bar_r, 0);
+  fence_async_smem();
   tc_fence_before();
   __syncthreads();
-  // ---- M1: dZ^T = dR^T T  (A: dR^T [v x i]; B: T^T tile X[r = j][c = i]) ---------------------------
+  // ---- M1: dZ^T = dR^T T ; M4 (first half): dKt^T = dS_1[:, v < 64] R[:, v < 64]^T -------------------
   if (tid == 0) {
     tc_fence_after();
     const uint32_t a0 = smem_u32(smem + kOffDrt), b0 = smem_u32(smem + kOffTt);
+    const uint32_t rn = smem_u32(smem + kOffRn), d1 = smem_u32(smem + kOffDs1);
     const uint32_t id = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
       mma_tf32_ss(tb + kColDz, smem_desc(a0 + ks * 256, 128, 2048), smem_desc(b0 + ks * 256, 128, 2048), id,
                   ks > 0 ? 1u : 0u);
     }
-    mma_commit(&ms.bar_m);
-  }
-  waiter.wait(&ms.bar_m, mma_phase & 1u);
-  ++mma_phase;
-  tc_fence_after();
-
-  // ---- bring in S_0 (whole) and the first half of dS_1 -------------------------------------------------
-  const float* s0_src = p.bnd + ((b * (p.n_chunks + 1) + c) * p.H + h) * kStateElems;
-  const float* ds1_src = p.d_bnd + ((b * (p.n_chunks + 1) + c + 1) * p.H + h) * kStateElems;
-  // (rounded to nearest tf32 on the way: the MMA would otherwise truncate, which biases the products)
-  auto rn4 = [](float4 x) { return make_float4(to_tf32(x.x), to_tf32(x.y), to_tf32(x.z), to_tf32(x.w)); };
-  {
-    float4 buf[16];
 #pragma unroll
-    for (int x = 0; x < 16; ++x) {
-      const int kr = (tid & 7) + 8 * x, v4 = ((tid >> 3) & 3) + 4 * ((tid >> 5) & 7);
-      buf[x] = *reinterpret_cast<const float4*>(s0_src + kr * kDim + 4 * v4);
-    }
-#pragma unroll
-    for (int x = 0; x < 16; ++x) {
-      const int v4 = ((tid >> 3) & 3) + 4 * ((tid >> 5) & 7);
-      *reinterpret_cast<float4*>(smem + kOffS0 + x * 4096 + v4 * 128 + (tid & 7) * 16) = rn4(buf[x]);
-    }
-  }
-  auto load_ds1_half = [&](int hf) {
-    float4 buf[8];
-#pragma unroll
-    for (int x = 0; x < 8; ++x) {
-      const int qd = tid + 256 * x;
-      const int kr = (qd & 7) + 8 * (qd >> 7), v4 = ((qd >> 3) & 3) + 4 * ((qd >> 5) & 3);
-      buf[x] = *reinterpret_cast<const float4*>(ds1_src + kr * kDim + 64 * hf + 4 * v4);
-    }
-#pragma unroll
-    for (int x = 0; x < 8; ++x) {
-      const int qd = tid + 256 * x;
-      const int v4 = ((qd >> 3) & 3) + 4 * ((qd >> 5) & 3);
-      *reinterpret_cast<float4*>(smem + kOffDs1 + (qd >> 7) * 2048 + v4 * 128 + (qd & 7) * 16) = rn4(buf[x]);
-    }
-  };
-  load_ds1_half(0);
-
-  // ---- dZ: into the stack (rows j), and dv = dZ w, dw = dZ v --------------------------------------------
-  {
-    const int vrow = 32 * q4 + lane;
-    uint32_t r[32];
-    tmem_ld32(tmem_addr(tb, 32 * q4, kColDz + 32 * half), r);
-    tmem_wait_ld();
-#pragma unroll
-    for (int jj = 0; jj < 32; ++jj) {
-      const int j = 32 * half + jj;
-      const float dz = __uint_as_float(r[jj]);
-      *reinterpret_cast<float*>(smem + kOffStack + blk_off<4>(j, vrow, 4096, 128)) = to_tf32(dz);
-      const int64_t idx = seq_idx(j) + vrow;
-      const float wv = ldf<T>(p.w, idx), vv = ldf<T>(p.v, idx);
-      stf<T>(p.dv, idx, dz * wv);
-      stf<T>(p.dw, idx, dz * vv);
-    }
-  }
-  waiter.wait(&ms.bar_r, 0);
-  fence_async_smem();
-  tc_fence_before();
-  __syncthreads();
-  // ---- M2 / M3 / M4 (first half) -------------------------------------------------------------------------
-  if (tid == 0) {
-    tc_fence_after();
-    const uint32_t st = smem_u32(smem + kOffStack), rn = smem_u32(smem + kOffRn);
-    const uint32_t s0 = smem_u32(smem + kOffS0), d1 = smem_u32(smem + kOffDs1);
-    const uint32_t id64 = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
-    const uint32_t id128 = idesc(128, 128, kFmtTF32, kMajorK, kMajorK);
-#pragma unroll
-    for (int ks = 0; ks < 16; ++ks) {  // [dZ;dO] R^T
-      mma_tf32_ss(tb + kColD2, smem_desc(st + ks * 256, 128, 4096), smem_desc(rn + ks * 256, 128, 4096), id64,
-                  ks > 0 ? 1u : 0u);
-    }
-#pragma unroll
-    for (int ks = 0; ks < 16; ++ks) {  // S_0 [dZ;dO]^T
-      mma_tf32_ss(tb + kColD3, smem_desc(s0 + ks * 256, 128, 4096), smem_desc(st + ks * 256, 128, 4096), id128,
-                  ks > 0 ? 1u : 0u);
-    }
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {  // dS_1[:, v < 64] R[:, v < 64]^T
-      mma_tf32_ss(tb + kColD4, smem_desc(d1 + ks * 256, 128, 2048), smem_desc(rn + ks * 256, 128, 4096), id64,
+    for (int ks = 0; ks < 8; ++ks) {
+      mma_tf32_ss(tb + kColD4, smem_desc(d1 + ks * 256, 128, 2048), smem_desc(rn + ks * 256, 128, 4096), id,
                   ks > 0 ? 1u : 0u);
     }
     mma_commit(&ms.bar_m);
   }
-  // dd partial (thread = key row) over the value half that is resident
-  auto dd_partial = [&](int hf) {
-    float acc = 0.f;
-    const uint8_t* a = smem + kOffDs1 + (tid >> 3) * 2048 + (tid & 7) * 16;
-    const uint8_t* s = smem + kOffS0 + (tid >> 3) * 4096 + (tid & 7) * 16 + hf * 16 * 128;
-#pragma unroll
-    for (int c4 = 0; c4 < 16; ++c4) {
-      const float4 x = *reinterpret_cast<const float4*>(a + c4 * 128);
-      const float4 y = *reinterpret_cast<const float4*>(s + c4 * 128);
-      acc = fmaf(x.x, y.x, acc); acc = fmaf(x.y, y.y, acc); acc = fmaf(x.z, y.z, acc); acc = fmaf(x.w, y.w, acc);
-    }
-    return acc;
-  };
-  float dd_acc = 0.f;
-  if (tid < kDim) dd_acc = dd_partial(0);
-  waiter.wait(&ms.bar_m, mma_phase & 1u);
-  ++mma_phase;
-  tc_fence_after();
-  __syncthreads();  // every dd reader is done with the first half before it is overwritten
-  load_ds1_half(1);
-  fence_async_smem();
-  tc_fence_before();
-  __syncthreads();
-  if (tid == 0) {
-    tc_fence_after();
-    const uint32_t rn = smem_u32(smem + kOffRn), d1 = smem_u32(smem + kOffDs1);
-    const uint32_t id64 = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {  // dS_1[:, v >= 64] R[:, v >= 64]^T
-      mma_tf32_ss(tb + kColD4, smem_desc(d1 + ks * 256, 128, 2048), smem_desc(rn + (8 + ks) * 256, 128, 4096), id64, 1u);
-    }
-    mma_commit(&ms.bar_m);
-  }
-  if (tid < kDim) ms.dd[tid] = dd_acc + dd_partial(1);
-  waiter.wait(&ms.bar_m, mma_phase & 1u);
-  ++mma_phase;
-  tc_fence_after();
-
-  // ================================ phase C: Gram VJP =============================================
-  // log-decay prefixes, same scheme as the forward prep kernel: thread = (4 tokens, 8 channels)
-  float Gc[4][8];
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    float gv[8];
-    load8<G>(p.g, seq_idx(4 * tg + e) + 8 * c8, gv);
-#pragma unroll
-    for (int f = 0; f < 8; ++f) Gc[e][f] = (e ? Gc[e - 1][f] : 0.f) + gv[f];
-  }
-#pragma unroll
-  for (int f = 0; f < 8; ++f) ms.part[tg][8 * c8 + f] = Gc[3][f];
-  __syncthreads();  // also: every thread is past the last phase-B wait, dd readers are done
+  // log-decay prefixes while the tensor cores work
   if (tid < kDim) {
     float run = 0.f;
 #pragma unroll
@@ -518,67 +470,137 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
     }
     ms.gend[tid] = run;
   }
-  __syncthreads();
+  waiter.wait(&ms.bar_m, mma_phase & 1u);
+  ++mma_phase;
+  tc_fence_after();
 
-  // [-dL_raw ; dA_raw] out of TMEM: masked tiles [dL ; dA] (rows) and their transposes
-  if (warp < 4) {
-    const int r = 32 * warp + lane, i = r & 63;
-    uint8_t* tr_base = smem + ((r < 64) ? kOffDLt : kOffDAt);
+  // ---- S_0 (whole) over the dR^T / T^T operands of M1, second half of dS_1 over the first -----------
+  {
+    float4 buf[8];
 #pragma unroll
-    for (int c0 = 0; c0 < 64; c0 += 16) {
-      uint32_t raw[16];
-      tmem_ld16(tmem_addr(tb, 32 * warp, kColD2 + c0), raw);
-      tmem_wait_ld();
-      float vals[16];
+    for (int x = 0; x < 8; ++x) {
+      const int qd = tid + 512 * x;  // key row = (qd & 7) + 8 (qd >> 8), 4-value chunk = (qd >> 3) & 31
+      buf[x] = *reinterpret_cast<const float4*>(s0_src + ((qd & 7) + 8 * (qd >> 8)) * kDim + 4 * ((qd >> 3) & 31));
+    }
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const int col = c0 + j;
-        const float x = __uint_as_float(raw[j]);
-        vals[j] = to_tf32((r < 64) ? ((col < i) ? -x : 0.f) : ((col <= i) ? x : 0.f));
-        *reinterpret_cast<float*>(tr_base + blk_off<4>(col, i, 2048, 128)) = vals[j];
-      }
-#pragma unroll
-      for (int j4 = 0; j4 < 4; ++j4) {
-        *reinterpret_cast<float4*>(smem + kOffStack2 + blk_off<4>(r, c0 + 4 * j4, 2048, 128)) =
-            make_float4(vals[4 * j4], vals[4 * j4 + 1], vals[4 * j4 + 2], vals[4 * j4 + 3]);
-      }
+    for (int x = 0; x < 8; ++x) {
+      const int qd = tid + 512 * x;
+      *reinterpret_cast<float4*>(smem + kOffS0 + (qd >> 8) * 4096 + ((qd >> 3) & 31) * 128 + (qd & 7) * 16) = rn4(buf[x]);
     }
   }
-  // anchored Gram operands, transposed tiles X[r = channel][c = token]
+  load_ds1_half(1);
+  // ---- dZ: into the stack (rows j), and dv = dZ w, dw = dZ v; each warp of a quadrant takes 16 tokens --
   {
-    const int my_block = tg >> 2;
-    float kk[4][8], eat[4][8], qat[4][8];
+    const int vrow = 32 * q4 + lane;
+    uint32_t r[16];
+    tmem_ld16(tmem_addr(tb, 32 * q4, kColDz + 16 * part), r);
+    tmem_wait_ld();
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj) {
+      const int j = 16 * part + jj;
+      const float dz = __uint_as_float(r[jj]);
+      *reinterpret_cast<float*>(smem + kOffStack + (j >> 3) * kRsN + (vrow >> 2) * kCsN + (j & 7) * 16 + (vrow & 3) * 4) =
+          to_tf32(dz);
+      const int64_t idx = seq_idx(j) + vrow;
+      const float wv = ldf<T>(p.w, idx), vv = ldf<T>(p.v, idx);
+      stf<T>(p.dv, idx, dz * wv);
+      stf<T>(p.dw, idx, dz * vv);
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  // ---- M2: [dZ;dO] R^T ; M3: S_0 [dZ;dO]^T ; M4 (second half) -------------------------------------------
+  if (tid == 0) {
+    tc_fence_after();
+    const uint32_t st = smem_u32(smem + kOffStack), rn = smem_u32(smem + kOffRn);
+    const uint32_t s0 = smem_u32(smem + kOffS0), d1 = smem_u32(smem + kOffDs1);
+    const uint32_t id64 = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
+    const uint32_t id128 = idesc(128, 128, kFmtTF32, kMajorK, kMajorK);
+#pragma unroll
+    for (int ks = 0; ks < 16; ++ks) {
+      mma_tf32_ss(tb + kColD2, smem_desc(st + ks * 2 * kCsN, kCsN, kRsN), smem_desc(rn + ks * 256, 128, 4096), id64,
+                  ks > 0 ? 1u : 0u);
+    }
+#pragma unroll
+    for (int ks = 0; ks < 16; ++ks) {
+      mma_tf32_ss(tb + kColD3, smem_desc(s0 + ks * 256, 128, 4096), smem_desc(st + ks * 2 * kCsN, kCsN, kRsN), id128,
+                  ks > 0 ? 1u : 0u);
+    }
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      mma_tf32_ss(tb + kColD4, smem_desc(d1 + ks * 256, 128, 2048), smem_desc(rn + (8 + ks) * 256, 128, 4096), id64, 1u);
+    }
+    mma_commit(&ms.bar_m);
+  }
+  // meanwhile: raw inputs of the Gram operands (loads in flight while the tensor cores work)
+  const int mb = tg >> 2;
+  float kk[4][4], qq[4][4], bb[4][4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int64_t idx = seq_idx(4 * tg + e) + kc0;
+    load4v<T>(p.k, idx, kk[e]);
+    load4v<T>(p.q, idx, qq[e]);
+    load4v<T>(p.beta, idx, bb[e]);
+  }
+  waiter.wait(&ms.bar_m, mma_phase & 1u);
+  ++mma_phase;
+  tc_fence_after();
+
+  // ================================ phase C: Gram VJP =============================================
+  // [-dL_raw ; dA_raw] out of TMEM: masked tiles [dL ; dA] (rows) and their transposes; the four
+  // warps of a quadrant take 16 columns each.  (Every thread is past the phase-B wait and the last
+  // shared-memory reads of phase B were MMA reads, so the phase-B regions may be overwritten.)
+  {
+    const int r = 32 * q4 + lane, i = r & 63;
+    uint8_t* tr_base = smem + ((r < 64) ? kOffDLt : kOffDAt);
+    const int c0 = 16 * part;
+    uint32_t raw[16];
+    tmem_ld16(tmem_addr(tb, 32 * q4, kColD2 + c0), raw);
+    tmem_wait_ld();
+    float vals[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int col = c0 + j;
+      const float x = __uint_as_float(raw[j]);
+      vals[j] = to_tf32((r < 64) ? ((col < i) ? -x : 0.f) : ((col <= i) ? x : 0.f));
+      *reinterpret_cast<float*>(tr_base + (col >> 3) * kRsS + (i >> 2) * kCsS + (col & 7) * 16 + (i & 3) * 4) = vals[j];
+    }
+#pragma unroll
+    for (int j4 = 0; j4 < 4; ++j4) {
+      *reinterpret_cast<float4*>(smem + kOffStack2 + blk_off<4>(r, c0 + 4 * j4, 2048, 128)) =
+          make_float4(vals[4 * j4], vals[4 * j4 + 1], vals[4 * j4 + 2], vals[4 * j4 + 3]);
+    }
+  }
+  // anchored Gram operands, transposed tiles X[r = channel][c = token] with padded row-group stride
+  {
+    float eat[4][4], qat[4][4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const int64_t idx = seq_idx(4 * tg + e) + 8 * c8;
-      float qq[8], bb[8];
-      load8<T>(p.k, idx, kk[e]);
-      load8<T>(p.q, idx, qq);
-      load8<T>(p.beta, idx, bb);
 #pragma unroll
-      for (int f = 0; f < 8; ++f) {
-        const int kc = 8 * c8 + f;
+      for (int f = 0; f < 4; ++f) {
+        const int kc = kc0 + f;
         const float Gi = Gc[e][f] + ms.part[tg][kc];
         Gc[e][f] = Gi;
-        const float anchored = __expf(Gi - ms.part[4 * my_block][kc]);
-        eat[e][f] = to_tf32(bb[f] * kk[e][f] * anchored);
-        qat[e][f] = to_tf32(p.scale * qq[f] * anchored);
+        const float anchored = __expf(Gi - ms.part[4 * mb][kc]);
+        eat[e][f] = to_tf32(bb[e][f] * kk[e][f] * anchored);
+        qat[e][f] = to_tf32(p.scale * qq[e][f] * anchored);
       }
     }
 #pragma unroll
-    for (int f = 0; f < 8; ++f) {
-      const uint32_t off = blk_off<4>(8 * c8 + f, 4 * tg, 2048, 128);
+    for (int f = 0; f < 4; ++f) {
+      const uint32_t off = blk_off<4>(kc0 + f, 4 * tg, kRsT, 128);
       *reinterpret_cast<float4*>(smem + kOffEat + off) = make_float4(eat[0][f], eat[1][f], eat[2][f], eat[3][f]);
       *reinterpret_cast<float4*>(smem + kOffQat + off) = make_float4(qat[0][f], qat[1][f], qat[2][f], qat[3][f]);
     }
 #pragma unroll
     for (int I = 0; I < 4; ++I) {
-      if (I >= my_block) {
+      if (I >= mb) {
 #pragma unroll
-        for (int f = 0; f < 8; ++f) {
-          const int kc = 8 * c8 + f;
+        for (int f = 0; f < 4; ++f) {
+          const int kc = kc0 + f;
           const float aI = ms.part[4 * I][kc];
-          *reinterpret_cast<float4*>(smem + kit_offset(I) + blk_off<4>(kc, 4 * tg, 512 * (I + 1), 128)) =
+          *reinterpret_cast<float4*>(smem + kit_offset(I) + blk_off<4>(kc, 4 * tg, kit_rs(I), 128)) =
               make_float4(to_tf32(kk[0][f] * __expf(aI - Gc[0][f])), to_tf32(kk[1][f] * __expf(aI - Gc[1][f])),
                           to_tf32(kk[2][f] * __expf(aI - Gc[2][f])), to_tf32(kk[3][f] * __expf(aI - Gc[3][f])));
         }
@@ -598,12 +620,12 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
 #pragma unroll
     for (int I = 0; I < 4; ++I) {
       const uint32_t kit = smem_u32(smem + kit_offset(I));
-      const uint32_t rs = 512u * (I + 1);
+      const uint32_t rs = uint32_t(kit_rs(I));
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
+      for (int pt = 0; pt < 2; ++pt) {
         for (int ks = 0; ks < 2 * (I + 1); ++ks) {
-          mma_tf32_ss(tb + kColD5 + part * 64 + 16 * I, smem_desc(kit + ks * 256, 128, rs),
-                      smem_desc(s2 + (part * 8 + 2 * I) * 2048 + ks * 256, 128, 2048), id16, ks > 0 ? 1u : 0u);
+          mma_tf32_ss(tb + kColD5 + pt * 64 + 16 * I, smem_desc(kit + ks * 256, 128, rs),
+                      smem_desc(s2 + (pt * 8 + 2 * I) * 2048 + ks * 256, 128, 2048), id16, ks > 0 ? 1u : 0u);
         }
       }
     }
@@ -612,13 +634,13 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
     for (int I = 0; I < 4; ++I) {
       const uint32_t idn = idesc(128, 16 * (I + 1), kFmtTF32, kMajorK, kMajorK);
 #pragma unroll
-      for (int part = 0; part < 2; ++part) {
-        const uint32_t a_base = (part ? qat0 : eat0) + 4 * I * 128;
-        const uint32_t b_base = (part ? dat : dlt) + 4 * I * 128;
+      for (int pt = 0; pt < 2; ++pt) {
+        const uint32_t a_base = (pt ? qat0 : eat0) + 4 * I * 128;
+        const uint32_t b_base = (pt ? dat : dlt) + 4 * I * kCsS;
 #pragma unroll
         for (int ks = 0; ks < 2; ++ks) {
-          mma_tf32_ss(tb + d6_col(I), smem_desc(a_base + ks * 256, 128, 2048), smem_desc(b_base + ks * 256, 128, 2048),
-                      idn, (part | ks) ? 1u : 0u);
+          mma_tf32_ss(tb + d6_col(I), smem_desc(a_base + ks * 256, 128, kRsT),
+                      smem_desc(b_base + ks * 2 * kCsS, kCsS, kRsS), idn, (pt | ks) ? 1u : 0u);
         }
       }
     }
@@ -629,102 +651,96 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
   tc_fence_after();
 
   // ================================ per-channel chain ==============================================
-  // One thread = one key channel over 32 tokens.  The log-decay G and the anchored operands are
-  // re-evaluated with exactly the expressions (and summation order) used when the MMA tiles were
+  // One thread = one key channel over one 16-token block.  The log-decay G and the anchored operands
+  // are re-evaluated with exactly the expressions (and summation order) used when the MMA tiles were
   // built, so that dG multiplies each Gram cotangent by the very tf32 value the tensor cores saw:
   // the row and column contributions of the Gram products to dG then cancel as they do exactly.
   {
-    const int kc = tid & 127;
+    const int kc = tid & 127, blk = part;
     const float gend = ms.gend[kc];
-    float dGv[32];
+    const float a_me = ms.part[4 * blk][kc];
+    float dGv[16];
     float e_part = 0.f, tot = 0.f;
 #pragma unroll
-    for (int bb = 0; bb < 2; ++bb) {
-      const int Ib = 2 * half + bb, i0 = 16 * Ib;
-      const float a_me = ms.part[4 * Ib][kc];
-      float Gb[16], qv[16], kv[16], bv[16], P3[16], dGa[16];
+    for (int sb = 0; sb < 2; ++sb) {
+      const int i0 = 16 * blk + 8 * sb;
+      float Gb[8], kv[8], bv[8], P3[8], P2[8], dG[8], x[8], y[8];
       float loc = 0.f;
 #pragma unroll
-      for (int t = 0; t < 16; ++t) {
+      for (int t = 0; t < 8; ++t) {
         const int64_t idx = seq_idx(i0 + t) + kc;
         loc = ((t & 3) ? loc : 0.f) + ldf<G>(p.g, idx);
         Gb[t] = loc + ms.part[(i0 + t) >> 2][kc];
-        qv[t] = ldf<T>(p.q, idx);
         kv[t] = ldf<T>(p.k, idx);
         bv[t] = ldf<T>(p.beta, idx);
       }
-      uint32_t r[16], r2[16];
-      tmem_ld16(tmem_addr(tb, 32 * q4, kColD4 + i0), r);
-      tmem_wait_ld();
+      tmem_ld8f(tmem_addr(tb, 32 * q4, kColD4 + i0), x);  // dKt
 #pragma unroll
-      for (int t = 0; t < 16; ++t) {
+      for (int t = 0; t < 8; ++t) {
         const float et = __expf(gend - Gb[t]);
-        const float dkt = __uint_as_float(r[t]);
         const float kt = kv[t] * et;
-        P3[t] = dkt * et;
-        e_part = fmaf(kt, dkt, e_part);
-        dGa[t] = -kt * dkt;
+        P3[t] = x[t] * et;
+        e_part = fmaf(kt, x[t], e_part);
+        dG[t] = -kt * x[t];
       }
 #pragma unroll
       for (int I = 0; I < 4; ++I) {
-        if (I >= Ib) {
+        if (I >= blk) {
           const float aI = ms.part[4 * I][kc];
-          tmem_ld16(tmem_addr(tb, 32 * q4, d6_col(I) + i0), r);
-          tmem_wait_ld();
+          tmem_ld8f(tmem_addr(tb, 32 * q4, d6_col(I) + i0), x);  // dK^I
 #pragma unroll
-          for (int t = 0; t < 16; ++t) {
+          for (int t = 0; t < 8; ++t) {
             const float ex = __expf(aI - Gb[t]);
-            const float dki = __uint_as_float(r[t]);
-            P3[t] = fmaf(dki, ex, P3[t]);
-            dGa[t] = fmaf(-to_tf32(kv[t] * ex), dki, dGa[t]);
+            P3[t] = fmaf(x[t], ex, P3[t]);
+            dG[t] = fmaf(-to_tf32(kv[t] * ex), x[t], dG[t]);
           }
         }
       }
-      float P2[16];
-      tmem_ld16(tmem_addr(tb, 32 * q4, kColD3 + i0), r);        // -dE (state part)
-      tmem_ld16(tmem_addr(tb, 32 * q4, kColD5 + i0), r2);       // dEa
-      tmem_wait_ld();
+      tmem_ld8f(tmem_addr(tb, 32 * q4, kColD3 + i0), x);  // -dE (state part)
+      tmem_ld8f(tmem_addr(tb, 32 * q4, kColD5 + i0), y);  // dEa
 #pragma unroll
-      for (int t = 0; t < 16; ++t) {
+      for (int t = 0; t < 8; ++t) {
         const float eg = __expf(Gb[t]), ea = __expf(Gb[t] - a_me);
-        const float de = -__uint_as_float(r[t]), dea = __uint_as_float(r2[t]);
+        const float de = -x[t], dea = y[t];
         P2[t] = fmaf(de, eg, dea * ea);
         const float bk = bv[t] * kv[t];
-        dGa[t] = fmaf(bk * eg, de, dGa[t]);
-        dGa[t] = fmaf(to_tf32(bk * ea), dea, dGa[t]);
+        dG[t] = fmaf(bk * eg, de, dG[t]);
+        dG[t] = fmaf(to_tf32(bk * ea), dea, dG[t]);
       }
-      tmem_ld16(tmem_addr(tb, 32 * q4, kColD3 + 64 + i0), r);   // dQg (state part)
-      tmem_ld16(tmem_addr(tb, 32 * q4, kColD5 + 64 + i0), r2);  // dQa
-      tmem_wait_ld();
+      tmem_ld8f(tmem_addr(tb, 32 * q4, kColD3 + 64 + i0), x);  // dQg (state part)
+      tmem_ld8f(tmem_addr(tb, 32 * q4, kColD5 + 64 + i0), y);  // dQa
 #pragma unroll
-      for (int t = 0; t < 16; ++t) {
-        const float eg = __expf(Gb[t]), ea = __expf(Gb[t] - a_me);
-        const float dqg = __uint_as_float(r[t]), dqa = __uint_as_float(r2[t]);
-        const float P1 = fmaf(dqg, eg, dqa * ea);
-        const float sq = p.scale * qv[t];
-        const float dG = fmaf(to_tf32(sq * ea), dqa, fmaf(sq * eg, dqg, dGa[t]));
+      for (int t = 0; t < 8; ++t) {
         const int64_t idx = seq_idx(i0 + t) + kc;
+        const float eg = __expf(Gb[t]), ea = __expf(Gb[t] - a_me);
+        const float P1 = fmaf(x[t], eg, y[t] * ea);
+        const float sq = p.scale * ldf<T>(p.q, idx);
+        const float dGt = fmaf(to_tf32(sq * ea), y[t], fmaf(sq * eg, x[t], dG[t]));
         stf<T>(p.dq, idx, p.scale * P1);
         stf<T>(p.dk, idx, fmaf(bv[t], P2[t], P3[t]));
         stf<T>(p.dbeta, idx, kv[t] * P2[t]);
-        dGv[16 * bb + t] = dG;
-        tot += dG;
+        dGv[8 * sb + t] = dGt;
+        tot += dGt;
       }
     }
-    ms.xe[half][kc] = e_part;
+    ms.xe[blk][kc] = e_part;
     __syncthreads();
-    if (half == 1) {
-      const float end_term = ms.xe[0][kc] + ms.xe[1][kc] + __expf(gend) * ms.dd[kc];
-      dGv[31] += end_term;
+    if (blk == 3) {
+      const float end_term = ms.xe[0][kc] + ms.xe[1][kc] + ms.xe[2][kc] + ms.xe[3][kc] + __expf(gend) * ms.dd[kc];
+      dGv[15] += end_term;
       tot += end_term;
     }
-    ms.xt[half][kc] = tot;
+    ms.xt[blk][kc] = tot;
     __syncthreads();
-    float run = (half == 0) ? ms.xt[1][kc] : 0.f;
+    float run = 0.f;
 #pragma unroll
-    for (int t = 31; t >= 0; --t) {
+    for (int bq = 3; bq > 0; --bq) {
+      if (bq > blk) run += ms.xt[bq][kc];
+    }
+#pragma unroll
+    for (int t = 15; t >= 0; --t) {
       run += dGv[t];
-      stf<G>(p.dg, seq_idx(32 * half + t) + kc, run);
+      stf<G>(p.dg, seq_idx(16 * blk + t) + kc, run);
     }
   }
   tc_fence_before();

@@ -33,17 +33,26 @@ namespace {
 // ---------------------------------------------------------------------------------------------
 // prep kernel
 // ---------------------------------------------------------------------------------------------
-constexpr int kPrepThreads = 256;
-constexpr int kLd = 65;  // leading dimension of the fp32 64x64 scratch matrices
+// 512 threads: warp = 4-token group tg (0..15), lane = 4-channel group c4 (0..31).  A thread owns
+// 4 tokens x 4 channels: one 16-byte chunk of every natural tile row (tokens x channels) and one
+// 16-byte chunk (4 tokens) per channel of every transposed tile (channels x tokens).
+// Shared-memory tiles written this way use padded strides so that the 8 lanes of a store phase hit
+// 8 different 16-byte bank groups: natural tiles CS = 144 (chunk stride), transposed tiles RS = 2064.
+constexpr int kPrepThreads = 512;
+constexpr int kLd = 65;           // leading dimension of the fp32 64x64 scratch matrices
+constexpr int kCsN = 144;         // natural tiles: byte stride between 16-byte column chunks
+constexpr int kRsN = 32 * kCsN;   // natural tiles of 128 fp32 columns: byte stride between 8-row groups (4608)
+constexpr int kRsT = 2064;        // transposed tiles (64 fp32 columns): byte stride between 8-row groups
+constexpr int kTileT = 16 * kRsT; // 33024 bytes
 
 struct PrepSmem {
-  // region 1: tf32 Gram A operand [E_anchored ; Q_anchored] X[r = 128][c = k], RS 4096;
-  //           after the Gram products: fp32 scratch for L, T, the block products and A_qk
-  alignas(128) uint8_t gram_a[65536];
-  // region 2: tf32 Gram B operands K^I X[r = j < 16 (I + 1)][c = k], RS 4096: 8 + 16 + 24 + 32 KiB;
-  //           after the Gram products: E^T at +0 and Z^T at +32 KiB, tiles X[r = channel][c = j], RS 2048
-  alignas(128) uint8_t gram_b[81920];
-  alignas(128) uint8_t tmat[32768];    // T    tile X[r = i][c = j], tf32 (rows 64..127 unused filler)
+  // region 1: tf32 Gram A operand [E_anchored ; Q_anchored] X[r = 128][c = k];
+  //           after the Gram products: fp32 scratch for L, T, A_qk and the block products
+  alignas(128) uint8_t gram_a[16 * kRsN];               // 73728
+  // region 2: tf32 Gram B operands K^I X[r = j < 16 (I + 1)][c = k]: 2 (I + 1) row groups each;
+  //           after the Gram products: E^T at +0 and Z^T at +kTileT, tiles X[r = channel][c = j]
+  alignas(128) uint8_t gram_b[20 * kRsN];               // 92160
+  alignas(128) uint8_t tmat[32768];    // T tile X[r = i][c = j], tf32, RS 2048 (rows 64..127 unused filler)
   float part[16][kDim];                // per 4-token group partial sums -> exclusive prefixes
   float gend[kDim];
   alignas(8) uint64_t bar[2];
@@ -58,8 +67,30 @@ struct PrepParams {
   int training;  // also write the transposed tiles that backward consumes
 };
 
-__device__ __forceinline__ int gram_b_offset(int I) { return (I == 0) ? 0 : (I == 1) ? 8192 : (I == 2) ? 24576 : 49152; }
+__device__ __forceinline__ int gram_b_offset(int I) { return kRsN * ((I == 0) ? 0 : (I == 1) ? 2 : (I == 2) ? 6 : 12); }
 __device__ __forceinline__ int gram_col(int I) { return (I == 0) ? 0 : (I == 1) ? 16 : (I == 2) ? 48 : 96; }
+
+// load 4 consecutive sequence elements
+template <typename T>
+__device__ __forceinline__ void load4s(const void* base, int64_t idx, float (&out)[4]);
+template <>
+__device__ __forceinline__ void load4s<__nv_bfloat16>(const void* base, int64_t idx, float (&out)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(base) + idx);
+  out[0] = __uint_as_float(raw.x << 16); out[1] = __uint_as_float(raw.x & 0xffff0000u);
+  out[2] = __uint_as_float(raw.y << 16); out[3] = __uint_as_float(raw.y & 0xffff0000u);
+}
+template <>
+__device__ __forceinline__ void load4s<__half>(const void* base, int64_t idx, float (&out)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __half*>(base) + idx);
+  const __half2* h = reinterpret_cast<const __half2*>(&raw);
+  const float2 a = __half22float2(h[0]), b = __half22float2(h[1]);
+  out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
+}
+template <>
+__device__ __forceinline__ void load4s<float>(const void* base, int64_t idx, float (&out)[4]) {
+  const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(base) + idx);
+  out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+}
 
 template <typename T, typename G>
 __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepParams p) {
@@ -87,19 +118,28 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     fence_mbar_init();
   }
 
-  // ---- cumulative log-decay: thread = (4-token group tg, 8-channel group c8) -----------------
-  const int tg = tid >> 4, c8 = tid & 15;
-  float Gc[4][8];
+  // ---- every global load of the chunk is issued up front ------------------------------------------
+  const int tg = warp, c4 = lane;
+  const int kc0 = 4 * c4;
+  float Gc[4][4], kk[4][4], qq[4][4], bb[4][4], zz[4][4];
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
-    const int64_t idx = ((b * p.T + t0 + 4 * tg + e) * p.H + h) * kDim + 8 * c8;
-    float gv[8];
-    load8<G>(p.g, idx, gv);
+    const int64_t idx = ((b * p.T + t0 + 4 * tg + e) * p.H + h) * kDim + kc0;
+    float gv[4], vv[4], ww[4];
+    load4s<G>(p.g, idx, gv);
+    load4s<T>(p.k, idx, kk[e]);
+    load4s<T>(p.q, idx, qq[e]);
+    load4s<T>(p.beta, idx, bb[e]);
+    load4s<T>(p.v, idx, vv);
+    load4s<T>(p.w, idx, ww);
 #pragma unroll
-    for (int f = 0; f < 8; ++f) Gc[e][f] = (e ? Gc[e - 1][f] : 0.f) + gv[f];
+    for (int f = 0; f < 4; ++f) {
+      Gc[e][f] = (e ? Gc[e - 1][f] : 0.f) + gv[f];
+      zz[e][f] = to_tf32(vv[f] * ww[f]);
+    }
   }
 #pragma unroll
-  for (int f = 0; f < 8; ++f) sm.part[tg][8 * c8 + f] = Gc[3][f];
+  for (int f = 0; f < 4; ++f) sm.part[tg][kc0 + f] = Gc[3][f];
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -116,87 +156,83 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
   }
   __syncthreads();
 
+  // ---- per-thread decay table: everything except three exponentials per element comes from here ----
+  const int mb = tg >> 2;  // 16-token block of this thread's tokens
+  float a_mb[4], a_nx[4], e_amb[4], t_end[4], t_far[2][4];
+#pragma unroll
+  for (int f = 0; f < 4; ++f) {
+    const int kc = kc0 + f;
+    a_mb[f] = sm.part[4 * mb][kc];
+    a_nx[f] = (mb < 3) ? sm.part[4 * (mb + 1)][kc] : sm.gend[kc];
+    e_amb[f] = __expf(a_mb[f]);
+    t_end[f] = __expf(sm.gend[kc] - a_nx[f]);
+    // blocks further than the next one: exp(a_I - a_next), I = mb + 2, mb + 3
+    t_far[0][f] = (mb + 2 < 4) ? __expf(sm.part[4 * (mb + 2)][kc] - a_nx[f]) : 0.f;
+    t_far[1][f] = (mb + 3 < 4) ? __expf(sm.part[4 * (mb + 3)][kc] - a_nx[f]) : 0.f;
+  }
+
   uint8_t* blob_q = p.ws + ws.off_q() + ch * kBlobQ;
   uint8_t* blob_kt = p.ws + ws.off_kt() + ch * kBlobKt;
-  const int my_block = tg >> 2;
   uint8_t* blob_kn = p.ws + ws.off_kn() + ch * kBlobKn;
-  float ebar[4][8], ktail[4][8], qgam[4][8];
+  float ebar[4][4], ktail[4][4], qgam[4][4];
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
     const int i = 4 * tg + e;
-    const int64_t idx = ((b * p.T + t0 + i) * p.H + h) * kDim + 8 * c8;
-    float kk[8], qq[8], bb[8];
-    load8<T>(p.k, idx, kk);
-    load8<T>(p.q, idx, qq);
-    load8<T>(p.beta, idx, bb);
-    float ea[8], qa[8], qg[8];
+    float ea[4], qa[4], kown[4], knb[4];
 #pragma unroll
-    for (int f = 0; f < 8; ++f) {
-      const int kc = 8 * c8 + f;
-      const float Gi = Gc[e][f] + sm.part[tg][kc];
-      Gc[e][f] = Gi;
-      const float anchored = __expf(Gi - sm.part[4 * my_block][kc]);
-      const float full = __expf(Gi);
-      const float bk = bb[f] * kk[f];
+    for (int f = 0; f < 4; ++f) {
+      const float Gi = Gc[e][f] + sm.part[tg][kc0 + f];
+      const float anchored = __expf(Gi - a_mb[f]);   // <= 1
+      const float own = __expf(a_mb[f] - Gi);        // >= 1, bounded by the 16-token contract
+      const float nb = __expf(a_nx[f] - Gi);         // <= 1: decay from token i to the next block start
+      const float bk = bb[e][f] * kk[e][f];
+      const float sq = p.scale * qq[e][f];
       ea[f] = to_tf32(bk * anchored);
-      qa[f] = to_tf32(p.scale * qq[f] * anchored);
-      ebar[e][f] = to_tf32(bk * full);
-      qg[f] = to_tf32(p.scale * qq[f] * full);
-      ktail[e][f] = to_tf32(kk[f] * __expf(sm.gend[kc] - Gi));
+      qa[f] = to_tf32(sq * anchored);
+      ebar[e][f] = to_tf32(bk * anchored * e_amb[f]);
+      qgam[e][f] = to_tf32(sq * anchored * e_amb[f]);
+      kown[f] = to_tf32(kk[e][f] * own);
+      knb[f] = kk[e][f] * nb;
+      ktail[e][f] = to_tf32(knb[f] * t_end[f]);
     }
-    // Gram A operand rows i (erase) and 64 + i (query), tf32, K-major
-    {
-      float4* ed = reinterpret_cast<float4*>(sm.gram_a + blk_off<4>(i, 8 * c8, 4096, 128));
-      ed[0] = make_float4(ea[0], ea[1], ea[2], ea[3]);
-      ed[8] = make_float4(ea[4], ea[5], ea[6], ea[7]);
-      float4* qd = reinterpret_cast<float4*>(sm.gram_a + blk_off<4>(64 + i, 8 * c8, 4096, 128));
-      qd[0] = make_float4(qa[0], qa[1], qa[2], qa[3]);
-      qd[8] = make_float4(qa[4], qa[5], qa[6], qa[7]);
-    }
+    // Gram A operand rows i (erase) and 64 + i (query), tf32, K-major, padded chunk stride
+    *reinterpret_cast<float4*>(sm.gram_a + (i >> 3) * kRsN + c4 * kCsN + (i & 7) * 16) =
+        make_float4(ea[0], ea[1], ea[2], ea[3]);
+    *reinterpret_cast<float4*>(sm.gram_a + ((64 + i) >> 3) * kRsN + c4 * kCsN + (i & 7) * 16) =
+        make_float4(qa[0], qa[1], qa[2], qa[3]);
     // Gram B operands: token i is a column of every row block I >= its own
+    const uint32_t row_off = (i >> 3) * kRsN + c4 * kCsN + (i & 7) * 16;
+    *reinterpret_cast<float4*>(sm.gram_b + gram_b_offset(mb) + row_off) =
+        make_float4(kown[0], kown[1], kown[2], kown[3]);
+    if (mb + 1 < 4) {
+      *reinterpret_cast<float4*>(sm.gram_b + gram_b_offset(mb + 1) + row_off) =
+          make_float4(to_tf32(knb[0]), to_tf32(knb[1]), to_tf32(knb[2]), to_tf32(knb[3]));
+    }
 #pragma unroll
-    for (int I = 0; I < 4; ++I) {
-      if (I >= my_block) {
-        float kb[8];
-#pragma unroll
-        for (int f = 0; f < 8; ++f) kb[f] = to_tf32(kk[f] * __expf(sm.part[4 * I][8 * c8 + f] - Gc[e][f]));
-        float4* kd = reinterpret_cast<float4*>(sm.gram_b + gram_b_offset(I) + blk_off<4>(i, 8 * c8, 4096, 128));
-        kd[0] = make_float4(kb[0], kb[1], kb[2], kb[3]);
-        kd[8] = make_float4(kb[4], kb[5], kb[6], kb[7]);
+    for (int far = 0; far < 2; ++far) {
+      if (mb + 2 + far < 4) {
+        *reinterpret_cast<float4*>(sm.gram_b + gram_b_offset(mb + 2 + far) + row_off) =
+            make_float4(to_tf32(knb[0] * t_far[far][0]), to_tf32(knb[1] * t_far[far][1]),
+                        to_tf32(knb[2] * t_far[far][2]), to_tf32(knb[3] * t_far[far][3]));
       }
     }
-    // Q_gamma tile X[r = i][c = k], tf32, straight to the workspace
-    float4* qdst = reinterpret_cast<float4*>(blob_q + blk_off<4>(i, 8 * c8, 4096, 128));
-    qdst[0] = make_float4(qg[0], qg[1], qg[2], qg[3]);
-    qdst[8] = make_float4(qg[4], qg[5], qg[6], qg[7]);  // next 16-byte column chunk: +128 bytes
-#pragma unroll
-    for (int f = 0; f < 8; ++f) qgam[e][f] = qg[f];
+    // natural workspace tiles X[r = i][c = k]: Q_gamma always, K_tail when training
+    *reinterpret_cast<float4*>(blob_q + blk_off<4>(i, kc0, 4096, 128)) =
+        make_float4(qgam[e][0], qgam[e][1], qgam[e][2], qgam[e][3]);
     if (training) {
-      float4* kdst = reinterpret_cast<float4*>(blob_kn + blk_off<4>(i, 8 * c8, 4096, 128));
-      kdst[0] = make_float4(ktail[e][0], ktail[e][1], ktail[e][2], ktail[e][3]);
-      kdst[8] = make_float4(ktail[e][4], ktail[e][5], ktail[e][6], ktail[e][7]);
+      *reinterpret_cast<float4*>(blob_kn + blk_off<4>(i, kc0, 4096, 128)) =
+          make_float4(ktail[e][0], ktail[e][1], ktail[e][2], ktail[e][3]);
     }
   }
-  // transposed tiles X[r = channel][c = token]: the thread's 4 tokens are one 16-byte chunk per channel,
-  // its 8 channels are 8 consecutive rows -> 128 contiguous bytes
+  // transposed workspace tiles X[r = channel][c = token]: one 16-byte chunk (4 tokens) per channel
 #pragma unroll
-  for (int f = 0; f < 8; ++f) {
-    const uint32_t off = blk_off<4>(8 * c8 + f, 4 * tg, 2048, 128);
+  for (int f = 0; f < 4; ++f) {
+    const uint32_t off = blk_off<4>(kc0 + f, 4 * tg, 2048, 128);
     *reinterpret_cast<float4*>(blob_kt + off) = make_float4(ktail[0][f], ktail[1][f], ktail[2][f], ktail[3][f]);
     if (training) {
       *reinterpret_cast<float4*>(p.ws + ws.off_qt() + ch * kBlobQt + off) =
           make_float4(qgam[0][f], qgam[1][f], qgam[2][f], qgam[3][f]);
     }
-  }
-  float zz[4][8];
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const int64_t idx = ((b * p.T + t0 + 4 * tg + e) * p.H + h) * kDim + 8 * c8;
-    float vv[8], ww[8];
-    load8<T>(p.v, idx, vv);
-    load8<T>(p.w, idx, ww);
-#pragma unroll
-    for (int f = 0; f < 8; ++f) zz[e][f] = to_tf32(vv[f] * ww[f]);
   }
   if (tid < kDim) {
     reinterpret_cast<float*>(p.ws + ws.off_d() + ch * kBlobD)[tid] = __expf(sm.gend[tid]);
@@ -214,8 +250,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
       const uint32_t a0 = smem_u32(sm.gram_a), b0 = smem_u32(sm.gram_b + gram_b_offset(I));
 #pragma unroll
       for (int ks = 0; ks < 16; ++ks) {
-        mma_tf32_ss(tb + gram_col(I), smem_desc(a0 + ks * 256, 128, 4096), smem_desc(b0 + ks * 256, 128, 4096), id,
-                    ks > 0 ? 1u : 0u);
+        mma_tf32_ss(tb + gram_col(I), smem_desc(a0 + ks * 2 * kCsN, kCsN, kRsN),
+                    smem_desc(b0 + ks * 2 * kCsN, kCsN, kRsN), id, ks > 0 ? 1u : 0u);
       }
     }
     mma_commit(&sm.bar[0]);
@@ -223,63 +259,62 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
   waiter.wait(&sm.bar[0], 0);
   tc_fence_after();
 
-  // ---- pull L (rows 0..63) into fp32 scratch, Aqk (rows 64..127) into the workspace ---------------
   // the Gram operands are dead: region 1 becomes fp32 scratch, region 2 receives E^T and Z^T
   float* Ln = reinterpret_cast<float*>(sm.gram_a);           // [64][kLd]   L
   float* Tn = Ln + 64 * kLd;                                  // [64][kLd]   T
   float* An = Tn + 64 * kLd;                                  // [64][kLd]   A_qk, natural (training)
   float* Wn = An + 64 * kLd;                                  // [3][16][17] block products
-  uint8_t* et_tile = sm.gram_b;                               // E^T  X[r = k][c = j], tf32, 32 KiB
-  uint8_t* zt_tile = sm.gram_b + 32768;                       // Z^T  X[r = v][c = j], tf32, 32 KiB
+  uint8_t* et_tile = sm.gram_b;                               // E^T  X[r = k][c = j], tf32, RS kRsT
+  uint8_t* zt_tile = sm.gram_b + kTileT;                      // Z^T  X[r = v][c = j], tf32, RS kRsT
 #pragma unroll
-  for (int f = 0; f < 8; ++f) {
-    const uint32_t off = blk_off<4>(8 * c8 + f, 4 * tg, 2048, 128);
+  for (int f = 0; f < 4; ++f) {
+    const uint32_t off = blk_off<4>(kc0 + f, 4 * tg, kRsT, 128);
     *reinterpret_cast<float4*>(et_tile + off) = make_float4(ebar[0][f], ebar[1][f], ebar[2][f], ebar[3][f]);
     *reinterpret_cast<float4*>(zt_tile + off) = make_float4(zz[0][f], zz[1][f], zz[2][f], zz[3][f]);
   }
-  if (warp < 4) {
-    const int r = 32 * warp + lane;       // TMEM lane = row of [E_a ; Q_a]
+  const int q4 = warp & 3, part = warp >> 2;  // TMEM lane quadrant of this warp, and its share of the columns
+  {
+    // pull L (rows 0..63) into fp32 scratch and A_qk (rows 64..127) into the workspace;
+    // the four warps of a quadrant take 16 columns each
+    const int r = 32 * q4 + lane;  // TMEM lane = row of [E_a ; Q_a]
     const int i = r & 63;
-    const int I_lo = (warp & 1) * 2;
+    const int I_lo = (q4 & 1) * 2;
     const int my_I = I_lo + (lane >> 4);
+    const int c0 = 16 * part;
     uint8_t* blob_a = p.ws + ws.off_a() + ch * kBlobA;
+    uint32_t lo[16], hi[16];
+    const bool need_lo = c0 < 16 * (I_lo + 1), need_hi = c0 < 16 * (I_lo + 2);
+    if (need_lo) tmem_ld16(tmem_addr(tb, 32 * q4, gram_col(I_lo) + c0), lo);
+    if (need_hi) tmem_ld16(tmem_addr(tb, 32 * q4, gram_col(I_lo + 1) + c0), hi);
+    tmem_wait_ld();
+    float vals[16];
 #pragma unroll
-    for (int c0 = 0; c0 < 64; c0 += 16) {
-      uint32_t lo[16], hi[16];
-      const bool need_lo = c0 < 16 * (I_lo + 1), need_hi = c0 < 16 * (I_lo + 2);
-      if (need_lo) tmem_ld16(tmem_addr(tb, 32 * warp, gram_col(I_lo) + c0), lo);
-      if (need_hi) tmem_ld16(tmem_addr(tb, 32 * warp, gram_col(I_lo + 1) + c0), hi);
-      tmem_wait_ld();
-      float vals[16];
+    for (int j = 0; j < 16; ++j) {
+      const bool mine_lo = (my_I == I_lo);
+      const float x = mine_lo ? (need_lo ? __uint_as_float(lo[j]) : 0.f) : (need_hi ? __uint_as_float(hi[j]) : 0.f);
+      const int col = c0 + j;
+      vals[j] = (r < 64) ? ((col < i) ? x : 0.f) : ((col <= i) ? to_tf32(x) : 0.f);
+    }
+    if (r < 64) {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        const bool mine_lo = (my_I == I_lo);
-        const float x = mine_lo ? (need_lo ? __uint_as_float(lo[j]) : 0.f) : (need_hi ? __uint_as_float(hi[j]) : 0.f);
-        const int col = c0 + j;
-        vals[j] = (r < 64) ? ((col < i) ? x : 0.f) : ((col <= i) ? to_tf32(x) : 0.f);
+      for (int j = 0; j < 16; ++j) Ln[i * kLd + c0 + j] = vals[j];
+    } else {
+#pragma unroll
+      for (int j4 = 0; j4 < 4; ++j4) {
+        *reinterpret_cast<float4*>(blob_a + blk_off<4>(i, c0 + 4 * j4, 2048, 128)) =
+            make_float4(vals[4 * j4], vals[4 * j4 + 1], vals[4 * j4 + 2], vals[4 * j4 + 3]);
       }
-      if (r < 64) {
+      if (training) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) Ln[i * kLd + c0 + j] = vals[j];
-      } else {
-#pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          *reinterpret_cast<float4*>(blob_a + blk_off<4>(i, c0 + 4 * j4, 2048, 128)) =
-              make_float4(vals[4 * j4], vals[4 * j4 + 1], vals[4 * j4 + 2], vals[4 * j4 + 3]);
-        }
-        if (training) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) An[i * kLd + c0 + j] = vals[j];
-        }
+        for (int j = 0; j < 16; ++j) An[i * kLd + c0 + j] = vals[j];
       }
     }
   }
+  for (int e = tid; e < 64 * 64; e += kPrepThreads) Tn[(e >> 6) * kLd + (e & 63)] = 0.f;
   tc_fence_before();
   __syncthreads();
 
   // ---- T = (I + L)^-1, blocked: 16x16 diagonal blocks by substitution, the rest by block products --
-  for (int e = tid; e < 64 * 64; e += kPrepThreads) Tn[(e >> 6) * kLd + (e & 63)] = 0.f;
-  __syncthreads();
   if (tid < 64) {
     const int I = tid >> 4, cc = tid & 15;
     float x[16];
@@ -320,21 +355,21 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
   {
     uint8_t* blob_t = p.ws + ws.off_t() + ch * kBlobT;
     for (int e = tid; e < 64 * 16; e += kPrepThreads) {
-      const int i = e & 63, c4 = e >> 6;  // consecutive threads -> consecutive rows -> contiguous 16-byte chunks
-      const float4 val = make_float4(to_tf32(Tn[i * kLd + 4 * c4]), to_tf32(Tn[i * kLd + 4 * c4 + 1]),
-                                     to_tf32(Tn[i * kLd + 4 * c4 + 2]), to_tf32(Tn[i * kLd + 4 * c4 + 3]));
-      const uint32_t off = blk_off<4>(i, 4 * c4, 2048, 128);
+      const int i = e & 63, c4t = e >> 6;  // consecutive threads -> consecutive rows -> contiguous 16-byte chunks
+      const float4 val = make_float4(to_tf32(Tn[i * kLd + 4 * c4t]), to_tf32(Tn[i * kLd + 4 * c4t + 1]),
+                                     to_tf32(Tn[i * kLd + 4 * c4t + 2]), to_tf32(Tn[i * kLd + 4 * c4t + 3]));
+      const uint32_t off = blk_off<4>(i, 4 * c4t, 2048, 128);
       *reinterpret_cast<float4*>(sm.tmat + off) = val;
       *reinterpret_cast<float4*>(blob_t + off) = val;
       if (training) {
-        // transposed tiles X[r = j][c = i]: here `i` plays the role of the row j, 4*c4.. of the column i
+        // transposed tiles X[r = j][c = i]: here `i` plays the role of the row j, 4*c4t.. of the column i
         const int j = i;
         *reinterpret_cast<float4*>(p.ws + ws.off_tt() + ch * kBlobTt + off) =
-            make_float4(to_tf32(Tn[(4 * c4) * kLd + j]), to_tf32(Tn[(4 * c4 + 1) * kLd + j]),
-                        to_tf32(Tn[(4 * c4 + 2) * kLd + j]), to_tf32(Tn[(4 * c4 + 3) * kLd + j]));
+            make_float4(to_tf32(Tn[(4 * c4t) * kLd + j]), to_tf32(Tn[(4 * c4t + 1) * kLd + j]),
+                        to_tf32(Tn[(4 * c4t + 2) * kLd + j]), to_tf32(Tn[(4 * c4t + 3) * kLd + j]));
         *reinterpret_cast<float4*>(p.ws + ws.off_at() + ch * kBlobAt + off) =
-            make_float4(An[(4 * c4) * kLd + j], An[(4 * c4 + 1) * kLd + j], An[(4 * c4 + 2) * kLd + j],
-                        An[(4 * c4 + 3) * kLd + j]);
+            make_float4(An[(4 * c4t) * kLd + j], An[(4 * c4t + 1) * kLd + j], An[(4 * c4t + 2) * kLd + j],
+                        An[(4 * c4t + 3) * kLd + j]);
       }
     }
   }
@@ -342,7 +377,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
   tc_fence_before();
   __syncthreads();
 
-  // ---- Y = T E (rows 0..63 of an M = 128 product) and U^T = Z^T T^T --------------------------------
+  // ---- Y = T E (rows 0..63 of an M = 128 product), U^T = Z^T T^T, and Y^T = E^T T^T when training ----
   if (tid == 0) {
     tc_fence_after();
     const uint32_t t0a = smem_u32(sm.tmat), e0 = smem_u32(et_tile), z0 = smem_u32(zt_tile);
@@ -350,19 +385,18 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     const uint32_t id_u = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
-      mma_tf32_ss(tb + 0, smem_desc(t0a + ks * 256, 128, 2048), smem_desc(e0 + ks * 256, 128, 2048), id_y,
+      mma_tf32_ss(tb + 0, smem_desc(t0a + ks * 256, 128, 2048), smem_desc(e0 + ks * 256, 128, kRsT), id_y,
                   ks > 0 ? 1u : 0u);
     }
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
-      mma_tf32_ss(tb + 128, smem_desc(z0 + ks * 256, 128, 2048), smem_desc(t0a + ks * 256, 128, 2048), id_u,
+      mma_tf32_ss(tb + 128, smem_desc(z0 + ks * 256, 128, kRsT), smem_desc(t0a + ks * 256, 128, 2048), id_u,
                   ks > 0 ? 1u : 0u);
     }
     if (training) {
-      // Y^T = E^T T^T (lane = key), columns 192..255
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        mma_tf32_ss(tb + 192, smem_desc(e0 + ks * 256, 128, 2048), smem_desc(t0a + ks * 256, 128, 2048), id_u,
+        mma_tf32_ss(tb + 192, smem_desc(e0 + ks * 256, 128, kRsT), smem_desc(t0a + ks * 256, 128, 2048), id_u,
                     ks > 0 ? 1u : 0u);
       }
     }
@@ -371,55 +405,45 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
   waiter.wait(&sm.bar[1], 0);
   tc_fence_after();
   {
-    // Y: lanes 0..63 hold rows i; warps 0,1 take key columns 0..63, warps 4,5 take 64..127
-    const int q4 = warp & 3;
+    auto rn4 = [](const uint32_t* r) {
+      return make_float4(to_tf32(__uint_as_float(r[0])), to_tf32(__uint_as_float(r[1])),
+                         to_tf32(__uint_as_float(r[2])), to_tf32(__uint_as_float(r[3])));
+    };
+    // Y: lanes 0..63 hold rows i; the four warps of quadrants 0 and 1 take 32 key columns each
     if (q4 < 2) {
       const int i = 32 * q4 + lane;
-      const int cbase = (warp >= 4) ? 64 : 0;
       uint8_t* blob_y = p.ws + ws.off_y() + ch * kBlobY;
 #pragma unroll
-      for (int c0 = 0; c0 < 64; c0 += 16) {
+      for (int c0 = 32 * part; c0 < 32 * part + 32; c0 += 16) {
         uint32_t r[16];
-        tmem_ld16(tmem_addr(tb, 32 * q4, cbase + c0), r);
+        tmem_ld16(tmem_addr(tb, 32 * q4, c0), r);
         tmem_wait_ld();
 #pragma unroll
         for (int j4 = 0; j4 < 4; ++j4) {
-          *reinterpret_cast<float4*>(blob_y + blk_off<4>(i, cbase + c0 + 4 * j4, 4096, 128)) =
-              make_float4(to_tf32(__uint_as_float(r[4 * j4])), to_tf32(__uint_as_float(r[4 * j4 + 1])),
-                          to_tf32(__uint_as_float(r[4 * j4 + 2])), to_tf32(__uint_as_float(r[4 * j4 + 3])));
+          *reinterpret_cast<float4*>(blob_y + blk_off<4>(i, c0 + 4 * j4, 4096, 128)) = rn4(r + 4 * j4);
         }
       }
     }
-    // U^T: lane = value row; warps 0..3 take tokens 0..31, warps 4..7 take 32..63 (kept in full fp32)
+    // U^T (kept in full fp32) and Y^T: lane = value / key row; each warp of a quadrant takes 16 tokens
     {
-      const int vrow = 32 * q4 + lane;
-      const int ibase = (warp >= 4) ? 32 : 0;
+      const int row = 32 * q4 + lane;
+      const int c0 = 16 * part;
       uint8_t* blob_ut = p.ws + ws.off_ut() + ch * kBlobUt;
+      uint32_t r[16];
+      tmem_ld16(tmem_addr(tb, 32 * q4, 128 + c0), r);
+      tmem_wait_ld();
 #pragma unroll
-      for (int c0 = 0; c0 < 32; c0 += 16) {
-        uint32_t r[16];
-        tmem_ld16(tmem_addr(tb, 32 * q4, 128 + ibase + c0), r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          *reinterpret_cast<float4*>(blob_ut + blk_off<4>(vrow, ibase + c0 + 4 * j4, 2048, 128)) =
-              make_float4(__uint_as_float(r[4 * j4]), __uint_as_float(r[4 * j4 + 1]),
-                          __uint_as_float(r[4 * j4 + 2]), __uint_as_float(r[4 * j4 + 3]));
-        }
+      for (int j4 = 0; j4 < 4; ++j4) {
+        *reinterpret_cast<uint4*>(blob_ut + blk_off<4>(row, c0 + 4 * j4, 2048, 128)) =
+            make_uint4(r[4 * j4], r[4 * j4 + 1], r[4 * j4 + 2], r[4 * j4 + 3]);
       }
       if (training) {
         uint8_t* blob_yt = p.ws + ws.off_yt() + ch * kBlobYt;
+        tmem_ld16(tmem_addr(tb, 32 * q4, 192 + c0), r);
+        tmem_wait_ld();
 #pragma unroll
-        for (int c0 = 0; c0 < 32; c0 += 16) {
-          uint32_t r[16];
-          tmem_ld16(tmem_addr(tb, 32 * q4, 192 + ibase + c0), r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int j4 = 0; j4 < 4; ++j4) {
-            *reinterpret_cast<float4*>(blob_yt + blk_off<4>(vrow, ibase + c0 + 4 * j4, 2048, 128)) =
-                make_float4(to_tf32(__uint_as_float(r[4 * j4])), to_tf32(__uint_as_float(r[4 * j4 + 1])),
-                            to_tf32(__uint_as_float(r[4 * j4 + 2])), to_tf32(__uint_as_float(r[4 * j4 + 3])));
-          }
+        for (int j4 = 0; j4 < 4; ++j4) {
+          *reinterpret_cast<float4*>(blob_yt + blk_off<4>(row, c0 + 4 * j4, 2048, 128)) = rn4(r + 4 * j4);
         }
       }
     }
