@@ -41,6 +41,13 @@ UNIT = "tokens/s"
 # algorithmic bytes per token-head (bf16 sequence tensors, fp32 g), K = V = 128
 FWD_BYTES = 5 * 256 + 512 + 256                 # read q k v beta w + g, write o
 BWD_BYTES = (5 * 256 + 512 + 256) + (5 * 256 + 512)  # read inputs + dO, write 6 grads
+# dram__bytes_read.sum + dram__bytes_write.sum per 64-token chunk-head from the ncu captures summarised in
+# profiles/chunk_kernels_*_ncu_full.md (B=1, H=8 cases, scaled by the number of chunk-heads: the kernels'
+# traffic is proportional to it); the forward/backward calls launch two kernels each.
+NCU_TRAFFIC_PER_CHUNK_HEAD = {
+    "gdn2_chunk_forward": 313.4e3 + 159.2e3,    # chunk_prep (T=4096 capture) + chunk_scan (T=2048 capture)
+    "gdn2_chunk_backward": 138.8e3 + 414.3e3,   # chunk_bwd_scan (T=2048 capture) + chunk_bwd_vjp (T=4096 capture)
+}
 DECODE_BYTES_PER_HEAD = 2 * 65536 + 1792 + 256
 T1_ZERO_BYTES_PER_HEAD = 65536 + 1280
 
@@ -179,7 +186,7 @@ class ClockSampler:
             os.close(fd)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-i", str(self.index), "-lms", "100"],
+                 "-i", str(self.index), "-lms", "20"],
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -269,12 +276,12 @@ def run_gpu_arm(args):
         torch.cuda.synchronize()
 
     # ---- device-resident timing -----------------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()  # nvidia-smi needs a moment to start: sample from the warm-up on, all under load
     for _ in range(max(args.warmup, 3)):
         train_step(pkg, leaves, s0)
     barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     launches_before = _lib.LAUNCHES[0]
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -311,9 +318,12 @@ def run_gpu_arm(args):
     roofline = None
     if dominant is not None:
         achieved = kernel_bytes.get(dominant, 0) / (kernel_ms[dominant] * 1e-3) / 1e9
+        per_ch = NCU_TRAFFIC_PER_CHUNK_HEAD.get(dominant)
+        traffic = per_ch * (token_heads // 64) if per_ch is not None else None
         roofline = {
             "bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak,
-            "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+            "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
+            "algorithmic_bytes": kernel_bytes.get(dominant, 0),
             "kernel_ms": kernel_ms,
             "step_algorithmic_gbs": (FWD_BYTES + BWD_BYTES) * token_heads / (ms_local * 1e-3) / 1e9,
         }
