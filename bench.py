@@ -369,6 +369,25 @@ def run_gpu_arm(args):
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
         cpu_baseline = run_cpu_baseline(H)
 
+    # ---- multi-GPU: the only collective of the path is the final gather of outputs / states ------
+    gather = None
+    if world > 1:
+        out_local, fin_local = pkg.chunk_gdn2(*[t.detach() for t in inputs[:6]], inputs[6].detach(),
+                                              output_final_state=True)
+        plan = shard.Shard(0, rank * B, (rank + 1) * B)
+        barrier()
+        gb, ge = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        gb.record()
+        full_out = shard.gather(out_local, plan, world)
+        full_fin = shard.gather(fin_local, plan, world, is_state=True)
+        ge.record()
+        barrier()
+        gather = {"ms": shard.max_over_ranks(gb.elapsed_time(ge), device),
+                  "bytes_per_rank": out_local.numel() * out_local.element_size()
+                  + fin_local.numel() * fin_local.element_size(),
+                  "what": "all_gather of o and S_T over NCCL, timed separately from the steps"}
+        del full_out, full_fin, out_local, fin_local
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -378,7 +397,7 @@ def run_gpu_arm(args):
                        "global_batch": B * world, "seq_len": T, "heads": H, "parallelism": f"dp{world} over batch",
                        "l2": "inputs (1.8 GB/step) exceed the 126 MB L2"},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
-            "cpu_baseline": cpu_baseline, "decode": decode,
+            "cpu_baseline": cpu_baseline, "decode": decode, "gather": gather,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -149,3 +149,32 @@ def test_input_distribution_respects_decay_contract():
     assert g.max() <= 0 and g.min() >= -5.0
     windows = g.unfold(1, 16, 16).sum(-1)
     assert windows.min() > -87.0
+
+
+@pytest.mark.parametrize("chunk,kdim,vdim", [(4, 7, 5), (7, 7, 5), (16, 8, 8)])
+def test_chunk_wy_stage_oracle_matches_recurrence_and_autograd(chunk, kdim, vdim):
+    """Compact-WY chunk form and its hand-derived VJP against the token recurrence and
+    torch.autograd in float64 (same role as the reference's tests/test_backward_wy.py:257-317)."""
+
+    gen = torch.Generator().manual_seed(91 + chunk)
+    dt = torch.float64
+    q, k, beta = (torch.randn(chunk, kdim, generator=gen, dtype=dt) for _ in range(3))
+    v, w = (torch.randn(chunk, vdim, generator=gen, dtype=dt) for _ in range(2))
+    g = -torch.rand(chunk, kdim, generator=gen, dtype=dt)
+    s0 = torch.randn(kdim, vdim, generator=gen, dtype=dt)
+    d_o = torch.randn(chunk, vdim, generator=gen, dtype=dt)
+    d_s1 = torch.randn(kdim, vdim, generator=gen, dtype=dt)
+    scale = 0.37
+
+    def batched(x):
+        return x[None, :, None]
+
+    leaves = [t.clone().requires_grad_(True) for t in (q, k, v, g, beta, w, s0)]
+    o, s1 = oracle.recurrence(*[batched(t) for t in leaves[:6]], leaves[6][None, None], scale=scale)
+    fwd = oracle.chunk_wy_forward(q, k, v, g, beta, w, s0, scale=scale)
+    torch.testing.assert_close(fwd["o"], o[0, :, 0].detach(), rtol=1e-10, atol=1e-12)
+    torch.testing.assert_close(fwd["s1"], s1[0, 0].detach(), rtol=1e-10, atol=1e-12)
+    want = torch.autograd.grad((o[0, :, 0] * d_o).sum() + (s1[0, 0] * d_s1).sum(), leaves)
+    got = oracle.chunk_wy_vjp(q, k, v, g, beta, w, s0, d_o, d_s1, scale=scale)
+    for a, b in zip(got, want):
+        torch.testing.assert_close(a, b, rtol=1e-9, atol=1e-11)
