@@ -235,12 +235,24 @@ def measured_peak_hbm():
     return 6650.0, "fallback"
 
 
+class _MeanSquare(torch.autograd.Function):
+    """mean(x^2) with fp32 accumulation: one read of x forward, one scaled copy backward (the
+    composite expression costs several full-size temporaries per direction)."""
+
+    @staticmethod
+    def forward(ctx, x):
+        ctx.save_for_backward(x)
+        return torch.linalg.vector_norm(x, dtype=torch.float32) ** 2 / x.numel()
+
+    @staticmethod
+    def backward(ctx, grad):
+        (x,) = ctx.saved_tensors
+        return x * (grad * (2.0 / x.numel())).to(x.dtype)
+
+
 def train_step(pkg, leaves, s0):
     out, fin = pkg.chunk_gdn2(*leaves, s0, output_final_state=True)
-    # mean(o^2) + mean(S_T^2), written as squared 2-norms with fp32 accumulation: one read of o
-    # forward and one scaled copy backward instead of several full-size fp32 temporaries
-    loss = (torch.linalg.vector_norm(out, dtype=torch.float32) ** 2 / out.numel()
-            + torch.linalg.vector_norm(fin) ** 2 / fin.numel())
+    loss = _MeanSquare.apply(out) + _MeanSquare.apply(fin)  # mean(o^2) + mean(S_T^2)
     grads = torch.autograd.grad(loss, (*leaves, s0))
     return loss, grads
 
