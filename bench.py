@@ -171,58 +171,111 @@ def device_inputs(batch, time_, heads, device, seed):
 
 
 class ClockSampler:
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons sampled while the timed steps run.
 
-    def __init__(self, index):
+    Reads NVML in a thread of this process (a few microseconds per query).  A separate
+    `nvidia-smi -lms` poller was measured to slow the timed steps by a third at short periods, and at
+    its usual 200 ms period it hardly lands inside a 100 ms timed region, so it is only the
+    fallback when the NVML binding is missing."""
+
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+               ("sw_power_cap", 0x4))
+
+    def __init__(self, index, period_s=0.01):
         self.index = index
-        self.proc = None
-        self.path = None
+        self.period_s = period_s
+        self.samples = []      # (sm_mhz, reasons bitmask)
+        self.max_mhz = None
+        self.thread = None
+        self.stop_flag = None
+        self.smi = None
+        self.smi_path = None
+        self.first = 0
+
+    def mark(self):
+        """Drop what was sampled so far (the warm-up): the report covers the timed region only."""
+        self.first = len(self.samples)
+
+    def _nvml_loop(self, nvml, handle):
+        while not self.stop_flag.is_set():
+            try:
+                mhz = nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM)
+                mask = nvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                self.samples.append((float(mhz), int(mask)))
+            except Exception:  # noqa: BLE001 - a failed query just yields no sample
+                pass
+            self.stop_flag.wait(self.period_s)
 
     def start(self):
         try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            import threading
+
+            import pynvml as nvml
+            nvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            physical = self.index
+            if visible:
+                entry = visible.split(",")[self.index].strip()
+                physical = int(entry) if entry.isdigit() else None
+            handle = (nvml.nvmlDeviceGetHandleByIndex(physical) if physical is not None
+                      else nvml.nvmlDeviceGetHandleByUUID(entry))
+            self.max_mhz = float(nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM))
+            self.stop_flag = threading.Event()
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nvml, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:  # noqa: BLE001 - fall back to the command-line poller
+            self.thread = None
+        try:
+            fd, self.smi_path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-i", str(self.index), "-lms", "20"],
-                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+            query = ("index,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+                     "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+                     "clocks_event_reasons.sw_power_cap")
+            self.smi = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={query}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "200"],
+                stdout=open(self.smi_path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
-            self.proc = None
+            self.smi = None
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            taken = self.samples[self.first:] or self.samples
+            clocks = [c for c, _ in taken]
+            reasons = sorted({name for _, mask in taken for name, bit in self.REASONS if mask & bit})
+            return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": self.max_mhz,
+                    "samples": len(clocks), "reasons": reasons, "source": "nvml thread"}
+        if self.smi is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["no clock source available"]}
+        self.smi.terminate()
         try:
-            self.proc.wait(timeout=5)
+            self.smi.wait(timeout=5)
         except subprocess.TimeoutExpired:
-            self.proc.kill()
+            self.smi.kill()
         clocks, maxes, reasons = [], [], set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        names = [name for name, _ in self.REASONS]
         try:
-            for row in open(self.path):
+            for row in open(self.smi_path):
                 cells = [c.strip() for c in row.split(",")]
-                if len(cells) < 9:
+                if len(cells) < 7:
                     continue
                 try:
                     clocks.append(float(cells[1]))
                     maxes.append(float(cells[2]))
                 except ValueError:
                     continue
-                for name, cell in zip(names, cells[5:9]):
+                for name, cell in zip(names, cells[3:7]):
                     if cell.lower().startswith("active"):
                         reasons.add(name)
-            os.unlink(self.path)
+            os.unlink(self.smi_path)
         except OSError:
             pass
-        return {
-            "sm_mhz": statistics.median(clocks) if clocks else None,
-            "sm_max_mhz": max(maxes) if maxes else None,
-            "samples": len(clocks),
-            "reasons": sorted(reasons),
-        }
+        return {"sm_mhz": statistics.median(clocks) if clocks else None,
+                "sm_max_mhz": max(maxes) if maxes else None, "samples": len(clocks),
+                "reasons": sorted(reasons), "source": "nvidia-smi -lms 200"}
 
 
 def measured_peak_hbm():
@@ -290,13 +343,14 @@ def run_gpu_arm(args):
     # ---- device-resident timing -----------------------------------------------------------
     sampler = ClockSampler(local_rank)
     if rank == 0:
-        sampler.start()  # nvidia-smi needs a moment to start: sample from the warm-up on, all under load
+        sampler.start()
     for _ in range(max(args.warmup, 3)):
         train_step(pkg, leaves, s0)
     barrier()
     launches_before = _lib.LAUNCHES[0]
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    sampler.mark()
     begin.record()
     for _ in range(args.steps):
         loss, grads = train_step(pkg, leaves, s0)
