@@ -31,10 +31,11 @@ constexpr int64_t kStateElems = int64_t(kDim) * kDim;
 // =============================================================================================
 // reverse scan
 // =============================================================================================
-constexpr int kBScanThreads = 128;
+constexpr int kBScanThreads = 512;
+constexpr int kRsDot = 2064;   // dO^T tile: padded row-group stride (16-byte chunk stores, 4 tokens each)
 
 struct BScanSmem {
-  alignas(128) uint8_t dot[32768];   // dO^T tile X[r = v][c = i], tf32 (built from dO)
+  alignas(128) uint8_t dot[16 * kRsDot];  // dO^T tile X[r = v][c = i], tf32 (built from dO)
   alignas(128) uint8_t kn[32768];    // K_tail   X[r = j][c = k]
   alignas(128) uint8_t qt[32768];    // Qg^T     X[r = k][c = i]
   alignas(128) uint8_t yt[32768];    // Y^T      X[r = k][c = j]
@@ -54,6 +55,25 @@ struct BScanParams {
   int64_t T, H, n_chunks, n_ch;
 };
 
+// raw 4-element load of a 16-bit sequence tensor (kept packed until it is needed)
+template <typename T>
+__device__ __forceinline__ uint2 load4_raw(const void* base, int64_t idx) {
+  return *reinterpret_cast<const uint2*>(static_cast<const T*>(base) + idx);
+}
+template <typename T>
+__device__ __forceinline__ void unpack4(uint2 raw, float (&out)[4]);
+template <>
+__device__ __forceinline__ void unpack4<__nv_bfloat16>(uint2 raw, float (&out)[4]) {
+  out[0] = __uint_as_float(raw.x << 16); out[1] = __uint_as_float(raw.x & 0xffff0000u);
+  out[2] = __uint_as_float(raw.y << 16); out[3] = __uint_as_float(raw.y & 0xffff0000u);
+}
+template <>
+__device__ __forceinline__ void unpack4<__half>(uint2 raw, float (&out)[4]) {
+  const __half2* hh = reinterpret_cast<const __half2*>(&raw);
+  const float2 a = __half22float2(hh[0]), c = __half22float2(hh[1]);
+  out[0] = a.x; out[1] = a.y; out[2] = c.x; out[3] = c.y;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const BScanParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -61,7 +81,11 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
   const WsLayout ws{p.n_ch, true};
   BoundedWaiter waiter(p.status);
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  // 16 warps.  TMEM phases: warp & 3 = lane quadrant, warp >> 2 = quarter of the columns.
+  // dO^T tile builder: warp = 4-token group tg, lane = 4-channel group.
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int q4 = warp & 3, part = warp >> 2;
+  const int tg = warp;
   const int64_t bh = blockIdx.x;
   const int64_t b = bh / p.H, h = bh % p.H;
   constexpr uint32_t kColS = 0, kColR = 128;
@@ -81,8 +105,9 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
   __syncthreads();
   tc_fence_after();
   const uint32_t tb = sm.tmem_base;
-  const uint32_t lane_base = 32u * warp;
-  const int vrow = tid;
+  const uint32_t lane_base = 32u * q4;
+  const int vrow = 32 * q4 + lane;
+  const int k0 = 32 * part, j0 = 16 * part;
 
   auto ch_of = [&](int64_t c) { return (b * p.n_chunks + c) * p.H + h; };
   auto load_ak = [&](int64_t c) {
@@ -98,69 +123,64 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
     bulk_g2s(sm.yt, p.ws + ws.off_yt() + ch * kBlobYt, uint32_t(kBlobYt), &sm.bar_qy);
     bulk_g2s(sm.d, p.ws + ws.off_d() + ch * kBlobD, uint32_t(kBlobD), &sm.bar_qy);
   };
+  // dO of one chunk: 4 tokens x 4 channels per thread, still packed
+  auto load_do = [&](int64_t c, uint2 (&raw)[4]) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      raw[e] = load4_raw<T>(p.d_out, ((b * p.T + c * kChunk + 4 * tg + e) * p.H + h) * kDim + 4 * lane);
+    }
+  };
 
-  if (tid == 0 && p.n_chunks > 0) {
-    load_ak(p.n_chunks - 1);
-    load_qy(p.n_chunks - 1);
+  uint2 do_raw[4] = {};
+  if (p.n_chunks > 0) {
+    if (tid == 0) {
+      load_ak(p.n_chunks - 1);
+      load_qy(p.n_chunks - 1);
+    }
+    load_do(p.n_chunks - 1, do_raw);
   }
 
-  // ---- dS^T <- dS_T^T (thread v gathers column v); also becomes the last boundary slot -----------
+  // ---- dS^T <- dS_T^T (32 key rows of column v per thread); also becomes the last boundary slot ----
   {
     const float* src = (p.ds_final != nullptr) ? p.ds_final + bh * kStateElems + vrow : nullptr;
     float* slot = p.d_bnd + ((b * (p.n_chunks + 1) + p.n_chunks) * p.H + h) * kStateElems + vrow;
+    uint32_t r[32];
 #pragma unroll
-    for (int c0 = 0; c0 < kDim; c0 += 32) {
-      uint32_t r[32];
+    for (int j = 0; j < 32; ++j) r[j] = (src != nullptr) ? __float_as_uint(src[(k0 + j) * kDim]) : 0u;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float x = (src != nullptr) ? src[(c0 + j) * kDim] : 0.f;
-        slot[(c0 + j) * kDim] = x;
-        r[j] = __float_as_uint(x);
-      }
-      tmem_st32(tmem_addr(tb, lane_base, kColS + c0), r);
-    }
+    for (int j = 0; j < 32; ++j) slot[(k0 + j) * kDim] = __uint_as_float(r[j]);
+    tmem_st32(tmem_addr(tb, lane_base, kColS + k0), r);
     tmem_wait_st();
   }
 
-  // dO^T tile builder: thread = (4-token group tg 0..15, 16-channel group c16 0..7)
-  const int tg = tid >> 3, c16 = tid & 7;
   uint32_t it = 0;
   for (int64_t c = p.n_chunks - 1; c >= 0; --c, ++it) {
     const uint32_t par = it & 1u;
-    const int64_t t0 = c * kChunk;
     if (it > 0) {
       // previous iteration's second MMA group read dO^T, Qt, Yt and dR^T
       waiter.wait(&sm.bar_mma2, par ^ 1u);
       tc_fence_after();
-      // cotangent at the start of chunk c + 1 (= end of chunk c)
-      float* slot = p.d_bnd + ((b * (p.n_chunks + 1) + c + 1) * p.H + h) * kStateElems + vrow;
-#pragma unroll
-      for (int c0 = 0; c0 < kDim; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_addr(tb, lane_base, kColS + c0), r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) slot[(c0 + j) * kDim] = __uint_as_float(r[j]);
-      }
       if (tid == 0) load_qy(c);
     }
-    // ---- dO^T tile -------------------------------------------------------------------------------
+    // ---- dO^T tile: one 16-byte chunk (4 tokens) per channel ------------------------------------------
     {
-      float dv[4][16];
+      float dv[4][4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int64_t idx = ((b * p.T + t0 + 4 * tg + e) * p.H + h) * kDim + 16 * c16;
-        float lo[8], hi[8];
-        load8<T>(p.d_out, idx, lo);
-        load8<T>(p.d_out, idx + 8, hi);
+      for (int e = 0; e < 4; ++e) unpack4<T>(do_raw[e], dv[e]);
 #pragma unroll
-        for (int f = 0; f < 8; ++f) { dv[e][f] = lo[f]; dv[e][8 + f] = hi[f]; }
-      }
-#pragma unroll
-      for (int f = 0; f < 16; ++f) {
-        *reinterpret_cast<float4*>(sm.dot + blk_off<4>(16 * c16 + f, 4 * tg, 2048, 128)) =
+      for (int f = 0; f < 4; ++f) {
+        *reinterpret_cast<float4*>(sm.dot + blk_off<4>(4 * lane + f, 4 * tg, kRsDot, 128)) =
             make_float4(dv[0][f], dv[1][f], dv[2][f], dv[3][f]);
       }
+    }
+    if (it > 0) {
+      // cotangent at the start of chunk c + 1 (= end of chunk c); off the MMA's critical path
+      float* slot = p.d_bnd + ((b * (p.n_chunks + 1) + c + 1) * p.H + h) * kStateElems + vrow;
+      uint32_t r[32];
+      tmem_ld32(tmem_addr(tb, lane_base, kColS + k0), r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) slot[(k0 + j) * kDim] = __uint_as_float(r[j]);
     }
     fence_async_smem();
     waiter.wait(&sm.bar_ak, par);
@@ -168,53 +188,51 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
-      const uint32_t d0 = smem_u32(sm.dot), a0 = smem_u32(sm.at), k0 = smem_u32(sm.kn);
+      const uint32_t d0 = smem_u32(sm.dot), a0 = smem_u32(sm.at), kn0 = smem_u32(sm.kn);
       const uint32_t id64 = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
       // dR^T = dO^T Aqk   (A: dO^T [v x i], B: Aqk^T tile X[r = j][c = i])
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        mma_tf32_ss(tb + kColR, smem_desc(d0 + ks * 256, 128, 2048), smem_desc(a0 + ks * 256, 128, 2048), id64,
+        mma_tf32_ss(tb + kColR, smem_desc(d0 + ks * 256, 128, kRsDot), smem_desc(a0 + ks * 256, 128, 2048), id64,
                     ks > 0 ? 1u : 0u);
       }
       // dR^T += dS^T Kt^T (A: cotangent columns, K = 128 keys; B: K_tail tile X[r = j][c = k])
 #pragma unroll
       for (int ks = 0; ks < 16; ++ks) {
-        mma_tf32_ts(tb + kColR, tb + kColS + ks * 8, smem_desc(k0 + ks * 256, 128, 4096), id64, 1u);
+        mma_tf32_ts(tb + kColR, tb + kColS + ks * 8, smem_desc(kn0 + ks * 256, 128, 4096), id64, 1u);
       }
       mma_commit(&sm.bar_mma1);
     }
+    // the next chunk's dO is on its way while the tensor cores work
+    if (c > 0) load_do(c - 1, do_raw);
     waiter.wait(&sm.bar_mma1, par);
     tc_fence_after();
     if (tid == 0 && c > 0) load_ak(c - 1);  // At / Kn are free again
 
-    // ---- dR^T out (tile X[r = v][c = j]) ------------------------------------------------------------
+    // ---- dR^T out (tile X[r = v][c = j]): 16 token columns per thread ----------------------------------
     {
-      uint8_t* blob = p.ws + ws.off_drt() + ch_of(c) * kBlobDRt + (vrow >> 3) * 2048 + (vrow & 7) * 16;
+      uint8_t* blob = p.ws + ws.off_drt() + ch_of(c) * kBlobDRt + (vrow >> 3) * 2048 + (vrow & 7) * 16 + (j0 / 4) * 128;
+      uint32_t r[16];
+      tmem_ld16(tmem_addr(tb, lane_base, kColR + j0), r);
+      tmem_wait_ld();
 #pragma unroll
-      for (int c0 = 0; c0 < kChunk; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_addr(tb, lane_base, kColR + c0), r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
-          *reinterpret_cast<float4*>(blob + (c0 / 4 + c4) * 128) =
-              make_float4(to_tf32(__uint_as_float(r[4 * c4])), to_tf32(__uint_as_float(r[4 * c4 + 1])),
-                          to_tf32(__uint_as_float(r[4 * c4 + 2])), to_tf32(__uint_as_float(r[4 * c4 + 3])));
-        }
+      for (int c4 = 0; c4 < 4; ++c4) {
+        *reinterpret_cast<float4*>(blob + c4 * 128) =
+            make_float4(to_tf32(__uint_as_float(r[4 * c4])), to_tf32(__uint_as_float(r[4 * c4 + 1])),
+                        to_tf32(__uint_as_float(r[4 * c4 + 2])), to_tf32(__uint_as_float(r[4 * c4 + 3])));
       }
     }
     // ---- decay: dS^T <- dS^T diag(d) -------------------------------------------------------------------
     waiter.wait(&sm.bar_qy, par);
-#pragma unroll
-    for (int c0 = 0; c0 < kDim; c0 += 32) {
+    {
       uint32_t r[32];
-      tmem_ld32(tmem_addr(tb, lane_base, kColS + c0), r);
+      tmem_ld32(tmem_addr(tb, lane_base, kColS + k0), r);
       tmem_wait_ld();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * sm.d[c0 + j]);
-      tmem_st32(tmem_addr(tb, lane_base, kColS + c0), r);
+      for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * sm.d[k0 + j]);
+      tmem_st32(tmem_addr(tb, lane_base, kColS + k0), r);
+      tmem_wait_st();
     }
-    tmem_wait_st();
     tc_fence_before();
     __syncthreads();
     if (tid == 0) {
@@ -225,7 +243,7 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
       // dS^T += dO^T Qg   (B: Qg^T tile X[r = k][c = i])
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        mma_tf32_ss(tb + kColS, smem_desc(d0 + ks * 256, 128, 2048), smem_desc(q0 + ks * 256, 128, 2048), id_pos, 1u);
+        mma_tf32_ss(tb + kColS, smem_desc(d0 + ks * 256, 128, kRsDot), smem_desc(q0 + ks * 256, 128, 2048), id_pos, 1u);
       }
       // dS^T -= dR^T Y    (A: dR^T columns, K = 64 tokens; B: Y^T tile X[r = k][c = j])
 #pragma unroll
@@ -244,16 +262,13 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
   {
     float* slot = p.d_bnd + ((b * (p.n_chunks + 1)) * p.H + h) * kStateElems + vrow;
     float* init = (p.ds_init != nullptr) ? p.ds_init + bh * kStateElems + vrow : nullptr;
+    uint32_t r[32];
+    tmem_ld32(tmem_addr(tb, lane_base, kColS + k0), r);
+    tmem_wait_ld();
 #pragma unroll
-    for (int c0 = 0; c0 < kDim; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld32(tmem_addr(tb, lane_base, kColS + c0), r);
-      tmem_wait_ld();
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        slot[(c0 + j) * kDim] = __uint_as_float(r[j]);
-        if (init != nullptr) init[(c0 + j) * kDim] = __uint_as_float(r[j]);
-      }
+    for (int j = 0; j < 32; ++j) {
+      slot[(k0 + j) * kDim] = __uint_as_float(r[j]);
+      if (init != nullptr) init[(k0 + j) * kDim] = __uint_as_float(r[j]);
     }
   }
   tc_fence_before();
@@ -419,20 +434,27 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
       if ((lane >> 3) == 0) atomicAdd(&ms.dd[(qd & 7) + 8 * (qd >> 7)], acc);
     }
   };
-  load_ds1_half(0);
-
-  // dO rows of the stack (rows 64 + i), natural tile with padded chunk stride
+  // dO rows of the stack (rows 64 + i), natural tile with padded chunk stride; their loads and those
+  // of the log-decay are in flight while the first half of dS_1 is staged
   float Gc[4][4];
+  {
+    float dv4[4][4];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const int i = 4 * tg + e;
-    float dv4[4], gv[4];
-    load4v<T>(p.d_out, seq_idx(i) + kc0, dv4);
-    load4v<G>(p.g, seq_idx(i) + kc0, gv);
-    *reinterpret_cast<float4*>(smem + kOffStack + ((64 + i) >> 3) * kRsN + c4 * kCsN + (i & 7) * 16) =
-        make_float4(dv4[0], dv4[1], dv4[2], dv4[3]);
+    for (int e = 0; e < 4; ++e) {
+      load4v<T>(p.d_out, seq_idx(4 * tg + e) + kc0, dv4[e]);
+      load4v<G>(p.g, seq_idx(4 * tg + e) + kc0, Gc[e]);
+    }
+    load_ds1_half(0);
 #pragma unroll
-    for (int f = 0; f < 4; ++f) Gc[e][f] = (e ? Gc[e - 1][f] : 0.f) + gv[f];
+    for (int e = 0; e < 4; ++e) {
+      const int i = 4 * tg + e;
+      *reinterpret_cast<float4*>(smem + kOffStack + ((64 + i) >> 3) * kRsN + c4 * kCsN + (i & 7) * 16) =
+          make_float4(dv4[e][0], dv4[e][1], dv4[e][2], dv4[e][3]);
+      if (e > 0) {
+#pragma unroll
+        for (int f = 0; f < 4; ++f) Gc[e][f] += Gc[e - 1][f];
+      }
+    }
   }
 #pragma unroll
   for (int f = 0; f < 4; ++f) ms.part[tg][kc0 + f] = Gc[3][f];
@@ -459,7 +481,13 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
     }
     mma_commit(&ms.bar_m);
   }
-  // log-decay prefixes while the tensor cores work
+  // S_0 on its way into registers, and the log-decay prefixes, while the tensor cores work
+  float4 s0buf[8];
+#pragma unroll
+  for (int x = 0; x < 8; ++x) {
+    const int qd = tid + 512 * x;  // key row = (qd & 7) + 8 (qd >> 8), 4-value chunk = (qd >> 3) & 31
+    s0buf[x] = *reinterpret_cast<const float4*>(s0_src + ((qd & 7) + 8 * (qd >> 8)) * kDim + 4 * ((qd >> 3) & 31));
+  }
   if (tid < kDim) {
     float run = 0.f;
 #pragma unroll
@@ -475,36 +503,39 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
   tc_fence_after();
 
   // ---- S_0 (whole) over the dR^T / T^T operands of M1, second half of dS_1 over the first -----------
-  {
-    float4 buf[8];
 #pragma unroll
-    for (int x = 0; x < 8; ++x) {
-      const int qd = tid + 512 * x;  // key row = (qd & 7) + 8 (qd >> 8), 4-value chunk = (qd >> 3) & 31
-      buf[x] = *reinterpret_cast<const float4*>(s0_src + ((qd & 7) + 8 * (qd >> 8)) * kDim + 4 * ((qd >> 3) & 31));
-    }
-#pragma unroll
-    for (int x = 0; x < 8; ++x) {
-      const int qd = tid + 512 * x;
-      *reinterpret_cast<float4*>(smem + kOffS0 + (qd >> 8) * 4096 + ((qd >> 3) & 31) * 128 + (qd & 7) * 16) = rn4(buf[x]);
-    }
+  for (int x = 0; x < 8; ++x) {
+    const int qd = tid + 512 * x;
+    *reinterpret_cast<float4*>(smem + kOffS0 + (qd >> 8) * 4096 + ((qd >> 3) & 31) * 128 + (qd & 7) * 16) = rn4(s0buf[x]);
   }
   load_ds1_half(1);
   // ---- dZ: into the stack (rows j), and dv = dZ w, dw = dZ v; each warp of a quadrant takes 16 tokens --
   {
     const int vrow = 32 * q4 + lane;
+    // every load is issued before the first store: the outputs may alias the inputs as far as the
+    // compiler knows, so a load placed after a store would wait for the round trip before it
+    float wv[16], vv[16];
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj) {
+      const int64_t idx = seq_idx(16 * part + jj) + vrow;
+      wv[jj] = ldf<T>(p.w, idx);
+      vv[jj] = ldf<T>(p.v, idx);
+    }
     uint32_t r[16];
     tmem_ld16(tmem_addr(tb, 32 * q4, kColDz + 16 * part), r);
     tmem_wait_ld();
 #pragma unroll
     for (int jj = 0; jj < 16; ++jj) {
       const int j = 16 * part + jj;
-      const float dz = __uint_as_float(r[jj]);
       *reinterpret_cast<float*>(smem + kOffStack + (j >> 3) * kRsN + (vrow >> 2) * kCsN + (j & 7) * 16 + (vrow & 3) * 4) =
-          to_tf32(dz);
-      const int64_t idx = seq_idx(j) + vrow;
-      const float wv = ldf<T>(p.w, idx), vv = ldf<T>(p.v, idx);
-      stf<T>(p.dv, idx, dz * wv);
-      stf<T>(p.dw, idx, dz * vv);
+          to_tf32(__uint_as_float(r[jj]));
+    }
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj) {
+      const int64_t idx = seq_idx(16 * part + jj) + vrow;
+      const float dz = __uint_as_float(r[jj]);
+      stf<T>(p.dv, idx, dz * wv[jj]);
+      stf<T>(p.dw, idx, dz * vv[jj]);
     }
   }
   fence_async_smem();
@@ -664,7 +695,7 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
 #pragma unroll
     for (int sb = 0; sb < 2; ++sb) {
       const int i0 = 16 * blk + 8 * sb;
-      float Gb[8], kv[8], bv[8], P3[8], P2[8], dG[8], x[8], y[8];
+      float Gb[8], kv[8], bv[8], sq[8], P3[8], P2[8], dG[8], x[8], y[8];
       float loc = 0.f;
 #pragma unroll
       for (int t = 0; t < 8; ++t) {
@@ -673,6 +704,7 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
         Gb[t] = loc + ms.part[(i0 + t) >> 2][kc];
         kv[t] = ldf<T>(p.k, idx);
         bv[t] = ldf<T>(p.beta, idx);
+        sq[t] = p.scale * ldf<T>(p.q, idx);  // loaded here: no global load may follow a global store
       }
       tmem_ld8f(tmem_addr(tb, 32 * q4, kColD4 + i0), x);  // dKt
 #pragma unroll
@@ -714,8 +746,7 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
         const int64_t idx = seq_idx(i0 + t) + kc;
         const float eg = __expf(Gb[t]), ea = __expf(Gb[t] - a_me);
         const float P1 = fmaf(x[t], eg, y[t] * ea);
-        const float sq = p.scale * ldf<T>(p.q, idx);
-        const float dGt = fmaf(to_tf32(sq * ea), y[t], fmaf(sq * eg, x[t], dG[t]));
+        const float dGt = fmaf(to_tf32(sq[t] * ea), y[t], fmaf(sq[t] * eg, x[t], dG[t]));
         stf<T>(p.dq, idx, p.scale * P1);
         stf<T>(p.dk, idx, fmaf(bv[t], P2[t], P3[t]));
         stf<T>(p.dbeta, idx, kv[t] * P2[t]);

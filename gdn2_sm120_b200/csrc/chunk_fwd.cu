@@ -456,7 +456,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
 // ---------------------------------------------------------------------------------------------
 // scan kernel
 // ---------------------------------------------------------------------------------------------
-constexpr int kScanThreads = 128;
+constexpr int kScanThreads = 512;
 
 struct ScanSmem {
   alignas(128) uint8_t y[32768];
@@ -488,7 +488,10 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
   const WsLayout ws{p.n_ch, p.training != 0};
   BoundedWaiter waiter(p.status);
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  // 16 warps: warp & 3 = TMEM lane quadrant (a warp reaches only the 32 lanes of its quadrant),
+  // warp >> 2 = its quarter of the columns of whatever accumulator is being moved
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int q4 = warp & 3, part = warp >> 2;
   const int64_t bh = blockIdx.x;
   const int64_t b = bh / p.H, h = bh % p.H;
   constexpr uint32_t kColS = 0, kColR = 128, kColO = 192;
@@ -509,8 +512,10 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
   __syncthreads();
   tc_fence_after();
   const uint32_t tb = sm.tmem_base;
-  const uint32_t lane_base = 32u * warp;   // this warp's TMEM lane quadrant; thread = lane = value row
-  const int vrow = tid;
+  const uint32_t lane_base = 32u * q4;
+  const int vrow = 32 * q4 + lane;   // value row of the transposed state = TMEM lane
+  const int k0 = 32 * part;          // this thread's quarter of the 128 key columns
+  const int i0 = 16 * part;          // ... and of the 64 token columns
 
   auto ch_of = [&](int64_t c) { return (b * p.n_chunks + c) * p.H + h; };
   auto load_yqa = [&](int64_t c) {
@@ -537,16 +542,13 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
     load_kt(0);
   }
 
-  // ---- S^T <- S_0^T : thread v gathers column v of the key-major state --------------------------
+  // ---- S^T <- S_0^T : thread (v, part) gathers 32 key rows of column v of the key-major state ------
   {
     const float* src = (p.s_in != nullptr) ? p.s_in + bh * int64_t(kDim) * kDim + vrow : nullptr;
+    uint32_t r[32];
 #pragma unroll
-    for (int c0 = 0; c0 < kDim; c0 += 32) {
-      uint32_t r[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) r[j] = (src != nullptr) ? __float_as_uint(src[(c0 + j) * kDim]) : 0u;
-      tmem_st32(tmem_addr(tb, lane_base, kColS + c0), r);
-    }
+    for (int j = 0; j < 32; ++j) r[j] = (src != nullptr) ? __float_as_uint(src[(k0 + j) * kDim]) : 0u;
+    tmem_st32(tmem_addr(tb, lane_base, kColS + k0), r);
     tmem_wait_st();
   }
 
@@ -559,20 +561,17 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
       tc_fence_after();
       if (tid == 0) load_kt(c);
     }
-    // ---- R^T <- U^T (thread v copies row v of the U^T tile into TMEM) ------------------------------
+    // ---- R^T <- U^T (16 token columns of row v of the U^T tile into TMEM) ---------------------------
     waiter.wait(&sm.bar_ut, par);
     {
-      const uint8_t* row = sm.ut + (vrow >> 3) * 2048 + (vrow & 7) * 16;
+      const uint8_t* row = sm.ut + (vrow >> 3) * 2048 + (vrow & 7) * 16 + (i0 / 4) * 128;
+      uint32_t r[16];
 #pragma unroll
-      for (int c0 = 0; c0 < kChunk; c0 += 32) {
-        uint32_t r[32];
-#pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
-          const uint4 x = *reinterpret_cast<const uint4*>(row + (c0 / 4 + c4) * 128);
-          r[4 * c4] = x.x; r[4 * c4 + 1] = x.y; r[4 * c4 + 2] = x.z; r[4 * c4 + 3] = x.w;
-        }
-        tmem_st32(tmem_addr(tb, lane_base, kColR + c0), r);
+      for (int c4 = 0; c4 < 4; ++c4) {
+        const uint4 x = *reinterpret_cast<const uint4*>(row + c4 * 128);
+        r[4 * c4] = x.x; r[4 * c4 + 1] = x.y; r[4 * c4 + 2] = x.z; r[4 * c4 + 3] = x.w;
       }
+      tmem_st16(tmem_addr(tb, lane_base, kColR + i0), r);
       tmem_wait_st();
     }
     waiter.wait(&sm.bar_yqa, par);
@@ -606,32 +605,24 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
     if (tid == 0 && c + 1 < p.n_chunks) load_yqa(c + 1);  // the three MMAs no longer read Y, Q, A
 
     // ---- training: keep the residual R = U - Y S_0 (natural tile X[r = j][c = v]) for backward ------
-    if (p.training) {
-      uint8_t* blob_rn = p.ws_out + ws.off_rn() + ch_of(c) * kBlobRn + (vrow >> 2) * 128 + (vrow & 3) * 4;
+    {
+      uint32_t rr[16], ro[16];
+      if (p.training) tmem_ld16(tmem_addr(tb, lane_base, kColR + i0), rr);
+      tmem_ld16(tmem_addr(tb, lane_base, kColO + i0), ro);
+      tmem_wait_ld();
+      if (p.training) {
+        uint8_t* blob_rn = p.ws_out + ws.off_rn() + ch_of(c) * kBlobRn + (vrow >> 2) * 128 + (vrow & 3) * 4;
 #pragma unroll
-      for (int c0 = 0; c0 < kChunk; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_addr(tb, lane_base, kColR + c0), r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int tok = c0 + j;
-          *reinterpret_cast<float*>(blob_rn + (tok >> 3) * 4096 + (tok & 7) * 16) = to_tf32(__uint_as_float(r[j]));
+        for (int j = 0; j < 16; ++j) {
+          const int tok = i0 + j;
+          *reinterpret_cast<float*>(blob_rn + (tok >> 3) * 4096 + (tok & 7) * 16) = to_tf32(__uint_as_float(rr[j]));
         }
       }
-    }
-    // ---- output rows of this chunk: thread v writes o[t0 + i][v] ----------------------------------
-    {
+      // ---- output rows of this chunk: o[t0 + i][v] ---------------------------------------------------
       T* out = static_cast<T*>(p.out);
 #pragma unroll
-      for (int c0 = 0; c0 < kChunk; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_addr(tb, lane_base, kColO + c0), r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          out[((b * p.T + t0 + c0 + j) * p.H + h) * kDim + vrow] = from_float<T>(__uint_as_float(r[j]));
-        }
+      for (int j = 0; j < 16; ++j) {
+        out[((b * p.T + t0 + i0 + j) * p.H + h) * kDim + vrow] = from_float<T>(__uint_as_float(ro[j]));
       }
     }
     // ---- checkpoint the chunk-start state, then decay the accumulator: S^T <- S^T diag(d) ----------
@@ -640,31 +631,28 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
       float* ck = (p.bnd != nullptr)
                       ? p.bnd + ((b * (p.n_chunks + 1) + c) * p.H + h) * int64_t(kDim) * kDim + vrow
                       : nullptr;
+      uint32_t r[32];
+      tmem_ld32(tmem_addr(tb, lane_base, kColS + k0), r);
+      tmem_wait_ld();
+      if (ck != nullptr) {
 #pragma unroll
-      for (int c0 = 0; c0 < kDim; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_addr(tb, lane_base, kColS + c0), r);
-        tmem_wait_ld();
-        if (ck != nullptr) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) ck[(c0 + j) * kDim] = __uint_as_float(r[j]);
-        }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * sm.d[c0 + j]);
-        tmem_st32(tmem_addr(tb, lane_base, kColS + c0), r);
+        for (int j = 0; j < 32; ++j) ck[(k0 + j) * kDim] = __uint_as_float(r[j]);
       }
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * sm.d[k0 + j]);
+      tmem_st32(tmem_addr(tb, lane_base, kColS + k0), r);
       tmem_wait_st();
     }
     tc_fence_before();
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
-      const uint32_t k0 = smem_u32(sm.kt);
+      const uint32_t kt0 = smem_u32(sm.kt);
       const uint32_t id_s = idesc(128, 128, kFmtTF32, kMajorK, kMajorK);
       // S^T += R^T Kt   (B tile X[r = key][c = token])
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        mma_tf32_ts(tb + kColS, tb + kColR + ks * 8, smem_desc(k0 + ks * 256, 128, 2048), id_s, 1u);
+        mma_tf32_ts(tb + kColS, tb + kColR + ks * 8, smem_desc(kt0 + ks * 256, 128, 2048), id_s, 1u);
       }
       mma_commit(&sm.bar_mma2);
     }
@@ -680,16 +668,13 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
     float* ck = (p.bnd != nullptr)
                     ? p.bnd + ((b * (p.n_chunks + 1) + p.n_chunks) * p.H + h) * int64_t(kDim) * kDim + vrow
                     : nullptr;
+    uint32_t r[32];
+    tmem_ld32(tmem_addr(tb, lane_base, kColS + k0), r);
+    tmem_wait_ld();
 #pragma unroll
-    for (int c0 = 0; c0 < kDim; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld32(tmem_addr(tb, lane_base, kColS + c0), r);
-      tmem_wait_ld();
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        if (fin != nullptr) fin[(c0 + j) * kDim] = __uint_as_float(r[j]);
-        if (ck != nullptr) ck[(c0 + j) * kDim] = __uint_as_float(r[j]);
-      }
+    for (int j = 0; j < 32; ++j) {
+      if (fin != nullptr) fin[(k0 + j) * kDim] = __uint_as_float(r[j]);
+      if (ck != nullptr) ck[(k0 + j) * kDim] = __uint_as_float(r[j]);
     }
   }
   tc_fence_before();
