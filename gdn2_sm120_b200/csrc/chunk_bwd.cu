@@ -55,25 +55,6 @@ struct BScanParams {
   int64_t T, H, n_chunks, n_ch;
 };
 
-// raw 4-element load of a 16-bit sequence tensor (kept packed until it is needed)
-template <typename T>
-__device__ __forceinline__ uint2 load4_raw(const void* base, int64_t idx) {
-  return *reinterpret_cast<const uint2*>(static_cast<const T*>(base) + idx);
-}
-template <typename T>
-__device__ __forceinline__ void unpack4(uint2 raw, float (&out)[4]);
-template <>
-__device__ __forceinline__ void unpack4<__nv_bfloat16>(uint2 raw, float (&out)[4]) {
-  out[0] = __uint_as_float(raw.x << 16); out[1] = __uint_as_float(raw.x & 0xffff0000u);
-  out[2] = __uint_as_float(raw.y << 16); out[3] = __uint_as_float(raw.y & 0xffff0000u);
-}
-template <>
-__device__ __forceinline__ void unpack4<__half>(uint2 raw, float (&out)[4]) {
-  const __half2* hh = reinterpret_cast<const __half2*>(&raw);
-  const float2 a = __half22float2(hh[0]), c = __half22float2(hh[1]);
-  out[0] = a.x; out[1] = a.y; out[2] = c.x; out[3] = c.y;
-}
-
 template <typename T>
 __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const BScanParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -124,14 +105,14 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
     bulk_g2s(sm.d, p.ws + ws.off_d() + ch * kBlobD, uint32_t(kBlobD), &sm.bar_qy);
   };
   // dO of one chunk: 4 tokens x 4 channels per thread, still packed
-  auto load_do = [&](int64_t c, uint2 (&raw)[4]) {
+  auto load_do = [&](int64_t c, typename Raw4<T>::type (&raw)[4]) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       raw[e] = load4_raw<T>(p.d_out, ((b * p.T + c * kChunk + 4 * tg + e) * p.H + h) * kDim + 4 * lane);
     }
   };
 
-  uint2 do_raw[4] = {};
+  typename Raw4<T>::type do_raw[4] = {};
   if (p.n_chunks > 0) {
     if (tid == 0) {
       load_ak(p.n_chunks - 1);

@@ -111,6 +111,32 @@ __device__ __forceinline__ void load8<float>(const void* base, int64_t idx, floa
   out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
 }
 
+// 4 consecutive sequence elements, kept packed until they are needed (a prefetch then costs 2 or 4
+// registers per group instead of 4 floats)
+template <typename T> struct Raw4 { using type = uint2; };
+template <> struct Raw4<float> { using type = float4; };
+template <typename T>
+__device__ __forceinline__ typename Raw4<T>::type load4_raw(const void* base, int64_t idx) {
+  return *reinterpret_cast<const typename Raw4<T>::type*>(static_cast<const T*>(base) + idx);
+}
+template <typename T>
+__device__ __forceinline__ void unpack4(typename Raw4<T>::type raw, float (&out)[4]);
+template <>
+__device__ __forceinline__ void unpack4<__nv_bfloat16>(uint2 raw, float (&out)[4]) {
+  out[0] = __uint_as_float(raw.x << 16); out[1] = __uint_as_float(raw.x & 0xffff0000u);
+  out[2] = __uint_as_float(raw.y << 16); out[3] = __uint_as_float(raw.y & 0xffff0000u);
+}
+template <>
+__device__ __forceinline__ void unpack4<__half>(uint2 raw, float (&out)[4]) {
+  const __half2* hh = reinterpret_cast<const __half2*>(&raw);
+  const float2 a = __half22float2(hh[0]), c = __half22float2(hh[1]);
+  out[0] = a.x; out[1] = a.y; out[2] = c.x; out[3] = c.y;
+}
+template <>
+__device__ __forceinline__ void unpack4<float>(float4 raw, float (&out)[4]) {
+  out[0] = raw.x; out[1] = raw.y; out[2] = raw.z; out[3] = raw.w;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);

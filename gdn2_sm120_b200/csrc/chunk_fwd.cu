@@ -39,7 +39,8 @@ namespace {
 // Shared-memory tiles written this way use padded strides so that the 8 lanes of a store phase hit
 // 8 different 16-byte bank groups: natural tiles CS = 144 (chunk stride), transposed tiles RS = 2064.
 constexpr int kPrepThreads = 512;
-constexpr int kLd = 65;           // leading dimension of the fp32 64x64 scratch matrices
+constexpr int kLd = 68;           // leading dimension of the fp32 64x64 scratch matrices (16-byte rows, banks shift by 4)
+constexpr int kLdW = 20;          // leading dimension of the transposed 16x16 block products
 constexpr int kCsN = 144;         // natural tiles: byte stride between 16-byte column chunks
 constexpr int kRsN = 32 * kCsN;   // natural tiles of 128 fp32 columns: byte stride between 8-row groups (4608)
 constexpr int kRsT = 2064;        // transposed tiles (64 fp32 columns): byte stride between 8-row groups
@@ -70,28 +71,6 @@ struct PrepParams {
 __device__ __forceinline__ int gram_b_offset(int I) { return kRsN * ((I == 0) ? 0 : (I == 1) ? 2 : (I == 2) ? 6 : 12); }
 __device__ __forceinline__ int gram_col(int I) { return (I == 0) ? 0 : (I == 1) ? 16 : (I == 2) ? 48 : 96; }
 
-// load 4 consecutive sequence elements
-template <typename T>
-__device__ __forceinline__ void load4s(const void* base, int64_t idx, float (&out)[4]);
-template <>
-__device__ __forceinline__ void load4s<__nv_bfloat16>(const void* base, int64_t idx, float (&out)[4]) {
-  const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(base) + idx);
-  out[0] = __uint_as_float(raw.x << 16); out[1] = __uint_as_float(raw.x & 0xffff0000u);
-  out[2] = __uint_as_float(raw.y << 16); out[3] = __uint_as_float(raw.y & 0xffff0000u);
-}
-template <>
-__device__ __forceinline__ void load4s<__half>(const void* base, int64_t idx, float (&out)[4]) {
-  const uint2 raw = *reinterpret_cast<const uint2*>(static_cast<const __half*>(base) + idx);
-  const __half2* h = reinterpret_cast<const __half2*>(&raw);
-  const float2 a = __half22float2(h[0]), b = __half22float2(h[1]);
-  out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
-}
-template <>
-__device__ __forceinline__ void load4s<float>(const void* base, int64_t idx, float (&out)[4]) {
-  const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(base) + idx);
-  out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
-}
-
 template <typename T, typename G>
 __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -102,11 +81,6 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
   const bool training = p.training != 0;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int64_t ch = blockIdx.x;
-  const int64_t h = ch % p.H;
-  const int64_t c = (ch / p.H) % p.n_chunks;
-  const int64_t b = ch / (p.H * p.n_chunks);
-  const int64_t t0 = c * kChunk;
 
   if (warp == 0) {
     tmem_alloc(&sm.tmem_base, 256);
@@ -118,31 +92,58 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     fence_mbar_init();
   }
 
-  // ---- every global load of the chunk is issued up front ------------------------------------------
-  const int tg = warp, c4 = lane;
+  // a warp holds two neighbouring token groups x 16 channel groups: a store of one token row per lane
+  // then touches 16 lines of a blocked tile (two 16-byte pieces each) instead of 32
+  const int tg = 2 * (warp >> 1) + (lane >> 4), c4 = 16 * (warp & 1) + (lane & 15);
   const int kc0 = 4 * c4;
+  const int q4 = warp & 3, part = warp >> 2;  // TMEM lane quadrant of this warp, and its share of the columns
+
+  const int64_t ch = blockIdx.x;
+  auto seq_index = [&](int64_t ch_, int e) {
+    const int64_t h_ = ch_ % p.H, c_ = (ch_ / p.H) % p.n_chunks, b_ = ch_ / (p.H * p.n_chunks);
+    return ((b_ * p.T + c_ * kChunk + 4 * tg + e) * p.H + h_) * kDim + kc0;
+  };
+  // ---- every global load of the chunk is issued up front, the log-decay first: the prefix sums below
+  // wait for it alone while the other five tensors are still streaming in -----------------------------
   float Gc[4][4], kk[4][4], qq[4][4], bb[4][4], zz[4][4];
+  {
+    typename Raw4<G>::type rg[4];
+    typename Raw4<T>::type rk[4], rq[4], rb[4], rv[4], rw[4];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const int64_t idx = ((b * p.T + t0 + 4 * tg + e) * p.H + h) * kDim + kc0;
-    float gv[4], vv[4], ww[4];
-    load4s<G>(p.g, idx, gv);
-    load4s<T>(p.k, idx, kk[e]);
-    load4s<T>(p.q, idx, qq[e]);
-    load4s<T>(p.beta, idx, bb[e]);
-    load4s<T>(p.v, idx, vv);
-    load4s<T>(p.w, idx, ww);
+    for (int e = 0; e < 4; ++e) rg[e] = load4_raw<G>(p.g, seq_index(ch, e));
 #pragma unroll
-    for (int f = 0; f < 4; ++f) {
-      Gc[e][f] = (e ? Gc[e - 1][f] : 0.f) + gv[f];
-      zz[e][f] = to_tf32(vv[f] * ww[f]);
+    for (int e = 0; e < 4; ++e) {
+      const int64_t idx = seq_index(ch, e);
+      rk[e] = load4_raw<T>(p.k, idx);
+      rq[e] = load4_raw<T>(p.q, idx);
+      rb[e] = load4_raw<T>(p.beta, idx);
+      rv[e] = load4_raw<T>(p.v, idx);
+      rw[e] = load4_raw<T>(p.w, idx);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float gv[4];
+      unpack4<G>(rg[e], gv);
+#pragma unroll
+      for (int f = 0; f < 4; ++f) Gc[e][f] = (e ? Gc[e - 1][f] : 0.f) + gv[f];
+    }
+#pragma unroll
+    for (int f = 0; f < 4; ++f) sm.part[tg][kc0 + f] = Gc[3][f];
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float vv[4], ww[4];
+      unpack4<T>(rk[e], kk[e]);
+      unpack4<T>(rq[e], qq[e]);
+      unpack4<T>(rb[e], bb[e]);
+      unpack4<T>(rv[e], vv);
+      unpack4<T>(rw[e], ww);
+#pragma unroll
+      for (int f = 0; f < 4; ++f) zz[e][f] = to_tf32(vv[f] * ww[f]);
     }
   }
-#pragma unroll
-  for (int f = 0; f < 4; ++f) sm.part[tg][kc0 + f] = Gc[3][f];
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
   const uint32_t tb = sm.tmem_base;
   if (tid < kDim) {
     float run = 0.f;
@@ -244,15 +245,14 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
   // ---- Gram products on the tensor cores: P_I = [E_a ; Q_a] (K^I)^T -----------------------------
   if (tid == 0) {
     tc_fence_after();
+    // the four anchored copies K^0 .. K^3 are stacked (16 + 32 + 48 + 64 = 160 rows) and their products
+    // sit side by side in TMEM, so one N = 160 instruction per k-step reads the A tile once for all four
+    const uint32_t id = idesc(128, 160, kFmtTF32, kMajorK, kMajorK);
+    const uint32_t a0 = smem_u32(sm.gram_a), b0 = smem_u32(sm.gram_b);
 #pragma unroll
-    for (int I = 0; I < 4; ++I) {
-      const uint32_t id = idesc(128, 16 * (I + 1), kFmtTF32, kMajorK, kMajorK);
-      const uint32_t a0 = smem_u32(sm.gram_a), b0 = smem_u32(sm.gram_b + gram_b_offset(I));
-#pragma unroll
-      for (int ks = 0; ks < 16; ++ks) {
-        mma_tf32_ss(tb + gram_col(I), smem_desc(a0 + ks * 2 * kCsN, kCsN, kRsN),
-                    smem_desc(b0 + ks * 2 * kCsN, kCsN, kRsN), id, ks > 0 ? 1u : 0u);
-      }
+    for (int ks = 0; ks < 16; ++ks) {
+      mma_tf32_ss(tb, smem_desc(a0 + ks * 2 * kCsN, kCsN, kRsN), smem_desc(b0 + ks * 2 * kCsN, kCsN, kRsN), id,
+                  ks > 0 ? 1u : 0u);
     }
     mma_commit(&sm.bar[0]);
   }
@@ -263,7 +263,9 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
   float* Ln = reinterpret_cast<float*>(sm.gram_a);           // [64][kLd]   L
   float* Tn = Ln + 64 * kLd;                                  // [64][kLd]   T
   float* An = Tn + 64 * kLd;                                  // [64][kLd]   A_qk, natural (training)
-  float* Wn = An + 64 * kLd;                                  // [3][16][17] block products
+  float* Tc = An + 64 * kLd;                                  // [64][kLd]   T transposed: Tc[j][i] = T[i][j]
+  float* Wt = Tc + 64 * kLd;                                  // [3][16][kLdW] block products, transposed
+  static_assert((4 * 64 * kLd + 3 * 16 * kLdW) * 4 <= 16 * kRsN, "fp32 scratch exceeds the Gram A region");
   uint8_t* et_tile = sm.gram_b;                               // E^T  X[r = k][c = j], tf32, RS kRsT
   uint8_t* zt_tile = sm.gram_b + kTileT;                      // Z^T  X[r = v][c = j], tf32, RS kRsT
 #pragma unroll
@@ -272,7 +274,6 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     *reinterpret_cast<float4*>(et_tile + off) = make_float4(ebar[0][f], ebar[1][f], ebar[2][f], ebar[3][f]);
     *reinterpret_cast<float4*>(zt_tile + off) = make_float4(zz[0][f], zz[1][f], zz[2][f], zz[3][f]);
   }
-  const int q4 = warp & 3, part = warp >> 2;  // TMEM lane quadrant of this warp, and its share of the columns
   {
     // pull L (rows 0..63) into fp32 scratch and A_qk (rows 64..127) into the workspace;
     // the four warps of a quadrant take 16 columns each
@@ -310,11 +311,20 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
       }
     }
   }
-  for (int e = tid; e < 64 * 64; e += kPrepThreads) Tn[(e >> 6) * kLd + (e & 63)] = 0.f;
+  for (int e = tid; e < 64 * kLd / 4; e += kPrepThreads) {
+    reinterpret_cast<float4*>(Tn)[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+    reinterpret_cast<float4*>(Tc)[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   tc_fence_before();
   __syncthreads();
 
-  // ---- T = (I + L)^-1, blocked: 16x16 diagonal blocks by substitution, the rest by block products --
+  // ---- T = (I + L)^-1, blocked: 16x16 diagonal blocks by substitution, the rest by block products.
+  // T is kept in both orientations (Tn row-major, Tc column-major) and the block products W transposed,
+  // so that both factors of every inner product are read as 16-byte vectors along the summed index.
+  auto ld4 = [](const float* ptr) { return *reinterpret_cast<const float4*>(ptr); };
+  auto dot4 = [](float4 a, float4 b, float s) {
+    return fmaf(a.w, b.w, fmaf(a.z, b.z, fmaf(a.y, b.y, fmaf(a.x, b.x, s))));
+  };
   if (tid < 64) {
     const int I = tid >> 4, cc = tid & 15;
     float x[16];
@@ -322,11 +332,22 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     for (int r = 0; r < 16; ++r) {
       float s = (r == cc) ? 1.f : 0.f;
 #pragma unroll
-      for (int m = 0; m < r; ++m) s = fmaf(-Ln[(16 * I + r) * kLd + 16 * I + m], x[m], s);
+      for (int m4 = 0; m4 < (r + 3) / 4; ++m4) {
+        const float4 l = ld4(Ln + (16 * I + r) * kLd + 16 * I + 4 * m4);
+        if (4 * m4 + 0 < r) s = fmaf(-l.x, x[4 * m4 + 0], s);
+        if (4 * m4 + 1 < r) s = fmaf(-l.y, x[4 * m4 + 1], s);
+        if (4 * m4 + 2 < r) s = fmaf(-l.z, x[4 * m4 + 2], s);
+        if (4 * m4 + 3 < r) s = fmaf(-l.w, x[4 * m4 + 3], s);
+      }
       x[r] = s;
     }
 #pragma unroll
     for (int r = 0; r < 16; ++r) Tn[(16 * I + r) * kLd + 16 * I + cc] = x[r];
+#pragma unroll
+    for (int r4 = 0; r4 < 4; ++r4) {
+      *reinterpret_cast<float4*>(Tc + (16 * I + cc) * kLd + 16 * I + 4 * r4) =
+          make_float4(x[4 * r4], x[4 * r4 + 1], x[4 * r4 + 2], x[4 * r4 + 3]);
+    }
   }
   __syncthreads();
   for (int d = 1; d < 4; ++d) {
@@ -335,19 +356,24 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     for (int e = tid; e < n_pairs * 256; e += kPrepThreads) {
       const int pair = e >> 8, r = (e >> 4) & 15, cc = e & 15;
       const int J = pair, I = pair + d;
+      const float* lrow = Ln + (16 * I + r) * kLd + 16 * J;
+      const float* tcol = Tc + (16 * J + cc) * kLd + 16 * J;
       float s = 0.f;
-      for (int m = 16 * J; m < 16 * I; ++m) s = fmaf(Ln[(16 * I + r) * kLd + m], Tn[m * kLd + 16 * J + cc], s);
-      Wn[(pair * 16 + r) * 17 + cc] = s;
+      for (int m4 = 0; m4 < 4 * d; ++m4) s = dot4(ld4(lrow + 4 * m4), ld4(tcol + 4 * m4), s);
+      Wt[(pair * 16 + cc) * kLdW + r] = s;
     }
     __syncthreads();
     // T_IJ = -T_II W
     for (int e = tid; e < n_pairs * 256; e += kPrepThreads) {
       const int pair = e >> 8, r = (e >> 4) & 15, cc = e & 15;
       const int J = pair, I = pair + d;
+      const float* trow = Tn + (16 * I + r) * kLd + 16 * I;
+      const float* wcol = Wt + (pair * 16 + cc) * kLdW;
       float s = 0.f;
 #pragma unroll
-      for (int m = 0; m < 16; ++m) s = fmaf(Tn[(16 * I + r) * kLd + 16 * I + m], Wn[(pair * 16 + m) * 17 + cc], s);
+      for (int m4 = 0; m4 < 4; ++m4) s = dot4(ld4(trow + 4 * m4), ld4(wcol + 4 * m4), s);
       Tn[(16 * I + r) * kLd + 16 * J + cc] = -s;
+      Tc[(16 * J + cc) * kLd + 16 * I + r] = -s;
     }
     __syncthreads();
   }
@@ -356,17 +382,17 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     uint8_t* blob_t = p.ws + ws.off_t() + ch * kBlobT;
     for (int e = tid; e < 64 * 16; e += kPrepThreads) {
       const int i = e & 63, c4t = e >> 6;  // consecutive threads -> consecutive rows -> contiguous 16-byte chunks
-      const float4 val = make_float4(to_tf32(Tn[i * kLd + 4 * c4t]), to_tf32(Tn[i * kLd + 4 * c4t + 1]),
-                                     to_tf32(Tn[i * kLd + 4 * c4t + 2]), to_tf32(Tn[i * kLd + 4 * c4t + 3]));
+      const float4 tn = ld4(Tn + i * kLd + 4 * c4t);
+      const float4 val = make_float4(to_tf32(tn.x), to_tf32(tn.y), to_tf32(tn.z), to_tf32(tn.w));
       const uint32_t off = blk_off<4>(i, 4 * c4t, 2048, 128);
       *reinterpret_cast<float4*>(sm.tmat + off) = val;
       *reinterpret_cast<float4*>(blob_t + off) = val;
       if (training) {
         // transposed tiles X[r = j][c = i]: here `i` plays the role of the row j, 4*c4t.. of the column i
         const int j = i;
+        const float4 tc = ld4(Tc + j * kLd + 4 * c4t);
         *reinterpret_cast<float4*>(p.ws + ws.off_tt() + ch * kBlobTt + off) =
-            make_float4(to_tf32(Tn[(4 * c4t) * kLd + j]), to_tf32(Tn[(4 * c4t + 1) * kLd + j]),
-                        to_tf32(Tn[(4 * c4t + 2) * kLd + j]), to_tf32(Tn[(4 * c4t + 3) * kLd + j]));
+            make_float4(to_tf32(tc.x), to_tf32(tc.y), to_tf32(tc.z), to_tf32(tc.w));
         *reinterpret_cast<float4*>(p.ws + ws.off_at() + ch * kBlobAt + off) =
             make_float4(An[(4 * c4t) * kLd + j], An[(4 * c4t + 1) * kLd + j], An[(4 * c4t + 2) * kLd + j],
                         An[(4 * c4t + 3) * kLd + j]);
