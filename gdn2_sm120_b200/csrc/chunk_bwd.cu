@@ -3,12 +3,12 @@
 //
 //   chunk_bwd_scan_kernel  one CTA per (batch, head), chunks in reverse order.  The state
 //                          cotangent lives transposed (dS^T: value rows x key columns) in TMEM:
-//                              dR^T  = dO^T Aqk + dS^T Kt^T
+//                              dR^T  = dO^T Aqk + dS^T Kt^T        dZ^T = dR^T T
 //                              dS^T <- dS^T diag(d) + dO^T Qg - dR^T Y
-//                          It writes dR^T per chunk and the cotangent at every chunk start.
+//                          It writes dZ = T^T dR per chunk and the cotangent at every chunk start.
 //   chunk_bwd_vjp_kernel   one CTA per (batch, chunk, head), all chunks in parallel.  With
 //                          R = T (Z - E S_0) as the parametrisation (no Y / U needed):
-//                              dZ = T^T dR                      dv = dZ w, dw = dZ v
+//                              dv = dZ w, dw = dZ v             (dZ = T^T dR comes from the scan)
 //                              [-dE ; dQg] = [dZ ; dO] S_0^T    dKt = R dS_1^T
 //                              [-dL ; dA]  = [dZ ; dO] R^T      (strictly lower / lower part)
 //                          then the Gram products' VJP with the same 16-token block anchors as the
@@ -17,6 +17,8 @@
 //
 // Reference counterparts: boundary scan  src/gdn2_sm120/backward_parallel.py:721-1049,
 // compact-WY VJP  src/gdn2_sm120/backward_wy.py:226-1168 (a 10-12 launch graph there).
+
+#include <cuda.h>
 
 #include "chunk_common.cuh"
 
@@ -33,6 +35,7 @@ constexpr int64_t kStateElems = int64_t(kDim) * kDim;
 // =============================================================================================
 constexpr int kBScanThreads = 512;
 constexpr int kRsDot = 2064;   // dO^T tile: padded row-group stride (16-byte chunk stores, 4 tokens each)
+constexpr int kCsZ = 144, kRsZ = 32 * kCsZ;  // dZ tile: the padded strides of the VJP kernel's [dZ ; dO] stack
 
 struct BScanSmem {
   alignas(128) uint8_t dot[16 * kRsDot];  // dO^T tile X[r = v][c = i], tf32 (built from dO)
@@ -40,6 +43,8 @@ struct BScanSmem {
   alignas(128) uint8_t qt[32768];    // Qg^T     X[r = k][c = i]
   alignas(128) uint8_t yt[32768];    // Y^T      X[r = k][c = j]
   alignas(128) uint8_t at[16384];    // Aqk^T    X[r = j][c = i]
+  alignas(128) uint8_t tt[16384];    // T^T      X[r = j][c = i]
+  alignas(128) uint8_t dz[kBlobDZ];  // dZ staging, natural tile X[r = j][c = v] with the padded strides
   alignas(16) float d[kDim];
   alignas(8) uint64_t bar_ak, bar_qy, bar_mma1, bar_mma2;
   uint32_t tmem_base;
@@ -69,7 +74,7 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
   const int tg = warp;
   const int64_t bh = blockIdx.x;
   const int64_t b = bh / p.H, h = bh % p.H;
-  constexpr uint32_t kColS = 0, kColR = 128;
+  constexpr uint32_t kColS = 0, kColR = 128, kColZ = 192;
 
   if (warp == 0) {
     tmem_alloc(&sm.tmem_base, 256);
@@ -93,8 +98,9 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
   auto ch_of = [&](int64_t c) { return (b * p.n_chunks + c) * p.H + h; };
   auto load_ak = [&](int64_t c) {
     const int64_t ch = ch_of(c);
-    mbar_arrive_expect_tx(&sm.bar_ak, uint32_t(kBlobAt + kBlobKn));
+    mbar_arrive_expect_tx(&sm.bar_ak, uint32_t(kBlobAt + kBlobKn + kBlobTt));
     bulk_g2s(sm.at, p.ws + ws.off_at() + ch * kBlobAt, uint32_t(kBlobAt), &sm.bar_ak);
+    bulk_g2s(sm.tt, p.ws + ws.off_tt() + ch * kBlobTt, uint32_t(kBlobTt), &sm.bar_ak);
     bulk_g2s(sm.kn, p.ws + ws.off_kn() + ch * kBlobKn, uint32_t(kBlobKn), &sm.bar_ak);
   };
   auto load_qy = [&](int64_t c) {
@@ -165,6 +171,7 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
     }
     fence_async_smem();
     waiter.wait(&sm.bar_ak, par);
+    if (tid == 0) bulk_wait_read_all();  // the previous dZ tile has left its staging buffer
     tc_fence_before();
     __syncthreads();
     if (tid == 0) {
@@ -182,6 +189,12 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
       for (int ks = 0; ks < 16; ++ks) {
         mma_tf32_ts(tb + kColR, tb + kColS + ks * 8, smem_desc(kn0 + ks * 256, 128, 4096), id64, 1u);
       }
+      // dZ^T = dR^T T     (A: the accumulator just produced, K = 64 tokens; B: T^T tile X[r = j][c = i])
+      const uint32_t tt0 = smem_u32(sm.tt);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        mma_tf32_ts(tb + kColZ, tb + kColR + ks * 8, smem_desc(tt0 + ks * 256, 128, 2048), id64, ks > 0 ? 1u : 0u);
+      }
       mma_commit(&sm.bar_mma1);
     }
     // the next chunk's dO is on its way while the tensor cores work
@@ -190,17 +203,16 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
     tc_fence_after();
     if (tid == 0 && c > 0) load_ak(c - 1);  // At / Kn are free again
 
-    // ---- dR^T out (tile X[r = v][c = j]): 16 token columns per thread ----------------------------------
+    // ---- dZ out: 16 token columns of value row v into the staging tile X[r = j][c = v] ----------------
     {
-      uint8_t* blob = p.ws + ws.off_drt() + ch_of(c) * kBlobDRt + (vrow >> 3) * 2048 + (vrow & 7) * 16 + (j0 / 4) * 128;
+      uint8_t* col = sm.dz + (vrow >> 2) * kCsZ + (vrow & 3) * 4;
       uint32_t r[16];
-      tmem_ld16(tmem_addr(tb, lane_base, kColR + j0), r);
+      tmem_ld16(tmem_addr(tb, lane_base, kColZ + j0), r);
       tmem_wait_ld();
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        *reinterpret_cast<float4*>(blob + c4 * 128) =
-            make_float4(to_tf32(__uint_as_float(r[4 * c4])), to_tf32(__uint_as_float(r[4 * c4 + 1])),
-                        to_tf32(__uint_as_float(r[4 * c4 + 2])), to_tf32(__uint_as_float(r[4 * c4 + 3])));
+      for (int jj = 0; jj < 16; ++jj) {
+        const int j = j0 + jj;
+        *reinterpret_cast<float*>(col + (j >> 3) * kRsZ + (j & 7) * 16) = to_tf32(__uint_as_float(r[jj]));
       }
     }
     // ---- decay: dS^T <- dS^T diag(d) -------------------------------------------------------------------
@@ -214,10 +226,13 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
       tmem_st32(tmem_addr(tb, lane_base, kColS + k0), r);
       tmem_wait_st();
     }
+    fence_async_smem();
     tc_fence_before();
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
+      bulk_s2g(p.ws + ws.off_dz() + ch_of(c) * kBlobDZ, sm.dz, uint32_t(kBlobDZ));
+      bulk_commit();
       const uint32_t d0 = smem_u32(sm.dot), q0 = smem_u32(sm.qt), y0 = smem_u32(sm.yt);
       const uint32_t id_pos = idesc(128, 128, kFmtTF32, kMajorK, kMajorK);
       const uint32_t id_neg = idesc(128, 128, kFmtTF32, kMajorK, kMajorK, 1, 0);
@@ -252,6 +267,7 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
       if (init != nullptr) init[(k0 + j) * kDim] = __uint_as_float(r[j]);
     }
   }
+  if (tid == 0) bulk_wait_all();  // the last dZ tile is in global memory before the CTA retires
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tb, 256);
@@ -272,11 +288,9 @@ constexpr int kCsS = 144;              // 64-column tiles written by scattered 4
 constexpr int kRsS = 16 * kCsS;        // 2304
 
 // dynamic shared memory map (bytes).  Phase B = products with the states, phase C = Gram VJP.
-constexpr int kOffStack = 0;                      // B: [dZ ; dO] X[r = 128][c = v], RS kRsN     73728
+constexpr int kOffStack = 0;                      // B: [dZ ; dO] X[r = 128][c = v], RS kRsN     73728 (dZ rows: bulk copy)
 constexpr int kOffRn = kOffStack + 16 * kRsN;     // B: R X[r = j][c = v], RS 4096 (bulk copy)   32768
 constexpr int kOffS0 = kOffRn + 32768;            // B: S_0 X[r = k][c = v], RS 4096             65536
-constexpr int kOffDrt = kOffS0;                   //    (before S_0 arrives) dR^T X[r = v][c = i] 32768
-constexpr int kOffTt = kOffS0 + 32768;            //    (before S_0 arrives) T^T  X[r = j][c = i] 16384
 constexpr int kOffDs1 = kOffS0 + 65536;           // B: dS_1 half X[r = k][c = 64 v], RS 2048    32768
 constexpr int kEndB = kOffDs1 + 32768;            // 204800
 constexpr int kOffStack2 = 0;                     // C: [dL ; dA] X[r = 128][c = j], RS 2048     32768
@@ -294,7 +308,7 @@ struct VjpMisc {
   float dd[kDim];         // sum_v dS_1 * S_0
   float xe[4][kDim];      // per-block sum_j Kt_j dKt_j
   float xt[4][kDim];      // per-block sum of dG
-  alignas(8) uint64_t bar_a, bar_r, bar_m;
+  alignas(8) uint64_t bar_a, bar_r, bar_m, bar_d;
   uint32_t tmem_base;
 };
 constexpr int kVjpSmemBytes = kOffMisc + int(sizeof(VjpMisc));
@@ -338,6 +352,19 @@ __device__ __forceinline__ void load4v<float>(const void* base, int64_t idx, flo
   out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
 }
 
+template <typename T>
+__device__ __forceinline__ void store4v(void* base, int64_t idx, float a, float b, float c, float d);
+template <>
+__device__ __forceinline__ void store4v<__nv_bfloat16>(void* base, int64_t idx, float a, float b, float c, float d) {
+  *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(base) + idx) = make_uint2(pack_bf16(a, b), pack_bf16(c, d));
+}
+template <>
+__device__ __forceinline__ void store4v<__half>(void* base, int64_t idx, float a, float b, float c, float d) {
+  const __half2 lo = __floats2half2_rn(a, b), hi = __floats2half2_rn(c, d);
+  *reinterpret_cast<uint2*>(static_cast<__half*>(base) + idx) =
+      make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+
 __device__ __forceinline__ void tmem_ld8f(uint32_t taddr, float (&x)[8]) {
   uint32_t r[8];
   tmem_ld8(taddr, r);
@@ -347,7 +374,9 @@ __device__ __forceinline__ void tmem_ld8f(uint32_t taddr, float (&x)[8]) {
 }
 
 template <typename T, typename G>
-__global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const VjpParams p) {
+__global__ void __launch_bounds__(kVjpThreads, 1)
+chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s0,
+                     const __grid_constant__ CUtensorMap tm_ds) {
   extern __shared__ __align__(128) uint8_t smem[];
   VjpMisc& ms = *reinterpret_cast<VjpMisc*>(smem + kOffMisc);
   const WsLayout ws{p.n_ch, true};
@@ -371,6 +400,7 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
     mbar_init(&ms.bar_a, 1);
     mbar_init(&ms.bar_r, 1);
     mbar_init(&ms.bar_m, 1);
+    mbar_init(&ms.bar_d, 1);
     fence_mbar_init();
   }
   if (tid < kDim) ms.dd[tid] = 0.f;
@@ -379,44 +409,41 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
   tc_fence_after();
   const uint32_t tb = ms.tmem_base;
   uint32_t mma_phase = 0;
-  constexpr uint32_t kColDz = 0, kColD2 = 64, kColD3 = 128, kColD4 = 256, kColD5 = 320;
+  constexpr uint32_t kColD2 = 64, kColD3 = 128, kColD4 = 256, kColD5 = 320;
 
+  // Everything the first MMA batch reads arrives asynchronously: the dZ rows of the stack and the
+  // residual R as 1-D bulk copies, S_0 and the first 64 value columns of dS_1 as 5-D tiled TMA loads
+  // that turn the row-major fp32 checkpoints into blocked K-major tiles on the way (the tensor cores
+  // read the fp32 containers as tf32).  No register staging: the copy engine keeps far more bytes in
+  // flight than 512 threads with a few 16-byte loads each could.
+  const int s0_slot = int((b * (p.n_chunks + 1) + c) * p.H + h);
+  const int ds1_slot = int((b * (p.n_chunks + 1) + c + 1) * p.H + h);
   if (tid == 0) {
-    mbar_arrive_expect_tx(&ms.bar_a, uint32_t(kBlobDRt + kBlobTt));
-    bulk_g2s(smem + kOffDrt, p.ws + ws.off_drt() + ch * kBlobDRt, uint32_t(kBlobDRt), &ms.bar_a);
-    bulk_g2s(smem + kOffTt, p.ws + ws.off_tt() + ch * kBlobTt, uint32_t(kBlobTt), &ms.bar_a);
-    mbar_arrive_expect_tx(&ms.bar_r, uint32_t(kBlobRn));
-    bulk_g2s(smem + kOffRn, p.ws + ws.off_rn() + ch * kBlobRn, uint32_t(kBlobRn), &ms.bar_r);
+    mbar_arrive_expect_tx(&ms.bar_a, uint32_t(kBlobDZ + kBlobRn + 65536 + 32768));
+    tma_load_5d(smem + kOffDs1, &tm_ds, 0, 0, 0, 0, ds1_slot, &ms.bar_a);
+    bulk_g2s(smem + kOffRn, p.ws + ws.off_rn() + ch * kBlobRn, uint32_t(kBlobRn), &ms.bar_a);
+    bulk_g2s(smem + kOffStack, p.ws + ws.off_dz() + ch * kBlobDZ, uint32_t(kBlobDZ), &ms.bar_a);
+    tma_load_5d(smem + kOffS0, &tm_s0, 0, 0, 0, 0, s0_slot, &ms.bar_a);
   }
-  const float* s0_src = p.bnd + ((b * (p.n_chunks + 1) + c) * p.H + h) * kStateElems;
-  const float* ds1_src = p.d_bnd + ((b * (p.n_chunks + 1) + c + 1) * p.H + h) * kStateElems;
-  auto rn4 = [](float4 x) { return make_float4(to_tf32(x.x), to_tf32(x.y), to_tf32(x.z), to_tf32(x.w)); };
-  // One half (64 value columns) of dS_1 into shared memory, rounded to nearest tf32, and on the way
-  // its contribution to dd[k] = sum_v dS_1[k][v] S_0[k][v] (S_0 re-read through L2).
-  // chunk id qd = tid + 512 x: key row = (qd & 7) + 8 (qd >> 7), 4-value chunk = ((qd >> 3) & 15)
-  auto load_ds1_half = [&](int hf) {
-    float4 buf[4], sbuf[4];
-#pragma unroll
-    for (int x = 0; x < 4; ++x) {
-      const int qd = tid + 512 * x;
-      const int kr = (qd & 7) + 8 * (qd >> 7), v4 = (qd >> 3) & 15;
-      buf[x] = *reinterpret_cast<const float4*>(ds1_src + kr * kDim + 64 * hf + 4 * v4);
-      sbuf[x] = *reinterpret_cast<const float4*>(s0_src + kr * kDim + 64 * hf + 4 * v4);
-    }
+  // dd[k] += sum over the 64 value columns of half `hf` of dS_1[k][v] S_0[k][v], both read from their
+  // shared-memory tiles.  chunk id qd = tid + 512 x: key row = (qd & 7) + 8 (qd >> 7), 4-value chunk = (qd >> 3) & 15
+  auto dd_half = [&](int hf) {
 #pragma unroll
     for (int x = 0; x < 4; ++x) {
       const int qd = tid + 512 * x;
       const int v4 = (qd >> 3) & 15;
-      *reinterpret_cast<float4*>(smem + kOffDs1 + (qd >> 7) * 2048 + v4 * 128 + (qd & 7) * 16) = rn4(buf[x]);
-      float acc = buf[x].x * sbuf[x].x + buf[x].y * sbuf[x].y + buf[x].z * sbuf[x].z + buf[x].w * sbuf[x].w;
+      const float4 ds = *reinterpret_cast<const float4*>(smem + kOffDs1 + (qd >> 7) * 2048 + v4 * 128 + (qd & 7) * 16);
+      const float4 s0 = *reinterpret_cast<const float4*>(smem + kOffS0 + (qd >> 7) * 4096 + (v4 + 16 * hf) * 128 + (qd & 7) * 16);
+      float acc = ds.x * s0.x + ds.y * s0.y + ds.z * s0.z + ds.w * s0.w;
       // lanes that differ in bits 3, 4 hold other value chunks of the same key row
       acc += __shfl_xor_sync(0xffffffffu, acc, 8);
       acc += __shfl_xor_sync(0xffffffffu, acc, 16);
       if ((lane >> 3) == 0) atomicAdd(&ms.dd[(qd & 7) + 8 * (qd >> 7)], acc);
     }
   };
-  // dO rows of the stack (rows 64 + i), natural tile with padded chunk stride; their loads and those
-  // of the log-decay are in flight while the first half of dS_1 is staged
+
+  // ---- phase A: dO rows of the stack (rows 64 + i), natural tile with padded chunk stride, and the
+  // log-decay sums of this thread's tokens
   float Gc[4][4];
   {
     float dv4[4][4];
@@ -425,7 +452,6 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
       load4v<T>(p.d_out, seq_idx(4 * tg + e) + kc0, dv4[e]);
       load4v<G>(p.g, seq_idx(4 * tg + e) + kc0, Gc[e]);
     }
-    load_ds1_half(0);
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int i = 4 * tg + e;
@@ -440,95 +466,24 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
 #pragma unroll
   for (int f = 0; f < 4; ++f) ms.part[tg][kc0 + f] = Gc[3][f];
   waiter.wait(&ms.bar_a, 0);
-  waiter.wait(&ms.bar_r, 0);
+  dd_half(0);
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
-  // ---- M1: dZ^T = dR^T T ; M4 (first half): dKt^T = dS_1[:, v < 64] R[:, v < 64]^T -------------------
-  if (tid == 0) {
-    tc_fence_after();
-    const uint32_t a0 = smem_u32(smem + kOffDrt), b0 = smem_u32(smem + kOffTt);
-    const uint32_t rn = smem_u32(smem + kOffRn), d1 = smem_u32(smem + kOffDs1);
-    const uint32_t id = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      mma_tf32_ss(tb + kColDz, smem_desc(a0 + ks * 256, 128, 2048), smem_desc(b0 + ks * 256, 128, 2048), id,
-                  ks > 0 ? 1u : 0u);
-    }
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      mma_tf32_ss(tb + kColD4, smem_desc(d1 + ks * 256, 128, 2048), smem_desc(rn + ks * 256, 128, 4096), id,
-                  ks > 0 ? 1u : 0u);
-    }
-    mma_commit(&ms.bar_m);
-  }
-  // S_0 on its way into registers, and the log-decay prefixes, while the tensor cores work
-  float4 s0buf[8];
-#pragma unroll
-  for (int x = 0; x < 8; ++x) {
-    const int qd = tid + 512 * x;  // key row = (qd & 7) + 8 (qd >> 8), 4-value chunk = (qd >> 3) & 31
-    s0buf[x] = *reinterpret_cast<const float4*>(s0_src + ((qd & 7) + 8 * (qd >> 8)) * kDim + 4 * ((qd >> 3) & 31));
-  }
-  if (tid < kDim) {
-    float run = 0.f;
-#pragma unroll
-    for (int t = 0; t < 16; ++t) {
-      const float x = ms.part[t][tid];
-      ms.part[t][tid] = run;
-      run += x;
-    }
-    ms.gend[tid] = run;
-  }
-  waiter.wait(&ms.bar_m, mma_phase & 1u);
-  ++mma_phase;
-  tc_fence_after();
-
-  // ---- S_0 (whole) over the dR^T / T^T operands of M1, second half of dS_1 over the first -----------
-#pragma unroll
-  for (int x = 0; x < 8; ++x) {
-    const int qd = tid + 512 * x;
-    *reinterpret_cast<float4*>(smem + kOffS0 + (qd >> 8) * 4096 + ((qd >> 3) & 31) * 128 + (qd & 7) * 16) = rn4(s0buf[x]);
-  }
-  load_ds1_half(1);
-  // ---- dZ: into the stack (rows j), and dv = dZ w, dw = dZ v; each warp of a quadrant takes 16 tokens --
-  {
-    const int vrow = 32 * q4 + lane;
-    // every load is issued before the first store: the outputs may alias the inputs as far as the
-    // compiler knows, so a load placed after a store would wait for the round trip before it
-    float wv[16], vv[16];
-#pragma unroll
-    for (int jj = 0; jj < 16; ++jj) {
-      const int64_t idx = seq_idx(16 * part + jj) + vrow;
-      wv[jj] = ldf<T>(p.w, idx);
-      vv[jj] = ldf<T>(p.v, idx);
-    }
-    uint32_t r[16];
-    tmem_ld16(tmem_addr(tb, 32 * q4, kColDz + 16 * part), r);
-    tmem_wait_ld();
-#pragma unroll
-    for (int jj = 0; jj < 16; ++jj) {
-      const int j = 16 * part + jj;
-      *reinterpret_cast<float*>(smem + kOffStack + (j >> 3) * kRsN + (vrow >> 2) * kCsN + (j & 7) * 16 + (vrow & 3) * 4) =
-          to_tf32(__uint_as_float(r[jj]));
-    }
-#pragma unroll
-    for (int jj = 0; jj < 16; ++jj) {
-      const int64_t idx = seq_idx(16 * part + jj) + vrow;
-      const float dz = __uint_as_float(r[jj]);
-      stf<T>(p.dv, idx, dz * wv[jj]);
-      stf<T>(p.dw, idx, dz * vv[jj]);
-    }
-  }
-  fence_async_smem();
-  tc_fence_before();
-  __syncthreads();
-  // ---- M2: [dZ;dO] R^T ; M3: S_0 [dZ;dO]^T ; M4 (second half) -------------------------------------------
+  // ---- first MMA batch: M4 (first half) dKt^T = dS_1[:, v < 64] R[:, v < 64]^T ;
+  //      M2 [-dL ; dA] = [dZ ; dO] R^T ;  M3 [-dE ; dQg]^T = S_0 [dZ ; dO]^T ------------------------------
   if (tid == 0) {
     tc_fence_after();
     const uint32_t st = smem_u32(smem + kOffStack), rn = smem_u32(smem + kOffRn);
     const uint32_t s0 = smem_u32(smem + kOffS0), d1 = smem_u32(smem + kOffDs1);
     const uint32_t id64 = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
     const uint32_t id128 = idesc(128, 128, kFmtTF32, kMajorK, kMajorK);
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      mma_tf32_ss(tb + kColD4, smem_desc(d1 + ks * 256, 128, 2048), smem_desc(rn + ks * 256, 128, 4096), id64,
+                  ks > 0 ? 1u : 0u);
+    }
+    mma_commit(&ms.bar_r);  // the dS_1 buffer may be refilled once these have run
 #pragma unroll
     for (int ks = 0; ks < 16; ++ks) {
       mma_tf32_ss(tb + kColD2, smem_desc(st + ks * 2 * kCsN, kCsN, kRsN), smem_desc(rn + ks * 256, 128, 4096), id64,
@@ -539,21 +494,64 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
       mma_tf32_ss(tb + kColD3, smem_desc(s0 + ks * 256, 128, 4096), smem_desc(st + ks * 2 * kCsN, kCsN, kRsN), id128,
                   ks > 0 ? 1u : 0u);
     }
+    mma_commit(&ms.bar_m);
+    // the second 64 value columns of dS_1 replace the first as soon as their product has run
+    waiter.wait(&ms.bar_r, 0);
+    mbar_arrive_expect_tx(&ms.bar_d, 32768u);
+    tma_load_5d(smem + kOffDs1, &tm_ds, 0, 0, 16, 0, ds1_slot, &ms.bar_d);
+  }
+  // ---- under the tensor cores: log-decay prefixes, dv = dZ w, dw = dZ v, and the raw inputs of the
+  // Gram operands.  Every load is issued before the first store: the outputs may alias the inputs as
+  // far as the compiler knows, so a load placed after a store would wait for its round trip.
+  if (tid < kDim) {
+    float run = 0.f;
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      const float x = ms.part[t][tid];
+      ms.part[t][tid] = run;
+      run += x;
+    }
+    ms.gend[tid] = run;
+  }
+  const int mb = tg >> 2;
+  float kk[4][4], qq[4][4], bb[4][4];
+  {
+    typename Raw4<T>::type wr[4], vr[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int64_t idx = seq_idx(4 * tg + e) + kc0;
+      wr[e] = load4_raw<T>(p.w, idx);
+      vr[e] = load4_raw<T>(p.v, idx);
+      load4v<T>(p.k, idx, kk[e]);
+      load4v<T>(p.q, idx, qq[e]);
+      load4v<T>(p.beta, idx, bb[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int j = 4 * tg + e;
+      const float4 dz = *reinterpret_cast<const float4*>(smem + kOffStack + (j >> 3) * kRsN + c4 * kCsN + (j & 7) * 16);
+      const int64_t idx = seq_idx(j) + kc0;
+      float wv[4], vv[4];
+      unpack4<T>(wr[e], wv);
+      unpack4<T>(vr[e], vv);
+      store4v<T>(p.dv, idx, dz.x * wv[0], dz.y * wv[1], dz.z * wv[2], dz.w * wv[3]);
+      store4v<T>(p.dw, idx, dz.x * vv[0], dz.y * vv[1], dz.z * vv[2], dz.w * vv[3]);
+    }
+  }
+  // ---- M4 (second half) once the second half of dS_1 has landed -----------------------------------------
+  waiter.wait(&ms.bar_d, 0);
+  dd_half(1);
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0) {
+    tc_fence_after();
+    const uint32_t rn = smem_u32(smem + kOffRn), d1 = smem_u32(smem + kOffDs1);
+    const uint32_t id64 = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
       mma_tf32_ss(tb + kColD4, smem_desc(d1 + ks * 256, 128, 2048), smem_desc(rn + (8 + ks) * 256, 128, 4096), id64, 1u);
     }
-    mma_commit(&ms.bar_m);
-  }
-  // meanwhile: raw inputs of the Gram operands (loads in flight while the tensor cores work)
-  const int mb = tg >> 2;
-  float kk[4][4], qq[4][4], bb[4][4];
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const int64_t idx = seq_idx(4 * tg + e) + kc0;
-    load4v<T>(p.k, idx, kk[e]);
-    load4v<T>(p.q, idx, qq[e]);
-    load4v<T>(p.beta, idx, bb[e]);
+    mma_commit(&ms.bar_r);
   }
   waiter.wait(&ms.bar_m, mma_phase & 1u);
   ++mma_phase;
@@ -584,7 +582,10 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
           make_float4(vals[4 * j4], vals[4 * j4 + 1], vals[4 * j4 + 2], vals[4 * j4 + 3]);
     }
   }
-  // anchored Gram operands, transposed tiles X[r = channel][c = token] with padded row-group stride
+  // anchored Gram operands, transposed tiles X[r = channel][c = token] with padded row-group stride.
+  // They overwrite R and the dS_1 buffer: the second half of M4 must have run.
+  waiter.wait(&ms.bar_r, 1);
+  tc_fence_after();
   {
     float eat[4][4], qat[4][4];
 #pragma unroll
@@ -762,6 +763,39 @@ __global__ void __launch_bounds__(kVjpThreads, 1) chunk_bwd_vjp_kernel(const Vjp
 
 }  // namespace
 
+// ---- tensor maps ------------------------------------------------------------------------------------
+// A [n_slots][128 k][128 v] fp32 array of states seen as a 5-D tensor (v % 4, k % 8, v / 4, k / 8, slot):
+// a box (4, 8, box_v4, 16, 1) lands in shared memory as the blocked K-major tile X[r = k][c = v] of
+// 4 * box_v4 value columns (8 rows x 16 bytes core matrices, CS = 128, RS = 128 * box_v4).
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &query) != cudaSuccess ||
+        query != cudaDriverEntryPointSuccess) {
+      return EncodeTiledFn(nullptr);
+    }
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+static bool encode_state_map(CUtensorMap* tm, const float* base, int64_t n_slots, int box_v4) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[5] = {4, 8, 32, 16, cuuint64_t(n_slots)};
+  const cuuint64_t strides[4] = {512, 16, 4096, 65536};  // bytes, dimensions 1..4
+  const cuuint32_t box[5] = {4, 8, cuuint32_t(box_v4), 16, 1};
+  const cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
+  return encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float*>(base), dims, strides, box, elem_strides,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // ---- launcher ---------------------------------------------------------------------------------------
 int launch_chunk_backward(const void* q, const void* k, const void* v, const void* g, const void* beta,
                           const void* w, const void* d_out, const float* ds_final, const float* bnd,
@@ -791,13 +825,19 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
   int st = check_launch();
   if (st != GDN2_OK) return st;
 
+  CUtensorMap tm_s0, tm_ds;
+  const int64_t n_slots = B * (n_chunks + 1) * H;
+  if ((reinterpret_cast<uintptr_t>(bnd) & 15u) != 0 || (reinterpret_cast<uintptr_t>(d_bnd) & 15u) != 0 ||
+      !encode_state_map(&tm_s0, bnd, n_slots, 32) || !encode_state_map(&tm_ds, d_bnd, n_slots, 16)) {
+    return GDN2_ERR_LAUNCH;
+  }
   VjpParams vp{q, k, v, g, beta, w, d_out, workspace, bnd, d_bnd, dq, dk, dv, dg, dbeta, dw,
                status, T, H, n_chunks, n_ch, scale};
   GDN2_DISPATCH_TYPES(dtype, g_dtype, {
     auto kernel = chunk_bwd_vjp_kernel<T, G>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kVjpSmemBytes);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
-    kernel<<<unsigned(n_ch), kVjpThreads, kVjpSmemBytes, stream>>>(vp);
+    kernel<<<unsigned(n_ch), kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds);
   });
   return check_launch();
 }

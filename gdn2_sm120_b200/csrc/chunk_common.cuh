@@ -19,7 +19,8 @@
 //   At   X[r = token j (64)][c = token i (64)]  RS = 2048   16 KiB   A_qk^T
 //   Tt   X[r = token j (64)][c = token i (64)]  RS = 2048   16 KiB   ((I+L)^-1)^T
 //   Rn   X[r = token j (64)][c = value v (128)] RS = 4096   32 KiB   R = U - Y S_0 (forward scan)
-//   dRt  X[r = value v (128)][c = token j (64)] RS = 2048   32 KiB   dR^T (backward scan)
+//   dZ   X[r = token j (64)][c = value v (128)] RS = 4608, CS = 144   36 KiB   dZ = T^T dR (backward
+//        scan; the padded strides are those of the shared-memory tile it is copied into)
 //
 // Arrays are stored one after another (struct of arrays), each n_ch entries long.
 #pragma once
@@ -35,7 +36,7 @@ constexpr int64_t kBlobY = 32768, kBlobUt = 32768, kBlobQ = 32768, kBlobKt = 327
 constexpr int64_t kBlobA = 16384, kBlobT = 16384, kBlobD = 512;
 constexpr int64_t kBlobFwd = kBlobY + kBlobUt + kBlobQ + kBlobKt + kBlobA + kBlobT + kBlobD;
 constexpr int64_t kBlobYt = 32768, kBlobQt = 32768, kBlobKn = 32768, kBlobAt = 16384, kBlobTt = 16384;
-constexpr int64_t kBlobRn = 32768, kBlobDRt = 32768;
+constexpr int64_t kBlobRn = 32768, kBlobDZ = 8 * 4608;
 
 struct WsLayout {
   int64_t n_ch;
@@ -55,9 +56,9 @@ struct WsLayout {
   __host__ __device__ int64_t off_at() const { return off_kn() + n_ch * kBlobKn; }
   __host__ __device__ int64_t off_tt() const { return off_at() + n_ch * kBlobAt; }
   __host__ __device__ int64_t off_rn() const { return off_tt() + n_ch * kBlobTt; }
-  __host__ __device__ int64_t off_drt() const { return off_rn() + n_ch * kBlobRn; }
+  __host__ __device__ int64_t off_dz() const { return off_rn() + n_ch * kBlobRn; }
   __host__ __device__ int64_t total() const {
-    return training ? off_drt() + n_ch * kBlobDRt : off_status() + 256;
+    return training ? off_dz() + n_ch * kBlobDZ : off_status() + 256;
   }
 };
 
