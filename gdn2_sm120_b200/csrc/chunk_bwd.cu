@@ -308,7 +308,7 @@ struct VjpMisc {
   float dd[kDim];         // sum_v dS_1 * S_0
   float xe[4][kDim];      // per-block sum_j Kt_j dKt_j
   float xt[4][kDim];      // per-block sum of dG
-  alignas(8) uint64_t bar_a, bar_r, bar_m, bar_d;
+  alignas(8) uint64_t bar_a, bar_s, bar_r, bar_m, bar_d;
   uint32_t tmem_base;
 };
 constexpr int kVjpSmemBytes = kOffMisc + int(sizeof(VjpMisc));
@@ -385,12 +385,6 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int q4 = warp & 3, part = warp >> 2;
   const int tg = warp, c4 = lane, kc0 = 4 * lane;
-  const int64_t ch = blockIdx.x;
-  const int64_t h = ch % p.H;
-  const int64_t c = (ch / p.H) % p.n_chunks;
-  const int64_t b = ch / (p.H * p.n_chunks);
-  const int64_t t0 = c * kChunk;
-  auto seq_idx = [&](int tok) { return ((b * p.T + t0 + tok) * p.H + h) * int64_t(kDim); };
 
   if (warp == 0) {
     tmem_alloc(&ms.tmem_base, 512);
@@ -401,9 +395,9 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     mbar_init(&ms.bar_r, 1);
     mbar_init(&ms.bar_m, 1);
     mbar_init(&ms.bar_d, 1);
+    mbar_init(&ms.bar_s, 1);
     fence_mbar_init();
   }
-  if (tid < kDim) ms.dd[tid] = 0.f;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -411,20 +405,34 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
   uint32_t mma_phase = 0;
   constexpr uint32_t kColD2 = 64, kColD3 = 128, kColD4 = 256, kColD5 = 320;
 
-  // Everything the first MMA batch reads arrives asynchronously: the dZ rows of the stack and the
-  // residual R as 1-D bulk copies, S_0 and the first 64 value columns of dS_1 as 5-D tiled TMA loads
-  // that turn the row-major fp32 checkpoints into blocked K-major tiles on the way (the tensor cores
-  // read the fp32 containers as tf32).  No register staging: the copy engine keeps far more bytes in
-  // flight than 512 threads with a few 16-byte loads each could.
-  const int s0_slot = int((b * (p.n_chunks + 1) + c) * p.H + h);
+  // Everything the first MMA batch of a chunk-head reads arrives asynchronously: the dZ rows of the
+  // stack and the residual R as 1-D bulk copies, S_0 and the first 64 value columns of dS_1 as 5-D tiled
+  // TMA loads that turn the row-major fp32 checkpoints into blocked K-major tiles on the way (the
+  // tensor cores read the fp32 containers as tf32).  No register staging.  The kernel is persistent:
+  // one SM takes in bytes at a limited rate, so the copies for the CTA's next chunk-head are issued as
+  // soon as the last MMA of the current one has read shared memory, and land during its final chain.
+  auto issue_loads = [&](int64_t ch_) {
+    const int64_t h_ = ch_ % p.H, c_ = (ch_ / p.H) % p.n_chunks, b_ = ch_ / (p.H * p.n_chunks);
+    const int s0_slot_ = int((b_ * (p.n_chunks + 1) + c_) * p.H + h_);
+    mbar_arrive_expect_tx(&ms.bar_s, uint32_t(65536 + 32768));
+    tma_load_5d(smem + kOffDs1, &tm_ds, 0, 0, 0, 0, s0_slot_ + int(p.H), &ms.bar_s);
+    tma_load_5d(smem + kOffS0, &tm_s0, 0, 0, 0, 0, s0_slot_, &ms.bar_s);
+    mbar_arrive_expect_tx(&ms.bar_a, uint32_t(kBlobDZ + kBlobRn));
+    bulk_g2s(smem + kOffRn, p.ws + ws.off_rn() + ch_ * kBlobRn, uint32_t(kBlobRn), &ms.bar_a);
+    bulk_g2s(smem + kOffStack, p.ws + ws.off_dz() + ch_ * kBlobDZ, uint32_t(kBlobDZ), &ms.bar_a);
+  };
+  if (tid == 0 && int64_t(blockIdx.x) < p.n_ch) issue_loads(blockIdx.x);
+
+  uint32_t iter = 0;
+  for (int64_t ch = blockIdx.x; ch < p.n_ch; ch += gridDim.x, ++iter) {
+  const uint32_t par = iter & 1u;
+  const int64_t h = ch % p.H;
+  const int64_t c = (ch / p.H) % p.n_chunks;
+  const int64_t b = ch / (p.H * p.n_chunks);
+  const int64_t t0 = c * kChunk;
+  auto seq_idx = [&](int tok) { return ((b * p.T + t0 + tok) * p.H + h) * int64_t(kDim); };
   const int ds1_slot = int((b * (p.n_chunks + 1) + c + 1) * p.H + h);
-  if (tid == 0) {
-    mbar_arrive_expect_tx(&ms.bar_a, uint32_t(kBlobDZ + kBlobRn + 65536 + 32768));
-    tma_load_5d(smem + kOffDs1, &tm_ds, 0, 0, 0, 0, ds1_slot, &ms.bar_a);
-    bulk_g2s(smem + kOffRn, p.ws + ws.off_rn() + ch * kBlobRn, uint32_t(kBlobRn), &ms.bar_a);
-    bulk_g2s(smem + kOffStack, p.ws + ws.off_dz() + ch * kBlobDZ, uint32_t(kBlobDZ), &ms.bar_a);
-    tma_load_5d(smem + kOffS0, &tm_s0, 0, 0, 0, 0, s0_slot, &ms.bar_a);
-  }
+  if (tid < kDim) ms.dd[tid] = 0.f;
   // dd[k] += sum over the 64 value columns of half `hf` of dS_1[k][v] S_0[k][v], both read from their
   // shared-memory tiles.  chunk id qd = tid + 512 x: key row = (qd & 7) + 8 (qd >> 7), 4-value chunk = (qd >> 3) & 15
   auto dd_half = [&](int hf) {
@@ -465,7 +473,9 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
   }
 #pragma unroll
   for (int f = 0; f < 4; ++f) ms.part[tg][kc0 + f] = Gc[3][f];
-  waiter.wait(&ms.bar_a, 0);
+  __syncthreads();  // dd is zero and the prefix slots are written before anyone adds to or reads them
+  waiter.wait(&ms.bar_a, par);
+  waiter.wait(&ms.bar_s, par);
   dd_half(0);
   fence_async_smem();
   tc_fence_before();
@@ -539,7 +549,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     }
   }
   // ---- M4 (second half) once the second half of dS_1 has landed -----------------------------------------
-  waiter.wait(&ms.bar_d, 0);
+  waiter.wait(&ms.bar_d, par);
   dd_half(1);
   tc_fence_before();
   __syncthreads();
@@ -662,6 +672,8 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
   waiter.wait(&ms.bar_m, mma_phase & 1u);
   ++mma_phase;
   tc_fence_after();
+  // shared memory (all but the small arrays of VjpMisc) is dead from here on: fetch the next chunk-head
+  if (tid == 0 && ch + gridDim.x < p.n_ch) issue_loads(ch + gridDim.x);
 
   // ================================ per-channel chain ==============================================
   // One thread = one key channel over one 16-token block.  The log-decay G and the anchored operands
@@ -756,8 +768,11 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
       stf<G>(p.dg, seq_idx(16 * blk + t) + kc, run);
     }
   }
+  // the next chunk-head reuses the arrays of VjpMisc and the TMEM columns
   tc_fence_before();
   __syncthreads();
+  tc_fence_after();
+  }  // chunk-head loop
   if (warp == 0) tmem_dealloc(tb, 512);
 }
 
@@ -825,6 +840,10 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
   int st = check_launch();
   if (st != GDN2_OK) return st;
 
+  int device = 0, sm_count = 0;
+  err = cudaGetDevice(&device);
+  if (err == cudaSuccess) err = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+  if (err != cudaSuccess || sm_count <= 0) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
   CUtensorMap tm_s0, tm_ds;
   const int64_t n_slots = B * (n_chunks + 1) * H;
   if ((reinterpret_cast<uintptr_t>(bnd) & 15u) != 0 || (reinterpret_cast<uintptr_t>(d_bnd) & 15u) != 0 ||
@@ -837,7 +856,7 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
     auto kernel = chunk_bwd_vjp_kernel<T, G>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kVjpSmemBytes);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
-    kernel<<<unsigned(n_ch), kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds);
+    kernel<<<unsigned(n_ch < int64_t(sm_count) ? n_ch : int64_t(sm_count)), kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds);
   });
   return check_launch();
 }
