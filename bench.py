@@ -41,12 +41,14 @@ UNIT = "tokens/s"
 # algorithmic bytes per token-head (bf16 sequence tensors, fp32 g), K = V = 128
 FWD_BYTES = 5 * 256 + 512 + 256                 # read q k v beta w + g, write o
 BWD_BYTES = (5 * 256 + 512 + 256) + (5 * 256 + 512)  # read inputs + dO, write 6 grads
-# dram__bytes_read.sum + dram__bytes_write.sum per 64-token chunk-head from the ncu captures summarised in
-# profiles/chunk_kernels_*_ncu_full.md (B=1, H=8 cases, scaled by the number of chunk-heads: the kernels'
-# traffic is proportional to it); the forward/backward calls launch two kernels each.
+# dram__bytes_read.sum + dram__bytes_write.sum per 64-token chunk-head and kernel, from the ncu capture
+# summarised in profiles/chunk_kernels_B1_T4096_H8_ncu_full.md (512 chunk-heads, scaled by the number of
+# chunk-heads: the kernels' traffic is proportional to it)
 NCU_TRAFFIC_PER_CHUNK_HEAD = {
-    "gdn2_chunk_forward": 313.4e3 + 159.2e3,    # chunk_prep (T=4096 capture) + chunk_scan (T=2048 capture)
-    "gdn2_chunk_backward": 138.8e3 + 414.3e3,   # chunk_bwd_scan (T=2048 capture) + chunk_bwd_vjp (T=4096 capture)
+    "chunk_prep_kernel": 305.6e3,
+    "chunk_scan_kernel": 188.3e3,
+    "chunk_bwd_scan_kernel": 186.4e3,
+    "chunk_bwd_vjp_kernel": 403.0e3,
 }
 DECODE_BYTES_PER_HEAD = 2 * 65536 + 1792 + 256
 T1_ZERO_BYTES_PER_HEAD = 65536 + 1280
@@ -365,19 +367,34 @@ def run_gpu_arm(args):
     value = world * tokens_per_rank / (ms * 1e-3)
     del grads
 
-    # ---- live per-kernel timing (dominant kernel -> roofline) ------------------------------
+    # ---- live per-kernel timing (dominant kernel -> roofline) ------------------------------------
+    # per C-ABI call with CUDA events around it, and per kernel with the library's own events between
+    # the two kernels of a chunk call (both on the launching stream)
     _lib.KERNEL_EVENTS = {}
+    _lib.profile_enable(True)
+    per_kernel = {}
     for _ in range(3):
         train_step(pkg, leaves, s0)
+        for name, value in _lib.profile_chunk_kernels().items():
+            per_kernel.setdefault(name, []).append(value)
     torch.cuda.synchronize()
-    kernel_ms = {name: statistics.mean(b.elapsed_time(e) for b, e in pairs)
-                 for name, pairs in _lib.KERNEL_EVENTS.items()}
+    _lib.profile_enable(False)
+    call_ms = {name: statistics.mean(b.elapsed_time(e) for b, e in pairs)
+               for name, pairs in _lib.KERNEL_EVENTS.items()}
     _lib.KERNEL_EVENTS = None
+    kernel_ms = {name: statistics.mean(values) for name, values in per_kernel.items()}
+    if not kernel_ms:  # short sequences run the per-token kernels: one kernel per call
+        kernel_ms = dict(call_ms)
+    # compulsory bytes a kernel's launch stands for: the forward pair shares the forward figure (prep reads
+    # the inputs, the scan writes o and S_T), the backward figure is carried by the VJP kernel (it reads
+    # every input and dO and writes the six gradients)
     kernel_bytes = {
         "gdn2_token_forward": FWD_BYTES * token_heads,
-        "gdn2_chunk_forward": FWD_BYTES * token_heads,
+        "chunk_prep_kernel": FWD_BYTES * token_heads,
+        "chunk_scan_kernel": FWD_BYTES * token_heads,
         "gdn2_token_chunk_vjp": BWD_BYTES * token_heads,
-        "gdn2_chunk_backward": BWD_BYTES * token_heads,
+        "chunk_bwd_vjp_kernel": BWD_BYTES * token_heads,
+        "chunk_bwd_scan_kernel": (256 + 2 * 65536 / 64) * token_heads,   # dO in, one state cotangent per chunk out
         # the cotangent scan re-reads q, k, g, beta, dO: overhead traffic, its own compulsory bytes
         "gdn2_token_dstate_scan": (3 * 256 + 512 + 256) * token_heads,
     }
@@ -391,8 +408,9 @@ def run_gpu_arm(args):
         roofline = {
             "bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak,
             "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
+            "traffic_gbs": (traffic / (kernel_ms[dominant] * 1e-3) / 1e9) if traffic else None,
             "algorithmic_bytes": kernel_bytes.get(dominant, 0),
-            "kernel_ms": kernel_ms,
+            "kernel_ms": kernel_ms, "call_ms": call_ms,
             "step_algorithmic_gbs": (FWD_BYTES + BWD_BYTES) * token_heads / (ms_local * 1e-3) / 1e9,
         }
 

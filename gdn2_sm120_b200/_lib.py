@@ -44,6 +44,8 @@ _PROTOTYPES: dict[str, list] = {
     "gdn2_chunk_backward": [_P] * 18 + [_I64] * 4 + [_INT, _INT, _F32, _P],
     "gdn2_chunk_read_status": [_P] + [_I64] * 3 + [_P],
     "gdn2_chunk_forward_static": [_P] * 9 + [_I64] * 4 + [_INT, _INT, _F32, _P],
+    "gdn2_profile_enable": [_INT],
+    "gdn2_profile_chunk_kernels": [_P] * 4,
 }
 _RESTYPES = {"gdn2_status_string": ctypes.c_char_p, "gdn2_last_cuda_error": ctypes.c_char_p,
              "gdn2_chunk_workspace_bytes": ctypes.c_int64}
@@ -150,3 +152,23 @@ def require_b200(device: torch.device) -> None:
         _capability_ok[index] = ok
     if not ok:
         raise RuntimeError("these kernels are built for sm_100a (B200) GPUs only")
+
+
+def profile_enable(on: bool) -> None:
+    """Switch the per-kernel event timing of the chunk entry points on or off."""
+
+    lib().gdn2_profile_enable(1 if on else 0)
+
+
+def profile_chunk_kernels() -> dict[str, float]:
+    """Durations (ms) of the four kernels of the most recent chunk forward / backward calls.
+
+    Waits for the recorded events.  Kernels whose call has not run since profiling was switched on
+    are left out."""
+
+    values = [ctypes.c_float(-1.0) for _ in range(4)]
+    status = lib().gdn2_profile_chunk_kernels(*[ctypes.byref(v) for v in values])
+    if status != 0:
+        raise RuntimeError(f"gdn2_profile_chunk_kernels failed with status {status}")
+    names = ("chunk_prep_kernel", "chunk_scan_kernel", "chunk_bwd_scan_kernel", "chunk_bwd_vjp_kernel")
+    return {n: v.value for n, v in zip(names, values) if v.value >= 0.0}

@@ -42,6 +42,22 @@ void record_cuda_error(cudaError_t err) {
                 cudaGetErrorString(err));
 }
 
+// ---- optional per-kernel timing of the chunk entry points -----------------------------------------
+// Events 0..2 bracket the two kernels of gdn2_chunk_forward, 3..5 those of gdn2_chunk_backward.
+namespace {
+bool g_profile_on = false;
+cudaEvent_t g_profile_events[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+bool g_profile_recorded[2] = {false, false};
+}  // namespace
+
+void profile_mark(int index, cudaStream_t stream) {
+  if (!g_profile_on) return;
+  if (g_profile_events[index] == nullptr && cudaEventCreate(&g_profile_events[index]) != cudaSuccess) return;
+  cudaEventRecord(g_profile_events[index], stream);
+  if (index == 2) g_profile_recorded[0] = true;
+  if (index == 5) g_profile_recorded[1] = true;
+}
+
 int check_launch() {
   const cudaError_t err = cudaGetLastError();
   if (err == cudaSuccess) return GDN2_OK;
@@ -238,3 +254,26 @@ int gdn2_chunk_read_status(const void* workspace, int64_t batch, int64_t full_to
 }
 
 }  // extern "C"
+
+extern "C" int gdn2_profile_enable(int on) {
+  gdn2::g_profile_on = on != 0;
+  gdn2::g_profile_recorded[0] = gdn2::g_profile_recorded[1] = false;
+  return GDN2_OK;
+}
+
+extern "C" int gdn2_profile_chunk_kernels(float* prep_ms, float* scan_ms, float* bwd_scan_ms, float* vjp_ms) {
+  if (prep_ms == nullptr || scan_ms == nullptr || bwd_scan_ms == nullptr || vjp_ms == nullptr) {
+    return GDN2_ERR_NULL_POINTER;
+  }
+  float* out[4] = {prep_ms, scan_ms, bwd_scan_ms, vjp_ms};
+  for (int call = 0; call < 2; ++call) {
+    out[2 * call][0] = out[2 * call + 1][0] = -1.f;
+    if (!gdn2::g_profile_recorded[call]) continue;
+    cudaEvent_t* ev = gdn2::g_profile_events + 3 * call;
+    cudaError_t err = cudaEventSynchronize(ev[2]);
+    if (err == cudaSuccess) err = cudaEventElapsedTime(out[2 * call], ev[0], ev[1]);
+    if (err == cudaSuccess) err = cudaEventElapsedTime(out[2 * call + 1], ev[1], ev[2]);
+    if (err != cudaSuccess) { gdn2::record_cuda_error(err); return GDN2_ERR_LAUNCH; }
+  }
+  return GDN2_OK;
+}

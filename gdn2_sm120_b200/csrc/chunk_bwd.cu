@@ -305,9 +305,8 @@ constexpr int kOffMisc = (kEndB > kEndC ? kEndB : kEndC);
 struct VjpMisc {
   float part[16][kDim];   // exclusive prefixes of the log-decay per 4-token group
   float gend[kDim];
-  float dd[kDim];         // sum_v dS_1 * S_0
   float xe[4][kDim];      // per-block sum_j Kt_j dKt_j
-  float xt[4][kDim];      // per-block sum of dG
+  float xt[4][kDim];      // partial sums of dd = sum_v dS_1 * S_0, then the per-block sums of dG
   alignas(8) uint64_t bar_a, bar_s, bar_r, bar_m, bar_d;
   uint32_t tmem_base;
 };
@@ -363,6 +362,13 @@ __device__ __forceinline__ void store4v<__half>(void* base, int64_t idx, float a
   const __half2 lo = __floats2half2_rn(a, b), hi = __floats2half2_rn(c, d);
   *reinterpret_cast<uint2*>(static_cast<__half*>(base) + idx) =
       make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+
+// tf32 value of k times its anchored decay, as stored in the (K^I)^T tiles: `decay` alone, or
+// `decay * far` for row blocks beyond the next one.  Tile build and chain both call this, so that the
+// chain multiplies the Gram cotangents by exactly the operand values the tensor cores saw.
+__device__ __forceinline__ float anchored_k(float k, float decay, float far, bool use_far) {
+  return to_tf32(k * (use_far ? decay * far : decay));
 }
 
 __device__ __forceinline__ void tmem_ld8f(uint32_t taddr, float (&x)[8]) {
@@ -432,7 +438,6 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
   const int64_t t0 = c * kChunk;
   auto seq_idx = [&](int tok) { return ((b * p.T + t0 + tok) * p.H + h) * int64_t(kDim); };
   const int ds1_slot = int((b * (p.n_chunks + 1) + c + 1) * p.H + h);
-  if (tid < kDim) ms.dd[tid] = 0.f;
   // dd[k] += sum over the 64 value columns of half `hf` of dS_1[k][v] S_0[k][v], both read from their
   // shared-memory tiles.  chunk id qd = tid + 512 x: key row = (qd & 7) + 8 (qd >> 7), 4-value chunk = (qd >> 3) & 15
   auto dd_half = [&](int hf) {
@@ -446,7 +451,12 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
       // lanes that differ in bits 3, 4 hold other value chunks of the same key row
       acc += __shfl_xor_sync(0xffffffffu, acc, 8);
       acc += __shfl_xor_sync(0xffffffffu, acc, 16);
-      if ((lane >> 3) == 0) atomicAdd(&ms.dd[(qd & 7) + 8 * (qd >> 7)], acc);
+      // one owner per (warp & 3, key row): partial sums in a fixed order, no atomics, so that the
+      // result does not depend on the timing of the warps (xt is free until the end of the chain)
+      if ((lane >> 3) == 0) {
+        float* slot = &ms.xt[warp & 3][(qd & 7) + 8 * (qd >> 7)];
+        *slot = (hf == 0) ? acc : *slot + acc;
+      }
     }
   };
 
@@ -473,7 +483,6 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
   }
 #pragma unroll
   for (int f = 0; f < 4; ++f) ms.part[tg][kc0 + f] = Gc[3][f];
-  __syncthreads();  // dd is zero and the prefix slots are written before anyone adds to or reads them
   waiter.wait(&ms.bar_a, par);
   waiter.wait(&ms.bar_s, par);
   dd_half(0);
@@ -616,16 +625,31 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
       *reinterpret_cast<float4*>(smem + kOffEat + off) = make_float4(eat[0][f], eat[1][f], eat[2][f], eat[3][f]);
       *reinterpret_cast<float4*>(smem + kOffQat + off) = make_float4(qat[0][f], qat[1][f], qat[2][f], qat[3][f]);
     }
+    // (K^I)^T for every row block I >= the token's own block mb, three exponentials per element:
+    //   I = mb      k exp(a_mb - G)                      (own block: >= 1, bounded by the 16-token contract)
+    //   I = mb + 1  k exp(a_next - G)                    (a_next = start of the next block)
+    //   I > mb + 1  k (exp(a_next - G) exp(a_I - a_next))
+    // The final chain forms the same products with the same expressions (anchored_k below).
 #pragma unroll
-    for (int I = 0; I < 4; ++I) {
-      if (I >= mb) {
+    for (int f = 0; f < 4; ++f) {
+      const int kc = kc0 + f;
+      const float a_mb = ms.part[4 * mb][kc];
+      const float a_nx = (mb < 3) ? ms.part[4 * (mb + 1)][kc] : ms.gend[kc];
+      float own[4], nb[4];
 #pragma unroll
-        for (int f = 0; f < 4; ++f) {
-          const int kc = kc0 + f;
-          const float aI = ms.part[4 * I][kc];
+      for (int e = 0; e < 4; ++e) {
+        own[e] = __expf(a_mb - Gc[e][f]);
+        nb[e] = __expf(a_nx - Gc[e][f]);
+      }
+#pragma unroll
+      for (int I = 0; I < 4; ++I) {
+        if (I >= mb) {
+          const float far = (I > mb + 1) ? __expf(ms.part[4 * I][kc] - a_nx) : 1.f;
+          float val[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) val[e] = anchored_k(kk[e][f], (I == mb) ? own[e] : nb[e], far, I > mb + 1);
           *reinterpret_cast<float4*>(smem + kit_offset(I) + blk_off<4>(kc, 4 * tg, kit_rs(I), 128)) =
-              make_float4(to_tf32(kk[0][f] * __expf(aI - Gc[0][f])), to_tf32(kk[1][f] * __expf(aI - Gc[1][f])),
-                          to_tf32(kk[2][f] * __expf(aI - Gc[2][f])), to_tf32(kk[3][f] * __expf(aI - Gc[3][f])));
+              make_float4(val[0], val[1], val[2], val[3]);
         }
       }
     }
@@ -683,7 +707,15 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
   {
     const int kc = tid & 127, blk = part;
     const float gend = ms.gend[kc];
+    // dd[k] = sum_v dS_1[k][v] S_0[k][v]: read here, before xt is reused for the block sums of dG
+    const float dd_k = (ms.xt[0][kc] + ms.xt[1][kc]) + (ms.xt[2][kc] + ms.xt[3][kc]);
     const float a_me = ms.part[4 * blk][kc];
+    const float a_nx = (blk < 3) ? ms.part[4 * (blk + 1)][kc] : gend;
+    // per-thread constants: everything but three exponentials per token comes from these
+    const float e_ame = __expf(a_me);            // exp(G) = exp(G - a_me) e_ame
+    const float t_end = __expf(gend - a_nx);     // exp(G_end - G) = exp(a_next - G) t_end
+    const float far2 = (blk + 2 < 4) ? __expf(ms.part[4 * (blk + 2)][kc] - a_nx) : 1.f;  // row block blk + 2
+    const float far3 = (blk + 3 < 4) ? __expf(ms.part[4 * (blk + 3)][kc] - a_nx) : 1.f;  // row block blk + 3
     float dGv[16];
     float e_part = 0.f, tot = 0.f;
 #pragma unroll
@@ -700,25 +732,37 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
         bv[t] = ldf<T>(p.beta, idx);
         sq[t] = p.scale * ldf<T>(p.q, idx);  // loaded here: no global load may follow a global store
       }
+      // row blocks I = blk + d that contain these tokens as columns, nearest first: the own block uses
+      // exp(a_me - G), the others exp(a_next - G) (times the block-to-block factor from d = 2 on)
+      tmem_ld8f(tmem_addr(tb, 32 * q4, d6_col(blk) + i0), x);  // dK^blk
+      float nb[8];
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        const float own = __expf(a_me - Gb[t]);
+        nb[t] = __expf(a_nx - Gb[t]);
+        Gb[t] = __expf(Gb[t] - a_me);  // from here on Gb holds the anchored decay exp(G - a_me)
+        P3[t] = x[t] * own;
+        dG[t] = -anchored_k(kv[t], own, 1.f, false) * x[t];
+      }
       tmem_ld8f(tmem_addr(tb, 32 * q4, kColD4 + i0), x);  // dKt
 #pragma unroll
       for (int t = 0; t < 8; ++t) {
-        const float et = __expf(gend - Gb[t]);
+        const float et = nb[t] * t_end;
         const float kt = kv[t] * et;
-        P3[t] = x[t] * et;
+        P3[t] = fmaf(x[t], et, P3[t]);
         e_part = fmaf(kt, x[t], e_part);
-        dG[t] = -kt * x[t];
+        dG[t] = fmaf(-kt, x[t], dG[t]);
       }
 #pragma unroll
-      for (int I = 0; I < 4; ++I) {
-        if (I >= blk) {
-          const float aI = ms.part[4 * I][kc];
-          tmem_ld8f(tmem_addr(tb, 32 * q4, d6_col(I) + i0), x);  // dK^I
+      for (int d = 1; d < 4; ++d) {
+        if (blk + d < 4) {
+          const float far = (d == 2) ? far2 : far3;
+          tmem_ld8f(tmem_addr(tb, 32 * q4, d6_col(blk + d) + i0), x);  // dK^(blk + d)
 #pragma unroll
           for (int t = 0; t < 8; ++t) {
-            const float ex = __expf(aI - Gb[t]);
+            const float ex = (d > 1) ? nb[t] * far : nb[t];
             P3[t] = fmaf(x[t], ex, P3[t]);
-            dG[t] = fmaf(-to_tf32(kv[t] * ex), x[t], dG[t]);
+            dG[t] = fmaf(-anchored_k(kv[t], nb[t], far, d > 1), x[t], dG[t]);
           }
         }
       }
@@ -726,7 +770,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
       tmem_ld8f(tmem_addr(tb, 32 * q4, kColD5 + i0), y);  // dEa
 #pragma unroll
       for (int t = 0; t < 8; ++t) {
-        const float eg = __expf(Gb[t]), ea = __expf(Gb[t] - a_me);
+        const float ea = Gb[t], eg = ea * e_ame;
         const float de = -x[t], dea = y[t];
         P2[t] = fmaf(de, eg, dea * ea);
         const float bk = bv[t] * kv[t];
@@ -738,7 +782,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
 #pragma unroll
       for (int t = 0; t < 8; ++t) {
         const int64_t idx = seq_idx(i0 + t) + kc;
-        const float eg = __expf(Gb[t]), ea = __expf(Gb[t] - a_me);
+        const float ea = Gb[t], eg = ea * e_ame;
         const float P1 = fmaf(x[t], eg, y[t] * ea);
         const float dGt = fmaf(to_tf32(sq[t] * ea), y[t], fmaf(sq[t] * eg, x[t], dG[t]));
         stf<T>(p.dq, idx, p.scale * P1);
@@ -751,7 +795,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     ms.xe[blk][kc] = e_part;
     __syncthreads();
     if (blk == 3) {
-      const float end_term = ms.xe[0][kc] + ms.xe[1][kc] + ms.xe[2][kc] + ms.xe[3][kc] + __expf(gend) * ms.dd[kc];
+      const float end_term = ms.xe[0][kc] + ms.xe[1][kc] + ms.xe[2][kc] + ms.xe[3][kc] + __expf(gend) * dd_k;
       dGv[15] += end_term;
       tot += end_term;
     }
@@ -824,6 +868,7 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
   int* status = reinterpret_cast<int*>(workspace + ws.off_status());
   cudaError_t err;
 
+  profile_mark(3, stream);
   BScanParams sp{workspace, d_out, ds_final, d_bnd, ds_init, status, T, H, n_chunks, n_ch};
   const int scan_smem = int(sizeof(BScanSmem));
   if (dtype == GDN2_BF16) {
@@ -839,6 +884,7 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
   }
   int st = check_launch();
   if (st != GDN2_OK) return st;
+  profile_mark(4, stream);
 
   int device = 0, sm_count = 0;
   err = cudaGetDevice(&device);
@@ -858,7 +904,9 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
     kernel<<<unsigned(n_ch < int64_t(sm_count) ? n_ch : int64_t(sm_count)), kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds);
   });
-  return check_launch();
+  st = check_launch();
+  profile_mark(5, stream);
+  return st;
 }
 
 }  // namespace gdn2

@@ -733,6 +733,7 @@ int launch_chunk_forward(const void* q, const void* k, const void* v, const void
   cudaError_t err = cudaMemsetAsync(status, 0, 256, stream);
   if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
 
+  profile_mark(0, stream);
   PrepParams pp{q, k, v, g, beta, w, workspace, T, H, n_chunks, n_ch, scale, training};
   GDN2_DISPATCH_TYPES(dtype, g_dtype, {
     auto kernel = chunk_prep_kernel<T, G>;
@@ -743,6 +744,7 @@ int launch_chunk_forward(const void* q, const void* k, const void* v, const void
   });
   int st = check_launch();
   if (st != GDN2_OK) return st;
+  profile_mark(1, stream);
 
   ScanParams sp{workspace, s_in, out, s_out, bnd, status, T, H, n_chunks, n_ch, workspace, training};
   const int smem = int(sizeof(ScanSmem));
@@ -757,7 +759,9 @@ int launch_chunk_forward(const void* q, const void* k, const void* v, const void
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
     kernel<<<unsigned(B * H), kScanThreads, smem, stream>>>(sp);
   }
-  return check_launch();
+  st = check_launch();
+  profile_mark(2, stream);
+  return st;
 }
 
 }  // namespace gdn2

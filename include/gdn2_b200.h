@@ -206,6 +206,17 @@ int gdn2_chunk_read_status(const void* workspace, int64_t batch, int64_t full_to
                            int64_t heads, void* stream);
 
 /*
+ * Per-kernel timing of the chunk entry points.  While enabled, gdn2_chunk_forward and
+ * gdn2_chunk_backward record CUDA events on their stream before, between and after their
+ * two kernels; gdn2_profile_chunk_kernels waits for the most recent ones and returns the
+ * four durations in milliseconds (prep, forward scan, reverse scan, VJP; a value is -1
+ * when that call has not run since profiling was enabled).  Off by default; measuring
+ * aid for benchmarks, no counterpart in the reference.
+ */
+int gdn2_profile_enable(int on);
+int gdn2_profile_chunk_kernels(float* prep_ms, float* scan_ms, float* bwd_scan_ms, float* vjp_ms);
+
+/*
  * Chunk forward (inference) for callers that must not allocate.  No counterpart in the
  * reference: it exists for hosts such as a serving runtime that partitions device memory
  * once at start-up, or a plugin hook that runs inside another component's memory plan,
