@@ -171,3 +171,23 @@ def test_prefill_configuration_properties():
     check(out[3:4, :, 5:7], state[3:4, 5:7], ref_out, ref_state)
     out_sub, state_sub = chunk_gdn2(*dev(*sub), output_final_state=True)
     assert torch.equal(out_sub, out[3:4, :, 5:7]) and torch.equal(state_sub, state[3:4, 5:7])
+
+
+def test_per_kernel_profile_events():
+    """`gdn2_profile_enable` / `gdn2_profile_chunk_kernels`: four positive durations after a
+    training forward + backward, nothing once profiling is switched off again."""
+
+    from gdn2_sm120_b200 import _lib
+
+    cpu = oracle.make_inputs(1, 256, 2, seed=21)
+    leaves = [t.to(DEV).requires_grad_(True) for t in cpu]
+    _lib.profile_enable(True)
+    try:
+        out, fin = chunk_gdn2(*leaves[:6], leaves[6], output_final_state=True)
+        torch.autograd.grad(out.float().sum() + fin.sum(), leaves)
+        times = _lib.profile_chunk_kernels()
+    finally:
+        _lib.profile_enable(False)
+    assert set(times) == {"chunk_prep_kernel", "chunk_scan_kernel", "chunk_bwd_scan_kernel", "chunk_bwd_vjp_kernel"}
+    assert all(0.0 < value < 100.0 for value in times.values())
+    assert _lib.profile_chunk_kernels() == {}
