@@ -302,7 +302,8 @@ class _MeanSquare(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad):
         (x,) = ctx.saved_tensors
-        return x * (grad * (2.0 / x.numel())).to(x.dtype)
+        # the multi-tensor kernel reads the 0-dim device scalar and keeps its loads vectorised (a broadcast `*` does not)
+        return torch._foreach_mul([x], (grad * (2.0 / x.numel())).to(x.dtype))[0]
 
 
 def train_step(pkg, leaves, s0):
