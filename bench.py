@@ -365,7 +365,6 @@ def run_gpu_arm(args):
     clocks = sampler.stop() if rank == 0 else None
     ms_local = begin.elapsed_time(end) / args.steps
     ms = shard.max_over_ranks(ms_local, device)
-    value = world * tokens_per_rank / (ms * 1e-3)
     del grads
 
     # ---- live per-kernel timing (dominant kernel -> roofline) ------------------------------------
@@ -376,8 +375,8 @@ def run_gpu_arm(args):
     per_kernel = {}
     for _ in range(3):
         train_step(pkg, leaves, s0)
-        for name, value in _lib.profile_chunk_kernels().items():
-            per_kernel.setdefault(name, []).append(value)
+        for name, duration in _lib.profile_chunk_kernels().items():
+            per_kernel.setdefault(name, []).append(duration)
     torch.cuda.synchronize()
     _lib.profile_enable(False)
     call_ms = {name: statistics.mean(b.elapsed_time(e) for b, e in pairs)
@@ -495,7 +494,8 @@ def run_gpu_arm(args):
 
     if rank == 0:
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "metric": METRIC, "value": world * tokens_per_rank / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "host_enqueue_ms_per_step": host_ms,
             "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16 inputs, fp32 state", "data": "synthetic",
