@@ -10,7 +10,6 @@
 //   Q    X[r = token i (64)][c = key k (128)]   RS = 4096   32 KiB   scale * gamma * q
 //   Kt   X[r = key k (128)][c = token j (64)]   RS = 2048   32 KiB   (k * gamma_end / gamma)^T
 //   A    X[r = token i (64)][c = token j (64)]  RS = 2048   16 KiB   tril(Q_gamma Kbar^T)
-//   Tm   X[r = token i (64)][c = token j (64)]  RS = 2048   16 KiB   (I+L)^-1
 //   D    float[128]                                         512 B    gamma_end
 // and, for training calls only (consumed by backward, which contracts over the other index):
 //   Yt   X[r = key k (128)][c = token i (64)]   RS = 2048   32 KiB   Y^T
@@ -33,8 +32,8 @@ namespace gdn2 {
 constexpr int kChunk = GDN2_CHUNK;  // 64
 
 constexpr int64_t kBlobY = 32768, kBlobUt = 32768, kBlobQ = 32768, kBlobKt = 32768;
-constexpr int64_t kBlobA = 16384, kBlobT = 16384, kBlobD = 512;
-constexpr int64_t kBlobFwd = kBlobY + kBlobUt + kBlobQ + kBlobKt + kBlobA + kBlobT + kBlobD;
+constexpr int64_t kBlobA = 16384, kBlobD = 512;
+constexpr int64_t kBlobFwd = kBlobY + kBlobUt + kBlobQ + kBlobKt + kBlobA + kBlobD;
 constexpr int64_t kBlobYt = 32768, kBlobQt = 32768, kBlobKn = 32768, kBlobAt = 16384, kBlobTt = 16384;
 constexpr int64_t kBlobRn = 32768, kBlobDZ = 8 * 4608;
 
@@ -46,8 +45,7 @@ struct WsLayout {
   __host__ __device__ int64_t off_q() const { return n_ch * (kBlobY + kBlobUt); }
   __host__ __device__ int64_t off_kt() const { return n_ch * (kBlobY + kBlobUt + kBlobQ); }
   __host__ __device__ int64_t off_a() const { return n_ch * (kBlobY + kBlobUt + kBlobQ + kBlobKt); }
-  __host__ __device__ int64_t off_t() const { return off_a() + n_ch * kBlobA; }
-  __host__ __device__ int64_t off_d() const { return off_t() + n_ch * kBlobT; }
+  __host__ __device__ int64_t off_d() const { return off_a() + n_ch * kBlobA; }
   __host__ __device__ int64_t off_status() const { return off_d() + n_ch * kBlobD; }
   // training-only arrays follow the status block
   __host__ __device__ int64_t off_yt() const { return off_status() + 256; }

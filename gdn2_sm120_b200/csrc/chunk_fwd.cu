@@ -377,16 +377,14 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     }
     __syncthreads();
   }
-  // T as tf32 tile X[r = i][c = j] in shared memory (MMA operand) and in the workspace (for backward)
+  // T as tf32 tile X[r = i][c = j] in shared memory (MMA operand); its transpose goes to the workspace when training
   {
-    uint8_t* blob_t = p.ws + ws.off_t() + ch * kBlobT;
     for (int e = tid; e < 64 * 16; e += kPrepThreads) {
       const int i = e & 63, c4t = e >> 6;  // consecutive threads -> consecutive rows -> contiguous 16-byte chunks
       const float4 tn = ld4(Tn + i * kLd + 4 * c4t);
       const float4 val = make_float4(to_tf32(tn.x), to_tf32(tn.y), to_tf32(tn.z), to_tf32(tn.w));
       const uint32_t off = blk_off<4>(i, 4 * c4t, 2048, 128);
       *reinterpret_cast<float4*>(sm.tmat + off) = val;
-      *reinterpret_cast<float4*>(blob_t + off) = val;
       if (training) {
         // transposed tiles X[r = j][c = i]: here `i` plays the role of the row j, 4*c4t.. of the column i
         const int j = i;

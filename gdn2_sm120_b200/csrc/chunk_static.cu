@@ -8,8 +8,8 @@
 //
 // Consequences the caller must know:
 //   * the array has a fixed size: batch * (full_tokens / 64) * heads <= GDN2_STATIC_MAX_CHUNK_HEADS
-//     (64), about 10 MiB; larger problems are rejected with GDN2_ERR_TOO_LARGE.  Every GPU that loads
-//     the library holds those 10 MiB until the process exits.
+//     (64), about 9 MiB; larger problems are rejected with GDN2_ERR_TOO_LARGE.  Every GPU that loads
+//     the library holds those 9 MiB until the process exits.
 //   * the first call on each device looks up the array's device address (a one-off driver query that
 //     may load the module); make that first call before starting any stream capture.
 //   * all calls on a device share the one array and it keeps whatever the previous call left in it.

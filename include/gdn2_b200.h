@@ -222,7 +222,7 @@ int gdn2_profile_chunk_kernels(float* prep_ms, float* scan_ms, float* bwd_scan_m
  * once at start-up, or a plugin hook that runs inside another component's memory plan,
  * where obtaining a workspace per call is not possible.  Same kernels and results as
  * gdn2_chunk_forward with training = 0 and chunk_boundaries = NULL, but the WY workspace
- * is a fixed ~10 MiB array inside the library image (held by every GPU that loads the
+ * is a fixed ~9 MiB array inside the library image (held by every GPU that loads the
  * library, until the process exits).
  *   limit      batch * (full_tokens / 64) * heads <= GDN2_STATIC_MAX_CHUNK_HEADS, otherwise
  *              GDN2_ERR_TOO_LARGE
