@@ -217,22 +217,29 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
                         to_tf32(knb[2] * t_far[far][2]), to_tf32(knb[3] * t_far[far][3]));
       }
     }
-    // natural workspace tiles X[r = i][c = k]: Q_gamma always, K_tail when training
-    *reinterpret_cast<float4*>(blob_q + blk_off<4>(i, kc0, 4096, 128)) =
-        make_float4(qgam[e][0], qgam[e][1], qgam[e][2], qgam[e][3]);
-    if (training) {
-      *reinterpret_cast<float4*>(blob_kn + blk_off<4>(i, kc0, 4096, 128)) =
-          make_float4(ktail[e][0], ktail[e][1], ktail[e][2], ktail[e][3]);
+    // natural workspace tiles X[r = i][c = k]: Q_gamma always, K_tail when training.  The chunks of
+    // tokens i - 1 and i (i odd) are neighbours in a blocked tile: one 32-byte store for the pair.
+    if (e & 1) {
+      const uint32_t off = blk_off<4>(i - 1, kc0, 4096, 128);
+      store_global_32b(blob_q + off, make_float4(qgam[e - 1][0], qgam[e - 1][1], qgam[e - 1][2], qgam[e - 1][3]),
+                       make_float4(qgam[e][0], qgam[e][1], qgam[e][2], qgam[e][3]));
+      if (training) {
+        store_global_32b(blob_kn + off, make_float4(ktail[e - 1][0], ktail[e - 1][1], ktail[e - 1][2], ktail[e - 1][3]),
+                         make_float4(ktail[e][0], ktail[e][1], ktail[e][2], ktail[e][3]));
+      }
     }
   }
-  // transposed workspace tiles X[r = channel][c = token]: one 16-byte chunk (4 tokens) per channel
+  // transposed workspace tiles X[r = channel][c = token]: one 16-byte chunk (4 tokens) per channel, the
+  // chunks of channels f and f + 1 next to each other
 #pragma unroll
-  for (int f = 0; f < 4; ++f) {
+  for (int f = 0; f < 4; f += 2) {
     const uint32_t off = blk_off<4>(kc0 + f, 4 * tg, 2048, 128);
-    *reinterpret_cast<float4*>(blob_kt + off) = make_float4(ktail[0][f], ktail[1][f], ktail[2][f], ktail[3][f]);
+    store_global_32b(blob_kt + off, make_float4(ktail[0][f], ktail[1][f], ktail[2][f], ktail[3][f]),
+                     make_float4(ktail[0][f + 1], ktail[1][f + 1], ktail[2][f + 1], ktail[3][f + 1]));
     if (training) {
-      *reinterpret_cast<float4*>(p.ws + ws.off_qt() + ch * kBlobQt + off) =
-          make_float4(qgam[0][f], qgam[1][f], qgam[2][f], qgam[3][f]);
+      store_global_32b(p.ws + ws.off_qt() + ch * kBlobQt + off,
+                       make_float4(qgam[0][f], qgam[1][f], qgam[2][f], qgam[3][f]),
+                       make_float4(qgam[0][f + 1], qgam[1][f + 1], qgam[2][f + 1], qgam[3][f + 1]));
     }
   }
   if (tid < kDim) {
