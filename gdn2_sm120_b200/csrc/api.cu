@@ -3,6 +3,7 @@
 
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -56,6 +57,40 @@ void profile_mark(int index, cudaStream_t stream) {
   cudaEventRecord(g_profile_events[index], stream);
   if (index == 2) g_profile_recorded[0] = true;
   if (index == 5) g_profile_recorded[1] = true;
+}
+
+// Opt a kernel in to more than 48 KiB of dynamic shared memory, once per (kernel, device): launches
+// after the first make no attribute call (cheaper, and nothing but the launch itself happens on the
+// stream's behalf, which keeps the entry points usable under stream capture).
+namespace {
+struct SmemOptIn { const void* kernel; uint64_t devices; int bytes; };
+SmemOptIn g_smem_opt_in[64];
+int g_smem_opt_in_count = 0;
+std::mutex g_smem_opt_in_mutex;
+}  // namespace
+
+cudaError_t ensure_dynamic_smem(const void* kernel, int bytes) {
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return err;
+  const uint64_t bit = 1ull << (device & 63);
+  std::lock_guard<std::mutex> lock(g_smem_opt_in_mutex);
+  SmemOptIn* entry = nullptr;
+  for (int i = 0; i < g_smem_opt_in_count; ++i) {
+    if (g_smem_opt_in[i].kernel == kernel) { entry = &g_smem_opt_in[i]; break; }
+  }
+  if (entry != nullptr && (entry->devices & bit) != 0 && entry->bytes >= bytes) return cudaSuccess;
+  err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (err != cudaSuccess) return err;
+  if (entry == nullptr && g_smem_opt_in_count < 64) {
+    entry = &g_smem_opt_in[g_smem_opt_in_count++];
+    *entry = SmemOptIn{kernel, 0, bytes};
+  }
+  if (entry != nullptr) {
+    if (entry->bytes != bytes) { entry->bytes = bytes; entry->devices = 0; }
+    entry->devices |= bit;
+  }
+  return cudaSuccess;
 }
 
 int check_launch() {

@@ -873,12 +873,12 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
   const int scan_smem = int(sizeof(BScanSmem));
   if (dtype == GDN2_BF16) {
     auto kernel = chunk_bwd_scan_kernel<__nv_bfloat16>;
-    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, scan_smem);
+    err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), scan_smem);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
     kernel<<<unsigned(B * H), kBScanThreads, scan_smem, stream>>>(sp);
   } else {
     auto kernel = chunk_bwd_scan_kernel<__half>;
-    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, scan_smem);
+    err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), scan_smem);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
     kernel<<<unsigned(B * H), kBScanThreads, scan_smem, stream>>>(sp);
   }
@@ -900,7 +900,7 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
                status, T, H, n_chunks, n_ch, scale};
   GDN2_DISPATCH_TYPES(dtype, g_dtype, {
     auto kernel = chunk_bwd_vjp_kernel<T, G>;
-    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kVjpSmemBytes);
+    err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kVjpSmemBytes);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
     kernel<<<unsigned(n_ch < int64_t(sm_count) ? n_ch : int64_t(sm_count)), kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds);
   });

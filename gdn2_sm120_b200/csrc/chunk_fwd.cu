@@ -743,7 +743,7 @@ int launch_chunk_forward(const void* q, const void* k, const void* v, const void
   GDN2_DISPATCH_TYPES(dtype, g_dtype, {
     auto kernel = chunk_prep_kernel<T, G>;
     const int smem = int(sizeof(PrepSmem));
-    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
     kernel<<<unsigned(n_ch), kPrepThreads, smem, stream>>>(pp);
   });
@@ -755,12 +755,12 @@ int launch_chunk_forward(const void* q, const void* k, const void* v, const void
   const int smem = int(sizeof(ScanSmem));
   if (dtype == GDN2_BF16) {
     auto kernel = chunk_scan_kernel<__nv_bfloat16>;
-    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
     kernel<<<unsigned(B * H), kScanThreads, smem, stream>>>(sp);
   } else {
     auto kernel = chunk_scan_kernel<__half>;
-    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
     kernel<<<unsigned(B * H), kScanThreads, smem, stream>>>(sp);
   }

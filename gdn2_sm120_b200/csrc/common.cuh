@@ -62,6 +62,7 @@ __device__ __forceinline__ void store4(float* p, bool vec, const float (&x)[4]) 
 // ---- host-side status helpers ---------------------------------------------------
 void record_cuda_error(cudaError_t err);  // defined in api.cu
 int check_launch();                       // cudaGetLastError -> status
+cudaError_t ensure_dynamic_smem(const void* kernel, int bytes);  // once per (kernel, device) opt-in (api.cu)
 void profile_mark(int index, cudaStream_t stream);  // records timing event `index` when profiling is on (api.cu)
 
 inline bool valid_seq_dtype(int d) { return d == GDN2_BF16 || d == GDN2_FP16; }

@@ -666,7 +666,7 @@ int launch_token_forward(const void* q, const void* k, const void* v, const void
     const unsigned grid = unsigned(B * H < sms ? B * H : sms);
     GDN2_DISPATCH_TYPES(dtype, g_dtype, {
       auto kernel = token_decode_ring_kernel<T, G>;
-      err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
       if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
       kernel<<<grid, kDecThreads, smem, stream>>>(dp);
     });
@@ -723,7 +723,7 @@ int launch_token_chunk_vjp(const void* q, const void* k, const void* v, const vo
     auto kernel = token_chunk_vjp_kernel<T, G>;
     const int smem = int(sizeof(VjpSmem<T>));
     cudaError_t err =
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     if (err != cudaSuccess) {
       record_cuda_error(err);
       return GDN2_ERR_LAUNCH;
