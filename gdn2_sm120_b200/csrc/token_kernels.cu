@@ -250,27 +250,29 @@ __global__ void __launch_bounds__(kDecThreads, 1) token_decode_ring_kernel(const
   for (int64_t n = 0; n < n_mine; ++n) {
     const int s = int(n % kDecStages), buf = int(n & 1);
     const int64_t bh = first + n * stride;
-    if (tid == 0 && n + 2 < n_mine) {
-      // slot of head n + 2 was last used by head n - 1: its store must have finished reading it
-      tc::bulk_wait_read_all();
-      issue_load(n + 2);
-    }
     if (n + 1 < n_mine) fetch_vectors(n + 1);
     if (!dead && !tc::mbar_wait(&sm.full[s], uint32_t((n / kDecStages) & 1), 1u << 20)) dead = true;
 
     float* S = sm.state[s] + col;
     const int k0 = 64 * kh;
     // pass 1: r[v] = sum_k S[k][v] * (a[k] e[k])
-    float r = 0.f;
+    float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;  // four chains: the sum is latency-bound otherwise
 #pragma unroll 4
     for (int kq = 0; kq < 64; kq += 4) {
       const float4 f = *reinterpret_cast<const float4*>(&sm.ae[buf][k0 + kq]);
-      r = fmaf(S[(k0 + kq) * kDim], f.x, r);
-      r = fmaf(S[(k0 + kq + 1) * kDim], f.y, r);
-      r = fmaf(S[(k0 + kq + 2) * kDim], f.z, r);
-      r = fmaf(S[(k0 + kq + 3) * kDim], f.w, r);
+      r0 = fmaf(S[(k0 + kq) * kDim], f.x, r0);
+      r1 = fmaf(S[(k0 + kq + 1) * kDim], f.y, r1);
+      r2 = fmaf(S[(k0 + kq + 2) * kDim], f.z, r2);
+      r3 = fmaf(S[(k0 + kq + 3) * kDim], f.w, r3);
     }
-    sm.red[buf][kh][col] = r;
+    sm.red[buf][kh][col] = (r0 + r1) + (r2 + r3);
+    if (tid == 0 && n + 2 < n_mine) {
+      // The slot of head n + 2 was last used by head n - 1, whose store was issued at the end of the
+      // previous iteration: by now it has normally finished reading the slot, so this wait does not
+      // hold up the warp (at the top of the iteration it stalled every head by the store's read time).
+      tc::bulk_wait_read_all();
+      issue_load(n + 2);
+    }
     __syncthreads();
     const float u = sm.z[buf][col] - (sm.red[buf][0][col] + sm.red[buf][1][col]);
     // pass 2: S <- a S + k u^T ; o[v] = sum_k S[k][v] (scale q[k])
