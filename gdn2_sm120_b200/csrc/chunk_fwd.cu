@@ -329,9 +329,6 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
   // T is kept in both orientations (Tn row-major, Tc column-major) and the block products W transposed,
   // so that both factors of every inner product are read as 16-byte vectors along the summed index.
   auto ld4 = [](const float* ptr) { return *reinterpret_cast<const float4*>(ptr); };
-  auto dot4 = [](float4 a, float4 b, float s) {
-    return fmaf(a.w, b.w, fmaf(a.z, b.z, fmaf(a.y, b.y, fmaf(a.x, b.x, s))));
-  };
   if (tid < 64) {
     const int I = tid >> 4, cc = tid & 15;
     float x[16];
@@ -365,9 +362,14 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
       const int J = pair, I = pair + d;
       const float* lrow = Ln + (16 * I + r) * kLd + 16 * J;
       const float* tcol = Tc + (16 * J + cc) * kLd + 16 * J;
-      float s = 0.f;
-      for (int m4 = 0; m4 < 4 * d; ++m4) s = dot4(ld4(lrow + 4 * m4), ld4(tcol + 4 * m4), s);
-      Wt[(pair * 16 + cc) * kLdW + r] = s;
+      // four independent chains (one per vector component): the sum is latency-bound otherwise
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int m4 = 0; m4 < 4 * d; ++m4) {
+        const float4 a = ld4(lrow + 4 * m4), b = ld4(tcol + 4 * m4);
+        acc.x = fmaf(a.x, b.x, acc.x); acc.y = fmaf(a.y, b.y, acc.y);
+        acc.z = fmaf(a.z, b.z, acc.z); acc.w = fmaf(a.w, b.w, acc.w);
+      }
+      Wt[(pair * 16 + cc) * kLdW + r] = (acc.x + acc.y) + (acc.z + acc.w);
     }
     __syncthreads();
     // T_IJ = -T_II W
@@ -376,9 +378,14 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
       const int J = pair, I = pair + d;
       const float* trow = Tn + (16 * I + r) * kLd + 16 * I;
       const float* wcol = Wt + (pair * 16 + cc) * kLdW;
-      float s = 0.f;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int m4 = 0; m4 < 4; ++m4) s = dot4(ld4(trow + 4 * m4), ld4(wcol + 4 * m4), s);
+      for (int m4 = 0; m4 < 4; ++m4) {
+        const float4 a = ld4(trow + 4 * m4), b = ld4(wcol + 4 * m4);
+        acc.x = fmaf(a.x, b.x, acc.x); acc.y = fmaf(a.y, b.y, acc.y);
+        acc.z = fmaf(a.z, b.z, acc.z); acc.w = fmaf(a.w, b.w, acc.w);
+      }
+      const float s = (acc.x + acc.y) + (acc.z + acc.w);
       Tn[(16 * I + r) * kLd + 16 * J + cc] = -s;
       Tc[(16 * J + cc) * kLd + 16 * I + r] = -s;
     }
