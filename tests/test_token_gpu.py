@@ -271,3 +271,32 @@ def test_decode_ring_kernel_out_of_place_and_odd_head_count(dtype, low_g):
     check_forward(out, fin, ref_out, ref_state, dtype)
     out2, fin2 = recurrent_gdn2(q, k, v, g, beta, w, s0, scale=0.11)
     assert torch.equal(out, out2) and torch.equal(fin, fin2)
+
+
+def test_decode_step_replays_from_a_cuda_graph():
+    """The serving call with caller-owned buffers (`out=`, `inplace_final_state=True`) makes no
+    allocation and no synchronisation, so a decode step can be captured once and replayed: three
+    replays must equal three eager steps."""
+
+    cpu = oracle.make_inputs(8, 1, 32, seed=31)   # 256 heads: the persistent ring kernel
+    tensors = [t.to(DEV) for t in cpu]
+    eager_state = tensors[6].clone()
+    eager_out = torch.empty_like(tensors[0])
+    for _ in range(3):
+        recurrent_gdn2(*tensors[:6], eager_state, out=eager_out, inplace_final_state=True)
+
+    state = tensors[6].clone()
+    out = torch.empty_like(tensors[0])
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):   # warm-up outside the capture (first-use set-up of the kernels)
+        recurrent_gdn2(*tensors[:6], state.clone(), out=out, inplace_final_state=True)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        recurrent_gdn2(*tensors[:6], state, out=out, inplace_final_state=True)
+    state.copy_(tensors[6])         # the capture itself did not run the step
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(state, eager_state) and torch.equal(out, eager_out)
