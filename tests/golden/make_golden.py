@@ -96,4 +96,6 @@ def main(reference_src: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference/src")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to the reference checkout's src directory>")
+    main(sys.argv[1])
