@@ -45,10 +45,10 @@ BWD_BYTES = (5 * 256 + 512 + 256) + (5 * 256 + 512)  # read inputs + dO, write 6
 # summarised in profiles/chunk_kernels_B1_T4096_H8_ncu_full.md (512 chunk-heads, scaled by the number of
 # chunk-heads: the kernels' traffic is proportional to it)
 NCU_TRAFFIC_PER_CHUNK_HEAD = {
-    "chunk_prep_kernel": 305.6e3,
-    "chunk_scan_kernel": 188.3e3,
-    "chunk_bwd_scan_kernel": 186.4e3,
-    "chunk_bwd_vjp_kernel": 403.0e3,
+    "chunk_prep_kernel": 282.8e3,
+    "chunk_scan_kernel": 187.8e3,
+    "chunk_bwd_scan_kernel": 185.8e3,
+    "chunk_bwd_vjp_kernel": 400.7e3,
 }
 DECODE_BYTES_PER_HEAD = 2 * 65536 + 1792 + 256
 T1_ZERO_BYTES_PER_HEAD = 65536 + 1280
