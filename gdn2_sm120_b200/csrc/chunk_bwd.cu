@@ -578,8 +578,9 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
 
   // ================================ phase C: Gram VJP =============================================
   // [-dL_raw ; dA_raw] out of TMEM: masked tiles [dL ; dA] (rows) and their transposes; the four
-  // warps of a quadrant take 16 columns each.  (Every thread is past the phase-B wait and the last
-  // shared-memory reads of phase B were MMA reads, so the phase-B regions may be overwritten.)
+  // warps of a quadrant take 16 columns each.  These tiles lie over the [dZ ; dO] stack, whose last
+  // readers (the first MMA batch and the dv / dw pass) are done; R and the dS_1 buffer may still be
+  // read by the second half of M4 and are not touched before the wait further down.
   {
     const int r = 32 * q4 + lane, i = r & 63;
     uint8_t* tr_base = smem + ((r < 64) ? kOffDLt : kOffDAt);
