@@ -293,7 +293,7 @@ constexpr int kOffRn = kOffStack + 16 * kRsN;     // B: R X[r = j][c = v], RS 40
 constexpr int kOffS0 = kOffRn + 32768;            // B: S_0 X[r = k][c = v], RS 4096             65536
 constexpr int kOffDs1 = kOffS0 + 65536;           // B: dS_1 half X[r = k][c = 64 v], RS 2048    32768
 constexpr int kEndB = kOffDs1 + 32768;            // 204800
-constexpr int kOffStack2 = 0;                     // C: [dL ; dA] X[r = 128][c = j], RS 2048     32768
+constexpr int kOffStack2 = 0;                     // C: [dL_I ; dA_I] for I = 0..3, X[r = 128][c = j], RS 2048   32768
 constexpr int kOffDLt = 32768;                    // C: dL^T X[r = j][c = i], RS kRsS            18432
 constexpr int kOffDAt = kOffDLt + 8 * kRsS;       // C: dA^T                                     18432
 constexpr int kOffKIt = kOffDAt + 8 * kRsS;       // C: (K^I)^T X[r = k][c = j < 16 (I+1)], RS 512 (I+1) + 16
@@ -583,6 +583,9 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
   // read by the second half of M4 and are not touched before the wait further down.
   {
     const int r = 32 * q4 + lane, i = r & 63;
+    // row of the stacked tile: the dL and dA rows of a 16-token block sit next to each other, so that
+    // one N = 32 instruction multiplies both by (K^I)^T
+    const int row2 = 32 * (i >> 4) + ((r < 64) ? 0 : 16) + (i & 15);
     uint8_t* tr_base = smem + ((r < 64) ? kOffDLt : kOffDAt);
     const int c0 = 16 * part;
     uint32_t raw[16];
@@ -598,7 +601,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     }
 #pragma unroll
     for (int j4 = 0; j4 < 4; ++j4) {
-      *reinterpret_cast<float4*>(smem + kOffStack2 + blk_off<4>(r, c0 + 4 * j4, 2048, 128)) =
+      *reinterpret_cast<float4*>(smem + kOffStack2 + blk_off<4>(row2, c0 + 4 * j4, 2048, 128)) =
           make_float4(vals[4 * j4], vals[4 * j4 + 1], vals[4 * j4 + 2], vals[4 * j4 + 3]);
     }
   }
@@ -663,18 +666,15 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     const uint32_t s2 = smem_u32(smem + kOffStack2);
     const uint32_t dlt = smem_u32(smem + kOffDLt), dat = smem_u32(smem + kOffDAt);
     const uint32_t eat0 = smem_u32(smem + kOffEat), qat0 = smem_u32(smem + kOffQat);
-    const uint32_t id16 = idesc(128, 16, kFmtTF32, kMajorK, kMajorK);
-    // dEa^T | dQa^T: columns 16 I .. of each 64-column half = (K^I)^T x rows of block I of [dL ; dA]
+    const uint32_t id32 = idesc(128, 32, kFmtTF32, kMajorK, kMajorK);
+    // [dEa_I^T | dQa_I^T] (columns 32 I .. 32 I + 31) = (K^I)^T x the 32 stacked rows [dL_I ; dA_I]
 #pragma unroll
     for (int I = 0; I < 4; ++I) {
       const uint32_t kit = smem_u32(smem + kit_offset(I));
       const uint32_t rs = uint32_t(kit_rs(I));
-#pragma unroll
-      for (int pt = 0; pt < 2; ++pt) {
-        for (int ks = 0; ks < 2 * (I + 1); ++ks) {
-          mma_tf32_ss(tb + kColD5 + pt * 64 + 16 * I, smem_desc(kit + ks * 256, 128, rs),
-                      smem_desc(s2 + (pt * 8 + 2 * I) * 2048 + ks * 256, 128, 2048), id16, ks > 0 ? 1u : 0u);
-        }
+      for (int ks = 0; ks < 2 * (I + 1); ++ks) {
+        mma_tf32_ss(tb + kColD5 + 32 * I, smem_desc(kit + ks * 256, 128, rs),
+                    smem_desc(s2 + 4 * I * 2048 + ks * 256, 128, 2048), id32, ks > 0 ? 1u : 0u);
       }
     }
     // (dK^I)^T = Ea^T[:, block I] dL[block I, :] + Qa^T[:, block I] dA[block I, :]
@@ -768,7 +768,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
         }
       }
       tmem_ld8f(tmem_addr(tb, 32 * q4, kColD3 + i0), x);  // -dE (state part)
-      tmem_ld8f(tmem_addr(tb, 32 * q4, kColD5 + i0), y);  // dEa
+      tmem_ld8f(tmem_addr(tb, 32 * q4, kColD5 + 32 * blk + 8 * sb), y);  // dEa
 #pragma unroll
       for (int t = 0; t < 8; ++t) {
         const float ea = Gb[t], eg = ea * e_ame;
@@ -779,7 +779,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
         dG[t] = fmaf(to_tf32(bk * ea), dea, dG[t]);
       }
       tmem_ld8f(tmem_addr(tb, 32 * q4, kColD3 + 64 + i0), x);  // dQg (state part)
-      tmem_ld8f(tmem_addr(tb, 32 * q4, kColD5 + 64 + i0), y);  // dQa
+      tmem_ld8f(tmem_addr(tb, 32 * q4, kColD5 + 32 * blk + 16 + 8 * sb), y);  // dQa
 #pragma unroll
       for (int t = 0; t < 8; ++t) {
         const int64_t idx = seq_idx(i0 + t) + kc;
