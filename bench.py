@@ -390,7 +390,9 @@ def run_gpu_arm(args):
                 train_step(pkg, leaves, s0)
             torch.cuda.current_stream().wait_stream(side)
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            # thread-local error mode: other threads of the process (NCCL's watchdog polls events) may make
+            # calls that a global-mode capture would treat as errors
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                 graph_loss, graph_grads = train_step(pkg, leaves, s0)
             for _ in range(3):
                 graph.replay()
