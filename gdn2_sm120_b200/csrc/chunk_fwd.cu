@@ -354,43 +354,80 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     }
   }
   __syncthreads();
-  for (int d = 1; d < 4; ++d) {
-    const int n_pairs = 4 - d;
-    // W = L[I rows, 16J .. 16I) * T[16J .. 16I, J cols]
-    for (int e = tid; e < n_pairs * 256; e += kPrepThreads) {
-      const int pair = e >> 8, r = (e >> 4) & 15, cc = e & 15;
-      const int J = pair, I = pair + d;
-      const float* lrow = Ln + (16 * I + r) * kLd + 16 * J;
-      const float* tcol = Tc + (16 * J + cc) * kLd + 16 * J;
-      // four independent chains (one per vector component): the sum is latency-bound otherwise
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int m4 = 0; m4 < 4 * d; ++m4) {
-        const float4 a = ld4(lrow + 4 * m4), b = ld4(tcol + 4 * m4);
-        acc.x = fmaf(a.x, b.x, acc.x); acc.y = fmaf(a.y, b.y, acc.y);
-        acc.z = fmaf(a.z, b.z, acc.z); acc.w = fmaf(a.w, b.w, acc.w);
-      }
-      Wt[(pair * 16 + cc) * kLdW + r] = (acc.x + acc.y) + (acc.z + acc.w);
-    }
-    __syncthreads();
-    // T_IJ = -T_II W
-    for (int e = tid; e < n_pairs * 256; e += kPrepThreads) {
-      const int pair = e >> 8, r = (e >> 4) & 15, cc = e & 15;
-      const int J = pair, I = pair + d;
-      const float* trow = Tn + (16 * I + r) * kLd + 16 * I;
-      const float* wcol = Wt + (pair * 16 + cc) * kLdW;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  // Two levels of 2 x 2 blocking instead of one block row at a time (four barriers fewer):
+  // level 1: the 16 x 16 blocks (1,0) and (3,2) complete the two 32 x 32 diagonal inverses P and Q,
+  // level 2: T[32.., ..32) = -Q (L[32.., ..32) P).
+  // level 1, W = L_IJ T_JJ for (I, J) = (1, 0), (3, 2)
+  {
+    const int pair = tid >> 8, r = (tid >> 4) & 15, cc = tid & 15;
+    const int J = 2 * pair, I = J + 1;
+    const float* lrow = Ln + (16 * I + r) * kLd + 16 * J;
+    const float* tcol = Tc + (16 * J + cc) * kLd + 16 * J;
+    // four independent chains (one per vector component): the sum is latency-bound otherwise
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int m4 = 0; m4 < 4; ++m4) {
-        const float4 a = ld4(trow + 4 * m4), b = ld4(wcol + 4 * m4);
-        acc.x = fmaf(a.x, b.x, acc.x); acc.y = fmaf(a.y, b.y, acc.y);
-        acc.z = fmaf(a.z, b.z, acc.z); acc.w = fmaf(a.w, b.w, acc.w);
-      }
-      const float s = (acc.x + acc.y) + (acc.z + acc.w);
-      Tn[(16 * I + r) * kLd + 16 * J + cc] = -s;
-      Tc[(16 * J + cc) * kLd + 16 * I + r] = -s;
+    for (int m4 = 0; m4 < 4; ++m4) {
+      const float4 a = ld4(lrow + 4 * m4), b = ld4(tcol + 4 * m4);
+      acc.x = fmaf(a.x, b.x, acc.x); acc.y = fmaf(a.y, b.y, acc.y);
+      acc.z = fmaf(a.z, b.z, acc.z); acc.w = fmaf(a.w, b.w, acc.w);
     }
-    __syncthreads();
+    Wt[(pair * 16 + cc) * kLdW + r] = (acc.x + acc.y) + (acc.z + acc.w);
   }
+  __syncthreads();
+  // level 1, T_IJ = -T_II W
+  {
+    const int pair = tid >> 8, r = (tid >> 4) & 15, cc = tid & 15;
+    const int J = 2 * pair, I = J + 1;
+    const float* trow = Tn + (16 * I + r) * kLd + 16 * I;
+    const float* wcol = Wt + (pair * 16 + cc) * kLdW;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int m4 = 0; m4 < 4; ++m4) {
+      const float4 a = ld4(trow + 4 * m4), b = ld4(wcol + 4 * m4);
+      acc.x = fmaf(a.x, b.x, acc.x); acc.y = fmaf(a.y, b.y, acc.y);
+      acc.z = fmaf(a.z, b.z, acc.z); acc.w = fmaf(a.w, b.w, acc.w);
+    }
+    const float s = (acc.x + acc.y) + (acc.z + acc.w);
+    Tn[(16 * I + r) * kLd + 16 * J + cc] = -s;
+    Tc[(16 * J + cc) * kLd + 16 * I + r] = -s;
+  }
+  __syncthreads();
+  // level 2, W2 = L[32.., ..32) P, stored transposed over the (now dead) first 32 rows of L
+  float* W2t = Ln;  // W2t[c][r] = W2[r][c], leading dimension kLd
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int e = tid + kPrepThreads * half, r = e >> 5, cc = e & 31;
+    const float* lrow = Ln + (32 + r) * kLd;
+    const float* pcol = Tc + cc * kLd;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int m4 = 0; m4 < 8; ++m4) {
+      const float4 a = ld4(lrow + 4 * m4), b = ld4(pcol + 4 * m4);
+      acc.x = fmaf(a.x, b.x, acc.x); acc.y = fmaf(a.y, b.y, acc.y);
+      acc.z = fmaf(a.z, b.z, acc.z); acc.w = fmaf(a.w, b.w, acc.w);
+    }
+    // rows 32.. of L are read above by other threads; W2t lives in rows 0..31, which nobody reads any more
+    W2t[cc * kLd + r] = (acc.x + acc.y) + (acc.z + acc.w);
+  }
+  __syncthreads();
+  // level 2, T[32 + r][c] = -sum_m Q[r][m] W2[m][c]
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int e = tid + kPrepThreads * half, r = e >> 5, cc = e & 31;
+    const float* qrow = Tn + (32 + r) * kLd + 32;
+    const float* wcol = W2t + cc * kLd;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int m4 = 0; m4 < 8; ++m4) {
+      const float4 a = ld4(qrow + 4 * m4), b = ld4(wcol + 4 * m4);
+      acc.x = fmaf(a.x, b.x, acc.x); acc.y = fmaf(a.y, b.y, acc.y);
+      acc.z = fmaf(a.z, b.z, acc.z); acc.w = fmaf(a.w, b.w, acc.w);
+    }
+    const float s = (acc.x + acc.y) + (acc.z + acc.w);
+    Tn[(32 + r) * kLd + cc] = -s;
+    Tc[cc * kLd + 32 + r] = -s;
+  }
+  __syncthreads();
   // T as tf32 tile X[r = i][c = j] in shared memory (MMA operand); its transpose goes to the workspace when training
   {
     for (int e = tid; e < 64 * 16; e += kPrepThreads) {
