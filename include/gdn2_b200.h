@@ -146,7 +146,7 @@ int gdn2_token_chunk_vjp(const void* q, const void* k, const void* v, const void
  *
  * Bytes of caller-owned workspace the chunk kernels need for `full_tokens` leading
  * tokens (a multiple of GDN2_CHUNK) of a [batch, T, heads, 128] problem.  The workspace
- * holds the per-chunk WY factors (Y, U^T, Q_gamma, K_tail^T, A_qk, (I+L)^-1, gamma_end)
+ * holds the per-chunk WY factors (Y, U^T, Q_gamma, K_tail^T, A_qk, gamma_end)
  * as operand-ready tiles plus a device status word.  With `training` != 0 it is larger:
  * it also holds the transposed tiles and the residuals that gdn2_chunk_backward consumes,
  * and must stay alive (and unmodified) until that call has run.
@@ -183,10 +183,12 @@ int gdn2_chunk_forward(const void* q, const void* k, const void* v, const void* 
  *   d_final_state    cotangent of the state after token full_tokens-1, or NULL (zero)
  *   chunk_boundaries the forward's fp32 [B, full_tokens/64 + 1, H,128,128] checkpoints
  *   d_boundaries     caller-owned scratch of the same shape (cotangent at every chunk start)
- *   workspace        the forward's training workspace (read, and its dR^T slots written)
+ *   workspace        the forward's training workspace (read, and its dZ slots written)
  *   dq, dk, dv, dbeta, dw (`dtype`), dg (`g_dtype`): rows [0, full_tokens) are written
  *   d_initial_state  fp32 [B,H,128,128] or NULL
- * Every pointer must be 16-byte aligned.
+ * Every pointer must be 16-byte aligned.  The call encodes two TMA tensor maps over
+ * chunk_boundaries and d_boundaries on the host (cuTensorMapEncodeTiled, looked up through
+ * cudaGetDriverEntryPoint); GDN2_ERR_LAUNCH if the driver does not provide it.
  */
 int gdn2_chunk_backward(const void* q, const void* k, const void* v, const void* g,
                         const void* beta, const void* w, const void* d_out,
