@@ -578,36 +578,39 @@ def run_decode(pkg, device, peak):
     from gdn2_sm120_b200 import _lib
 
     results = {}
-    B, H = 64, 32
-    inp = device_inputs(B, 1, H, device, seed=7)
-    states = [inp[6].clone() for _ in range(4)]  # 4 x 128 MiB > L2
-    out = torch.empty_like(inp[0])
-    reps = 40
+    H = 32
+    # B = 64: the decode configuration; B = 128: one GPU's shard of the 8-GPU decode configuration (B = 1024)
+    for B in (64, 128):
+        inp = device_inputs(B, 1, H, device, seed=7)
+        states = [inp[6].clone() for _ in range(4)]  # 4 x 128 MiB (or more) > L2
+        out = torch.empty_like(inp[0])
+        reps = 40
 
-    def step(i):
-        pkg.recurrent_gdn2(*inp[:6], states[i % 4], out=out, inplace_final_state=True)
+        def step(i):
+            pkg.recurrent_gdn2(*inp[:6], states[i % 4], out=out, inplace_final_state=True)
 
-    for i in range(8):
-        step(i)
-    torch.cuda.synchronize()
-    b, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    b.record()
-    for i in range(reps):
-        step(i)
-    e.record()
-    torch.cuda.synchronize()
-    api_us = b.elapsed_time(e) * 1e3 / reps
-    _lib.KERNEL_EVENTS = {}
-    for i in range(reps):
-        step(i)
-    torch.cuda.synchronize()
-    pairs = _lib.KERNEL_EVENTS["gdn2_token_forward"]
-    _lib.KERNEL_EVENTS = None
-    kern_us = statistics.median(x.elapsed_time(y) for x, y in pairs) * 1e3
-    gbs = DECODE_BYTES_PER_HEAD * B * H / (kern_us * 1e-6) / 1e9
-    results["in_place_B64_H32"] = {
-        "us_per_step_api": api_us, "us_per_step_kernel": kern_us, "hbm_gbs": gbs,
-        "frac_of_measured_peak": gbs / peak, "frac_of_8TBs": gbs / 8000.0}
+        for i in range(8):
+            step(i)
+        torch.cuda.synchronize()
+        b, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b.record()
+        for i in range(reps):
+            step(i)
+        e.record()
+        torch.cuda.synchronize()
+        api_us = b.elapsed_time(e) * 1e3 / reps
+        _lib.KERNEL_EVENTS = {}
+        for i in range(reps):
+            step(i)
+        torch.cuda.synchronize()
+        pairs = _lib.KERNEL_EVENTS["gdn2_token_forward"]
+        _lib.KERNEL_EVENTS = None
+        kern_us = statistics.median(x.elapsed_time(y) for x, y in pairs) * 1e3
+        gbs = DECODE_BYTES_PER_HEAD * B * H / (kern_us * 1e-6) / 1e9
+        results[f"in_place_B{B}_H32"] = {
+            "us_per_step_api": api_us, "us_per_step_kernel": kern_us, "hbm_gbs": gbs,
+            "frac_of_measured_peak": gbs / peak, "frac_of_8TBs": gbs / 8000.0}
+        del states, inp, out
 
     B = 256
     inp = device_inputs(B, 1, H, device, seed=8)
