@@ -191,3 +191,36 @@ def test_per_kernel_profile_events():
     assert set(times) == {"chunk_prep_kernel", "chunk_scan_kernel", "chunk_bwd_scan_kernel", "chunk_bwd_vjp_kernel"}
     assert all(0.0 < value < 100.0 for value in times.values())
     assert _lib.profile_chunk_kernels() == {}
+
+
+def test_two_host_threads_on_their_own_streams():
+    """Launches are lock-free and the library keeps no per-call state: two Python threads, each on its
+    own stream with its own problem, get the results a single thread gets."""
+
+    import threading
+
+    problems = [oracle.make_inputs(1, 192 + 64 * i, 2, seed=300 + i) for i in range(2)]
+    expected = [chunk_gdn2(*dev(*cpu), output_final_state=True) for cpu in problems]
+    torch.cuda.synchronize()
+    results = [None, None]
+    errors = []
+
+    def worker(index):
+        try:
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                tensors = dev(*problems[index])
+                for _ in range(5):
+                    results[index] = chunk_gdn2(*tensors, output_final_state=True)
+            stream.synchronize()
+        except Exception as exc:  # noqa: BLE001 - reported by the main thread
+            errors.append(exc)
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for (out, state), (ref_out, ref_state) in zip(results, expected):
+        assert torch.equal(out, ref_out) and torch.equal(state, ref_state)
