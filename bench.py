@@ -41,15 +41,17 @@ UNIT = "tokens/s"
 # algorithmic bytes per token-head (bf16 sequence tensors, fp32 g), K = V = 128
 FWD_BYTES = 5 * 256 + 512 + 256                 # read q k v beta w + g, write o
 BWD_BYTES = (5 * 256 + 512 + 256) + (5 * 256 + 512)  # read inputs + dO, write 6 grads
-# dram__bytes_read.sum + dram__bytes_write.sum per 64-token chunk-head and kernel, from the ncu capture
-# summarised in profiles/chunk_kernels_B1_T4096_H8_ncu_full.md (512 chunk-heads, scaled by the number of
-# chunk-heads: the kernels' traffic is proportional to it)
-NCU_TRAFFIC_PER_CHUNK_HEAD = {
-    "chunk_prep_kernel": 282.8e3,
-    "chunk_scan_kernel": 187.8e3,
-    "chunk_bwd_scan_kernel": 185.8e3,
-    "chunk_bwd_vjp_kernel": 400.7e3,
-}
+# DRAM traffic per 64-token chunk-head and kernel as a profiler measured it on a small case (a kernel's
+# traffic is proportional to the number of chunk-heads it processes); absent file -> traffic is null
+TRAFFIC_FILE = ROOT / "profiles" / "chunk_kernels_traffic.json"
+
+
+def traffic_per_chunk_head():
+    try:
+        data = json.loads(TRAFFIC_FILE.read_text())
+        return {name: float(entry["dram_bytes_per_chunk_head"]) for name, entry in data["kernels"].items()}
+    except (OSError, KeyError, ValueError, TypeError):
+        return {}
 DECODE_BYTES_PER_HEAD = 2 * 65536 + 1792 + 256
 T1_ZERO_BYTES_PER_HEAD = 65536 + 1280
 
@@ -65,7 +67,11 @@ def parse_args():
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     ap.add_argument("--skip-decode", action="store_true")
+    ap.add_argument("--skip-extra-configs", action="store_true",
+                    help="leave out the T=8200 and T=16384 training steps")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--decode-only", action="store_true",
+                    help="run only the decode leg on one GPU and print its figures (small, for profiler captures)")
     ap.add_argument("--no-graph", action="store_true", help="time the eager loop only")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample clocks (debugging aid)")
     return ap.parse_args()
@@ -287,7 +293,7 @@ def measured_peak_bf16():
     try:
         return float(json.loads(path.read_text())["bf16_tflops_sustained"])
     except (OSError, KeyError, ValueError):
-        return 1400.0  # sustained figure of an earlier measurement on this pool
+        return 1400.0  # stand-in when no measured peak has been recorded for this machine
 
 
 def measured_peak_hbm():
@@ -355,10 +361,10 @@ def run_gpu_arm(args):
 
     # ---- device-resident timing -----------------------------------------------------------
     # The step (forward, loss, backward through the public API) is launched eagerly and, when the capture
-    # succeeds, also replayed from a CUDA graph of exactly the same launches.  On these shared hosts the
-    # time to enqueue a step from Python varies between 1 ms and 9 ms from run to run; above the 6 ms a
-    # step takes on the GPU the eager loop measures the host, not the kernels.  `value` is the graph
-    # replay when there is one; the eager figure is reported next to it.
+    # succeeds, also replayed from a CUDA graph of exactly the same launches.  The time to enqueue a step
+    # from Python depends on how busy the host is and has been seen anywhere between 1 ms and 9 ms; above
+    # the time a step takes on the GPU the eager loop measures the host, not the kernels.  `value` is the
+    # graph replay when there is one; the eager figure is reported next to it.
     sampler = ClockSampler(local_rank)
     if rank == 0 and not args.no_clocks:
         sampler.start()
@@ -456,16 +462,42 @@ def run_gpu_arm(args):
     dominant = max(kernel_ms, key=kernel_ms.get) if kernel_ms else None
     roofline = None
     if dominant is not None:
-        achieved = kernel_bytes.get(dominant, 0) / (kernel_ms[dominant] * 1e-3) / 1e9
-        per_ch = NCU_TRAFFIC_PER_CHUNK_HEAD.get(dominant)
-        traffic = per_ch * (token_heads // 64) if per_ch is not None else None
+        per_ch = traffic_per_chunk_head()
+        chunk_heads = token_heads // 64
+
+        def kernel_entry(name):
+            seconds = kernel_ms[name] * 1e-3
+            traffic = per_ch[name] * chunk_heads if name in per_ch else None
+            return {"ms": kernel_ms[name], "algorithmic_bytes": kernel_bytes.get(name, 0),
+                    "achieved": kernel_bytes.get(name, 0) / seconds / 1e9,
+                    "frac": kernel_bytes.get(name, 0) / seconds / 1e9 / peak,
+                    "traffic": traffic,
+                    "traffic_gbs": traffic / seconds / 1e9 if traffic else None}
+
+        per_kernel = {name: kernel_entry(name) for name in kernel_ms}
+        top = per_kernel[dominant]
+        # forward and backward as passes: the pass's compulsory bytes over the sum of its kernels' times
+        fwd_names = [n for n in ("chunk_prep_kernel", "chunk_scan_kernel", "gdn2_token_forward") if n in kernel_ms]
+        bwd_names = [n for n in ("chunk_bwd_scan_kernel", "chunk_bwd_vjp_kernel", "gdn2_token_dstate_scan",
+                                 "gdn2_token_chunk_vjp") if n in kernel_ms]
+        fwd_ms = sum(kernel_ms[n] for n in fwd_names)
+        bwd_ms = sum(kernel_ms[n] for n in bwd_names)
+        passes = {}
+        if fwd_ms > 0:
+            gbs = FWD_BYTES * token_heads / (fwd_ms * 1e-3) / 1e9
+            passes["forward"] = {"ms": fwd_ms, "kernels": fwd_names, "achieved": gbs, "frac": gbs / peak}
+        if bwd_ms > 0:
+            gbs = BWD_BYTES * token_heads / (bwd_ms * 1e-3) / 1e9
+            passes["backward"] = {"ms": bwd_ms, "kernels": bwd_names, "achieved": gbs, "frac": gbs / peak}
         roofline = {
-            "bound": "hbm", "kernel": dominant, "achieved": achieved, "peak": peak,
-            "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic,
-            "traffic_gbs": (traffic / (kernel_ms[dominant] * 1e-3) / 1e9) if traffic else None,
-            "algorithmic_bytes": kernel_bytes.get(dominant, 0),
-            "kernel_ms": kernel_ms, "call_ms": call_ms,
+            "bound": "hbm", "kernel": dominant, "achieved": top["achieved"], "peak": peak,
+            "peak_kind": peak_kind, "unit": "GB/s", "frac": top["frac"], "traffic": top["traffic"],
+            "traffic_gbs": top["traffic_gbs"],
+            "algorithmic_bytes": top["algorithmic_bytes"],
+            "kernel_ms": kernel_ms, "call_ms": call_ms, "per_kernel": per_kernel, "passes": passes,
+            "lowest_frac_pass": min(passes, key=lambda n: passes[n]["frac"]) if passes else None,
             "step_algorithmic_gbs": (FWD_BYTES + BWD_BYTES) * token_heads / (ms_local * 1e-3) / 1e9,
+            "step_frac": (FWD_BYTES + BWD_BYTES) * token_heads / (ms_local * 1e-3) / 1e9 / peak,
             # the same step against the tensor-core roofline (18 K V flops per token-head, chunk-size
             # independent state contractions only): far below it by construction, the path is HBM-bound
             "step_algorithmic_tflops": 18 * 128 * 128 * token_heads / (ms_local * 1e-3) / 1e12,
@@ -522,11 +554,31 @@ def run_gpu_arm(args):
                "overlap": "host->device copy of step i+1 on a second stream under the kernels of step i"}
         del host, staging
 
-    # ---- decode figures (rank-local, reported by rank 0) -------------------------------------
+    # the main configuration's tensors make room for the other configurations
+    del inputs, leaves, s0
+    torch.cuda.empty_cache()
+
+    # ---- decode figures: every rank runs them, the slowest rank's time counts -----------------
     decode = prefill = None
-    if not args.skip_decode and rank == 0:
-        decode = run_decode(pkg, device, peak)
-        prefill = run_prefill(pkg, device, peak)
+    if not args.skip_decode:
+        decode = run_decode(pkg, device, peak, shard)
+        if rank == 0:
+            prefill = run_prefill(pkg, device, peak)
+
+    # ---- the other training configurations: ragged tail, and one GPU's share of the 8-GPU one ----
+    extra = None
+    if not args.skip_extra_configs:
+        extra = {
+            "train_T8200": time_training_config(pkg, shard, device, B, 8200, H, seed=8200 + rank,
+                                                steps=min(args.steps, 5)),
+            "config4_per_gpu_share": time_training_config(pkg, shard, device, 4, 16384, 32, seed=16384 + rank,
+                                                          steps=min(args.steps, 5)),
+        }
+        extra["train_T8200"]["what"] = (f"fwd+bwd B={B} T=8200 H={H} per GPU: 128 full chunks on the chunk "
+                                        "kernels, the 8-token tail on the token kernels")
+        extra["config4_per_gpu_share"]["what"] = (
+            "fwd+bwd B=4 T=16384 H=32 per GPU = the 8-GPU configuration (global B=32) at N=8; with fewer "
+            "GPUs this is weak scaling of the same per-GPU share, device-timed, slowest rank")
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
@@ -535,6 +587,7 @@ def run_gpu_arm(args):
     # ---- multi-GPU: the only collective of the path is the final gather of outputs / states ------
     gather = None
     if world > 1:
+        inputs = device_inputs(B, T, H, device, seed=1000 * 0 + rank)
         out_local, fin_local = pkg.chunk_gdn2(*[t.detach() for t in inputs[:6]], inputs[6].detach(),
                                               output_final_state=True)
         plan = shard.Shard(0, rank * B, (rank + 1) * B)
@@ -565,21 +618,78 @@ def run_gpu_arm(args):
                        "l2": "inputs (1.8 GB/step) exceed the 126 MB L2"},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
             "cpu_baseline": cpu_baseline, "decode": decode, "prefill": prefill, "gather": gather,
+            "train_T8200": extra["train_T8200"] if extra else None,
+            "config4": ({"train": extra["config4_per_gpu_share"],
+                         "decode_B128_H32_per_gpu": decode.get("in_place_B128_H32") if decode else None,
+                         "scaling": "weak in the number of GPUs (fixed per-GPU share of global B=32 / B=1024)"}
+                        if extra else None),
         }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_decode(pkg, device, peak):
-    """Decode configuration (B=64, H=32, T=1, in-place state) and zero-state closed form
-    (B=256, H=32).  States rotate through buffers larger than L2."""
+def time_training_config(pkg, shard, device, batch, time_, heads, *, seed, steps, warmup=3):
+    """Device time of one fwd+bwd step of another configuration: eager loop and, when the capture
+    works, CUDA-graph replay of the same step; max over ranks."""
+
+    import torch.distributed as dist
+
+    world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+    inputs = device_inputs(batch, time_, heads, device, seed=seed)
+    leaves = [t.requires_grad_(True) for t in inputs[:6]]
+    s0 = inputs[6].requires_grad_(True)
+    for _ in range(warmup):
+        train_step(pkg, leaves, s0)
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(steps):
+        loss, grads = train_step(pkg, leaves, s0)
+    end.record()
+    torch.cuda.synchronize()
+    eager_ms = begin.elapsed_time(end) / steps
+    del loss, grads
+    graph_ms = None
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            g_loss, g_grads = train_step(pkg, leaves, s0)
+        for _ in range(2):
+            graph.replay()
+        torch.cuda.synchronize()
+        begin.record()
+        for _ in range(steps):
+            graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        graph_ms = begin.elapsed_time(end) / steps
+        del graph, g_loss, g_grads
+    except Exception as exc:  # noqa: BLE001 - the eager figure stands in
+        print(f"bench: CUDA-graph timing unavailable for T={time_} ({type(exc).__name__}: {exc})", file=sys.stderr)
+    graph_ok = shard.max_over_ranks(0.0 if graph_ms is not None else 1.0, device) == 0.0
+    ms = shard.max_over_ranks(graph_ms if graph_ok else eager_ms, device)
+    token_heads = batch * time_ * heads
+    peak, _ = measured_peak_hbm()
+    gbs = (FWD_BYTES + BWD_BYTES) * token_heads / (ms * 1e-3) / 1e9
+    result = {"ms_per_step": ms, "eager_ms_per_step": shard.max_over_ranks(eager_ms, device),
+              "launch": "cuda graph replay" if graph_ok else "eager",
+              "tokens_per_s": world * batch * time_ / (ms * 1e-3), "per_gpu_batch": batch, "seq_len": time_,
+              "heads": heads, "algorithmic_gbs_per_gpu": gbs, "frac_of_measured_peak": gbs / peak}
+    del inputs, leaves, s0
+    torch.cuda.empty_cache()
+    return result
+
+
+def run_decode(pkg, device, peak, shard):
+    """Decode configuration (B=64, H=32, T=1, in-place state), one GPU's share of the 8-GPU decode
+    configuration (B=128 of 1024) and the zero-state closed form (B=256, H=32).  States rotate through
+    buffers larger than L2.  Every rank runs the same thing; times are the slowest rank's."""
 
     from gdn2_sm120_b200 import _lib
 
     results = {}
     H = 32
-    # B = 64: the decode configuration; B = 128: one GPU's shard of the 8-GPU decode configuration (B = 1024)
     for B in (64, 128):
         inp = device_inputs(B, 1, H, device, seed=7)
         states = [inp[6].clone() for _ in range(4)]  # 4 x 128 MiB (or more) > L2
@@ -598,18 +708,19 @@ def run_decode(pkg, device, peak):
             step(i)
         e.record()
         torch.cuda.synchronize()
-        api_us = b.elapsed_time(e) * 1e3 / reps
+        api_us = shard.max_over_ranks(b.elapsed_time(e) * 1e3 / reps, device)
         _lib.KERNEL_EVENTS = {}
         for i in range(reps):
             step(i)
         torch.cuda.synchronize()
         pairs = _lib.KERNEL_EVENTS["gdn2_token_forward"]
         _lib.KERNEL_EVENTS = None
-        kern_us = statistics.median(x.elapsed_time(y) for x, y in pairs) * 1e3
+        kern_us = shard.max_over_ranks(statistics.median(x.elapsed_time(y) for x, y in pairs) * 1e3, device)
         gbs = DECODE_BYTES_PER_HEAD * B * H / (kern_us * 1e-6) / 1e9
         results[f"in_place_B{B}_H32"] = {
             "us_per_step_api": api_us, "us_per_step_kernel": kern_us, "hbm_gbs": gbs,
-            "frac_of_measured_peak": gbs / peak, "frac_of_8TBs": gbs / 8000.0}
+            "frac_of_measured_peak": gbs / peak, "frac_of_8TBs": gbs / 8000.0,
+            "timing": "per GPU, slowest rank"}
         del states, inp, out
 
     B = 256
@@ -625,7 +736,7 @@ def run_decode(pkg, device, peak):
     torch.cuda.synchronize()
     pairs = _lib.KERNEL_EVENTS["gdn2_token_forward_t1_zero"]
     _lib.KERNEL_EVENTS = None
-    kern_us = statistics.median(x.elapsed_time(y) for x, y in pairs) * 1e3
+    kern_us = shard.max_over_ranks(statistics.median(x.elapsed_time(y) for x, y in pairs) * 1e3, device)
     gbs = T1_ZERO_BYTES_PER_HEAD * B * H / (kern_us * 1e-6) / 1e9
     results["zero_state_B256_H32"] = {"us_per_step_kernel": kern_us, "hbm_gbs": gbs,
                                       "frac_of_measured_peak": gbs / peak, "frac_of_8TBs": gbs / 8000.0}
@@ -656,10 +767,24 @@ def run_prefill(pkg, device, peak):
                                  "frac_of_measured_peak": gbs / peak}}
 
 
+def run_decode_only():
+    import gdn2_sm120_b200 as pkg
+    from gdn2_sm120_b200 import _lib, shard
+
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    _lib.lib()
+    peak, peak_kind = measured_peak_hbm()
+    print(json.dumps({"decode": run_decode(pkg, device, peak, shard), "peak": peak, "peak_kind": peak_kind}),
+          flush=True)
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.decode_only:
+        run_decode_only()
     else:
         run_gpu_arm(args)
 

@@ -40,15 +40,19 @@ _PROTOTYPES: dict[str, list] = {
     "gdn2_token_dstate_scan": [_P] * 8 + [_I64] * 5 + [_INT, _INT, _F32, _P],
     "gdn2_token_chunk_vjp": [_P] * 15 + [_I64] * 5 + [_INT, _INT, _F32, _P],
     "gdn2_chunk_workspace_bytes": [_I64] * 3 + [_INT],
-    "gdn2_chunk_forward": [_P] * 11 + [_I64] * 4 + [_INT, _INT, _INT, _F32, _P],
-    "gdn2_chunk_backward": [_P] * 18 + [_I64] * 4 + [_INT, _INT, _F32, _P],
+    "gdn2_chunk_scratch_bytes": [_I64] * 3 + [_INT],
+    "gdn2_chunk_forward": [_P] * 12 + [_I64] * 4 + [_INT, _INT, _INT, _F32, _P],
+    "gdn2_chunk_backward": [_P] * 19 + [_I64] * 4 + [_INT, _INT, _F32, _P],
+    "gdn2_chunk_backward_f32grads": [_P] * 19 + [_I64] * 4 + [_F32, _P],
     "gdn2_chunk_read_status": [_P] + [_I64] * 3 + [_P],
+    "gdn2_debug_wait_expires": [_P] + [_I64] * 4 + [_P],
     "gdn2_chunk_forward_static": [_P] * 9 + [_I64] * 4 + [_INT, _INT, _F32, _P],
+    "gdn2_chunk_static_read_status": [_P],
     "gdn2_profile_enable": [_INT],
     "gdn2_profile_chunk_kernels": [_P] * 4,
 }
 _RESTYPES = {"gdn2_status_string": ctypes.c_char_p, "gdn2_last_cuda_error": ctypes.c_char_p,
-             "gdn2_chunk_workspace_bytes": ctypes.c_int64}
+             "gdn2_chunk_workspace_bytes": ctypes.c_int64, "gdn2_chunk_scratch_bytes": ctypes.c_int64}
 
 
 def library_path() -> pathlib.Path:
@@ -106,7 +110,8 @@ KERNEL_EVENTS: dict[str, list] | None = None
 
 
 # kernels launched by one successful call of each entry point (default 1)
-_KERNELS_PER_CALL = {"gdn2_chunk_forward": 2, "gdn2_chunk_backward": 2, "gdn2_chunk_forward_static": 2}
+_KERNELS_PER_CALL = {"gdn2_chunk_forward": 2, "gdn2_chunk_backward": 2, "gdn2_chunk_backward_f32grads": 2,
+                     "gdn2_chunk_forward_static": 2}
 
 
 def check(status: int, what: str) -> None:

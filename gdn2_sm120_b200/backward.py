@@ -6,9 +6,13 @@
 reference reconstructs earlier states from ``final_state`` by inverting the
 recurrence (Sherman-Morrison, docs/design.md:125-145 of the reference), whose error
 grows like exp(sum |g|).  Here the forward is re-run from ``initial_state`` (``None`` =
-zero) with fp32 checkpoints every 16 tokens and nothing is inverted, so callers whose
-forward started from a non-zero state must pass it.  ``final_state`` is validated but
-not read.
+zero) with fp32 checkpoints -- on the tensor-core chunk kernels from 64 tokens on, on the
+token kernels below -- and nothing is inverted, so callers whose forward started from a
+non-zero state must pass it, at every length (the reference needs it only above 128 tokens,
+backward.py:1286-1298).  ``final_state`` is used as a consistency check: the state the re-run
+arrives at is compared with it on the device, and a mismatch raises ``ValueError`` instead of
+returning gradients of a different forward.  The check cannot see a wrong starting state whose
+influence has decayed away by the end of the sequence.
 
 ``backward_from_aux`` is what the autograd wrapper calls: it consumes the checkpoints
 that ``chunk_forward(return_aux=True)`` saved.  The ragged tail is differentiated first
@@ -21,13 +25,17 @@ from __future__ import annotations
 import torch
 
 from . import _lib, _validate
-from .chunk import ChunkForwardAux, _token_slots
-from .recurrent import _launch_token_forward
+from .chunk import ChunkForwardAux, _token_slots, chunk_forward
+from .recurrent import _chunk_forward_compatible, _launch_token_forward, _use_recurrent_kernel
 
 _DIM = _validate.DIM
 # Kept for callers that imported the reference's constant (backward.py:57): there it is
 # the longest sequence the final-state-only inverse path accepts; here no cap exists.
 MAX_BACKWARD_TOKENS = 128
+# Largest relative L2 distance between the caller's final_state and the recomputed one that still
+# counts as "the same forward": the chunk kernels' tf32 contractions differ from an exact fp32
+# recurrence by up to ~5e-4, a wrong starting state by O(1).
+_FINAL_STATE_REL_TOL = 5e-3
 
 
 def _token_backward(q, k, v, g, beta, w, d_out, d_final_state, boundaries, grads,
@@ -106,18 +114,35 @@ def chunk_backward(
     args = tuple(_validate.detached(x) for x in (q, k, v, g, beta, w))
     do_arg, dfs_arg = _validate.detached(do), _validate.detached(d_final_state)
     s0 = _validate.detached(initial_state)
+    given_final = _validate.detached(final_state)
     if time == 0:
         grads = tuple(torch.empty_like(x) for x in args)
         return (*grads, dfs_arg.clone())
 
-    # recompute the forward with checkpoints (token path: exact fp32), then differentiate
-    boundaries = torch.empty((batch, _token_slots(time), heads, _DIM, _DIM), device=q.device,
-                             dtype=torch.float32)
-    scratch_out = torch.empty_like(v)
-    _launch_token_forward(*args, s0, scratch_out, None, boundaries, batch, time, heads, 0, time,
-                          output_scale)
-    aux = ChunkForwardAux(None, boundaries, 0)
-    return backward_from_aux(*args, aux, do_arg, dfs_arg, output_scale)
+    # recompute the forward with checkpoints, then differentiate
+    buffers = (*args, do_arg, dfs_arg) + (() if s0 is None else (s0,))
+    if not _use_recurrent_kernel(batch, time, heads) and _chunk_forward_compatible(buffers):
+        _, reached, aux = chunk_forward(*args, s0, scale=output_scale, return_aux=True)
+    else:
+        boundaries = torch.empty((batch, _token_slots(time), heads, _DIM, _DIM), device=q.device,
+                                 dtype=torch.float32)
+        reached = torch.empty((batch, heads, _DIM, _DIM), device=q.device, dtype=torch.float32)
+        scratch_out = torch.empty_like(v)
+        _launch_token_forward(*args, s0, scratch_out, reached, boundaries, batch, time, heads, 0, time,
+                              output_scale)
+        aux = ChunkForwardAux(None, boundaries, 0)
+    # one small reduction on the device, read back after the backward kernels have been queued
+    mismatch = torch.stack([(reached - given_final).square().sum(), given_final.square().sum()])
+    result = backward_from_aux(*args, aux, do_arg, dfs_arg, output_scale)
+    diff2, ref2 = mismatch.tolist()
+    if not diff2 <= _FINAL_STATE_REL_TOL ** 2 * max(ref2, 1e-30):
+        raise ValueError(
+            "final_state does not match the state the forward reaches from initial_state "
+            f"(relative L2 difference {(diff2 / max(ref2, 1e-30)) ** 0.5:.3e}): chunk_backward re-runs the "
+            "forward from initial_state (None = zero) and never inverts the recurrence, so a forward that "
+            "started from a non-zero state needs initial_state passed here"
+        )
+    return result
 
 
 __all__ = ["MAX_BACKWARD_TOKENS", "chunk_backward"]

@@ -8,12 +8,11 @@ never partially) and the ``return_aux`` contract used by the autograd wrapper.
 A sequence is split into ``full_tokens = 64 * (T // 64)`` tokens that the tensor-core
 chunk kernels process and a ragged tail of ``T - full_tokens < 64`` tokens that the
 exact fp32 token kernels process on the same buffers (the reference does the same with
-its scalar tail scan, chunk.py:1021-1053).  When the chunk kernels are not enabled for
-a call, ``full_tokens`` is 0 and the token kernels cover the whole sequence.
+its scalar tail scan, chunk.py:1021-1053).
 
 Activation checkpoints for backward are the fp32 states at chunk / span starts plus,
-for the chunk kernels, the workspace of per-chunk WY factors that the forward prep kernel
-wrote (the reference saves the same factors, chunk.py:1056-1075).
+for the chunk kernels, the workspaces of per-chunk WY factors that the forward prep kernel
+wrote, one per wave of batch rows (the reference saves the same factors, chunk.py:1056-1075).
 """
 
 from __future__ import annotations
@@ -41,25 +40,24 @@ class ChunkForwardAux:
                           ``None`` when there is no tail.
     ``full_tokens``       number of leading tokens covered by ``chunk_boundaries``.
     ``workspace``         the chunk kernels' per-chunk WY factors (operand-ready tiles written
-                          by the forward prep kernel and reused by backward), or ``None``.
+                          by the forward prep kernel and reused by backward), a tuple with one
+                          tensor per wave of batch rows, or ``None``.
     """
 
     chunk_boundaries: torch.Tensor | None
     tail_boundaries: torch.Tensor | None
     full_tokens: int
-    workspace: torch.Tensor | None = None
+    workspace: tuple[torch.Tensor, ...] | None = None
 
 
 def _token_slots(tokens: int) -> int:
     return -(-tokens // _TOKEN_INTERVAL) + 1
 
 
-def _chunk_kernel_tokens(time: int, training: bool) -> int:
-    """Leading tokens handed to the tensor-core chunk kernels for a call."""
+def _chunk_kernel_tokens(time: int) -> int:
+    """Leading tokens handed to the tensor-core chunk kernels: every full 64-token chunk."""
 
-    from . import chunk_kernels
-
-    return chunk_kernels.supported_tokens(time, training=training)
+    return (time // _CHUNK) * _CHUNK
 
 
 def chunk_forward(
@@ -119,11 +117,17 @@ def chunk_forward(
                     "final_state_out may exactly alias initial_state but must not partially overlap it"
                 )
 
-    full_tokens = _chunk_kernel_tokens(time, return_aux)
+    full_tokens = _chunk_kernel_tokens(time)
     tail = time - full_tokens
     chunk_boundaries = tail_boundaries = None
     if return_aux:
         if full_tokens:
+            from . import chunk_kernels
+
+            chunk_kernels.check_memory(
+                batch * (full_tokens // _CHUNK + 1) * heads * _DIM * _DIM * 4
+                + chunk_kernels.workspace_bytes(batch, full_tokens, heads, True),
+                q.device, "chunk forward with checkpoints")
             chunk_boundaries = torch.empty(
                 (batch, full_tokens // _CHUNK + 1, heads, _DIM, _DIM), device=q.device, dtype=torch.float32
             )

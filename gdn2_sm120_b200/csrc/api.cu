@@ -24,15 +24,17 @@ int launch_token_chunk_vjp(const void*, const void*, const void*, const void*, c
                            int64_t, int, int, float, cudaStream_t);
 
 int64_t chunk_workspace_bytes(int64_t, int64_t, int64_t, int);
+int64_t chunk_scratch_bytes(int64_t, int64_t, int64_t, int);
 int64_t chunk_status_offset(int64_t, int64_t, int64_t);
 int launch_chunk_forward(const void*, const void*, const void*, const void*, const void*, const void*,
-                         const float*, void*, float*, float*, uint8_t*, int64_t, int64_t, int64_t,
+                         const float*, void*, float*, float*, uint8_t*, uint8_t*, int64_t, int64_t, int64_t,
                          int64_t, int, int, int, float, cudaStream_t);
 
 int launch_chunk_backward(const void*, const void*, const void*, const void*, const void*, const void*,
-                          const void*, const float*, const float*, float*, uint8_t*, void*, void*, void*,
-                          void*, void*, void*, float*, int64_t, int64_t, int64_t, int64_t, int, int, float,
-                          cudaStream_t);
+                          const void*, const float*, const float*, float*, const uint8_t*, uint8_t*, void*,
+                          void*, void*, void*, void*, void*, float*, int64_t, int64_t, int64_t, int64_t, int,
+                          int, float, int, cudaStream_t);
+int launch_debug_wait_expires(int* status, uint32_t max_polls, cudaStream_t stream);
 
 namespace {
 thread_local char g_cuda_error[256] = {0};
@@ -45,18 +47,35 @@ void record_cuda_error(cudaError_t err) {
 
 // ---- optional per-kernel timing of the chunk entry points -----------------------------------------
 // Events 0..2 bracket the two kernels of gdn2_chunk_forward, 3..5 those of gdn2_chunk_backward.
+// One event set per device (events belong to the device that was current when they were created),
+// all state behind one mutex; meant for one measuring thread per device.
 namespace {
+constexpr int kProfileDevices = 64;
+struct ProfileSet {
+  cudaEvent_t events[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  bool recorded[2] = {false, false};
+};
 bool g_profile_on = false;
-cudaEvent_t g_profile_events[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
-bool g_profile_recorded[2] = {false, false};
+ProfileSet g_profile[kProfileDevices];
+std::mutex g_profile_mutex;
 }  // namespace
 
 void profile_mark(int index, cudaStream_t stream) {
   if (!g_profile_on) return;
-  if (g_profile_events[index] == nullptr && cudaEventCreate(&g_profile_events[index]) != cudaSuccess) return;
-  cudaEventRecord(g_profile_events[index], stream);
-  if (index == 2) g_profile_recorded[0] = true;
-  if (index == 5) g_profile_recorded[1] = true;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kProfileDevices) return;
+  std::lock_guard<std::mutex> lock(g_profile_mutex);
+  ProfileSet& set = g_profile[device];
+  if (set.events[index] == nullptr && cudaEventCreate(&set.events[index]) != cudaSuccess) return;
+  if (cudaEventRecord(set.events[index], stream) != cudaSuccess) {
+    (void)cudaGetLastError();
+    set.recorded[index / 3] = false;
+    return;
+  }
+  if (index == 0) set.recorded[0] = false;
+  if (index == 3) set.recorded[1] = false;
+  if (index == 2) set.recorded[0] = true;
+  if (index == 5) set.recorded[1] = true;
 }
 
 // Opt a kernel in to more than 48 KiB of dynamic shared memory, once per (kernel, device): launches
@@ -228,51 +247,85 @@ int gdn2_token_chunk_vjp(const void* q, const void* k, const void* v, const void
 
 int64_t gdn2_chunk_workspace_bytes(int64_t batch, int64_t full_tokens, int64_t heads, int training) {
   if (batch <= 0 || heads <= 0 || full_tokens <= 0 || full_tokens % GDN2_CHUNK != 0) return GDN2_ERR_BAD_SHAPE;
+  if (check_shape(batch, full_tokens, heads) != GDN2_OK) return GDN2_ERR_TOO_LARGE;
   return chunk_workspace_bytes(batch, full_tokens, heads, training);
+}
+
+int64_t gdn2_chunk_scratch_bytes(int64_t batch, int64_t full_tokens, int64_t heads, int backward) {
+  if (batch <= 0 || heads <= 0 || full_tokens <= 0 || full_tokens % GDN2_CHUNK != 0) return GDN2_ERR_BAD_SHAPE;
+  if (check_shape(batch, full_tokens, heads) != GDN2_OK) return GDN2_ERR_TOO_LARGE;
+  return chunk_scratch_bytes(batch, full_tokens, heads, backward);
 }
 
 int gdn2_chunk_forward(const void* q, const void* k, const void* v, const void* g,
                        const void* beta, const void* w, const float* initial_state, void* out,
-                       float* final_state, float* chunk_boundaries, void* workspace,
+                       float* final_state, float* chunk_boundaries, void* workspace, void* scratch,
                        int64_t batch, int64_t time, int64_t heads, int64_t full_tokens, int training,
                        int dtype, int g_dtype, float scale, void* stream) {
-  if (!q || !k || !v || !g || !beta || !w || !out || !workspace) return GDN2_ERR_NULL_POINTER;
+  if (!q || !k || !v || !g || !beta || !w || !out || !workspace || !scratch) return GDN2_ERR_NULL_POINTER;
   if (training && !chunk_boundaries) return GDN2_ERR_NULL_POINTER;
   int st = check_shape(batch, time, heads);
   if (st != GDN2_OK) return st;
   if (full_tokens <= 0 || full_tokens > time || full_tokens % GDN2_CHUNK != 0) return GDN2_ERR_BAD_RANGE;
   if ((st = check_types(dtype, g_dtype)) != GDN2_OK) return st;
-  const void* need16[] = {q, k, v, g, beta, w, initial_state, out, final_state, chunk_boundaries, workspace};
+  const void* need16[] = {q, k, v, g, beta, w, initial_state, out, final_state, chunk_boundaries, workspace,
+                          scratch};
   for (const void* ptr : need16) {
     if (!aligned(ptr, 16)) return GDN2_ERR_ALIGNMENT;
   }
   return launch_chunk_forward(q, k, v, g, beta, w, initial_state, out, final_state, chunk_boundaries,
-                              static_cast<uint8_t*>(workspace), batch, time, heads, full_tokens, training,
-                              dtype, g_dtype, scale, static_cast<cudaStream_t>(stream));
+                              static_cast<uint8_t*>(workspace), static_cast<uint8_t*>(scratch), batch, time,
+                              heads, full_tokens, training, dtype, g_dtype, scale,
+                              static_cast<cudaStream_t>(stream));
 }
 
-int gdn2_chunk_backward(const void* q, const void* k, const void* v, const void* g, const void* beta,
-                        const void* w, const void* d_out, const float* d_final_state,
-                        const float* chunk_boundaries, float* d_boundaries, void* workspace, void* dq,
-                        void* dk, void* dv, void* dg, void* dbeta, void* dw, float* d_initial_state,
-                        int64_t batch, int64_t time, int64_t heads, int64_t full_tokens, int dtype,
-                        int g_dtype, float scale, void* stream) {
+namespace {
+int chunk_backward_checked(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                           const void* w, const void* d_out, const float* d_final_state,
+                           const float* chunk_boundaries, float* d_boundaries, const void* workspace,
+                           void* scratch, void* dq, void* dk, void* dv, void* dg, void* dbeta, void* dw,
+                           float* d_initial_state, int64_t batch, int64_t time, int64_t heads,
+                           int64_t full_tokens, int dtype, int g_dtype, float scale, int grads_f32,
+                           void* stream) {
   if (!q || !k || !v || !g || !beta || !w || !d_out || !chunk_boundaries || !d_boundaries || !workspace ||
-      !dq || !dk || !dv || !dg || !dbeta || !dw)
+      !scratch || !dq || !dk || !dv || !dg || !dbeta || !dw)
     return GDN2_ERR_NULL_POINTER;
   int st = check_shape(batch, time, heads);
   if (st != GDN2_OK) return st;
   if (full_tokens <= 0 || full_tokens > time || full_tokens % GDN2_CHUNK != 0) return GDN2_ERR_BAD_RANGE;
   if ((st = check_types(dtype, g_dtype)) != GDN2_OK) return st;
   const void* need16[] = {q, k, v, g, beta, w, d_out, d_final_state, chunk_boundaries, d_boundaries, workspace,
-                          dq, dk, dv, dg, dbeta, dw, d_initial_state};
+                          scratch, dq, dk, dv, dg, dbeta, dw, d_initial_state};
   for (const void* ptr : need16) {
     if (!aligned(ptr, 16)) return GDN2_ERR_ALIGNMENT;
   }
   return launch_chunk_backward(q, k, v, g, beta, w, d_out, d_final_state, chunk_boundaries, d_boundaries,
-                               static_cast<uint8_t*>(workspace), dq, dk, dv, dg, dbeta, dw, d_initial_state,
-                               batch, time, heads, full_tokens, dtype, g_dtype, scale,
-                               static_cast<cudaStream_t>(stream));
+                               static_cast<const uint8_t*>(workspace), static_cast<uint8_t*>(scratch), dq, dk,
+                               dv, dg, dbeta, dw, d_initial_state, batch, time, heads, full_tokens, dtype,
+                               g_dtype, scale, grads_f32, static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+
+int gdn2_chunk_backward(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                        const void* w, const void* d_out, const float* d_final_state,
+                        const float* chunk_boundaries, float* d_boundaries, const void* workspace,
+                        void* scratch, void* dq, void* dk, void* dv, void* dg, void* dbeta, void* dw,
+                        float* d_initial_state, int64_t batch, int64_t time, int64_t heads,
+                        int64_t full_tokens, int dtype, int g_dtype, float scale, void* stream) {
+  return chunk_backward_checked(q, k, v, g, beta, w, d_out, d_final_state, chunk_boundaries, d_boundaries,
+                                workspace, scratch, dq, dk, dv, dg, dbeta, dw, d_initial_state, batch, time,
+                                heads, full_tokens, dtype, g_dtype, scale, 0, stream);
+}
+
+int gdn2_chunk_backward_f32grads(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                                 const void* w, const void* d_out, const float* d_final_state,
+                                 const float* chunk_boundaries, float* d_boundaries, const void* workspace,
+                                 void* scratch, float* dq, float* dk, float* dv, float* dg, float* dbeta,
+                                 float* dw, float* d_initial_state, int64_t batch, int64_t time,
+                                 int64_t heads, int64_t full_tokens, float scale, void* stream) {
+  return chunk_backward_checked(q, k, v, g, beta, w, d_out, d_final_state, chunk_boundaries, d_boundaries,
+                                workspace, scratch, dq, dk, dv, dg, dbeta, dw, d_initial_state, batch, time,
+                                heads, full_tokens, GDN2_BF16, GDN2_FP32, scale, 1, stream);
 }
 
 int gdn2_chunk_read_status(const void* workspace, int64_t batch, int64_t full_tokens, int64_t heads,
@@ -288,24 +341,50 @@ int gdn2_chunk_read_status(const void* workspace, int64_t batch, int64_t full_to
   return host;
 }
 
+int gdn2_debug_wait_expires(void* workspace, int64_t batch, int64_t full_tokens, int64_t heads,
+                            int64_t max_polls, void* stream) {
+  if (!workspace) return GDN2_ERR_NULL_POINTER;
+  if (batch <= 0 || heads <= 0 || full_tokens <= 0 || full_tokens % GDN2_CHUNK != 0) return GDN2_ERR_BAD_SHAPE;
+  if (check_shape(batch, full_tokens, heads) != GDN2_OK) return GDN2_ERR_TOO_LARGE;
+  if (!aligned(workspace, 16)) return GDN2_ERR_ALIGNMENT;
+  const int64_t polls = max_polls < 1 ? 1 : (max_polls > (int64_t(1) << 20) ? (int64_t(1) << 20) : max_polls);
+  int* status = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) +
+                                       chunk_status_offset(batch, full_tokens, heads));
+  return launch_debug_wait_expires(status, uint32_t(polls), static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"
 
 extern "C" int gdn2_profile_enable(int on) {
+  std::lock_guard<std::mutex> lock(gdn2::g_profile_mutex);
   gdn2::g_profile_on = on != 0;
-  gdn2::g_profile_recorded[0] = gdn2::g_profile_recorded[1] = false;
+  for (auto& set : gdn2::g_profile) set.recorded[0] = set.recorded[1] = false;
   return GDN2_OK;
 }
 
+// Durations of the most recent forward / backward pair recorded on the current device.
 extern "C" int gdn2_profile_chunk_kernels(float* prep_ms, float* scan_ms, float* bwd_scan_ms, float* vjp_ms) {
   if (prep_ms == nullptr || scan_ms == nullptr || bwd_scan_ms == nullptr || vjp_ms == nullptr) {
     return GDN2_ERR_NULL_POINTER;
   }
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) { gdn2::record_cuda_error(err); return GDN2_ERR_LAUNCH; }
+  if (device < 0 || device >= gdn2::kProfileDevices) return GDN2_ERR_DEVICE;
   float* out[4] = {prep_ms, scan_ms, bwd_scan_ms, vjp_ms};
+  cudaEvent_t events[6];
+  bool recorded[2];
+  {
+    std::lock_guard<std::mutex> lock(gdn2::g_profile_mutex);
+    for (int i = 0; i < 6; ++i) events[i] = gdn2::g_profile[device].events[i];
+    recorded[0] = gdn2::g_profile[device].recorded[0];
+    recorded[1] = gdn2::g_profile[device].recorded[1];
+  }
   for (int call = 0; call < 2; ++call) {
     out[2 * call][0] = out[2 * call + 1][0] = -1.f;
-    if (!gdn2::g_profile_recorded[call]) continue;
-    cudaEvent_t* ev = gdn2::g_profile_events + 3 * call;
-    cudaError_t err = cudaEventSynchronize(ev[2]);
+    if (!recorded[call]) continue;
+    cudaEvent_t* ev = events + 3 * call;
+    err = cudaEventSynchronize(ev[2]);
     if (err == cudaSuccess) err = cudaEventElapsedTime(out[2 * call], ev[0], ev[1]);
     if (err == cudaSuccess) err = cudaEventElapsedTime(out[2 * call + 1], ev[1], ev[2]);
     if (err != cudaSuccess) { gdn2::record_cuda_error(err); return GDN2_ERR_LAUNCH; }

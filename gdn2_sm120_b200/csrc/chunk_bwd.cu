@@ -20,6 +20,8 @@
 
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "chunk_common.cuh"
 
 namespace gdn2 {
@@ -51,7 +53,8 @@ struct BScanSmem {
 };
 
 struct BScanParams {
-  uint8_t* ws;
+  const uint8_t* ws;        // workspace of the training forward (Kn, Qt, Yt, At, Tt, D)
+  uint8_t* sc;              // scratch: receives dZ
   const void* d_out;        // [B,T,H,128]
   const float* ds_final;    // [B,H,128,128] or null
   float* d_bnd;             // [B, n_chunks+1, H,128,128]
@@ -65,7 +68,10 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
   extern __shared__ __align__(128) uint8_t smem_raw[];
   BScanSmem& sm = *reinterpret_cast<BScanSmem*>(smem_raw);
   const WsLayout ws{p.n_ch, true};
+  const ScratchLayout sc{p.n_ch};
   BoundedWaiter waiter(p.status);
+  // a wait that ran out earlier (forward or backward) left garbage behind: results become NaN
+  const bool upstream_failed = *static_cast<volatile const int*>(p.status) != kStatusOk;
 
   // 16 warps.  TMEM phases: warp & 3 = lane quadrant, warp >> 2 = quarter of the columns.
   // dO^T tile builder: warp = 4-token group tg, lane = 4-channel group.
@@ -212,7 +218,8 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
 #pragma unroll
       for (int jj = 0; jj < 16; ++jj) {
         const int j = j0 + jj;
-        *reinterpret_cast<float*>(col + (j >> 3) * kRsZ + (j & 7) * 16) = to_tf32(__uint_as_float(r[jj]));
+        *reinterpret_cast<float*>(col + (j >> 3) * kRsZ + (j & 7) * 16) =
+            (upstream_failed || waiter.dead) ? poison_nan() : to_tf32(__uint_as_float(r[jj]));
       }
     }
     // ---- decay: dS^T <- dS^T diag(d) -------------------------------------------------------------------
@@ -231,7 +238,7 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
-      bulk_s2g(p.ws + ws.off_dz() + ch_of(c) * kBlobDZ, sm.dz, uint32_t(kBlobDZ));
+      bulk_s2g(p.sc + sc.off_dz() + ch_of(c) * kBlobDZ, sm.dz, uint32_t(kBlobDZ));
       bulk_commit();
       const uint32_t d0 = smem_u32(sm.dot), q0 = smem_u32(sm.qt), y0 = smem_u32(sm.yt);
       const uint32_t id_pos = idesc(128, 128, kFmtTF32, kMajorK, kMajorK);
@@ -261,10 +268,12 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
     uint32_t r[32];
     tmem_ld32(tmem_addr(tb, lane_base, kColS + k0), r);
     tmem_wait_ld();
+    const bool failed = upstream_failed || waiter.dead;
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
-      slot[(k0 + j) * kDim] = __uint_as_float(r[j]);
-      if (init != nullptr) init[(k0 + j) * kDim] = __uint_as_float(r[j]);
+      const float x = failed ? poison_nan() : __uint_as_float(r[j]);
+      slot[(k0 + j) * kDim] = x;
+      if (init != nullptr) init[(k0 + j) * kDim] = x;
     }
   }
   if (tid == 0) bulk_wait_all();  // the last dZ tile is in global memory before the CTA retires
@@ -321,7 +330,8 @@ __device__ __forceinline__ uint32_t d6_col(int I) { return (I == 3) ? 0u : (I ==
 
 struct VjpParams {
   const void *q, *k, *v, *g, *beta, *w, *d_out;
-  const uint8_t* ws;
+  const uint8_t* ws;    // workspace of the training forward (Rn)
+  const uint8_t* sc;    // scratch: dZ written by the reverse scan
   const float* bnd;     // [B, n_chunks+1, H,128,128] forward states
   const float* d_bnd;   // same shape, cotangents
   void *dq, *dk, *dv, *dg, *dbeta, *dw;
@@ -358,6 +368,10 @@ __device__ __forceinline__ void store4v<__nv_bfloat16>(void* base, int64_t idx, 
   *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(base) + idx) = make_uint2(pack_bf16(a, b), pack_bf16(c, d));
 }
 template <>
+__device__ __forceinline__ void store4v<float>(void* base, int64_t idx, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(static_cast<float*>(base) + idx) = make_float4(a, b, c, d);
+}
+template <>
 __device__ __forceinline__ void store4v<__half>(void* base, int64_t idx, float a, float b, float c, float d) {
   const __half2 lo = __floats2half2_rn(a, b), hi = __floats2half2_rn(c, d);
   *reinterpret_cast<uint2*>(static_cast<__half*>(base) + idx) =
@@ -379,14 +393,20 @@ __device__ __forceinline__ void tmem_ld8f(uint32_t taddr, float (&x)[8]) {
   for (int i = 0; i < 8; ++i) x[i] = __uint_as_float(r[i]);
 }
 
-template <typename T, typename G>
+// kF32Grads: dq, dk, dv, dbeta, dw leave as fp32 instead of the sequence dtype (the values before
+// their final rounding; used by tests to judge the arithmetic apart from the 16-bit cast).
+template <typename T, typename G, bool kF32Grads = false>
 __global__ void __launch_bounds__(kVjpThreads, 1)
 chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s0,
                      const __grid_constant__ CUtensorMap tm_ds) {
+  using O = typename std::conditional<kF32Grads, float, T>::type;  // element type of dq, dk, dv, dbeta, dw
   extern __shared__ __align__(128) uint8_t smem[];
   VjpMisc& ms = *reinterpret_cast<VjpMisc*>(smem + kOffMisc);
   const WsLayout ws{p.n_ch, true};
+  const ScratchLayout sc{p.n_ch};
   BoundedWaiter waiter(p.status);
+  // a wait that ran out earlier (forward or reverse scan) left garbage behind: gradients become NaN
+  const bool upstream_failed = *static_cast<volatile const int*>(p.status) != kStatusOk;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int q4 = warp & 3, part = warp >> 2;
@@ -425,7 +445,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     tma_load_5d(smem + kOffS0, &tm_s0, 0, 0, 0, 0, s0_slot_, &ms.bar_s);
     mbar_arrive_expect_tx(&ms.bar_a, uint32_t(kBlobDZ + kBlobRn));
     bulk_g2s(smem + kOffRn, p.ws + ws.off_rn() + ch_ * kBlobRn, uint32_t(kBlobRn), &ms.bar_a);
-    bulk_g2s(smem + kOffStack, p.ws + ws.off_dz() + ch_ * kBlobDZ, uint32_t(kBlobDZ), &ms.bar_a);
+    bulk_g2s(smem + kOffStack, p.sc + sc.off_dz() + ch_ * kBlobDZ, uint32_t(kBlobDZ), &ms.bar_a);
   };
   if (tid == 0 && int64_t(blockIdx.x) < p.n_ch) issue_loads(blockIdx.x);
 
@@ -548,13 +568,14 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int j = 4 * tg + e;
-      const float4 dz = *reinterpret_cast<const float4*>(smem + kOffStack + (j >> 3) * kRsN + c4 * kCsN + (j & 7) * 16);
+      float4 dz = *reinterpret_cast<const float4*>(smem + kOffStack + (j >> 3) * kRsN + c4 * kCsN + (j & 7) * 16);
+      if (upstream_failed || waiter.dead) dz = make_float4(poison_nan(), poison_nan(), poison_nan(), poison_nan());
       const int64_t idx = seq_idx(j) + kc0;
       float wv[4], vv[4];
       unpack4<T>(wr[e], wv);
       unpack4<T>(vr[e], vv);
-      store4v<T>(p.dv, idx, dz.x * wv[0], dz.y * wv[1], dz.z * wv[2], dz.w * wv[3]);
-      store4v<T>(p.dw, idx, dz.x * vv[0], dz.y * vv[1], dz.z * vv[2], dz.w * vv[3]);
+      store4v<O>(p.dv, idx, dz.x * wv[0], dz.y * wv[1], dz.z * wv[2], dz.w * wv[3]);
+      store4v<O>(p.dw, idx, dz.x * vv[0], dz.y * vv[1], dz.z * vv[2], dz.w * vv[3]);
     }
   }
   // ---- M4 (second half) once the second half of dS_1 has landed -----------------------------------------
@@ -707,6 +728,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
   // the row and column contributions of the Gram products to dG then cancel as they do exactly.
   {
     const int kc = tid & 127, blk = part;
+    const bool failed = upstream_failed || waiter.dead;
     const float gend = ms.gend[kc];
     // dd[k] = sum_v dS_1[k][v] S_0[k][v]: read here, before xt is reused for the block sums of dG
     const float dd_k = (ms.xt[0][kc] + ms.xt[1][kc]) + (ms.xt[2][kc] + ms.xt[3][kc]);
@@ -784,11 +806,11 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
       for (int t = 0; t < 8; ++t) {
         const int64_t idx = seq_idx(i0 + t) + kc;
         const float ea = Gb[t], eg = ea * e_ame;
-        const float P1 = fmaf(x[t], eg, y[t] * ea);
+        const float P1 = failed ? poison_nan() : fmaf(x[t], eg, y[t] * ea);
         const float dGt = fmaf(to_tf32(sq[t] * ea), y[t], fmaf(sq[t] * eg, x[t], dG[t]));
-        stf<T>(p.dq, idx, p.scale * P1);
-        stf<T>(p.dk, idx, fmaf(bv[t], P2[t], P3[t]));
-        stf<T>(p.dbeta, idx, kv[t] * P2[t]);
+        stf<O>(p.dq, idx, p.scale * P1);
+        stf<O>(p.dk, idx, failed ? poison_nan() : fmaf(bv[t], P2[t], P3[t]));
+        stf<O>(p.dbeta, idx, failed ? poison_nan() : kv[t] * P2[t]);
         dGv[8 * sb + t] = dGt;
         tot += dGt;
       }
@@ -810,7 +832,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
 #pragma unroll
     for (int t = 15; t >= 0; --t) {
       run += dGv[t];
-      stf<G>(p.dg, seq_idx(16 * blk + t) + kc, run);
+      stf<G>(p.dg, seq_idx(16 * blk + t) + kc, failed ? poison_nan() : run);
     }
   }
   // the next chunk-head reuses the arrays of VjpMisc and the TMEM columns
@@ -859,18 +881,21 @@ static bool encode_state_map(CUtensorMap* tm, const float* base, int64_t n_slots
 // ---- launcher ---------------------------------------------------------------------------------------
 int launch_chunk_backward(const void* q, const void* k, const void* v, const void* g, const void* beta,
                           const void* w, const void* d_out, const float* ds_final, const float* bnd,
-                          float* d_bnd, uint8_t* workspace, void* dq, void* dk, void* dv, void* dg,
+                          float* d_bnd, const uint8_t* workspace, uint8_t* scratch, void* dq, void* dk, void* dv, void* dg,
                           void* dbeta, void* dw, float* ds_init, int64_t B, int64_t T, int64_t H,
-                          int64_t full_tokens, int dtype, int g_dtype, float scale, cudaStream_t stream) {
+                          int64_t full_tokens, int dtype, int g_dtype, float scale, int grads_f32,
+                          cudaStream_t stream) {
+  if (grads_f32 && !(dtype == GDN2_BF16 && g_dtype == GDN2_FP32)) return GDN2_ERR_UNSUPPORTED;
   const int64_t n_chunks = full_tokens / kChunk;
   const int64_t n_ch = B * n_chunks * H;
   if (n_ch <= 0 || n_ch > int64_t(0x7fffffff)) return GDN2_ERR_TOO_LARGE;
   const WsLayout ws{n_ch, true};
-  int* status = reinterpret_cast<int*>(workspace + ws.off_status());
+  // the status word is the one the forward cleared: a forward failure stays visible to backward
+  int* status = reinterpret_cast<int*>(const_cast<uint8_t*>(workspace) + ws.off_status());
   cudaError_t err;
 
   profile_mark(3, stream);
-  BScanParams sp{workspace, d_out, ds_final, d_bnd, ds_init, status, T, H, n_chunks, n_ch};
+  BScanParams sp{workspace, scratch, d_out, ds_final, d_bnd, ds_init, status, T, H, n_chunks, n_ch};
   const int scan_smem = int(sizeof(BScanSmem));
   if (dtype == GDN2_BF16) {
     auto kernel = chunk_bwd_scan_kernel<__nv_bfloat16>;
@@ -897,14 +922,22 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
       !encode_state_map(&tm_s0, bnd, n_slots, 32) || !encode_state_map(&tm_ds, d_bnd, n_slots, 16)) {
     return GDN2_ERR_LAUNCH;
   }
-  VjpParams vp{q, k, v, g, beta, w, d_out, workspace, bnd, d_bnd, dq, dk, dv, dg, dbeta, dw,
+  VjpParams vp{q, k, v, g, beta, w, d_out, workspace, scratch, bnd, d_bnd, dq, dk, dv, dg, dbeta, dw,
                status, T, H, n_chunks, n_ch, scale};
-  GDN2_DISPATCH_TYPES(dtype, g_dtype, {
-    auto kernel = chunk_bwd_vjp_kernel<T, G>;
+  const unsigned vjp_grid = unsigned(n_ch < int64_t(sm_count) ? n_ch : int64_t(sm_count));
+  if (grads_f32) {
+    auto kernel = chunk_bwd_vjp_kernel<__nv_bfloat16, float, true>;
     err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kVjpSmemBytes);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
-    kernel<<<unsigned(n_ch < int64_t(sm_count) ? n_ch : int64_t(sm_count)), kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds);
-  });
+    kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds);
+  } else {
+    GDN2_DISPATCH_TYPES(dtype, g_dtype, {
+      auto kernel = chunk_bwd_vjp_kernel<T, G>;
+      err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kVjpSmemBytes);
+      if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
+      kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds);
+    });
+  }
   st = check_launch();
   profile_mark(5, stream);
   return st;

@@ -1,25 +1,32 @@
 // Shared definitions of the 64-token tensor-core chunk path.
 //
-// Workspace ("WY blobs"): for every chunk-head ch = (b * n_chunks + c) * H + h the prep kernel
-// writes operand-ready tiles that the scan kernels pull into shared memory with 1-D bulk
-// copies and that backward reuses.  All tiles are "blocked" (see tc05.cuh), CS = 128, tf32
-// values in fp32 containers:
+// For every chunk-head ch = (b * n_chunks + c) * H + h the prep kernel writes operand-ready
+// tiles ("WY blobs") that the scan kernels pull into shared memory with 1-D bulk copies.  All
+// tiles are "blocked" (see tc05.cuh), CS = 128, tf32 values in fp32 containers.  They live in two
+// caller-provided buffers:
 //
+// scratch (dead when the call returns; one buffer can serve any number of calls on a stream)
+//   forward:
 //   Y    X[r = token i (64)][c = key k (128)]   RS = 4096   32 KiB   Y = (I+L)^-1 E
 //   Ut   X[r = value v (128)][c = token i (64)] RS = 2048   32 KiB   U^T, U = (I+L)^-1 (w*v)
 //   Q    X[r = token i (64)][c = key k (128)]   RS = 4096   32 KiB   scale * gamma * q
 //   Kt   X[r = key k (128)][c = token j (64)]   RS = 2048   32 KiB   (k * gamma_end / gamma)^T
 //   A    X[r = token i (64)][c = token j (64)]  RS = 2048   16 KiB   tril(Q_gamma Kbar^T)
+//   backward:
+//   dZ   X[r = token j (64)][c = value v (128)] RS = 4608, CS = 144   36 KiB   dZ = T^T dR (reverse
+//        scan -> VJP kernel; the padded strides are those of the shared-memory tile it is copied into)
+//
+// workspace (a training call's workspace is what backward consumes; an inference call's holds
+// only D and the status block)
 //   D    float[128]                                         512 B    gamma_end
-// and, for training calls only (consumed by backward, which contracts over the other index):
+//   status block, 256 B
+//   and, for training calls only (backward contracts over the other index of each tile):
 //   Yt   X[r = key k (128)][c = token i (64)]   RS = 2048   32 KiB   Y^T
 //   Qt   X[r = key k (128)][c = token i (64)]   RS = 2048   32 KiB   Q_gamma^T
 //   Kn   X[r = token j (64)][c = key k (128)]   RS = 4096   32 KiB   K_tail
 //   At   X[r = token j (64)][c = token i (64)]  RS = 2048   16 KiB   A_qk^T
 //   Tt   X[r = token j (64)][c = token i (64)]  RS = 2048   16 KiB   ((I+L)^-1)^T
 //   Rn   X[r = token j (64)][c = value v (128)] RS = 4096   32 KiB   R = U - Y S_0 (forward scan)
-//   dZ   X[r = token j (64)][c = value v (128)] RS = 4608, CS = 144   36 KiB   dZ = T^T dR (backward
-//        scan; the padded strides are those of the shared-memory tile it is copied into)
 //
 // Arrays are stored one after another (struct of arrays), each n_ch entries long.
 #pragma once
@@ -33,45 +40,57 @@ constexpr int kChunk = GDN2_CHUNK;  // 64
 
 constexpr int64_t kBlobY = 32768, kBlobUt = 32768, kBlobQ = 32768, kBlobKt = 32768;
 constexpr int64_t kBlobA = 16384, kBlobD = 512;
-constexpr int64_t kBlobFwd = kBlobY + kBlobUt + kBlobQ + kBlobKt + kBlobA + kBlobD;
+constexpr int64_t kBlobFwdScratch = kBlobY + kBlobUt + kBlobQ + kBlobKt + kBlobA;
 constexpr int64_t kBlobYt = 32768, kBlobQt = 32768, kBlobKn = 32768, kBlobAt = 16384, kBlobTt = 16384;
 constexpr int64_t kBlobRn = 32768, kBlobDZ = 8 * 4608;
+constexpr int64_t kStatusBytes = 256;
 
+// workspace: what a training forward leaves for backward (inference: D and the status block only)
 struct WsLayout {
   int64_t n_ch;
   bool training = false;
-  __host__ __device__ int64_t off_y() const { return 0; }
-  __host__ __device__ int64_t off_ut() const { return n_ch * kBlobY; }
-  __host__ __device__ int64_t off_q() const { return n_ch * (kBlobY + kBlobUt); }
-  __host__ __device__ int64_t off_kt() const { return n_ch * (kBlobY + kBlobUt + kBlobQ); }
-  __host__ __device__ int64_t off_a() const { return n_ch * (kBlobY + kBlobUt + kBlobQ + kBlobKt); }
-  __host__ __device__ int64_t off_d() const { return off_a() + n_ch * kBlobA; }
-  __host__ __device__ int64_t off_status() const { return off_d() + n_ch * kBlobD; }
+  __host__ __device__ int64_t off_d() const { return 0; }
+  __host__ __device__ int64_t off_status() const { return n_ch * kBlobD; }
   // training-only arrays follow the status block
-  __host__ __device__ int64_t off_yt() const { return off_status() + 256; }
+  __host__ __device__ int64_t off_yt() const { return off_status() + kStatusBytes; }
   __host__ __device__ int64_t off_qt() const { return off_yt() + n_ch * kBlobYt; }
   __host__ __device__ int64_t off_kn() const { return off_qt() + n_ch * kBlobQt; }
   __host__ __device__ int64_t off_at() const { return off_kn() + n_ch * kBlobKn; }
   __host__ __device__ int64_t off_tt() const { return off_at() + n_ch * kBlobAt; }
   __host__ __device__ int64_t off_rn() const { return off_tt() + n_ch * kBlobTt; }
-  __host__ __device__ int64_t off_dz() const { return off_rn() + n_ch * kBlobRn; }
-  __host__ __device__ int64_t total() const {
-    return training ? off_dz() + n_ch * kBlobDZ : off_status() + 256;
-  }
+  __host__ __device__ int64_t total() const { return training ? off_rn() + n_ch * kBlobRn : off_yt(); }
+};
+
+// scratch of one call
+struct ScratchLayout {
+  int64_t n_ch;
+  __host__ __device__ int64_t off_y() const { return 0; }
+  __host__ __device__ int64_t off_ut() const { return n_ch * kBlobY; }
+  __host__ __device__ int64_t off_q() const { return n_ch * (kBlobY + kBlobUt); }
+  __host__ __device__ int64_t off_kt() const { return n_ch * (kBlobY + kBlobUt + kBlobQ); }
+  __host__ __device__ int64_t off_a() const { return n_ch * (kBlobY + kBlobUt + kBlobQ + kBlobKt); }
+  __host__ __device__ int64_t total_forward() const { return n_ch * kBlobFwdScratch; }
+  __host__ __device__ int64_t off_dz() const { return 0; }
+  __host__ __device__ int64_t total_backward() const { return n_ch * kBlobDZ; }
 };
 
 // device status codes written to the workspace status word (0 = ok)
 enum : int { kStatusOk = 0, kStatusBarrierTimeout = 1 };
 
-// A wait that gives up: after the first timeout every later wait of the thread returns
-// immediately, the kernel runs to completion on garbage and the host sees the status word.
+__device__ __forceinline__ float poison_nan() { return __int_as_float(0x7fc00000); }
+
+// A wait that gives up: after `limit` failed polls the thread records kStatusBarrierTimeout in the
+// status word and every later wait of the thread returns immediately.  The kernel then runs to its
+// end (shared resources such as TMEM are always released) and writes NaN instead of results, so the
+// failure shows in the outputs themselves and not only in the status word.
 struct BoundedWaiter {
   bool dead = false;
   int* status;
-  __device__ explicit BoundedWaiter(int* s) : status(s) {}
+  uint32_t limit;
+  __device__ explicit BoundedWaiter(int* s, uint32_t max_polls = (1u << 20)) : status(s), limit(max_polls) {}
   __device__ __forceinline__ void wait(uint64_t* bar, uint32_t parity) {
     if (dead) return;
-    if (!tc::mbar_wait(bar, parity, 1u << 20)) {
+    if (!tc::mbar_wait(bar, parity, limit)) {
       dead = true;
       if (status != nullptr) atomicExch(status, kStatusBarrierTimeout);
     }

@@ -62,7 +62,8 @@ struct PrepSmem {
 
 struct PrepParams {
   const void *q, *k, *v, *g, *beta, *w;
-  uint8_t* ws;
+  uint8_t* ws;   // workspace (D, status; training: the tiles backward consumes)
+  uint8_t* sc;   // scratch (the tiles the forward scan consumes)
   int64_t T, H, n_chunks, n_ch;
   float scale;
   int training;  // also write the transposed tiles that backward consumes
@@ -76,6 +77,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
   extern __shared__ __align__(128) uint8_t smem_raw[];
   PrepSmem& sm = *reinterpret_cast<PrepSmem*>(smem_raw);
   const WsLayout ws{p.n_ch, p.training != 0};
+  const ScratchLayout sc{p.n_ch};
   int* status = reinterpret_cast<int*>(p.ws + ws.off_status());
   BoundedWaiter waiter(status);
   const bool training = p.training != 0;
@@ -172,8 +174,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     t_far[1][f] = (mb + 3 < 4) ? __expf(sm.part[4 * (mb + 3)][kc] - a_nx[f]) : 0.f;
   }
 
-  uint8_t* blob_q = p.ws + ws.off_q() + ch * kBlobQ;
-  uint8_t* blob_kt = p.ws + ws.off_kt() + ch * kBlobKt;
+  uint8_t* blob_q = p.sc + sc.off_q() + ch * kBlobQ;
+  uint8_t* blob_kt = p.sc + sc.off_kt() + ch * kBlobKt;
   uint8_t* blob_kn = p.ws + ws.off_kn() + ch * kBlobKn;
   float ebar[4][4], ktail[4][4], qgam[4][4];
 #pragma unroll
@@ -289,7 +291,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     const int I_lo = (q4 & 1) * 2;
     const int my_I = I_lo + (lane >> 4);
     const int c0 = 16 * part;
-    uint8_t* blob_a = p.ws + ws.off_a() + ch * kBlobA;
+    uint8_t* blob_a = p.sc + sc.off_a() + ch * kBlobA;
     uint32_t lo[16], hi[16];
     const bool need_lo = c0 < 16 * (I_lo + 1), need_hi = c0 < 16 * (I_lo + 2);
     if (need_lo) tmem_ld16(tmem_addr(tb, 32 * q4, gram_col(I_lo) + c0), lo);
@@ -487,7 +489,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     // Y: lanes 0..63 hold rows i; the four warps of quadrants 0 and 1 take 32 key columns each
     if (q4 < 2) {
       const int i = 32 * q4 + lane;
-      uint8_t* blob_y = p.ws + ws.off_y() + ch * kBlobY;
+      uint8_t* blob_y = p.sc + sc.off_y() + ch * kBlobY;
 #pragma unroll
       for (int c0 = 32 * part; c0 < 32 * part + 32; c0 += 16) {
         uint32_t r[16];
@@ -503,7 +505,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     {
       const int row = 32 * q4 + lane;
       const int c0 = 16 * part;
-      uint8_t* blob_ut = p.ws + ws.off_ut() + ch * kBlobUt;
+      uint8_t* blob_ut = p.sc + sc.off_ut() + ch * kBlobUt;
       uint32_t r[16];
       tmem_ld16(tmem_addr(tb, 32 * q4, 128 + c0), r);
       tmem_wait_ld();
@@ -545,7 +547,8 @@ struct ScanSmem {
 };
 
 struct ScanParams {
-  const uint8_t* ws;
+  const uint8_t* ws;   // workspace (D)
+  const uint8_t* sc;   // scratch (Y, Ut, Q, Kt, A)
   const float* s_in;   // [B,H,128,128] or null
   void* out;           // [B,T,H,128]
   float* s_out;        // [B,H,128,128] or null
@@ -561,7 +564,10 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
   extern __shared__ __align__(128) uint8_t smem_raw[];
   ScanSmem& sm = *reinterpret_cast<ScanSmem*>(smem_raw);
   const WsLayout ws{p.n_ch, p.training != 0};
+  const ScratchLayout sc{p.n_ch};
   BoundedWaiter waiter(p.status);
+  // a wait that ran out in the prep kernel left garbage tiles: results become NaN from the start
+  const bool upstream_failed = *static_cast<volatile const int*>(p.status) != kStatusOk;
 
   // 16 warps: warp & 3 = TMEM lane quadrant (a warp reaches only the 32 lanes of its quadrant),
   // warp >> 2 = its quarter of the columns of whatever accumulator is being moved
@@ -596,18 +602,18 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
   auto load_yqa = [&](int64_t c) {
     const int64_t ch = ch_of(c);
     mbar_arrive_expect_tx(&sm.bar_yqa, uint32_t(kBlobY + kBlobQ + kBlobA));
-    bulk_g2s(sm.y, p.ws + ws.off_y() + ch * kBlobY, uint32_t(kBlobY), &sm.bar_yqa);
-    bulk_g2s(sm.q, p.ws + ws.off_q() + ch * kBlobQ, uint32_t(kBlobQ), &sm.bar_yqa);
-    bulk_g2s(sm.a, p.ws + ws.off_a() + ch * kBlobA, uint32_t(kBlobA), &sm.bar_yqa);
+    bulk_g2s(sm.y, p.sc + sc.off_y() + ch * kBlobY, uint32_t(kBlobY), &sm.bar_yqa);
+    bulk_g2s(sm.q, p.sc + sc.off_q() + ch * kBlobQ, uint32_t(kBlobQ), &sm.bar_yqa);
+    bulk_g2s(sm.a, p.sc + sc.off_a() + ch * kBlobA, uint32_t(kBlobA), &sm.bar_yqa);
   };
   auto load_ut = [&](int64_t c) {
     mbar_arrive_expect_tx(&sm.bar_ut, uint32_t(kBlobUt));
-    bulk_g2s(sm.ut, p.ws + ws.off_ut() + ch_of(c) * kBlobUt, uint32_t(kBlobUt), &sm.bar_ut);
+    bulk_g2s(sm.ut, p.sc + sc.off_ut() + ch_of(c) * kBlobUt, uint32_t(kBlobUt), &sm.bar_ut);
   };
   auto load_kt = [&](int64_t c) {
     const int64_t ch = ch_of(c);
     mbar_arrive_expect_tx(&sm.bar_kt, uint32_t(kBlobKt + kBlobD));
-    bulk_g2s(sm.kt, p.ws + ws.off_kt() + ch * kBlobKt, uint32_t(kBlobKt), &sm.bar_kt);
+    bulk_g2s(sm.kt, p.sc + sc.off_kt() + ch * kBlobKt, uint32_t(kBlobKt), &sm.bar_kt);
     bulk_g2s(sm.d, p.ws + ws.off_d() + ch * kBlobD, uint32_t(kBlobD), &sm.bar_kt);
   };
 
@@ -695,9 +701,11 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
       }
       // ---- output rows of this chunk: o[t0 + i][v] ---------------------------------------------------
       T* out = static_cast<T*>(p.out);
+      const bool failed = upstream_failed || waiter.dead;
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        out[((b * p.T + t0 + i0 + j) * p.H + h) * kDim + vrow] = from_float<T>(__uint_as_float(ro[j]));
+        out[((b * p.T + t0 + i0 + j) * p.H + h) * kDim + vrow] =
+            from_float<T>(failed ? poison_nan() : __uint_as_float(ro[j]));
       }
     }
     // ---- checkpoint the chunk-start state, then decay the accumulator: S^T <- S^T diag(d) ----------
@@ -746,10 +754,12 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
     uint32_t r[32];
     tmem_ld32(tmem_addr(tb, lane_base, kColS + k0), r);
     tmem_wait_ld();
+    const bool failed = upstream_failed || waiter.dead;
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
-      if (fin != nullptr) fin[(k0 + j) * kDim] = __uint_as_float(r[j]);
-      if (ck != nullptr) ck[(k0 + j) * kDim] = __uint_as_float(r[j]);
+      const float x = failed ? poison_nan() : __uint_as_float(r[j]);
+      if (fin != nullptr) fin[(k0 + j) * kDim] = x;
+      if (ck != nullptr) ck[(k0 + j) * kDim] = x;
     }
   }
   tc_fence_before();
@@ -757,12 +767,49 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
   if (warp == 0) tmem_dealloc(tb, 256);
 }
 
+// ---------------------------------------------------------------------------------------------
+// test aid: a bounded wait that runs out
+// ---------------------------------------------------------------------------------------------
+// One CTA allocates tensor memory like the real kernels, waits with their BoundedWaiter on an
+// mbarrier that nothing arms, and must come back by itself: status word set, tensor memory freed.
+__global__ void __launch_bounds__(128, 1) debug_wait_expires_kernel(int* status, uint32_t max_polls) {
+  __shared__ alignas(8) uint64_t bar;
+  __shared__ uint32_t tmem_base;
+  const int warp = threadIdx.x >> 5;
+  if (warp == 0) {
+    tmem_alloc(&tmem_base, 32);
+    tmem_relinquish();
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  BoundedWaiter waiter(status, max_polls);
+  waiter.wait(&bar, 0);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, 32);
+}
+
 }  // namespace
+
+int launch_debug_wait_expires(int* status, uint32_t max_polls, cudaStream_t stream) {
+  debug_wait_expires_kernel<<<1, 128, 0, stream>>>(status, max_polls);
+  return check_launch();
+}
 
 // ---- launcher ---------------------------------------------------------------------------------
 int64_t chunk_workspace_bytes(int64_t batch, int64_t full_tokens, int64_t heads, int training) {
   const WsLayout ws{batch * (full_tokens / kChunk) * heads, training != 0};
   return ws.total();
+}
+
+int64_t chunk_scratch_bytes(int64_t batch, int64_t full_tokens, int64_t heads, int backward) {
+  const ScratchLayout sc{batch * (full_tokens / kChunk) * heads};
+  return backward ? sc.total_backward() : sc.total_forward();
 }
 
 int64_t chunk_status_offset(int64_t batch, int64_t full_tokens, int64_t heads) {
@@ -772,18 +819,19 @@ int64_t chunk_status_offset(int64_t batch, int64_t full_tokens, int64_t heads) {
 
 int launch_chunk_forward(const void* q, const void* k, const void* v, const void* g, const void* beta,
                          const void* w, const float* s_in, void* out, float* s_out, float* bnd,
-                         uint8_t* workspace, int64_t B, int64_t T, int64_t H, int64_t full_tokens,
-                         int training, int dtype, int g_dtype, float scale, cudaStream_t stream) {
+                         uint8_t* workspace, uint8_t* scratch, int64_t B, int64_t T, int64_t H,
+                         int64_t full_tokens, int training, int dtype, int g_dtype, float scale,
+                         cudaStream_t stream) {
   const int64_t n_chunks = full_tokens / kChunk;
   const int64_t n_ch = B * n_chunks * H;
   if (n_ch <= 0 || n_ch > int64_t(0x7fffffff)) return GDN2_ERR_TOO_LARGE;
   const WsLayout ws{n_ch, training != 0};
   int* status = reinterpret_cast<int*>(workspace + ws.off_status());
-  cudaError_t err = cudaMemsetAsync(status, 0, 256, stream);
+  cudaError_t err = cudaMemsetAsync(status, 0, kStatusBytes, stream);
   if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
 
   profile_mark(0, stream);
-  PrepParams pp{q, k, v, g, beta, w, workspace, T, H, n_chunks, n_ch, scale, training};
+  PrepParams pp{q, k, v, g, beta, w, workspace, scratch, T, H, n_chunks, n_ch, scale, training};
   GDN2_DISPATCH_TYPES(dtype, g_dtype, {
     auto kernel = chunk_prep_kernel<T, G>;
     const int smem = int(sizeof(PrepSmem));
@@ -795,7 +843,7 @@ int launch_chunk_forward(const void* q, const void* k, const void* v, const void
   if (st != GDN2_OK) return st;
   profile_mark(1, stream);
 
-  ScanParams sp{workspace, s_in, out, s_out, bnd, status, T, H, n_chunks, n_ch, workspace, training};
+  ScanParams sp{workspace, scratch, s_in, out, s_out, bnd, status, T, H, n_chunks, n_ch, workspace, training};
   const int smem = int(sizeof(ScanSmem));
   if (dtype == GDN2_BF16) {
     auto kernel = chunk_scan_kernel<__nv_bfloat16>;

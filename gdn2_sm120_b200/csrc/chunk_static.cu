@@ -4,7 +4,7 @@
 // carves up all device memory once at start-up and forbids any allocator call afterwards, a plugin
 // whose enqueue hook runs inside someone else's memory plan, a control loop with a hard latency
 // budget where an allocator call (which may synchronise the device) is not acceptable.  For them the
-// WY workspace of the chunk forward lives in a fixed array inside the library image instead.
+// workspace and scratch of the chunk forward live in a fixed array inside the library image instead.
 //
 // Consequences the caller must know:
 //   * the array has a fixed size: batch * (full_tokens / 64) * heads <= GDN2_STATIC_MAX_CHUNK_HEADS
@@ -25,13 +25,17 @@
 namespace gdn2 {
 
 int launch_chunk_forward(const void*, const void*, const void*, const void*, const void*, const void*,
-                         const float*, void*, float*, float*, uint8_t*, int64_t, int64_t, int64_t,
+                         const float*, void*, float*, float*, uint8_t*, uint8_t*, int64_t, int64_t, int64_t,
                          int64_t, int, int, int, float, cudaStream_t);
+int64_t chunk_status_offset(int64_t, int64_t, int64_t);
 
 namespace {
 
-constexpr int64_t kStaticMaxChunkHeads = 64;
-constexpr int64_t kStaticBytes = kStaticMaxChunkHeads * kBlobFwd + 256;  // inference layout + status block
+constexpr int64_t kStaticMaxChunkHeads = GDN2_STATIC_MAX_CHUNK_HEADS;
+// inference workspace (chunk-end decays + status block) followed by the forward scratch tiles
+constexpr int64_t kStaticWorkspaceBytes = kStaticMaxChunkHeads * kBlobD + kStatusBytes;
+constexpr int64_t kStaticBytes = kStaticWorkspaceBytes + kStaticMaxChunkHeads * kBlobFwdScratch;
+static_assert(kStaticWorkspaceBytes % 256 == 0, "the scratch part must keep the array's alignment");
 
 // Device-resident scratch.  In host code this name is only a handle for cudaGetSymbolAddress, never
 // a pointer that a kernel may be given.
@@ -40,6 +44,7 @@ static __device__ __align__(256) unsigned char g_static_workspace[kStaticBytes];
 constexpr int kMaxDevices = 64;
 std::mutex g_setup_mutex;
 unsigned char* g_device_address[kMaxDevices] = {nullptr};
+int64_t g_last_status_offset[kMaxDevices];  // status word of the most recent call's layout; valid once the address is
 
 // Once per device, with that device current: resolve the array's device address.
 int static_workspace_for_current_device(unsigned char** out) {
@@ -86,8 +91,37 @@ extern "C" int gdn2_chunk_forward_static(const void* q, const void* k, const voi
   unsigned char* workspace = nullptr;
   const int st = static_workspace_for_current_device(&workspace);
   if (st != GDN2_OK) return st;
+  {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices) {
+      std::lock_guard<std::mutex> lock(g_setup_mutex);
+      g_last_status_offset[dev] = chunk_status_offset(batch, full_tokens, heads);
+    }
+  }
   // same kernels as gdn2_chunk_forward (inference layout); the launcher clears the status word
   return launch_chunk_forward(q, k, v, g, beta, w, initial_state, out, final_state, nullptr, workspace,
-                              batch, time, heads, full_tokens, 0, dtype, g_dtype, scale,
-                              static_cast<cudaStream_t>(stream));
+                              workspace + kStaticWorkspaceBytes, batch, time, heads, full_tokens, 0, dtype,
+                              g_dtype, scale, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int gdn2_chunk_static_read_status(void* stream) {
+  using namespace gdn2;
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
+  if (dev < 0 || dev >= kMaxDevices) return GDN2_ERR_DEVICE;
+  const unsigned char* base = nullptr;
+  int64_t offset = 0;
+  {
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    base = g_device_address[dev];
+    offset = g_last_status_offset[dev];
+  }
+  if (base == nullptr) return GDN2_ERR_UNSUPPORTED;  // no static call has run on this device yet
+  int host = 0;
+  err = cudaMemcpyAsync(&host, base + offset, sizeof(int), cudaMemcpyDeviceToHost,
+                        static_cast<cudaStream_t>(stream));
+  if (err == cudaSuccess) err = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
+  return host;
 }

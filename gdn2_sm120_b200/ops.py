@@ -77,8 +77,8 @@ class _ChunkGDN2(torch.autograd.Function):
                 saved.append(aux.tail_boundaries)
                 ctx.n_tail_boundaries = 1
             if aux.workspace is not None:
-                saved.append(aux.workspace)
-                ctx.n_workspace = 1
+                saved.extend(aux.workspace)
+                ctx.n_workspace = len(aux.workspace)
         ctx.save_for_backward(*saved)
         ctx.set_materialize_grads(False)
         ctx.has_initial_state = initial_state is not None
@@ -108,7 +108,7 @@ class _ChunkGDN2(torch.autograd.Function):
             d_final_state = d_final_state.contiguous()
         chunk_boundaries = saved.pop(0) if ctx.n_chunk_boundaries else None
         tail_boundaries = saved.pop(0) if ctx.n_tail_boundaries else None
-        workspace = saved.pop(0) if ctx.n_workspace else None
+        workspace = tuple(saved[:ctx.n_workspace]) if ctx.n_workspace else None
         aux = ChunkForwardAux(chunk_boundaries, tail_boundaries, ctx.full_tokens, workspace)
         seq = tuple(_validate.detached(x) for x in (q, k, v, g, beta, w))
         *sequence_grads, d_initial_state = backward_from_aux(

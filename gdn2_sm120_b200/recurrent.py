@@ -36,8 +36,9 @@ def _use_recurrent_kernel(batch: int, time: int, heads: int, *, chunk_api: bool 
         return True
     if time >= _CHUNK_ALWAYS_MIN_TOKENS:
         return False
-    if not chunk_api:
-        return True
+    # 33..63 tokens: the reference sends the chunk API to its chunk kernel at 48 tokens (three of its
+    # 16-token chunks); here the window holds no full chunk for either API
+    del chunk_api
     return True
 
 
@@ -45,17 +46,6 @@ def _chunk_forward_compatible(tensors: Sequence[torch.Tensor]) -> bool:
     """The chunk path needs every buffer 16-byte aligned (TMA / 128-bit access)."""
 
     return all(t.data_ptr() % 16 == 0 for t in tensors)
-
-
-def _canonical_strides(shape) -> tuple[int, ...]:
-    """Row-major strides, counting size-0/1 modes as size 1."""
-
-    strides = []
-    running = 1
-    for size in reversed(tuple(shape)):
-        strides.append(running)
-        running *= max(int(size), 1)
-    return tuple(reversed(strides))
 
 
 _byte_span = _validate.byte_span

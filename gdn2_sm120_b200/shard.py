@@ -58,11 +58,32 @@ def take(tensor: torch.Tensor | None, shard: Shard, *, is_state: bool = False):
 
 def gather(local: torch.Tensor, shard: Shard, world_size: int, *, is_state: bool = False,
            group=None) -> torch.Tensor:
-    """All-gather equally sized shards back into the global tensor (every rank gets it)."""
+    """All-gather equally sized shards back into the global tensor (every rank gets it).
+
+    Every rank must hold a shard of the same shape: collectives over unequal buffers are undefined
+    (NCCL) or fail (gloo).  The shard sizes are compared first -- one tiny collective -- and a
+    ``ValueError`` is raised on every rank when they differ, before any data moves.  Batch-axis
+    shards are gathered straight into the result (``all_gather_into_tensor``); head-axis shards
+    need one concatenation."""
 
     axis = shard.axis if not is_state else (0 if shard.axis == 0 else 1)
+    sizes = torch.zeros(world_size, dtype=torch.int64, device=local.device)
+    sizes[dist.get_rank(group)] = shard.size
+    dist.all_reduce(sizes, op=dist.ReduceOp.SUM, group=group)
+    sizes = sizes.tolist()
+    if len(set(sizes)) != 1:
+        raise ValueError(
+            f"gather needs equally sized shards but the ranks hold {sizes} units along axis {shard.axis}; "
+            "choose a batch (or head count) divisible by the number of ranks"
+        )
+    local = local.contiguous()
+    if axis == 0:
+        full = torch.empty((local.shape[0] * world_size, *local.shape[1:]), dtype=local.dtype,
+                           device=local.device)
+        dist.all_gather_into_tensor(full, local, group=group)
+        return full
     pieces = [torch.empty_like(local) for _ in range(world_size)]
-    dist.all_gather(pieces, local.contiguous(), group=group)
+    dist.all_gather(pieces, local, group=group)
     return torch.cat(pieces, dim=axis)
 
 

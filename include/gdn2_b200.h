@@ -144,15 +144,25 @@ int gdn2_token_chunk_vjp(const void* q, const void* k, const void* v, const void
 /*
  * ---- tensor-core chunk path (64-token chunks) ---------------------------------------
  *
- * Bytes of caller-owned workspace the chunk kernels need for `full_tokens` leading
- * tokens (a multiple of GDN2_CHUNK) of a [batch, T, heads, 128] problem.  The workspace
- * holds the per-chunk WY factors (Y, U^T, Q_gamma, K_tail^T, A_qk, gamma_end)
- * as operand-ready tiles plus a device status word.  With `training` != 0 it is larger:
- * it also holds the transposed tiles and the residuals that gdn2_chunk_backward consumes,
- * and must stay alive (and unmodified) until that call has run.
- * Replaces the intermediate allocations of chunk_forward (src/gdn2_sm120/chunk.py:1317-1362).
+ * The chunk kernels use two caller-owned buffers for `full_tokens` leading tokens (a multiple
+ * of GDN2_CHUNK) of a [batch, T, heads, 128] problem:
+ *
+ *   workspace  gdn2_chunk_workspace_bytes(batch, full_tokens, heads, training).  Holds the
+ *              chunk-end decays and a device status word; with `training` != 0 also the tiles
+ *              and residuals gdn2_chunk_backward consumes (Y^T, Q_gamma^T, K_tail, A_qk^T,
+ *              ((I+L)^-1)^T, R: 160 KiB per 64-token chunk and head), and must then stay alive
+ *              and unmodified until that call has run.
+ *   scratch    gdn2_chunk_scratch_bytes(batch, full_tokens, heads, backward).  Tiles that only
+ *              live inside one call (forward: Y, U^T, Q_gamma, K_tail^T, A_qk, 144 KiB per
+ *              chunk-head; backward: dZ, 36 KiB per chunk-head).  Dead when the call's kernels
+ *              have run, so one scratch buffer serves every call on a stream; a large batch can
+ *              be processed as several calls over batch slices that share it.
+ * Together they replace the intermediate allocations of chunk_forward
+ * (src/gdn2_sm120/chunk.py:1317-1362) and of the backward launchers
+ * (src/gdn2_sm120/backward_wy.py:1669-1984).
  */
 int64_t gdn2_chunk_workspace_bytes(int64_t batch, int64_t full_tokens, int64_t heads, int training);
+int64_t gdn2_chunk_scratch_bytes(int64_t batch, int64_t full_tokens, int64_t heads, int backward);
 
 /*
  * Chunkwise forward over tokens [0, full_tokens).  Replaces _prepare_wy_kernel and
@@ -163,14 +173,17 @@ int64_t gdn2_chunk_workspace_bytes(int64_t batch, int64_t full_tokens, int64_t h
  *   final_state    fp32 state after token full_tokens-1 (may alias initial_state exactly); or NULL
  *   chunk_boundaries  NULL, or fp32 [B, full_tokens/64 + 1, H,128,128]: state before every
  *                  chunk and after the last one (the activation checkpoints of backward)
+ *   workspace, scratch  see above (forward scratch)
  *   training       non-zero: workspace was sized with training = 1, chunk_boundaries is
  *                  required, and everything backward needs is saved
- * All sequence pointers, states and the workspace must be 16-byte aligned.
+ * All sequence pointers, states, the workspace and the scratch must be 16-byte aligned.
+ * If a bounded wait inside a kernel expires, the workspace status word becomes 1 and `out`
+ * and `final_state` are filled with NaN from that point on.
  */
 int gdn2_chunk_forward(const void* q, const void* k, const void* v, const void* g,
                        const void* beta, const void* w, const float* initial_state,
                        void* out, float* final_state, float* chunk_boundaries,
-                       void* workspace, int64_t batch, int64_t time, int64_t heads,
+                       void* workspace, void* scratch, int64_t batch, int64_t time, int64_t heads,
                        int64_t full_tokens, int training, int dtype, int g_dtype, float scale,
                        void* stream);
 
@@ -183,29 +196,57 @@ int gdn2_chunk_forward(const void* q, const void* k, const void* v, const void* 
  *   d_final_state    cotangent of the state after token full_tokens-1, or NULL (zero)
  *   chunk_boundaries the forward's fp32 [B, full_tokens/64 + 1, H,128,128] checkpoints
  *   d_boundaries     caller-owned scratch of the same shape (cotangent at every chunk start)
- *   workspace        the forward's training workspace (read, and its dZ slots written)
+ *   workspace        the forward's training workspace (read only, apart from its status word)
+ *   scratch          backward scratch (see above)
  *   dq, dk, dv, dbeta, dw (`dtype`), dg (`g_dtype`): rows [0, full_tokens) are written
  *   d_initial_state  fp32 [B,H,128,128] or NULL
  * Every pointer must be 16-byte aligned.  The call encodes two TMA tensor maps over
  * chunk_boundaries and d_boundaries on the host (cuTensorMapEncodeTiled, looked up through
  * cudaGetDriverEntryPoint); GDN2_ERR_LAUNCH if the driver does not provide it.
+ * If the workspace status word is non-zero when a kernel starts (a wait expired in the forward
+ * or earlier in this call), or a wait expires, the gradients are filled with NaN.
  */
 int gdn2_chunk_backward(const void* q, const void* k, const void* v, const void* g,
                         const void* beta, const void* w, const void* d_out,
                         const float* d_final_state, const float* chunk_boundaries,
-                        float* d_boundaries, void* workspace,
+                        float* d_boundaries, const void* workspace, void* scratch,
                         void* dq, void* dk, void* dv, void* dg, void* dbeta, void* dw,
                         float* d_initial_state, int64_t batch, int64_t time, int64_t heads,
                         int64_t full_tokens, int dtype, int g_dtype, float scale, void* stream);
 
 /*
+ * Test aid: gdn2_chunk_backward for bf16 inputs with fp32 g, with dq, dk, dv, dbeta, dw written
+ * as fp32 (the values before their final rounding to bf16), so that the arithmetic can be
+ * held to the fp32 tolerance.  Other dtypes: GDN2_ERR_UNSUPPORTED.  No counterpart in the
+ * reference.
+ */
+int gdn2_chunk_backward_f32grads(const void* q, const void* k, const void* v, const void* g,
+                                 const void* beta, const void* w, const void* d_out,
+                                 const float* d_final_state, const float* chunk_boundaries,
+                                 float* d_boundaries, const void* workspace, void* scratch,
+                                 float* dq, float* dk, float* dv, float* dg, float* dbeta, float* dw,
+                                 float* d_initial_state, int64_t batch, int64_t time, int64_t heads,
+                                 int64_t full_tokens, float scale, void* stream);
+
+/*
  * Synchronise `stream` and return the device status word of a workspace: 0 = ok,
- * 1 = a bounded wait inside a kernel expired (results are invalid).  Diagnostic call
+ * 1 = a bounded wait inside a kernel expired (results are NaN).  Diagnostic call
  * for tests and smoke checks; no counterpart in the reference (its kernels have no
  * asynchronous waits).
  */
 int gdn2_chunk_read_status(const void* workspace, int64_t batch, int64_t full_tokens,
                            int64_t heads, void* stream);
+
+/*
+ * Test aid for the bounded waits: launches one small CTA that allocates tensor memory, waits
+ * with the kernels' own bounded waiter (at most `max_polls` polls, clamped to [1, 2^20]) on an
+ * mbarrier that nothing ever arms, records status 1 in the workspace's status word when the
+ * wait gives up, releases the tensor memory and returns.  Nothing faults, traps or spins
+ * without limit.  `workspace` is a workspace of gdn2_chunk_workspace_bytes(batch, full_tokens,
+ * heads, training).  No counterpart in the reference.
+ */
+int gdn2_debug_wait_expires(void* workspace, int64_t batch, int64_t full_tokens, int64_t heads,
+                            int64_t max_polls, void* stream);
 
 /*
  * Per-kernel timing of the chunk entry points.  While enabled, gdn2_chunk_forward and
@@ -223,8 +264,8 @@ int gdn2_profile_chunk_kernels(float* prep_ms, float* scan_ms, float* bwd_scan_m
  * reference: it exists for hosts such as a serving runtime that partitions device memory
  * once at start-up, or a plugin hook that runs inside another component's memory plan,
  * where obtaining a workspace per call is not possible.  Same kernels and results as
- * gdn2_chunk_forward with training = 0 and chunk_boundaries = NULL, but the WY workspace
- * is a fixed ~9 MiB array inside the library image (held by every GPU that loads the
+ * gdn2_chunk_forward with training = 0 and chunk_boundaries = NULL, but workspace and scratch
+ * are a fixed ~9 MiB array inside the library image (held by every GPU that loads the
  * library, until the process exits).
  *   limit      batch * (full_tokens / 64) * heads <= GDN2_STATIC_MAX_CHUNK_HEADS, otherwise
  *              GDN2_ERR_TOO_LARGE
@@ -241,6 +282,14 @@ int gdn2_chunk_forward_static(const void* q, const void* k, const void* v, const
                               void* out, float* final_state,
                               int64_t batch, int64_t time, int64_t heads, int64_t full_tokens,
                               int dtype, int g_dtype, float scale, void* stream);
+
+/*
+ * Synchronise `stream` and return the status word of the fixed array on the current device
+ * (as gdn2_chunk_read_status does for a caller-owned workspace) for the problem size of the
+ * most recent gdn2_chunk_forward_static call.  GDN2_ERR_UNSUPPORTED before the first such call
+ * on the device.  Allocates nothing.  No counterpart in the reference.
+ */
+int gdn2_chunk_static_read_status(void* stream);
 
 #ifdef __cplusplus
 } /* extern "C" */

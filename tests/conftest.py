@@ -47,7 +47,7 @@ def load_golden(name: str) -> dict:
     g_dtype = _TORCH_DTYPES[str(raw["g_dtype"])]
     scale = float(raw["scale"])
     out = {"dtype": dtype, "g_dtype": g_dtype, "scale": None if scale < 0 else scale}
-    low = {"q", "k", "v", "beta", "w", "out", "out_chunk16", "dq", "dk", "dv", "dbeta", "dw"}
+    low = {"q", "k", "v", "beta", "w", "out", "out_chunk16", "dq", "dk", "dv", "dbeta", "dw", "d_out"}
     for key in raw.files:
         if key in ("dtype", "g_dtype", "scale"):
             continue

@@ -59,11 +59,6 @@ def test_empty_byte_span_does_not_overlap():
     assert not recurrent_module._spans_overlap((0, 256), (256, 300))
 
 
-def test_canonical_strides_treat_singletons_as_one():
-    assert recurrent_module._canonical_strides((2, 1, 3, 128)) == (384, 384, 128, 1)
-    assert recurrent_module._canonical_strides((1, 0, 1, 128)) == (128, 128, 128, 1)
-
-
 def test_scale_validation():
     assert _validate.float32_scale(None) == pytest.approx(128 ** -0.5, rel=1e-7)
     assert _validate.float32_scale(-0.0) == 0.0

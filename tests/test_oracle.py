@@ -178,3 +178,54 @@ def test_chunk_wy_stage_oracle_matches_recurrence_and_autograd(chunk, kdim, vdim
     got = oracle.chunk_wy_vjp(q, k, v, g, beta, w, s0, d_o, d_s1, scale=scale)
     for a, b in zip(got, want):
         torch.testing.assert_close(a, b, rtol=1e-9, atol=1e-11)
+
+
+# ---- the package's public reference functions (same two names the reference exports) --------
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_public_reference_functions_reproduce_the_reference(name):
+    """``gdn2_sm120_b200.recurrent_forward_reference`` in its default float32 mode gives the bits
+    the reference's reference.py:47-99 gave; the chunkwise form agrees with reference.py:102-179."""
+
+    from gdn2_sm120_b200 import chunkwise_forward_reference, recurrent_forward_reference
+
+    torch.set_num_threads(1)
+    rec = load_golden(name)
+    q, k, v, g, beta, w, s0 = _inputs(rec)
+    out, state = recurrent_forward_reference(q, k, v, g, beta, w, s0, scale=rec["scale"])
+    assert out.dtype == rec["dtype"] and state.dtype == torch.float32
+    assert torch.equal(out.view(torch.int16), rec["out"].view(torch.int16))
+    torch.testing.assert_close(state, rec["final_state"], rtol=0, atol=0)
+    out_c, state_c = chunkwise_forward_reference(q, k, v, g, beta, w, s0, scale=rec["scale"], chunk_size=16)
+    assert oracle.rel_l2(state_c, rec["final_state_chunk16"]) < 5e-6
+    assert oracle.rel_l2(out_c.double(), rec["out_chunk16"].double()) < 6e-3
+
+
+# ---- stage-level oracles pinned to the reference's executable proofs ---------------------------
+def _stage_record():
+    rec = load_golden("stage_chunk64")
+    seq = tuple(rec[n][0, :, 0] for n in ("q", "k", "v", "g", "beta", "w"))
+    return rec, seq, rec["initial_state"][0, 0], rec["d_out"][0, :, 0], rec["d_s1"][0, 0]
+
+
+def test_stage_oracle_boundary_step_matches_reference_proof():
+    """dR = A^T dO + Kt dS1 and dS0 of one 64-token chunk against
+    boundary_dstate_wy_reference (backward_parallel.py:315-373 of the reference)."""
+
+    rec, seq, s0, d_o, d_s1 = _stage_record()
+    f = oracle.chunk_wy_forward(*seq, s0, scale=rec["scale"])
+    d_r = f["A"].T @ d_o.double() + f["Kt"] @ d_s1.double()
+    d_s0 = f["d"][:, None] * d_s1.double() + f["Qg"].T @ d_o.double() - f["Y"].T @ d_r
+    assert oracle.rel_l2(d_r, rec["d_residual"][0, :, 0]) < 2e-5
+    assert oracle.rel_l2(d_s0, rec["d_s0"][0, 0]) < 2e-5
+    assert oracle.rel_l2(f["s1"], rec["final_state"][0, 0]) < 2e-5
+
+
+def test_stage_oracle_chunk_vjp_matches_reference_proof():
+    """All six sequence gradients of one 64-token chunk against
+    compact_wy_chunk_vjp_reference (backward_wy.py:62-223 of the reference)."""
+
+    rec, seq, s0, d_o, d_s1 = _stage_record()
+    grads = oracle.chunk_wy_vjp(*seq, s0, d_o, d_s1, scale=rec["scale"])
+    for name, got in zip(("dq", "dk", "dv", "dg", "dbeta", "dw"), grads[:6]):
+        assert oracle.rel_l2(got, rec["stage_" + name][0, :, 0]) < 2e-5, name
+    assert oracle.rel_l2(grads[6], rec["d_s0"][0, 0]) < 2e-5

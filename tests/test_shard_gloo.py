@@ -72,6 +72,27 @@ def test_two_rank_shard_gather_and_timing_reduction(axis_case):
     mp.spawn(_worker, args=(2, port, axis_case), nprocs=2, join=True)
 
 
+def _uneven_worker(rank: int, world: int, port: int):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        seq = torch.zeros(5, 2, 3, 8)  # 5 batch rows over 2 ranks: shards of 3 and 2
+        plan = shard.plan(5, 3, world, rank)
+        assert plan.size == (3 if rank == 0 else 2)
+        with pytest.raises(ValueError, match="equally sized shards"):
+            shard.gather(shard.take(seq, plan), plan, world)
+        # the group is still usable afterwards: nothing was left half-done
+        assert shard.sum_over_ranks(1.0, torch.device("cpu")) == float(world)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_gather_rejects_uneven_shards_on_every_rank():
+    port = _free_port()
+    mp.spawn(_uneven_worker, args=(2, port), nprocs=2, join=True)
+
+
 def test_reductions_without_a_process_group_are_identity():
     assert shard.max_over_ranks(3.5, torch.device("cpu")) == 3.5
     assert shard.sum_over_ranks(3.5, torch.device("cpu")) == 3.5

@@ -231,6 +231,24 @@ def test_decode_config_in_place_full_size():
     torch.testing.assert_close(out.float().cpu(), ref_out.to(out.dtype).float(), rtol=2e-3, atol=2e-3)
 
 
+def test_decode_shard_of_the_eight_gpu_configuration():
+    """One GPU's share (B=128) of the sharded decode configuration B=1024, H=32, T=1 with the fp32
+    state updated in place, against the float32 recurrence; two steps, like a decode loop."""
+
+    cpu = oracle.make_inputs(128, 1, 32, seed=4)
+    ref_out, ref_state = oracle.recurrence(*cpu, dtype=torch.float32)
+    q, k, v, g, beta, w, s0 = dev(*cpu)
+    out = torch.empty_like(q)
+    out_ret, fin = recurrent_gdn2(q, k, v, g, beta, w, s0, out=out, inplace_final_state=True)
+    assert fin is s0 and out_ret is out
+    torch.testing.assert_close(out.float().cpu(), ref_out.to(q.dtype).float(), rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(s0.cpu(), ref_state, rtol=1e-5, atol=1e-5)
+    ref_out2, ref_state2 = oracle.recurrence(*cpu[:6], ref_state, dtype=torch.float32)
+    recurrent_gdn2(q, k, v, g, beta, w, s0, out=out, inplace_final_state=True)
+    torch.testing.assert_close(out.float().cpu(), ref_out2.to(q.dtype).float(), rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(s0.cpu(), ref_state2, rtol=2e-5, atol=2e-5)
+
+
 def test_raw_c_abi_call_with_token_sub_range():
     """Call the C entry point directly: process tokens [3, 9) of a T=12 tensor and write a
     boundary stack; rows outside the range of `out` must stay untouched."""

@@ -50,6 +50,8 @@ def test_static_workspace_entry_matches_ordinary_entry_twice(shapes):
         s0 = cpu[6].to(DEV) if with_state else None
         status, out_s, fin_s = _call_static(q, k, v, g, beta, w, s0, batch, time, heads, time, scale)
         assert status == 0, _lib.lib().gdn2_status_string(status)
+        # no bounded wait ran out inside the kernels (status word of the fixed array)
+        assert _lib.lib().gdn2_chunk_static_read_status(torch.cuda.current_stream().cuda_stream) == 0
         out_o, fin_o = _call_ordinary(q, k, v, g, beta, w, s0, batch, time, heads, time, scale)
         torch.cuda.synchronize()
         torch.testing.assert_close(out_s.float(), out_o.float(), rtol=2e-2, atol=1e-2)
