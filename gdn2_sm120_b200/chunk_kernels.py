@@ -28,6 +28,8 @@ _STATE_BYTES = 128 * 128 * 4
 
 # Upper bound on the scratch of one wave (forward tiles, or backward tiles plus cotangent checkpoints).
 SCRATCH_BUDGET_BYTES = 12 << 30
+# Requests below this size skip the free-memory check.
+CHECK_MEMORY_MIN_BYTES = 16 << 30
 
 
 def supported_tokens(time: int, *, training: bool = False) -> int:
@@ -74,8 +76,11 @@ def plan_waves(batch: int, full_tokens: int, heads: int, *, backward: bool = Fal
 def check_memory(needed: int, device: torch.device, what: str) -> None:
     """Fail with a clear message instead of an out-of-memory error in the middle of a pass."""
 
-    if needed < (256 << 20) or torch.cuda.is_current_stream_capturing():
-        return  # small requests are left to the allocator; nothing may be queried during a capture
+    # Asking the driver for the free memory costs about a millisecond: only requests large enough for
+    # that not to matter are checked, the rest is left to the allocator.  Nothing may be queried
+    # while a stream is being captured.
+    if needed < CHECK_MEMORY_MIN_BYTES or torch.cuda.is_current_stream_capturing():
+        return
     free, _ = torch.cuda.mem_get_info(device)
     if needed <= free:
         return

@@ -660,11 +660,12 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
       const int kc = kc0 + f;
       const float a_mb = ms.part[4 * mb][kc];
       const float a_nx = (mb < 3) ? ms.part[4 * (mb + 1)][kc] : ms.gend[kc];
+      const float c_nx = __expf(a_nx - a_mb);  // decay over the whole 16-token block
       float own[4], nb[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         own[e] = __expf(a_mb - Gc[e][f]);
-        nb[e] = __expf(a_nx - Gc[e][f]);
+        nb[e] = own[e] * c_nx;                 // exp(a_nx - G): the chain forms it the same way
       }
 #pragma unroll
       for (int I = 0; I < 4; ++I) {
@@ -736,6 +737,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     const float a_nx = (blk < 3) ? ms.part[4 * (blk + 1)][kc] : gend;
     // per-thread constants: everything but three exponentials per token comes from these
     const float e_ame = __expf(a_me);            // exp(G) = exp(G - a_me) e_ame
+    const float c_nx = __expf(a_nx - a_me);      // exp(a_next - G) = exp(a_me - G) c_nx, as in the tile build
     const float t_end = __expf(gend - a_nx);     // exp(G_end - G) = exp(a_next - G) t_end
     const float far2 = (blk + 2 < 4) ? __expf(ms.part[4 * (blk + 2)][kc] - a_nx) : 1.f;  // row block blk + 2
     const float far3 = (blk + 3 < 4) ? __expf(ms.part[4 * (blk + 3)][kc] - a_nx) : 1.f;  // row block blk + 3
@@ -762,7 +764,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
 #pragma unroll
       for (int t = 0; t < 8; ++t) {
         const float own = __expf(a_me - Gb[t]);
-        nb[t] = __expf(a_nx - Gb[t]);
+        nb[t] = own * c_nx;
         Gb[t] = __expf(Gb[t] - a_me);  // from here on Gb holds the anchored decay exp(G - a_me)
         P3[t] = x[t] * own;
         dG[t] = -anchored_k(kv[t], own, 1.f, false) * x[t];

@@ -161,13 +161,14 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
 
   // ---- per-thread decay table: everything except three exponentials per element comes from here ----
   const int mb = tg >> 2;  // 16-token block of this thread's tokens
-  float a_mb[4], a_nx[4], e_amb[4], t_end[4], t_far[2][4];
+  float a_mb[4], a_nx[4], e_amb[4], c_nx[4], t_end[4], t_far[2][4];
 #pragma unroll
   for (int f = 0; f < 4; ++f) {
     const int kc = kc0 + f;
     a_mb[f] = sm.part[4 * mb][kc];
     a_nx[f] = (mb < 3) ? sm.part[4 * (mb + 1)][kc] : sm.gend[kc];
     e_amb[f] = __expf(a_mb[f]);
+    c_nx[f] = __expf(a_nx[f] - a_mb[f]);  // decay over the whole 16-token block (<= 1)
     t_end[f] = __expf(sm.gend[kc] - a_nx[f]);
     // blocks further than the next one: exp(a_I - a_next), I = mb + 2, mb + 3
     t_far[0][f] = (mb + 2 < 4) ? __expf(sm.part[4 * (mb + 2)][kc] - a_nx[f]) : 0.f;
@@ -187,7 +188,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
       const float Gi = Gc[e][f] + sm.part[tg][kc0 + f];
       const float anchored = __expf(Gi - a_mb[f]);   // <= 1
       const float own = __expf(a_mb[f] - Gi);        // >= 1, bounded by the 16-token contract
-      const float nb = __expf(a_nx[f] - Gi);         // <= 1: decay from token i to the next block start
+      const float nb = own * c_nx[f];                // exp(a_nx - G_i) <= 1: decay from token i to the next block start
       const float bk = bb[e][f] * kk[e][f];
       const float sq = p.scale * qq[e][f];
       ea[f] = to_tf32(bk * anchored);

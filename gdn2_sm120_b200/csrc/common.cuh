@@ -14,7 +14,10 @@ constexpr int kDim = GDN2_DIM;
 constexpr int kTokenInterval = GDN2_TOKEN_INTERVAL;
 
 // ---- typed scalar loads / stores through float --------------------------------
-__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+// bf16 -> fp32 is a 16-bit shift (exact); spelled out so that it runs on the integer pipe
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) {
+  return __uint_as_float(uint32_t(__bfloat16_as_ushort(x)) << 16);
+}
 __device__ __forceinline__ float to_float(__half x) { return __half2float(x); }
 __device__ __forceinline__ float to_float(float x) { return x; }
 

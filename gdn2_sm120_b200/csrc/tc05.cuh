@@ -96,6 +96,13 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
 }
+// 8- or 16-byte asynchronous copy global -> shared by the calling thread
+template <int kBytes>
+__device__ __forceinline__ void cp_async(void* smem_dst, const void* gsrc) {
+  static_assert(kBytes == 8 || kBytes == 16, "cp.async copies 4, 8 or 16 bytes");
+  asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "n"(kBytes)
+               : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
@@ -246,11 +253,13 @@ __device__ __forceinline__ void store_global_32b(void* ptr, float4 lo, float4 hi
                : "memory");
 }
 
-// round-to-nearest fp32 -> tf32 (kept in an fp32 container)
+// round-to-nearest (ties away from zero) fp32 -> tf32, kept in an fp32 container: the value
+// cvt.rna.tf32.f32 gives for every finite input, formed with one integer add and one mask.  The
+// conversion instruction shares the transcendental unit (16 results per clock and SM) with the
+// exponentials; profiles of the chunk kernels showed that unit busy 75-90 % of the time with
+// hundreds of roundings per thread, while the integer pipe was nearly idle.
 __device__ __forceinline__ float to_tf32(float x) {
-  uint32_t u;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-  return __uint_as_float(u);
+  return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
 }
 
 }  // namespace tc

@@ -25,7 +25,8 @@ namespace gdn2 {
 
 namespace {
 
-// Fewest (batch, head) pairs for which a decode step runs on the persistent ring kernel.
+// Fewest (batch, head) pairs for which a decode step runs on the persistent ring kernel (below it
+// the ring has too few heads per SM to overlap anything; measured equal to the plain kernel at 160-192)
 #ifndef GDN2_DECODE_RING_MIN_HEADS
 #define GDN2_DECODE_RING_MIN_HEADS 256
 #endif
@@ -172,27 +173,20 @@ __global__ void __launch_bounds__(kTokThreads) token_forward_kernel(const TokenF
 
 // ---------------------------------------------------------------------------------
 // Decode step (T == 1, 16-byte aligned states, many heads): persistent CTAs, one per SM, each
-// walking over (batch, head) pairs.  A head's 64 KiB state travels global -> shared -> global as
-// 1-D bulk asynchronous copies and is updated in place in shared memory.
-// Thread = (value column v, key half kh): the sums over keys stay inside a thread except for one
+// walking over (batch, head) pairs.  A head's whole 64 KiB state travels global -> shared ->
+// global as 1-D bulk asynchronous copies through a three-slot ring, so two loads and one store
+// are in flight per SM while the current head is updated in place in shared memory.
+// Thread = (value column v, key half): the sums over keys stay inside a thread except for one
 // two-way combine, and shared-memory accesses to the state are conflict-free.
-// The two key halves are two independent copy pipelines: the 128 threads of a half own the 64 key
-// rows of that half as two 16 KiB tiles (32 rows each), three heads deep, with their own mbarriers,
-// their own leader thread issuing loads and stores, and a named barrier of their own.  A tile is
-// stored the moment its half has finished with it, so that copies of 16 KiB (not 64 KiB) bound the
-// time before the first and after the last arithmetic of a CTA.
 constexpr int kDecThreads = 256;
 constexpr int kDecStages = 3;
-constexpr int kDecTileRows = 32;
-constexpr int kDecTileFloats = kDecTileRows * kDim;
-constexpr uint32_t kDecTileBytes = kDecTileFloats * sizeof(float);
 
 struct DecodeSmem {
-  alignas(128) float tile[2][kDecStages][2][kDecTileFloats];  // [key half][stage][first | second 32 rows]
+  alignas(128) float state[kDecStages][kDim * kDim];
   alignas(16) float ae[2][kDim], a[2][kDim], kk[2][kDim], qs[2][kDim], z[2][kDim];
   float red[2][2][kDim];   // [parity][key half][column]  erase partial sums
   float redo[2][2][kDim];  //                             output partial sums
-  alignas(8) uint64_t full[2][kDecStages][2];
+  alignas(8) uint64_t full[kDecStages];
 };
 
 struct DecodeParams {
@@ -204,41 +198,27 @@ struct DecodeParams {
   float scale;
 };
 
-__device__ __forceinline__ void half_barrier(int kh) {
-  asm volatile("bar.sync %0, %1;" ::"r"(1 + kh), "r"(kDecThreads / 2) : "memory");
-}
-
 template <typename T, typename G>
 __global__ void __launch_bounds__(kDecThreads, 1) token_decode_ring_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) unsigned char dec_smem_raw[];
   DecodeSmem& sm = *reinterpret_cast<DecodeSmem*>(dec_smem_raw);
   const int tid = threadIdx.x;
   const int col = tid & (kDim - 1), kh = tid >> 7;
-  const bool leader = col == 0;  // threads 0 and 128: the copy engines' clients of the two halves
   const int64_t first = blockIdx.x, stride = gridDim.x;
   const int64_t n_mine = (p.n_heads > first) ? (p.n_heads - first + stride - 1) / stride : 0;
-  const int row0 = 64 * kh;  // first key row of this thread's half
+  constexpr uint32_t kStateBytes = kDim * kDim * sizeof(float);
 
   if (tid == 0) {
 #pragma unroll
-    for (int h2 = 0; h2 < 2; ++h2)
-#pragma unroll
-      for (int s = 0; s < kDecStages; ++s) {
-        tc::mbar_init(&sm.full[h2][s][0], 1);
-        tc::mbar_init(&sm.full[h2][s][1], 1);
-      }
+    for (int s = 0; s < kDecStages; ++s) tc::mbar_init(&sm.full[s], 1);
     tc::fence_mbar_init();
   }
   __syncthreads();
 
-  auto issue_load = [&](int64_t n) {  // leaders only: both tiles of head n for this half
+  auto issue_load = [&](int64_t n) {  // thread 0 only
     const int s = int(n % kDecStages);
-    const float* src = p.s_in + (first + n * stride) * int64_t(kDim) * kDim + row0 * kDim;
-#pragma unroll
-    for (int ab = 0; ab < 2; ++ab) {
-      tc::mbar_arrive_expect_tx(&sm.full[kh][s][ab], kDecTileBytes);
-      tc::bulk_g2s(sm.tile[kh][s][ab], src + ab * kDecTileFloats, kDecTileBytes, &sm.full[kh][s][ab]);
-    }
+    tc::mbar_arrive_expect_tx(&sm.full[s], kStateBytes);
+    tc::bulk_g2s(sm.state[s], p.s_in + (first + n * stride) * int64_t(kDim) * kDim, kStateBytes, &sm.full[s]);
   };
   // per-head vectors: threads 0..127 own a key channel, threads 128..255 a value channel
   float va = 0.f, vb = 0.f, vc = 0.f, vd = 0.f;
@@ -263,7 +243,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) token_decode_ring_kernel(const
   };
 
   if (n_mine > 0) {
-    if (leader) {
+    if (tid == 0) {
       issue_load(0);
       if (n_mine > 1) issue_load(1);
     }
@@ -275,68 +255,57 @@ __global__ void __launch_bounds__(kDecThreads, 1) token_decode_ring_kernel(const
   bool dead = false;
   for (int64_t n = 0; n < n_mine; ++n) {
     const int s = int(n % kDecStages), buf = int(n & 1);
-    const uint32_t par = uint32_t((n / kDecStages) & 1);
     const int64_t bh = first + n * stride;
     if (n + 1 < n_mine) fetch_vectors(n + 1);
+    if (!dead && !tc::mbar_wait(&sm.full[s], uint32_t((n / kDecStages) & 1), 1u << 20)) dead = true;
 
-    // pass 1: r[v] = sum_k S[k][v] * (a[k] e[k]) over this half's 64 rows, tile by tile as they land
+    float* S = sm.state[s] + col;
+    const int k0 = 64 * kh;
+    // pass 1: r[v] = sum_k S[k][v] * (a[k] e[k])
     float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;  // four chains: the sum is latency-bound otherwise
-#pragma unroll
-    for (int ab = 0; ab < 2; ++ab) {
-      if (!dead && !tc::mbar_wait(&sm.full[kh][s][ab], par, 1u << 20)) dead = true;
-      const float* S = sm.tile[kh][s][ab] + col;
-      const float* ae = &sm.ae[buf][row0 + ab * kDecTileRows];
 #pragma unroll 4
-      for (int kq = 0; kq < kDecTileRows; kq += 4) {
-        const float4 f = *reinterpret_cast<const float4*>(ae + kq);
-        r0 = fmaf(S[kq * kDim], f.x, r0);
-        r1 = fmaf(S[(kq + 1) * kDim], f.y, r1);
-        r2 = fmaf(S[(kq + 2) * kDim], f.z, r2);
-        r3 = fmaf(S[(kq + 3) * kDim], f.w, r3);
-      }
+    for (int kq = 0; kq < 64; kq += 4) {
+      const float4 f = *reinterpret_cast<const float4*>(&sm.ae[buf][k0 + kq]);
+      r0 = fmaf(S[(k0 + kq) * kDim], f.x, r0);
+      r1 = fmaf(S[(k0 + kq + 1) * kDim], f.y, r1);
+      r2 = fmaf(S[(k0 + kq + 2) * kDim], f.z, r2);
+      r3 = fmaf(S[(k0 + kq + 3) * kDim], f.w, r3);
     }
     sm.red[buf][kh][col] = (r0 + r1) + (r2 + r3);
-    if (leader && n + 2 < n_mine) {
-      // The slot of head n + 2 was last used by head n - 1, whose stores this thread issued during the
-      // previous iteration: by now they have normally finished reading the slot, so this wait does not
-      // hold up the warp.
+    if (tid == 0 && n + 2 < n_mine) {
+      // The slot of head n + 2 was last used by head n - 1, whose store was issued at the end of the
+      // previous iteration: by now it has normally finished reading the slot, so this wait does not
+      // hold up the warp (at the top of the iteration it stalled every head by the store's read time).
       tc::bulk_wait_read_all();
       issue_load(n + 2);
     }
     // a copy that never arrived, for any thread: the head's results are marked invalid for all
     dead = __syncthreads_or(dead ? 1 : 0) != 0;
     const float u = sm.z[buf][col] - (sm.red[buf][0][col] + sm.red[buf][1][col]);
-    // pass 2: S <- a S + k u^T ; o[v] = sum_k S[k][v] (scale q[k]); each tile leaves as soon as it is done
+    // pass 2: S <- a S + k u^T ; o[v] = sum_k S[k][v] (scale q[k])
     float o = 0.f;
-#pragma unroll
-    for (int ab = 0; ab < 2; ++ab) {
-      float* S = sm.tile[kh][s][ab] + col;
-      const int rbase = row0 + ab * kDecTileRows;
 #pragma unroll 4
-      for (int kq = 0; kq < kDecTileRows; kq += 4) {
-        const float4 fa = *reinterpret_cast<const float4*>(&sm.a[buf][rbase + kq]);
-        const float4 fk = *reinterpret_cast<const float4*>(&sm.kk[buf][rbase + kq]);
-        const float4 fq = *reinterpret_cast<const float4*>(&sm.qs[buf][rbase + kq]);
-        float x0 = fmaf(fk.x, u, fa.x * S[kq * kDim]);
-        float x1 = fmaf(fk.y, u, fa.y * S[(kq + 1) * kDim]);
-        float x2 = fmaf(fk.z, u, fa.z * S[(kq + 2) * kDim]);
-        float x3 = fmaf(fk.w, u, fa.w * S[(kq + 3) * kDim]);
-        S[kq * kDim] = x0; S[(kq + 1) * kDim] = x1;
-        S[(kq + 2) * kDim] = x2; S[(kq + 3) * kDim] = x3;
-        o = fmaf(x0, fq.x, o); o = fmaf(x1, fq.y, o); o = fmaf(x2, fq.z, o); o = fmaf(x3, fq.w, o);
-      }
-      if (ab == 1) {
-        sm.redo[buf][kh][col] = o;
-        if (n + 1 < n_mine) stage_vectors(buf ^ 1);
-      }
-      tc::fence_async_smem();
-      if (ab == 0) half_barrier(kh); else __syncthreads();
-      // A head whose state never arrived is not written back: the caller's state (which an in-place
-      // update would otherwise overwrite with garbage) survives and the NaN output says so.
-      if (leader && !dead) {
-        tc::bulk_s2g(p.s_out + bh * int64_t(kDim) * kDim + rbase * kDim, sm.tile[kh][s][ab], kDecTileBytes);
-        tc::bulk_commit();
-      }
+    for (int kq = 0; kq < 64; kq += 4) {
+      const float4 fa = *reinterpret_cast<const float4*>(&sm.a[buf][k0 + kq]);
+      const float4 fk = *reinterpret_cast<const float4*>(&sm.kk[buf][k0 + kq]);
+      const float4 fq = *reinterpret_cast<const float4*>(&sm.qs[buf][k0 + kq]);
+      float x0 = fmaf(fk.x, u, fa.x * S[(k0 + kq) * kDim]);
+      float x1 = fmaf(fk.y, u, fa.y * S[(k0 + kq + 1) * kDim]);
+      float x2 = fmaf(fk.z, u, fa.z * S[(k0 + kq + 2) * kDim]);
+      float x3 = fmaf(fk.w, u, fa.w * S[(k0 + kq + 3) * kDim]);
+      S[(k0 + kq) * kDim] = x0; S[(k0 + kq + 1) * kDim] = x1;
+      S[(k0 + kq + 2) * kDim] = x2; S[(k0 + kq + 3) * kDim] = x3;
+      o = fmaf(x0, fq.x, o); o = fmaf(x1, fq.y, o); o = fmaf(x2, fq.z, o); o = fmaf(x3, fq.w, o);
+    }
+    sm.redo[buf][kh][col] = o;
+    if (n + 1 < n_mine) stage_vectors(buf ^ 1);
+    tc::fence_async_smem();
+    __syncthreads();
+    // A head whose state never arrived is not written back: the caller's state (which an in-place
+    // update would otherwise overwrite with garbage) survives and the NaN output says so.
+    if (tid == 0 && !dead) {
+      tc::bulk_s2g(p.s_out + bh * int64_t(kDim) * kDim, sm.state[s], kStateBytes);
+      tc::bulk_commit();
     }
     if (kh == 0) {
       float ov = sm.redo[buf][0][col] + sm.redo[buf][1][col];
@@ -344,7 +313,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) token_decode_ring_kernel(const
       stf<T>(p.out, bh * kDim + col, ov);
     }
   }
-  if (leader) tc::bulk_wait_all();
+  if (tid == 0) tc::bulk_wait_all();
 }
 
 // ---------------------------------------------------------------------------------
