@@ -716,11 +716,35 @@ def run_decode(pkg, device, peak, shard):
         pairs = _lib.KERNEL_EVENTS["gdn2_token_forward"]
         _lib.KERNEL_EVENTS = None
         kern_us = shard.max_over_ranks(statistics.median(x.elapsed_time(y) for x, y in pairs) * 1e3, device)
-        gbs = DECODE_BYTES_PER_HEAD * B * H / (kern_us * 1e-6) / 1e9
+        # a decode loop as a serving engine runs it: the steps captured once in a CUDA graph and replayed,
+        # so that neither the host's enqueue time nor the gap around a lone launch is in the figure
+        graph_us = None
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                for i in range(reps):
+                    step(i)
+            graph.replay()
+            torch.cuda.synchronize()
+            b.record()
+            for _ in range(3):
+                graph.replay()
+            e.record()
+            torch.cuda.synchronize()
+            graph_us = b.elapsed_time(e) * 1e3 / (3 * reps)
+            del graph
+        except Exception as exc:  # noqa: BLE001 - the event-bracketed figure stands in
+            print(f"bench: decode graph timing unavailable ({type(exc).__name__}: {exc})", file=sys.stderr)
+        graph_ok = shard.max_over_ranks(0.0 if graph_us is not None else 1.0, device) == 0.0
+        step_us = shard.max_over_ranks(graph_us, device) if graph_ok else kern_us
+        gbs = DECODE_BYTES_PER_HEAD * B * H / (step_us * 1e-6) / 1e9
         results[f"in_place_B{B}_H32"] = {
+            "us_per_step": step_us,
+            "timing": ("mean over a CUDA-graph replay of 40 back-to-back steps" if graph_ok
+                       else "median of single launches bracketed by CUDA events") + "; per GPU, slowest rank",
             "us_per_step_api": api_us, "us_per_step_kernel": kern_us, "hbm_gbs": gbs,
             "frac_of_measured_peak": gbs / peak, "frac_of_8TBs": gbs / 8000.0,
-            "timing": "per GPU, slowest rank"}
+            "us_per_step_kernel_note": "one launch between two CUDA events: includes the launch gap"}
         del states, inp, out
 
     B = 256
@@ -737,8 +761,30 @@ def run_decode(pkg, device, peak, shard):
     pairs = _lib.KERNEL_EVENTS["gdn2_token_forward_t1_zero"]
     _lib.KERNEL_EVENTS = None
     kern_us = shard.max_over_ranks(statistics.median(x.elapsed_time(y) for x, y in pairs) * 1e3, device)
-    gbs = T1_ZERO_BYTES_PER_HEAD * B * H / (kern_us * 1e-6) / 1e9
-    results["zero_state_B256_H32"] = {"us_per_step_kernel": kern_us, "hbm_gbs": gbs,
+    graph_us = None
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            for i in range(20):
+                pkg.recurrent_gdn2(*inp[:6], out=out, final_state_out=finals[i % 2])
+        graph.replay()
+        torch.cuda.synchronize()
+        b, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b.record()
+        for _ in range(3):
+            graph.replay()
+        e.record()
+        torch.cuda.synchronize()
+        graph_us = b.elapsed_time(e) * 1e3 / 60
+        del graph
+    except Exception as exc:  # noqa: BLE001
+        print(f"bench: zero-state graph timing unavailable ({type(exc).__name__}: {exc})", file=sys.stderr)
+    graph_ok = shard.max_over_ranks(0.0 if graph_us is not None else 1.0, device) == 0.0
+    step_us = shard.max_over_ranks(graph_us, device) if graph_ok else kern_us
+    gbs = T1_ZERO_BYTES_PER_HEAD * B * H / (step_us * 1e-6) / 1e9
+    results["zero_state_B256_H32"] = {"us_per_step": step_us, "us_per_step_kernel": kern_us, "hbm_gbs": gbs,
+                                      "timing": "CUDA-graph replay of 20 back-to-back steps" if graph_ok
+                                      else "single launches bracketed by CUDA events",
                                       "frac_of_measured_peak": gbs / peak, "frac_of_8TBs": gbs / 8000.0}
     return results
 
