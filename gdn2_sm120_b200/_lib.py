@@ -46,6 +46,8 @@ _PROTOTYPES: dict[str, list] = {
     "gdn2_chunk_backward_f32grads": [_P] * 19 + [_I64] * 4 + [_F32, _P],
     "gdn2_chunk_read_status": [_P] + [_I64] * 3 + [_P],
     "gdn2_debug_wait_expires": [_P] + [_I64] * 4 + [_P],
+    "gdn2_gate_prologue": [_P] * 12 + [_I64] * 3 + [_INT, _INT, _P],
+    "gdn2_gate_prologue_vjp": [_P] * 17 + [_I64] * 3 + [_INT, _INT, _P],
     "gdn2_chunk_forward_static": [_P] * 9 + [_I64] * 4 + [_INT, _INT, _F32, _P],
     "gdn2_chunk_static_read_status": [_P],
     "gdn2_profile_enable": [_INT],

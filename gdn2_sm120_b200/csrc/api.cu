@@ -3,6 +3,7 @@
 
 #include <cstdio>
 #include <cstring>
+#include <initializer_list>
 #include <mutex>
 
 #include "common.cuh"
@@ -35,6 +36,11 @@ int launch_chunk_backward(const void*, const void*, const void*, const void*, co
                           void*, void*, void*, void*, void*, float*, int64_t, int64_t, int64_t, int64_t, int,
                           int, float, int, cudaStream_t);
 int launch_debug_wait_expires(int* status, uint32_t max_polls, cudaStream_t stream);
+int launch_gate_prologue(const void*, const void*, const void*, const void*, const void*, void*, void*, void*,
+                         void*, void*, float*, float*, int64_t, int, int, cudaStream_t);
+int launch_gate_prologue_vjp(const void*, const void*, const void*, const void*, const void*, const float*,
+                             const float*, const void*, const void*, const void*, const void*, const void*,
+                             void*, void*, void*, void*, void*, int64_t, int, int, cudaStream_t);
 
 namespace {
 thread_local char g_cuda_error[256] = {0};
@@ -339,6 +345,55 @@ int gdn2_chunk_read_status(const void* workspace, int64_t batch, int64_t full_to
   if (err == cudaSuccess) err = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
   if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
   return host;
+}
+
+namespace {
+// a group of pointers must be given completely or not at all; returns 1 / 0, or -1 when mixed
+int group_state(std::initializer_list<const void*> ptrs) {
+  int set = 0, total = 0;
+  for (const void* ptr : ptrs) { ++total; set += ptr != nullptr; }
+  return set == 0 ? 0 : (set == total ? 1 : -1);
+}
+}  // namespace
+
+int gdn2_gate_prologue(const void* q_raw, const void* k_raw, const void* g_raw, const void* beta_raw,
+                       const void* w_raw, void* q, void* k, void* g, void* beta, void* w,
+                       float* inv_norm_q, float* inv_norm_k, int64_t batch, int64_t time, int64_t heads,
+                       int dtype, int g_dtype, void* stream) {
+  const int norm = group_state({q_raw, k_raw, q, k, inv_norm_q, inv_norm_k});
+  const int gate = group_state({g_raw, beta_raw, w_raw, g, beta, w});
+  if (norm < 0 || gate < 0 || norm + gate == 0) return GDN2_ERR_NULL_POINTER;
+  int st = check_shape(batch, time, heads);
+  if (st != GDN2_OK) return st;
+  if ((st = check_types(dtype, g_dtype)) != GDN2_OK) return st;
+  for (const void* ptr : {q_raw, k_raw, g_raw, beta_raw, w_raw, (const void*)q, (const void*)k, (const void*)g,
+                          (const void*)beta, (const void*)w}) {
+    if (!aligned(ptr, 16)) return GDN2_ERR_ALIGNMENT;
+  }
+  if (time == 0) return GDN2_OK;
+  return launch_gate_prologue(q_raw, k_raw, g_raw, beta_raw, w_raw, q, k, g, beta, w, inv_norm_q, inv_norm_k,
+                              batch * time * heads, dtype, g_dtype, static_cast<cudaStream_t>(stream));
+}
+
+int gdn2_gate_prologue_vjp(const void* q_raw, const void* k_raw, const void* g_raw, const void* beta_raw,
+                           const void* w_raw, const float* inv_norm_q, const float* inv_norm_k,
+                           const void* dq, const void* dk, const void* dg, const void* dbeta, const void* dw,
+                           void* dq_raw, void* dk_raw, void* dg_raw, void* dbeta_raw, void* dw_raw,
+                           int64_t batch, int64_t time, int64_t heads, int dtype, int g_dtype, void* stream) {
+  const int norm = group_state({q_raw, k_raw, inv_norm_q, inv_norm_k, dq, dk, dq_raw, dk_raw});
+  const int gate = group_state({g_raw, beta_raw, w_raw, dg, dbeta, dw, dg_raw, dbeta_raw, dw_raw});
+  if (norm < 0 || gate < 0 || norm + gate == 0) return GDN2_ERR_NULL_POINTER;
+  int st = check_shape(batch, time, heads);
+  if (st != GDN2_OK) return st;
+  if ((st = check_types(dtype, g_dtype)) != GDN2_OK) return st;
+  for (const void* ptr : {q_raw, k_raw, g_raw, beta_raw, w_raw, dq, dk, dg, dbeta, dw, (const void*)dq_raw,
+                          (const void*)dk_raw, (const void*)dg_raw, (const void*)dbeta_raw, (const void*)dw_raw}) {
+    if (!aligned(ptr, 16)) return GDN2_ERR_ALIGNMENT;
+  }
+  if (time == 0) return GDN2_OK;
+  return launch_gate_prologue_vjp(q_raw, k_raw, g_raw, beta_raw, w_raw, inv_norm_q, inv_norm_k, dq, dk, dg,
+                                  dbeta, dw, dq_raw, dk_raw, dg_raw, dbeta_raw, dw_raw, batch * time * heads,
+                                  dtype, g_dtype, static_cast<cudaStream_t>(stream));
 }
 
 int gdn2_debug_wait_expires(void* workspace, int64_t batch, int64_t full_tokens, int64_t heads,

@@ -16,6 +16,7 @@ import torch
 from . import _validate
 from .backward import backward_from_aux
 from .chunk import ChunkForwardAux, _token_slots, chunk_forward
+from .prologue import gate_prologue
 from .recurrent import _launch_token_forward, _use_recurrent_kernel, token_forward
 
 _DIM = 128
@@ -128,18 +129,27 @@ def chunk_gdn2(
     *,
     scale: float | None = None,
     output_final_state: bool = False,
+    use_qk_l2norm_in_kernel: bool = False,
+    use_gate_in_kernel: bool = False,
 ) -> tuple[torch.Tensor, torch.Tensor | None]:
     """Gated DeltaNet-2 with shape-dispatched forward and native backward.
 
     Sequence tensors are contiguous ``[B, T, H, 128]``; q/k/v/beta/w fp16 or bf16, ``g``
-    additionally fp32; states fp32 ``[B, H, 128, 128]``.  Gate activations and q/k
-    normalisation stay with the caller.  ``g`` must be finite and non-positive with every
-    16-token prefix sum above ln(FLT_MIN).  Returns ``(o, S_T)`` or ``(o, None)``.
+    additionally fp32; states fp32 ``[B, H, 128, 128]``.  By default (as in the reference) gate
+    activations and q/k normalisation stay with the caller and ``g`` must be finite and
+    non-positive with every 16-token prefix sum above ln(FLT_MIN).  With
+    ``use_qk_l2norm_in_kernel`` q and k are the raw projections and are L2-normalised first; with
+    ``use_gate_in_kernel`` beta, w and g are pre-activations (beta = sigmoid, w = sigmoid,
+    g = -softplus); both run as one fused kernel in front of the primitive and one behind its
+    backward (``prologue.gate_prologue``).  Returns ``(o, S_T)`` or ``(o, None)``.
     """
 
     output_scale = float(scale) if scale is not None else 1.0 / math.sqrt(_DIM)
     if not math.isfinite(output_scale):
         raise ValueError("scale must be finite")
+    if use_qk_l2norm_in_kernel or use_gate_in_kernel:
+        q, k, g, beta, w = gate_prologue(q, k, g, beta, w, normalize_qk=use_qk_l2norm_in_kernel,
+                                         activate_gates=use_gate_in_kernel)
     wants_grad = torch.is_grad_enabled() and any(
         isinstance(t, torch.Tensor) and t.requires_grad for t in (q, k, v, g, beta, w, initial_state)
     )
@@ -169,8 +179,18 @@ def recurrent_gdn2(
     out: torch.Tensor | None = None,
     final_state_out: torch.Tensor | None = None,
     inplace_final_state: bool = False,
+    use_qk_l2norm_in_kernel: bool = False,
+    use_gate_in_kernel: bool = False,
 ) -> tuple[torch.Tensor, torch.Tensor]:
-    """Forward-only GDN2 for serving, with the recurrent/chunk crossover."""
+    """Forward-only GDN2 for serving, with the recurrent/chunk crossover.
+
+    The two ``use_*_in_kernel`` keywords (default off) send raw projections / gate pre-activations
+    through the fused prologue kernel first, as in ``chunk_gdn2``."""
+
+    if use_qk_l2norm_in_kernel or use_gate_in_kernel:
+        with torch.no_grad():
+            q, k, g, beta, w = gate_prologue(q, k, g, beta, w, normalize_qk=use_qk_l2norm_in_kernel,
+                                             activate_gates=use_gate_in_kernel)
 
     return token_forward(q, k, v, g, beta, w, initial_state, scale=scale, out=out,
                          final_state_out=final_state_out, inplace_final_state=inplace_final_state)

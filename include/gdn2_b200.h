@@ -249,6 +249,40 @@ int gdn2_debug_wait_expires(void* workspace, int64_t batch, int64_t full_tokens,
                             int64_t max_polls, void* stream);
 
 /*
+ * ---- fused input prologue of a layer (next to the primitive, not inside it) ----------------
+ *
+ * One pass over the [B, T, H, 128] sequence tensors that does what a Gated DeltaNet-2 layer does to
+ * its projections before the primitive:
+ *     q = q_raw / sqrt(sum_c q_raw^2 + 1e-6), k likewise      (fp32 arithmetic, result in `dtype`)
+ *     beta = sigmoid(beta_raw), w = sigmoid(w_raw), g = -softplus(g_raw)
+ * and stores the reciprocal norms (fp32 [B, T, H]) for the VJP.  The reference leaves these steps
+ * to the caller (README.md:127-131, docs/design.md:32-34); the official implementation it compares
+ * against exposes them as use_qk_l2norm_in_kernel / use_gate_in_kernel
+ * (src/gdn2_sm120/benchmark.py:230-231).  Either group may be left out by passing NULL for all of
+ * its pointers (normalisation: q_raw, k_raw, q, k, inv_norm_q, inv_norm_k; gates: g_raw, beta_raw,
+ * w_raw, g, beta, w).  Outputs may alias their inputs exactly.  Pointers 16-byte aligned.
+ */
+int gdn2_gate_prologue(const void* q_raw, const void* k_raw, const void* g_raw, const void* beta_raw,
+                       const void* w_raw, void* q, void* k, void* g, void* beta, void* w,
+                       float* inv_norm_q, float* inv_norm_k,
+                       int64_t batch, int64_t time, int64_t heads, int dtype, int g_dtype, void* stream);
+
+/*
+ * VJP of gdn2_gate_prologue: from the raw inputs, the stored reciprocal norms and the cotangents of
+ * the activated tensors (what gdn2_chunk_backward / gdn2_token_chunk_vjp produced) to the cotangents
+ * of the raw tensors:
+ *     dq_raw = inv (dq - q^ (q^ . dq)), q^ = q_raw inv;   dbeta_raw = s (1 - s) dbeta, s = sigmoid(beta_raw);
+ *     dg_raw = -sigmoid(g_raw) dg.
+ * Each output may alias the corresponding incoming cotangent exactly (in-place conversion).
+ * Same NULL-group rule as the forward.
+ */
+int gdn2_gate_prologue_vjp(const void* q_raw, const void* k_raw, const void* g_raw, const void* beta_raw,
+                           const void* w_raw, const float* inv_norm_q, const float* inv_norm_k,
+                           const void* dq, const void* dk, const void* dg, const void* dbeta, const void* dw,
+                           void* dq_raw, void* dk_raw, void* dg_raw, void* dbeta_raw, void* dw_raw,
+                           int64_t batch, int64_t time, int64_t heads, int dtype, int g_dtype, void* stream);
+
+/*
  * Per-kernel timing of the chunk entry points.  While enabled, gdn2_chunk_forward and
  * gdn2_chunk_backward record CUDA events on their stream before, between and after their
  * two kernels; gdn2_profile_chunk_kernels waits for the most recent ones and returns the

@@ -229,3 +229,19 @@ def test_stage_oracle_chunk_vjp_matches_reference_proof():
     for name, got in zip(("dq", "dk", "dv", "dg", "dbeta", "dw"), grads[:6]):
         assert oracle.rel_l2(got, rec["stage_" + name][0, :, 0]) < 2e-5, name
     assert oracle.rel_l2(grads[6], rec["d_s0"][0, 0]) < 2e-5
+
+
+# ---- layer prologue (normalisation + gate activations) -------------------------------------------
+def test_prologue_oracle_vjp_matches_autograd():
+    torch.manual_seed(3)
+    raw = [torch.randn(2, 5, 3, 16, dtype=torch.float64, requires_grad=True) for _ in range(5)]
+    outs = oracle.gate_prologue(*raw)
+    cots = [torch.randn_like(o) for o in outs]
+    want = torch.autograd.grad(outs, raw, cots)
+    got = oracle.gate_prologue_vjp(*[r.detach() for r in raw], *cots)
+    for a, b in zip(got, want):
+        torch.testing.assert_close(a, b, rtol=1e-10, atol=1e-12)
+    # activated values follow the primitive's contract: unit-norm q/k, gates in (0, 1), g <= 0
+    q, k, g, beta, w = (o.detach() for o in outs)
+    torch.testing.assert_close(q.norm(dim=-1), torch.ones_like(q[..., 0]), rtol=1e-5, atol=1e-5)
+    assert (g <= 0).all() and ((beta > 0) & (beta < 1)).all() and ((w > 0) & (w < 1)).all()
