@@ -61,12 +61,17 @@ def _token_backward(q, k, v, g, beta, w, d_out, d_final_state, boundaries, grads
     )
 
 
-def backward_from_aux(q, k, v, g, beta, w, aux: ChunkForwardAux, d_out, d_final_state, scale):
-    """Gradients from saved checkpoints; ``d_final_state`` may be ``None`` (zero)."""
+def backward_from_aux(q, k, v, g, beta, w, aux: ChunkForwardAux, d_out, d_final_state, scale, *,
+                      grads_out=None, d_initial_state_out=None):
+    """Gradients from saved checkpoints; ``d_final_state`` may be ``None`` (zero).
+
+    ``grads_out`` (six contiguous tensors shaped like the inputs) and ``d_initial_state_out`` let a
+    caller have the kernels write into buffers it owns (slices of packed tensors, for instance)."""
 
     batch, time, heads, _ = q.shape
-    grads = tuple(torch.empty_like(x) for x in (q, k, v, g, beta, w))
-    d_initial_state = torch.empty((batch, heads, _DIM, _DIM), device=q.device, dtype=torch.float32)
+    grads = grads_out if grads_out is not None else tuple(torch.empty_like(x) for x in (q, k, v, g, beta, w))
+    d_initial_state = d_initial_state_out if d_initial_state_out is not None else torch.empty(
+        (batch, heads, _DIM, _DIM), device=q.device, dtype=torch.float32)
     full = aux.full_tokens
     d_state = d_final_state
     if time > full:

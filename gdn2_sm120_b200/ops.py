@@ -37,6 +37,61 @@ def _use_compact_wy_backward(batch: int, time: int, heads: int) -> bool:
     return time >= _PARALLEL_BACKWARD_MIN_TOKENS
 
 
+def _forward_with_aux(seq, state, scale: float, prepare_backward: bool):
+    """Forward of one (detached) problem on the shape-dispatched kernels.
+
+    Returns ``(output, final_state, aux)``; ``aux`` (the checkpoints backward consumes) is ``None``
+    unless ``prepare_backward`` and the sequence is not empty."""
+
+    q = seq[0]
+    batch, time, heads = q.shape[0], q.shape[1], q.shape[2]
+    aux = None
+    if _use_recurrent_kernel(batch, time, heads, chunk_api=True):
+        if prepare_backward and time > 0:
+            # token path with fp32 checkpoints every 16 tokens
+            batch, time, heads = _validate.sequence_inputs(*seq)
+            if state is not None:
+                _validate.state("initial_state", state, batch, heads, q.device)
+            output = torch.empty_like(seq[2])
+            final_state = torch.empty((batch, heads, _DIM, _DIM), device=q.device, dtype=torch.float32)
+            boundaries = torch.empty((batch, _token_slots(time), heads, _DIM, _DIM),
+                                     device=q.device, dtype=torch.float32)
+            _launch_token_forward(*seq, state, output, final_state, boundaries, batch, time,
+                                  heads, 0, time, _validate.float32_scale(scale))
+            aux = ChunkForwardAux(None, boundaries, 0)
+        else:
+            output, final_state = token_forward(*seq, state, scale=scale)
+    elif prepare_backward:
+        output, final_state, aux = chunk_forward(*seq, state, scale=scale, return_aux=True)
+    else:
+        output, final_state = chunk_forward(*seq, state, scale=scale)
+    return output, final_state, aux
+
+
+def _aux_tensors(aux) -> tuple[list, tuple[int, int, int, int]]:
+    """Flatten an aux bundle for ``save_for_backward``: tensors and (counts..., full_tokens)."""
+
+    if aux is None:
+        return [], (0, 0, 0, 0)
+    tensors, counts = [], []
+    for item in (aux.chunk_boundaries, aux.tail_boundaries):
+        counts.append(0 if item is None else 1)
+        if item is not None:
+            tensors.append(item)
+    workspaces = aux.workspace or ()
+    tensors.extend(workspaces)
+    return tensors, (counts[0], counts[1], len(workspaces), aux.full_tokens)
+
+
+def _aux_from_tensors(tensors: list, layout: tuple[int, int, int, int]) -> ChunkForwardAux:
+    n_chunk, n_tail, n_ws, full_tokens = layout
+    tensors = list(tensors)
+    chunk_boundaries = tensors.pop(0) if n_chunk else None
+    tail_boundaries = tensors.pop(0) if n_tail else None
+    workspace = tuple(tensors[:n_ws]) if n_ws else None
+    return ChunkForwardAux(chunk_boundaries, tail_boundaries, full_tokens, workspace)
+
+
 class _ChunkGDN2(torch.autograd.Function):
     """Connects the forward kernels, their state checkpoints and the backward kernels."""
 
@@ -44,43 +99,9 @@ class _ChunkGDN2(torch.autograd.Function):
     def forward(ctx, q, k, v, g, beta, w, initial_state, scale: float, prepare_backward: bool):
         seq = tuple(_validate.detached(x) for x in (q, k, v, g, beta, w))
         state = _validate.detached(initial_state)
-        batch, time, heads = q.shape[0], q.shape[1], q.shape[2]
-        aux = None
-        if _use_recurrent_kernel(batch, time, heads, chunk_api=True):
-            if prepare_backward and time > 0:
-                # token path with fp32 checkpoints every 16 tokens
-                batch, time, heads = _validate.sequence_inputs(*seq)
-                if state is not None:
-                    _validate.state("initial_state", state, batch, heads, q.device)
-                output = torch.empty_like(seq[2])
-                final_state = torch.empty((batch, heads, _DIM, _DIM), device=q.device,
-                                          dtype=torch.float32)
-                boundaries = torch.empty((batch, _token_slots(time), heads, _DIM, _DIM),
-                                         device=q.device, dtype=torch.float32)
-                _launch_token_forward(*seq, state, output, final_state, boundaries, batch, time,
-                                      heads, 0, time, _validate.float32_scale(scale))
-                aux = ChunkForwardAux(None, boundaries, 0)
-            else:
-                output, final_state = token_forward(*seq, state, scale=scale)
-        elif prepare_backward:
-            output, final_state, aux = chunk_forward(*seq, state, scale=scale, return_aux=True)
-        else:
-            output, final_state = chunk_forward(*seq, state, scale=scale)
-        saved = [q, k, v, g, beta, w]
-        ctx.n_chunk_boundaries = ctx.n_tail_boundaries = ctx.n_workspace = 0
-        ctx.full_tokens = 0
-        if aux is not None:
-            ctx.full_tokens = aux.full_tokens
-            if aux.chunk_boundaries is not None:
-                saved.append(aux.chunk_boundaries)
-                ctx.n_chunk_boundaries = 1
-            if aux.tail_boundaries is not None:
-                saved.append(aux.tail_boundaries)
-                ctx.n_tail_boundaries = 1
-            if aux.workspace is not None:
-                saved.extend(aux.workspace)
-                ctx.n_workspace = len(aux.workspace)
-        ctx.save_for_backward(*saved)
+        output, final_state, aux = _forward_with_aux(seq, state, scale, prepare_backward)
+        tensors, ctx.aux_layout = _aux_tensors(aux)
+        ctx.save_for_backward(q, k, v, g, beta, w, *tensors)
         ctx.set_materialize_grads(False)
         ctx.has_initial_state = initial_state is not None
         ctx.scale = scale
@@ -107,10 +128,7 @@ class _ChunkGDN2(torch.autograd.Function):
             d_output = d_output.contiguous()
         if d_final_state is not None and not d_final_state.is_contiguous():
             d_final_state = d_final_state.contiguous()
-        chunk_boundaries = saved.pop(0) if ctx.n_chunk_boundaries else None
-        tail_boundaries = saved.pop(0) if ctx.n_tail_boundaries else None
-        workspace = tuple(saved[:ctx.n_workspace]) if ctx.n_workspace else None
-        aux = ChunkForwardAux(chunk_boundaries, tail_boundaries, ctx.full_tokens, workspace)
+        aux = _aux_from_tensors(saved, ctx.aux_layout)
         seq = tuple(_validate.detached(x) for x in (q, k, v, g, beta, w))
         *sequence_grads, d_initial_state = backward_from_aux(
             *seq, aux, d_output, d_final_state, _validate.float32_scale(ctx.scale)
