@@ -46,6 +46,9 @@ _PROTOTYPES: dict[str, list] = {
     "gdn2_chunk_backward_f32grads": [_P] * 19 + [_I64] * 4 + [_F32, _P],
     "gdn2_chunk_read_status": [_P] + [_I64] * 3 + [_P],
     "gdn2_debug_wait_expires": [_P] + [_I64] * 4 + [_P],
+    "gdn2_token_forward_fused": [_P] * 9 + [_I64] * 5 + [_INT, _INT, _F32, _INT, _P],
+    "gdn2_token_forward_t1_zero_fused": [_P] * 6 + [_I64] * 2 + [_INT, _F32, _INT, _P],
+    "gdn2_chunk_forward_fused": [_P] * 11 + [_I64] * 4 + [_INT, _INT, _F32, _INT, _P],
     "gdn2_gate_prologue": [_P] * 12 + [_I64] * 3 + [_INT, _INT, _P],
     "gdn2_gate_prologue_vjp": [_P] * 17 + [_I64] * 3 + [_INT, _INT, _P],
     "gdn2_chunk_forward_static": [_P] * 9 + [_I64] * 4 + [_INT, _INT, _F32, _P],
@@ -112,7 +115,7 @@ KERNEL_EVENTS: dict[str, list] | None = None
 
 
 # kernels launched by one successful call of each entry point (default 1)
-_KERNELS_PER_CALL = {"gdn2_chunk_forward": 2, "gdn2_chunk_backward": 2, "gdn2_chunk_backward_f32grads": 2,
+_KERNELS_PER_CALL = {"gdn2_chunk_forward": 2, "gdn2_chunk_forward_fused": 2, "gdn2_chunk_backward": 2, "gdn2_chunk_backward_f32grads": 2,
                      "gdn2_chunk_forward_static": 2}
 
 

@@ -73,8 +73,13 @@ def chunk_forward(
     return_aux: bool = False,
     out=None,
     final_state_out=None,
+    prologue: int = 0,
 ):
-    """Run the chunkwise forward; returns ``(output, final_state[, aux])``."""
+    """Run the chunkwise forward; returns ``(output, final_state[, aux])``.
+
+    ``prologue`` (not in the reference's signature): bit flags of the layer prologue the forward
+    kernels apply themselves to raw inputs (see ``prologue.py``); forward-only, so it excludes
+    ``return_aux``."""
 
     batch, time, heads = _validate.sequence_inputs(
         q, k, v, g, beta, w, dim_error=NotImplementedError, need_tokens=True, need_alignment=True
@@ -84,6 +89,8 @@ def chunk_forward(
     output_scale = _validate.float32_scale(scale)
     if return_aux and (out is not None or final_state_out is not None):
         raise ValueError("preallocated outputs are supported only when return_aux=False")
+    if return_aux and prologue:
+        raise ValueError("the fused prologue is forward-only: activate with gate_prologue when training")
 
     state_shape = (batch, heads, _DIM, _DIM)
     if out is None:
@@ -143,11 +150,11 @@ def chunk_forward(
 
         workspace = chunk_kernels.forward(q, k, v, g, beta, w, state, output, final_state,
                                           chunk_boundaries, batch, time, heads, full_tokens,
-                                          output_scale)
+                                          output_scale, prologue=prologue)
         state = final_state
     if tail:
         _launch_token_forward(q, k, v, g, beta, w, state, output, final_state, tail_boundaries,
-                              batch, time, heads, full_tokens, time, output_scale)
+                              batch, time, heads, full_tokens, time, output_scale, prologue)
     if not return_aux:
         return output, final_state
     return output, final_state, ChunkForwardAux(chunk_boundaries, tail_boundaries, full_tokens,

@@ -95,10 +95,14 @@ def check_memory(needed: int, device: torch.device, what: str) -> None:
 
 
 def forward(q, k, v, g, beta, w, initial_state, output, final_state, chunk_boundaries,
-            batch, time, heads, full_tokens, scale) -> tuple[torch.Tensor, ...]:
-    """Run the chunk forward over tokens [0, full_tokens); returns one workspace per wave."""
+            batch, time, heads, full_tokens, scale, *, prologue: int = 0) -> tuple[torch.Tensor, ...]:
+    """Run the chunk forward over tokens [0, full_tokens); returns one workspace per wave.
+
+    ``prologue`` != 0 (inference only) selects the entry point whose prep kernel activates raw inputs."""
 
     training = chunk_boundaries is not None
+    if prologue and training:
+        raise ValueError("the fused prologue is forward-only")
     waves = plan_waves(batch, full_tokens, heads)
     rows = waves[0][1] - waves[0][0]
     needed = scratch_bytes(rows, full_tokens, heads, False) + sum(
@@ -111,16 +115,22 @@ def forward(q, k, v, g, beta, w, initial_state, output, final_state, chunk_bound
     for b0, b1 in waves:
         workspace = torch.empty(workspace_bytes(b1 - b0, full_tokens, heads, training), device=q.device,
                                 dtype=torch.uint8)
-        _lib.call(
-            "gdn2_chunk_forward", q.device,
+        common = [
             q[b0:b1].data_ptr(), k[b0:b1].data_ptr(), v[b0:b1].data_ptr(), g[b0:b1].data_ptr(),
             beta[b0:b1].data_ptr(), w[b0:b1].data_ptr(),
             None if initial_state is None else initial_state[b0:b1].data_ptr(),
             output[b0:b1].data_ptr(), None if final_state is None else final_state[b0:b1].data_ptr(),
-            None if chunk_boundaries is None else chunk_boundaries[b0:b1].data_ptr(),
-            workspace.data_ptr(), scratch.data_ptr(), b1 - b0, time, heads, full_tokens, int(training),
-            dtype, g_dtype, scale, stream,
-        )
+        ]
+        if prologue:
+            _lib.call("gdn2_chunk_forward_fused", q.device, *common, workspace.data_ptr(), scratch.data_ptr(),
+                      b1 - b0, time, heads, full_tokens, dtype, g_dtype, scale, prologue, stream)
+        else:
+            _lib.call(
+                "gdn2_chunk_forward", q.device, *common,
+                None if chunk_boundaries is None else chunk_boundaries[b0:b1].data_ptr(),
+                workspace.data_ptr(), scratch.data_ptr(), b1 - b0, time, heads, full_tokens, int(training),
+                dtype, g_dtype, scale, stream,
+            )
         workspaces.append(workspace)
     return tuple(workspaces)
 

@@ -13,9 +13,9 @@ namespace gdn2 {
 // launchers defined next to their kernels
 int launch_token_forward(const void*, const void*, const void*, const void*, const void*,
                          const void*, const float*, void*, float*, float*, int64_t, int64_t,
-                         int64_t, int64_t, int64_t, int, int, float, cudaStream_t);
+                         int64_t, int64_t, int64_t, int, int, float, int, cudaStream_t);
 int launch_token_t1_zero(const void*, const void*, const void*, const void*, void*, float*,
-                         int64_t, int64_t, int, float, cudaStream_t);
+                         int64_t, int64_t, int, float, int, cudaStream_t);
 int launch_token_dstate_scan(const void*, const void*, const void*, const void*, const void*,
                              const float*, float*, float*, int64_t, int64_t, int64_t, int64_t,
                              int64_t, int, int, float, cudaStream_t);
@@ -29,7 +29,7 @@ int64_t chunk_scratch_bytes(int64_t, int64_t, int64_t, int);
 int64_t chunk_status_offset(int64_t, int64_t, int64_t);
 int launch_chunk_forward(const void*, const void*, const void*, const void*, const void*, const void*,
                          const float*, void*, float*, float*, uint8_t*, uint8_t*, int64_t, int64_t, int64_t,
-                         int64_t, int, int, int, float, cudaStream_t);
+                         int64_t, int, int, int, float, int, cudaStream_t);
 
 int launch_chunk_backward(const void*, const void*, const void*, const void*, const void*, const void*,
                           const void*, const float*, const float*, float*, const uint8_t*, uint8_t*, void*,
@@ -185,33 +185,70 @@ int gdn2_device_supported(void) {
   return major == 10 ? 1 : 0;
 }
 
-int gdn2_token_forward(const void* q, const void* k, const void* v, const void* g,
-                       const void* beta, const void* w, const float* initial_state, void* out,
-                       float* final_state, float* boundaries, int64_t batch, int64_t time,
-                       int64_t heads, int64_t t_begin, int64_t t_end, int dtype, int g_dtype,
-                       float scale, void* stream) {
+namespace {
+inline bool valid_prologue(int prologue) {
+  return (prologue & ~(GDN2_PROLOGUE_NORMALIZE_QK | GDN2_PROLOGUE_ACTIVATE_GATES)) == 0;
+}
+
+int token_forward_checked(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                          const void* w, const float* initial_state, void* out, float* final_state,
+                          float* boundaries, int64_t batch, int64_t time, int64_t heads, int64_t t_begin,
+                          int64_t t_end, int dtype, int g_dtype, float scale, int prologue, void* stream) {
   if (!q || !k || !v || !g || !beta || !w || !out) return GDN2_ERR_NULL_POINTER;
   int st = check_shape(batch, time, heads);
   if (st != GDN2_OK) return st;
   if ((st = check_range(time, t_begin, t_end)) != GDN2_OK) return st;
   if ((st = check_types(dtype, g_dtype)) != GDN2_OK) return st;
+  if (!valid_prologue(prologue)) return GDN2_ERR_UNSUPPORTED;
   if (!aligned(initial_state, 4) || !aligned(final_state, 4) || !aligned(boundaries, 4))
     return GDN2_ERR_ALIGNMENT;
   return launch_token_forward(q, k, v, g, beta, w, initial_state, out, final_state, boundaries,
-                              batch, time, heads, t_begin, t_end, dtype, g_dtype, scale,
+                              batch, time, heads, t_begin, t_end, dtype, g_dtype, scale, prologue,
                               static_cast<cudaStream_t>(stream));
+}
+
+int token_t1_zero_checked(const void* q, const void* k, const void* v, const void* w, void* out,
+                          float* final_state, int64_t batch, int64_t heads, int dtype, float scale,
+                          int prologue, void* stream) {
+  if (!q || !k || !v || !w || !out || !final_state) return GDN2_ERR_NULL_POINTER;
+  int st = check_shape(batch, 1, heads);
+  if (st != GDN2_OK) return st;
+  if (!valid_seq_dtype(dtype)) return GDN2_ERR_BAD_DTYPE;
+  if (!valid_prologue(prologue)) return GDN2_ERR_UNSUPPORTED;
+  if (!aligned(final_state, 4)) return GDN2_ERR_ALIGNMENT;
+  return launch_token_t1_zero(q, k, v, w, out, final_state, batch, heads, dtype, scale, prologue,
+                              static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+
+int gdn2_token_forward(const void* q, const void* k, const void* v, const void* g,
+                       const void* beta, const void* w, const float* initial_state, void* out,
+                       float* final_state, float* boundaries, int64_t batch, int64_t time,
+                       int64_t heads, int64_t t_begin, int64_t t_end, int dtype, int g_dtype,
+                       float scale, void* stream) {
+  return token_forward_checked(q, k, v, g, beta, w, initial_state, out, final_state, boundaries, batch, time,
+                               heads, t_begin, t_end, dtype, g_dtype, scale, 0, stream);
+}
+
+int gdn2_token_forward_fused(const void* q, const void* k, const void* v, const void* g,
+                             const void* beta, const void* w, const float* initial_state, void* out,
+                             float* final_state, int64_t batch, int64_t time, int64_t heads,
+                             int64_t t_begin, int64_t t_end, int dtype, int g_dtype, float scale,
+                             int prologue, void* stream) {
+  return token_forward_checked(q, k, v, g, beta, w, initial_state, out, final_state, nullptr, batch, time,
+                               heads, t_begin, t_end, dtype, g_dtype, scale, prologue, stream);
 }
 
 int gdn2_token_forward_t1_zero(const void* q, const void* k, const void* v, const void* w,
                                void* out, float* final_state, int64_t batch, int64_t heads,
                                int dtype, float scale, void* stream) {
-  if (!q || !k || !v || !w || !out || !final_state) return GDN2_ERR_NULL_POINTER;
-  int st = check_shape(batch, 1, heads);
-  if (st != GDN2_OK) return st;
-  if (!valid_seq_dtype(dtype)) return GDN2_ERR_BAD_DTYPE;
-  if (!aligned(final_state, 4)) return GDN2_ERR_ALIGNMENT;
-  return launch_token_t1_zero(q, k, v, w, out, final_state, batch, heads, dtype, scale,
-                              static_cast<cudaStream_t>(stream));
+  return token_t1_zero_checked(q, k, v, w, out, final_state, batch, heads, dtype, scale, 0, stream);
+}
+
+int gdn2_token_forward_t1_zero_fused(const void* q, const void* k, const void* v, const void* w,
+                                     void* out, float* final_state, int64_t batch, int64_t heads,
+                                     int dtype, float scale, int prologue, void* stream) {
+  return token_t1_zero_checked(q, k, v, w, out, final_state, batch, heads, dtype, scale, prologue, stream);
 }
 
 int gdn2_token_dstate_scan(const void* q, const void* k, const void* g, const void* beta,
@@ -263,17 +300,20 @@ int64_t gdn2_chunk_scratch_bytes(int64_t batch, int64_t full_tokens, int64_t hea
   return chunk_scratch_bytes(batch, full_tokens, heads, backward);
 }
 
-int gdn2_chunk_forward(const void* q, const void* k, const void* v, const void* g,
-                       const void* beta, const void* w, const float* initial_state, void* out,
-                       float* final_state, float* chunk_boundaries, void* workspace, void* scratch,
-                       int64_t batch, int64_t time, int64_t heads, int64_t full_tokens, int training,
-                       int dtype, int g_dtype, float scale, void* stream) {
+namespace {
+int chunk_forward_checked(const void* q, const void* k, const void* v, const void* g, const void* beta,
+                          const void* w, const float* initial_state, void* out, float* final_state,
+                          float* chunk_boundaries, void* workspace, void* scratch, int64_t batch, int64_t time,
+                          int64_t heads, int64_t full_tokens, int training, int dtype, int g_dtype, float scale,
+                          int prologue, void* stream) {
   if (!q || !k || !v || !g || !beta || !w || !out || !workspace || !scratch) return GDN2_ERR_NULL_POINTER;
   if (training && !chunk_boundaries) return GDN2_ERR_NULL_POINTER;
   int st = check_shape(batch, time, heads);
   if (st != GDN2_OK) return st;
   if (full_tokens <= 0 || full_tokens > time || full_tokens % GDN2_CHUNK != 0) return GDN2_ERR_BAD_RANGE;
   if ((st = check_types(dtype, g_dtype)) != GDN2_OK) return st;
+  // the fused prologue is a forward-only feature: backward differentiates the activated tensors
+  if (!valid_prologue(prologue) || (prologue != 0 && training)) return GDN2_ERR_UNSUPPORTED;
   const void* need16[] = {q, k, v, g, beta, w, initial_state, out, final_state, chunk_boundaries, workspace,
                           scratch};
   for (const void* ptr : need16) {
@@ -281,8 +321,28 @@ int gdn2_chunk_forward(const void* q, const void* k, const void* v, const void* 
   }
   return launch_chunk_forward(q, k, v, g, beta, w, initial_state, out, final_state, chunk_boundaries,
                               static_cast<uint8_t*>(workspace), static_cast<uint8_t*>(scratch), batch, time,
-                              heads, full_tokens, training, dtype, g_dtype, scale,
+                              heads, full_tokens, training, dtype, g_dtype, scale, prologue,
                               static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+
+int gdn2_chunk_forward(const void* q, const void* k, const void* v, const void* g,
+                       const void* beta, const void* w, const float* initial_state, void* out,
+                       float* final_state, float* chunk_boundaries, void* workspace, void* scratch,
+                       int64_t batch, int64_t time, int64_t heads, int64_t full_tokens, int training,
+                       int dtype, int g_dtype, float scale, void* stream) {
+  return chunk_forward_checked(q, k, v, g, beta, w, initial_state, out, final_state, chunk_boundaries, workspace,
+                               scratch, batch, time, heads, full_tokens, training, dtype, g_dtype, scale, 0,
+                               stream);
+}
+
+int gdn2_chunk_forward_fused(const void* q, const void* k, const void* v, const void* g,
+                             const void* beta, const void* w, const float* initial_state, void* out,
+                             float* final_state, void* workspace, void* scratch, int64_t batch, int64_t time,
+                             int64_t heads, int64_t full_tokens, int dtype, int g_dtype, float scale,
+                             int prologue, void* stream) {
+  return chunk_forward_checked(q, k, v, g, beta, w, initial_state, out, final_state, nullptr, workspace, scratch,
+                               batch, time, heads, full_tokens, 0, dtype, g_dtype, scale, prologue, stream);
 }
 
 namespace {

@@ -56,6 +56,7 @@ struct PrepSmem {
   alignas(128) uint8_t tmat[32768];    // T tile X[r = i][c = j], tf32, RS 2048 (rows 64..127 unused filler)
   float part[16][kDim];                // per 4-token group partial sums -> exclusive prefixes
   float gend[kDim];
+  float nrm[16][2][4][2];              // fused prologue: per (warp, token group, token) sums of q^2, k^2 over 64 channels
   alignas(8) uint64_t bar[2];
   uint32_t tmem_base;
 };
@@ -67,6 +68,7 @@ struct PrepParams {
   int64_t T, H, n_chunks, n_ch;
   float scale;
   int training;  // also write the transposed tiles that backward consumes
+  int prologue;  // kPrologueNorm | kPrologueGate: the inputs are raw projections / gate pre-activations
 };
 
 __device__ __forceinline__ int gram_b_offset(int I) { return kRsN * ((I == 0) ? 0 : (I == 1) ? 2 : (I == 2) ? 6 : 12); }
@@ -122,15 +124,41 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
       rv[e] = load4_raw<T>(p.v, idx);
       rw[e] = load4_raw<T>(p.w, idx);
     }
+    const bool pro_norm = (p.prologue & kPrologueNorm) != 0, pro_gate = (p.prologue & kPrologueGate) != 0;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       float gv[4];
       unpack4<G>(rg[e], gv);
 #pragma unroll
-      for (int f = 0; f < 4; ++f) Gc[e][f] = (e ? Gc[e - 1][f] : 0.f) + gv[f];
+      for (int f = 0; f < 4; ++f) {
+        if (pro_gate) gv[f] = prologue_log_decay(gv[f]);
+        Gc[e][f] = (e ? Gc[e - 1][f] : 0.f) + gv[f];
+      }
     }
 #pragma unroll
     for (int f = 0; f < 4; ++f) sm.part[tg][kc0 + f] = Gc[3][f];
+    if (pro_norm) {
+      // sums of q^2 and k^2 of this thread's four tokens over its four channels, then over the 16 lanes
+      // that hold the other channels of the same tokens in this warp (the other 64 channels are in the
+      // neighbouring warp: combined after the barrier)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float kf[4], qf[4];
+        unpack4<T>(rk[e], kf);
+        unpack4<T>(rq[e], qf);
+        float sq = qf[0] * qf[0] + qf[1] * qf[1] + qf[2] * qf[2] + qf[3] * qf[3];
+        float sk = kf[0] * kf[0] + kf[1] * kf[1] + kf[2] * kf[2] + kf[3] * kf[3];
+#pragma unroll
+        for (int off = 1; off < 16; off <<= 1) {
+          sq += __shfl_xor_sync(0xffffffffu, sq, off);
+          sk += __shfl_xor_sync(0xffffffffu, sk, off);
+        }
+        if ((lane & 15) == 0) {
+          sm.nrm[warp][lane >> 4][e][0] = sq;
+          sm.nrm[warp][lane >> 4][e][1] = sk;
+        }
+      }
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -142,6 +170,16 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
       unpack4<T>(rb[e], bb[e]);
       unpack4<T>(rv[e], vv);
       unpack4<T>(rw[e], ww);
+      if (pro_norm) {
+        const float inv_q = rsqrtf(sm.nrm[warp][lane >> 4][e][0] + sm.nrm[warp ^ 1][lane >> 4][e][0] + kPrologueEps);
+        const float inv_k = rsqrtf(sm.nrm[warp][lane >> 4][e][1] + sm.nrm[warp ^ 1][lane >> 4][e][1] + kPrologueEps);
+#pragma unroll
+        for (int f = 0; f < 4; ++f) { qq[e][f] *= inv_q; kk[e][f] *= inv_k; }
+      }
+      if (pro_gate) {
+#pragma unroll
+        for (int f = 0; f < 4; ++f) { bb[e][f] = prologue_sigmoid(bb[e][f]); ww[f] = prologue_sigmoid(ww[f]); }
+      }
 #pragma unroll
       for (int f = 0; f < 4; ++f) zz[e][f] = to_tf32(vv[f] * ww[f]);
     }
@@ -822,7 +860,7 @@ int launch_chunk_forward(const void* q, const void* k, const void* v, const void
                          const void* w, const float* s_in, void* out, float* s_out, float* bnd,
                          uint8_t* workspace, uint8_t* scratch, int64_t B, int64_t T, int64_t H,
                          int64_t full_tokens, int training, int dtype, int g_dtype, float scale,
-                         cudaStream_t stream) {
+                         int prologue, cudaStream_t stream) {
   const int64_t n_chunks = full_tokens / kChunk;
   const int64_t n_ch = B * n_chunks * H;
   if (n_ch <= 0 || n_ch > int64_t(0x7fffffff)) return GDN2_ERR_TOO_LARGE;
@@ -832,7 +870,7 @@ int launch_chunk_forward(const void* q, const void* k, const void* v, const void
   if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
 
   profile_mark(0, stream);
-  PrepParams pp{q, k, v, g, beta, w, workspace, scratch, T, H, n_chunks, n_ch, scale, training};
+  PrepParams pp{q, k, v, g, beta, w, workspace, scratch, T, H, n_chunks, n_ch, scale, training, prologue};
   GDN2_DISPATCH_TYPES(dtype, g_dtype, {
     auto kernel = chunk_prep_kernel<T, G>;
     const int smem = int(sizeof(PrepSmem));

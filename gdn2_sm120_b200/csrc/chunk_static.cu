@@ -26,7 +26,7 @@ namespace gdn2 {
 
 int launch_chunk_forward(const void*, const void*, const void*, const void*, const void*, const void*,
                          const float*, void*, float*, float*, uint8_t*, uint8_t*, int64_t, int64_t, int64_t,
-                         int64_t, int, int, int, float, cudaStream_t);
+                         int64_t, int, int, int, float, int, cudaStream_t);
 int64_t chunk_status_offset(int64_t, int64_t, int64_t);
 
 namespace {
@@ -101,7 +101,7 @@ extern "C" int gdn2_chunk_forward_static(const void* q, const void* k, const voi
   // same kernels as gdn2_chunk_forward (inference layout); the launcher clears the status word
   return launch_chunk_forward(q, k, v, g, beta, w, initial_state, out, final_state, nullptr, workspace,
                               workspace + kStaticWorkspaceBytes, batch, time, heads, full_tokens, 0, dtype,
-                              g_dtype, scale, static_cast<cudaStream_t>(stream));
+                              g_dtype, scale, 0, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int gdn2_chunk_static_read_status(void* stream) {

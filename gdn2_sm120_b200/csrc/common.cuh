@@ -62,6 +62,16 @@ __device__ __forceinline__ void store4(float* p, bool vec, const float (&x)[4]) 
   }
 }
 
+// ---- layer prologue (optional, fused into the forward kernels) ------------------------------
+// bit flags of the `prologue` argument of the *_fused entry points
+constexpr int kPrologueNorm = GDN2_PROLOGUE_NORMALIZE_QK;   // q, k are raw projections: L2-normalise them
+constexpr int kPrologueGate = GDN2_PROLOGUE_ACTIVATE_GATES; // beta, w, g are pre-activations
+constexpr float kPrologueEps = 1e-6f;
+
+__device__ __forceinline__ float prologue_sigmoid(float x) { return 1.f / (1.f + expf(-x)); }
+// log-decay g = -softplus(x); softplus(x) equals x to fp32 precision beyond 20
+__device__ __forceinline__ float prologue_log_decay(float x) { return x > 20.f ? -x : -log1pf(expf(x)); }
+
 // ---- host-side status helpers ---------------------------------------------------
 void record_cuda_error(cudaError_t err);  // defined in api.cu
 int check_launch();                       // cudaGetLastError -> status

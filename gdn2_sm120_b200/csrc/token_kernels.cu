@@ -45,6 +45,7 @@ struct TokenFwdParams {
   float* bnd;
   int64_t T, H, t_begin, t_end, n_slots;
   float scale;
+  int prologue;  // kPrologueNorm | kPrologueGate: raw projections / gate pre-activations are activated here
 };
 
 __device__ __forceinline__ float4 ld_red4(const float (*red)[kTokVT], int col) {
@@ -63,6 +64,7 @@ __global__ void __launch_bounds__(kTokThreads) token_forward_kernel(const TokenF
   __shared__ float s_a[2][kDim], s_e[2][kDim], s_k[2][kDim], s_q[2][kDim];
   __shared__ float s_z[2][kTokVT];
   __shared__ __align__(16) float s_red[2][2][4][kTokVT];  // [buffer][erase|output][warp][column]
+  __shared__ float s_nrm[2][4][2];                        // fused prologue: per warp sums of q^2, k^2
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int cg = tid & 7, rg = tid >> 3;
@@ -70,16 +72,31 @@ __global__ void __launch_bounds__(kTokThreads) token_forward_kernel(const TokenF
   const int64_t bh = blockIdx.x / kTokTiles;
   const int64_t b = bh / p.H, h = bh % p.H;
   const int col0 = vt * kTokVT + cg * 4;
+  const bool pro_norm = (p.prologue & kPrologueNorm) != 0, pro_gate = (p.prologue & kPrologueGate) != 0;
 
   auto stage = [&](int64_t t, int buf) {
     const int64_t idx = ((b * p.T + t) * p.H + h) * kDim;
     const float kv = ldf<T>(p.k, idx + tid);
-    s_a[buf][tid] = expf(ldf<G>(p.g, idx + tid));
-    s_e[buf][tid] = ldf<T>(p.beta, idx + tid) * kv;
+    float gv = ldf<G>(p.g, idx + tid), bv = ldf<T>(p.beta, idx + tid);
+    const float qv = ldf<T>(p.q, idx + tid);
+    if (pro_gate) { gv = prologue_log_decay(gv); bv = prologue_sigmoid(bv); }
+    s_a[buf][tid] = expf(gv);
+    s_e[buf][tid] = bv * kv;
     s_k[buf][tid] = kv;
-    s_q[buf][tid] = p.scale * ldf<T>(p.q, idx + tid);
+    s_q[buf][tid] = p.scale * qv;
     if (tid < kTokVT) {
-      s_z[buf][tid] = ldf<T>(p.w, idx + vt * kTokVT + tid) * ldf<T>(p.v, idx + vt * kTokVT + tid);
+      float wv = ldf<T>(p.w, idx + vt * kTokVT + tid);
+      if (pro_gate) wv = prologue_sigmoid(wv);
+      s_z[buf][tid] = wv * ldf<T>(p.v, idx + vt * kTokVT + tid);
+    }
+    if (pro_norm) {
+      float sq = qv * qv, sk = kv * kv;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        sq += __shfl_xor_sync(0xffffffffu, sq, off);
+        sk += __shfl_xor_sync(0xffffffffu, sk, off);
+      }
+      if (lane == 0) { s_nrm[buf][warp][0] = sq; s_nrm[buf][warp][1] = sk; }
     }
   };
 
@@ -111,11 +128,17 @@ __global__ void __launch_bounds__(kTokThreads) token_forward_kernel(const TokenF
     if (p.bnd != nullptr && (rel % kTokenInterval) == 0) {
       store_tile(p.bnd + ((b * p.n_slots + rel / kTokenInterval) * p.H + h) * kStateElems);
     }
+    // reciprocal norms of this token's raw q and k (1 when the inputs are already normalised)
+    float iq = 1.f, ik = 1.f;
+    if (pro_norm) {
+      iq = rsqrtf(s_nrm[buf][0][0] + s_nrm[buf][1][0] + s_nrm[buf][2][0] + s_nrm[buf][3][0] + kPrologueEps);
+      ik = rsqrtf(s_nrm[buf][0][1] + s_nrm[buf][1][1] + s_nrm[buf][2][1] + s_nrm[buf][3][1] + kPrologueEps);
+    }
     // X = a * S ; partial r = X^T e over this thread's rows
     float r[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < kRowsPerThread; ++i) {
-      const float a = s_a[buf][rg + 16 * i], e = s_e[buf][rg + 16 * i];
+      const float a = s_a[buf][rg + 16 * i], e = s_e[buf][rg + 16 * i] * ik;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         S[i][c] *= a;
@@ -140,7 +163,7 @@ __global__ void __launch_bounds__(kTokThreads) token_forward_kernel(const TokenF
     float o[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < kRowsPerThread; ++i) {
-      const float kv = s_k[buf][rg + 16 * i], qv = s_q[buf][rg + 16 * i];
+      const float kv = s_k[buf][rg + 16 * i] * ik, qv = s_q[buf][rg + 16 * i] * iq;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         S[i][c] = fmaf(kv, u[c], S[i][c]);
@@ -186,6 +209,7 @@ struct DecodeSmem {
   alignas(16) float ae[2][kDim], a[2][kDim], kk[2][kDim], qs[2][kDim], z[2][kDim];
   float red[2][2][kDim];   // [parity][key half][column]  erase partial sums
   float redo[2][2][kDim];  //                             output partial sums
+  float nrm[2][4][2];      // fused prologue: [parity][warp of the key half][q | k] sums of squares
   alignas(8) uint64_t full[kDecStages];
 };
 
@@ -196,6 +220,7 @@ struct DecodeParams {
   float* s_out;
   int64_t n_heads;  // batch * heads; T == 1 so sequence row index == head index
   float scale;
+  int prologue;     // kPrologueNorm | kPrologueGate
 };
 
 template <typename T, typename G>
@@ -230,14 +255,26 @@ __global__ void __launch_bounds__(kDecThreads, 1) token_decode_ring_kernel(const
       va = ldf<T>(p.w, idx); vb = ldf<T>(p.v, idx);
     }
   };
+  const bool pro_norm = (p.prologue & kPrologueNorm) != 0, pro_gate = (p.prologue & kPrologueGate) != 0;
   auto stage_vectors = [&](int buf) {
     if (kh == 0) {
+      if (pro_gate) { va = prologue_log_decay(va); vb = prologue_sigmoid(vb); }
       const float av = expf(va);
       sm.a[buf][col] = av;
       sm.ae[buf][col] = av * (vb * vc);
       sm.kk[buf][col] = vc;
       sm.qs[buf][col] = p.scale * vd;
+      if (pro_norm) {  // warps 0..3 hold the 128 key channels
+        float sq = vd * vd, sk = vc * vc;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+          sq += __shfl_xor_sync(0xffffffffu, sq, off);
+          sk += __shfl_xor_sync(0xffffffffu, sk, off);
+        }
+        if ((tid & 31) == 0) { sm.nrm[buf][tid >> 5][0] = sq; sm.nrm[buf][tid >> 5][1] = sk; }
+      }
     } else {
+      if (pro_gate) va = prologue_sigmoid(va);
       sm.z[buf][col] = va * vb;
     }
   };
@@ -281,7 +318,13 @@ __global__ void __launch_bounds__(kDecThreads, 1) token_decode_ring_kernel(const
     }
     // a copy that never arrived, for any thread: the head's results are marked invalid for all
     dead = __syncthreads_or(dead ? 1 : 0) != 0;
-    const float u = sm.z[buf][col] - (sm.red[buf][0][col] + sm.red[buf][1][col]);
+    // raw q / k: the erase sum is linear in k, the output in q, so the reciprocal norms scale the sums
+    float iq = 1.f, ik = 1.f;
+    if (pro_norm) {
+      iq = rsqrtf(sm.nrm[buf][0][0] + sm.nrm[buf][1][0] + sm.nrm[buf][2][0] + sm.nrm[buf][3][0] + kPrologueEps);
+      ik = rsqrtf(sm.nrm[buf][0][1] + sm.nrm[buf][1][1] + sm.nrm[buf][2][1] + sm.nrm[buf][3][1] + kPrologueEps);
+    }
+    const float u = (sm.z[buf][col] - ik * (sm.red[buf][0][col] + sm.red[buf][1][col])) * ik;  // u * ik: S += (k ik) u
     // pass 2: S <- a S + k u^T ; o[v] = sum_k S[k][v] (scale q[k])
     float o = 0.f;
 #pragma unroll 4
@@ -308,7 +351,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) token_decode_ring_kernel(const
       tc::bulk_commit();
     }
     if (kh == 0) {
-      float ov = sm.redo[buf][0][col] + sm.redo[buf][1][col];
+      float ov = iq * (sm.redo[buf][0][col] + sm.redo[buf][1][col]);
       if (dead) ov = __int_as_float(0x7fc00000);  // a bulk copy never arrived: make the failure visible
       stf<T>(p.out, bh * kDim + col, ov);
     }
@@ -323,6 +366,7 @@ struct T1ZeroParams {
   float* s_out;
   int64_t H;
   float scale;
+  int prologue;
 };
 
 template <typename T>
@@ -330,23 +374,45 @@ __global__ void __launch_bounds__(kTokThreads) token_t1_zero_kernel(const T1Zero
   __shared__ float s_k[kDim];
   __shared__ float s_z[kTokVT];
   __shared__ float s_part[4];
+  __shared__ float s_nrm[4][2];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int cg = tid & 7, rg = tid >> 3;
   const int vt = int(blockIdx.x % kTokTiles);
   const int64_t bh = blockIdx.x / kTokTiles;
   const int64_t idx = bh * kDim;  // T == 1: [B, 1, H, 128]
 
+  const bool pro_norm = (p.prologue & kPrologueNorm) != 0, pro_gate = (p.prologue & kPrologueGate) != 0;
   const float kv = ldf<T>(p.k, idx + tid);
-  s_k[tid] = kv;
-  float qk = p.scale * ldf<T>(p.q, idx + tid) * kv;
+  const float qv = ldf<T>(p.q, idx + tid);
+  float qk = p.scale * qv * kv;
   if (tid < kTokVT) {
-    s_z[tid] = ldf<T>(p.w, idx + vt * kTokVT + tid) * ldf<T>(p.v, idx + vt * kTokVT + tid);
+    float wv = ldf<T>(p.w, idx + vt * kTokVT + tid);
+    if (pro_gate) wv = prologue_sigmoid(wv);
+    s_z[tid] = wv * ldf<T>(p.v, idx + vt * kTokVT + tid);
   }
+  float sq = qv * qv, sk = kv * kv;
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) qk += __shfl_xor_sync(0xffffffffu, qk, off);
-  if (lane == 0) s_part[warp] = qk;
+  for (int off = 16; off > 0; off >>= 1) {
+    qk += __shfl_xor_sync(0xffffffffu, qk, off);
+    if (pro_norm) {
+      sq += __shfl_xor_sync(0xffffffffu, sq, off);
+      sk += __shfl_xor_sync(0xffffffffu, sk, off);
+    }
+  }
+  if (lane == 0) {
+    s_part[warp] = qk;
+    s_nrm[warp][0] = sq;
+    s_nrm[warp][1] = sk;
+  }
+  if (!pro_norm) s_k[tid] = kv;
   __syncthreads();
   qk = s_part[0] + s_part[1] + s_part[2] + s_part[3];
+  if (pro_norm) {  // raw q, k: scale by the reciprocal norms
+    const float ik = rsqrtf(s_nrm[0][1] + s_nrm[1][1] + s_nrm[2][1] + s_nrm[3][1] + kPrologueEps);
+    qk *= ik * rsqrtf(s_nrm[0][0] + s_nrm[1][0] + s_nrm[2][0] + s_nrm[3][0] + kPrologueEps);
+    s_k[tid] = kv * ik;
+    __syncthreads();
+  }
 
   float z[4];
 #pragma unroll
@@ -662,7 +728,7 @@ int launch_token_forward(const void* q, const void* k, const void* v, const void
                          const void* beta, const void* w, const float* s_in, void* out,
                          float* s_out, float* bnd, int64_t B, int64_t T, int64_t H,
                          int64_t t_begin, int64_t t_end, int dtype, int g_dtype, float scale,
-                         cudaStream_t stream) {
+                         int prologue, cudaStream_t stream) {
   const int64_t blocks = B * H * kTokTiles;
   if (!grid_fits(blocks)) return GDN2_ERR_TOO_LARGE;
   // decode fast path: one token, state in and out, 16-byte aligned, enough heads to fill the GPU
@@ -673,7 +739,7 @@ int launch_token_forward(const void* q, const void* k, const void* v, const void
     cudaError_t err = cudaGetDevice(&dev);
     if (err == cudaSuccess) err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
-    DecodeParams dp{q, k, v, g, beta, w, s_in, out, s_out, B * H, scale};
+    DecodeParams dp{q, k, v, g, beta, w, s_in, out, s_out, B * H, scale, prologue};
     const int smem = int(sizeof(DecodeSmem));
     const unsigned grid = unsigned(B * H < sms ? B * H : sms);
     GDN2_DISPATCH_TYPES(dtype, g_dtype, {
@@ -685,18 +751,18 @@ int launch_token_forward(const void* q, const void* k, const void* v, const void
     return check_launch();
   }
   TokenFwdParams p{q, k, v, g, beta, w, s_in, out, s_out, bnd,
-                   T, H, t_begin, t_end, slots_for(t_begin, t_end), scale};
+                   T, H, t_begin, t_end, slots_for(t_begin, t_end), scale, prologue};
   GDN2_DISPATCH_TYPES(dtype, g_dtype,
                       (token_forward_kernel<T, G><<<unsigned(blocks), kTokThreads, 0, stream>>>(p)));
   return check_launch();
 }
 
 int launch_token_t1_zero(const void* q, const void* k, const void* v, const void* w, void* out,
-                         float* s_out, int64_t B, int64_t H, int dtype, float scale,
+                         float* s_out, int64_t B, int64_t H, int dtype, float scale, int prologue,
                          cudaStream_t stream) {
   const int64_t blocks = B * H * kTokTiles;
   if (!grid_fits(blocks)) return GDN2_ERR_TOO_LARGE;
-  T1ZeroParams p{q, k, v, w, out, s_out, H, scale};
+  T1ZeroParams p{q, k, v, w, out, s_out, H, scale, prologue};
   if (dtype == GDN2_BF16) {
     token_t1_zero_kernel<__nv_bfloat16><<<unsigned(blocks), kTokThreads, 0, stream>>>(p);
   } else {

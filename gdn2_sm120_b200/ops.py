@@ -24,6 +24,12 @@ _CHUNK_SIZE = 64
 _PARALLEL_BACKWARD_MIN_TOKENS = 64
 
 
+def _prologue_flags(normalize_qk: bool, activate_gates: bool) -> int:
+    """Bit flags of the fused prologue (GDN2_PROLOGUE_NORMALIZE_QK = 1, GDN2_PROLOGUE_ACTIVATE_GATES = 2)."""
+
+    return (1 if normalize_qk else 0) | (2 if activate_gates else 0)
+
+
 def _use_compact_wy_backward(batch: int, time: int, heads: int) -> bool:
     """True when backward runs the tensor-core compact-WY chunk VJP for the leading
     full chunks (reference selector: src/gdn2_sm120/ops.py:22-28).
@@ -158,29 +164,33 @@ def chunk_gdn2(
     non-positive with every 16-token prefix sum above ln(FLT_MIN).  With
     ``use_qk_l2norm_in_kernel`` q and k are the raw projections and are L2-normalised first; with
     ``use_gate_in_kernel`` beta, w and g are pre-activations (beta = sigmoid, w = sigmoid,
-    g = -softplus); both run as one fused kernel in front of the primitive and one behind its
-    backward (``prologue.gate_prologue``).  Returns ``(o, S_T)`` or ``(o, None)``.
+    g = -softplus).  Without gradients the forward kernels apply both themselves as they load the
+    inputs; a call that needs gradients runs them as one fused kernel in front of the primitive
+    and one behind its backward (``prologue.gate_prologue``).  Returns ``(o, S_T)`` or ``(o, None)``.
     """
 
     output_scale = float(scale) if scale is not None else 1.0 / math.sqrt(_DIM)
     if not math.isfinite(output_scale):
         raise ValueError("scale must be finite")
-    if use_qk_l2norm_in_kernel or use_gate_in_kernel:
-        q, k, g, beta, w = gate_prologue(q, k, g, beta, w, normalize_qk=use_qk_l2norm_in_kernel,
-                                         activate_gates=use_gate_in_kernel)
     wants_grad = torch.is_grad_enabled() and any(
         isinstance(t, torch.Tensor) and t.requires_grad for t in (q, k, v, g, beta, w, initial_state)
     )
     if wants_grad:
+        # training: the activated tensors are what backward differentiates, so they are materialised
+        if use_qk_l2norm_in_kernel or use_gate_in_kernel:
+            q, k, g, beta, w = gate_prologue(q, k, g, beta, w, normalize_qk=use_qk_l2norm_in_kernel,
+                                             activate_gates=use_gate_in_kernel)
         output, final_state = _ChunkGDN2.apply(q, k, v, g, beta, w, initial_state, output_scale, True)
         return output, final_state if output_final_state else None
 
+    # inference: the forward kernels apply the prologue themselves
+    prologue = _prologue_flags(use_qk_l2norm_in_kernel, use_gate_in_kernel)
     seq = tuple(_validate.detached(x) for x in (q, k, v, g, beta, w))
     state = _validate.detached(initial_state)
     if _use_recurrent_kernel(q.shape[0], q.shape[1], q.shape[2], chunk_api=True):
-        output, final_state = token_forward(*seq, state, scale=output_scale)
+        output, final_state = token_forward(*seq, state, scale=output_scale, prologue=prologue)
     else:
-        output, final_state = chunk_forward(*seq, state, scale=output_scale, return_aux=False)
+        output, final_state = chunk_forward(*seq, state, scale=output_scale, return_aux=False, prologue=prologue)
     return output, final_state if output_final_state else None
 
 
@@ -202,16 +212,12 @@ def recurrent_gdn2(
 ) -> tuple[torch.Tensor, torch.Tensor]:
     """Forward-only GDN2 for serving, with the recurrent/chunk crossover.
 
-    The two ``use_*_in_kernel`` keywords (default off) send raw projections / gate pre-activations
-    through the fused prologue kernel first, as in ``chunk_gdn2``."""
-
-    if use_qk_l2norm_in_kernel or use_gate_in_kernel:
-        with torch.no_grad():
-            q, k, g, beta, w = gate_prologue(q, k, g, beta, w, normalize_qk=use_qk_l2norm_in_kernel,
-                                             activate_gates=use_gate_in_kernel)
+    With the two ``use_*_in_kernel`` keywords (default off) the inputs are raw projections / gate
+    pre-activations and the decode and prefill kernels apply the prologue as they load them."""
 
     return token_forward(q, k, v, g, beta, w, initial_state, scale=scale, out=out,
-                         final_state_out=final_state_out, inplace_final_state=inplace_final_state)
+                         final_state_out=final_state_out, inplace_final_state=inplace_final_state,
+                         prologue=_prologue_flags(use_qk_l2norm_in_kernel, use_gate_in_kernel))
 
 
 __all__ = ["chunk_gdn2", "recurrent_gdn2"]

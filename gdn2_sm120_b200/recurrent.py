@@ -53,7 +53,18 @@ _spans_overlap = _validate.spans_overlap
 
 
 def _launch_token_forward(q, k, v, g, beta, w, initial_state, output, final_state, boundaries,
-                          batch, time, heads, t_begin, t_end, scale) -> None:
+                          batch, time, heads, t_begin, t_end, scale, prologue: int = 0) -> None:
+    if prologue:
+        if boundaries is not None:
+            raise ValueError("the fused prologue is forward-only: no checkpoints")
+        _lib.call(
+            "gdn2_token_forward_fused", q.device,
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), w.data_ptr(),
+            _lib.ptr(initial_state), output.data_ptr(), _lib.ptr(final_state),
+            batch, time, heads, t_begin, t_end,
+            _lib.dtype_code(q.dtype), _lib.dtype_code(g.dtype), scale, prologue, _lib.stream_ptr(q.device),
+        )
+        return
     _lib.call(
         "gdn2_token_forward", q.device,
         q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), beta.data_ptr(), w.data_ptr(),
@@ -63,7 +74,15 @@ def _launch_token_forward(q, k, v, g, beta, w, initial_state, output, final_stat
     )
 
 
-def _launch_t1_zero(q, k, v, w, output, final_state, batch, heads, scale) -> None:
+def _launch_t1_zero(q, k, v, w, output, final_state, batch, heads, scale, prologue: int = 0) -> None:
+    if prologue:
+        _lib.call(
+            "gdn2_token_forward_t1_zero_fused", q.device,
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), output.data_ptr(),
+            final_state.data_ptr(), batch, heads, _lib.dtype_code(q.dtype), scale, prologue,
+            _lib.stream_ptr(q.device),
+        )
+        return
     _lib.call(
         "gdn2_token_forward_t1_zero", q.device,
         q.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), output.data_ptr(),
@@ -85,8 +104,12 @@ def token_forward(
     out: torch.Tensor | None = None,
     final_state_out: torch.Tensor | None = None,
     inplace_final_state: bool = False,
+    prologue: int = 0,
 ) -> tuple[torch.Tensor, torch.Tensor]:
     """Evaluate the GDN2 recurrence; returns ``(output, final_state)``.
+
+    ``prologue`` (not part of the reference's signature; bit 0 = L2-normalise raw q / k, bit 1 =
+    activate raw beta / w / g) makes the forward kernels apply a layer's input prologue themselves.
 
     Inputs are contiguous ``[B, T, H, 128]``; q/k/v/beta/w fp16 or bf16, ``g`` the same
     type or fp32; ``initial_state`` optional fp32 ``[B, H, 128, 128]``.  By default fresh
@@ -153,13 +176,13 @@ def token_forward(
         from .chunk import chunk_forward  # lazy: decode never pays for the chunk module
 
         return chunk_forward(q, k, v, g, beta, w, initial_state, scale=output_scale,
-                             out=output, final_state_out=final_state)
+                             out=output, final_state_out=final_state, prologue=prologue)
 
     if time == 1 and initial_state is None:
-        _launch_t1_zero(q, k, v, w, output, final_state, batch, heads, output_scale)
+        _launch_t1_zero(q, k, v, w, output, final_state, batch, heads, output_scale, prologue)
     else:
         _launch_token_forward(q, k, v, g, beta, w, initial_state, output, final_state, None,
-                              batch, time, heads, 0, time, output_scale)
+                              batch, time, heads, 0, time, output_scale, prologue)
     return output, final_state
 
 

@@ -45,6 +45,10 @@ typedef enum gdn2_dtype {
   GDN2_FP32 = 2 /* only valid for g_dtype */
 } gdn2_dtype;
 
+/* bit flags of the `prologue` argument of the *_fused forward entry points */
+#define GDN2_PROLOGUE_NORMALIZE_QK 1   /* q, k are raw projections: q / sqrt(sum q^2 + 1e-6), k likewise */
+#define GDN2_PROLOGUE_ACTIVATE_GATES 2 /* beta, w, g are pre-activations: sigmoid, sigmoid, -softplus */
+
 typedef enum gdn2_status {
   GDN2_OK = 0,
   GDN2_ERR_NULL_POINTER = -1,
@@ -266,6 +270,31 @@ int gdn2_gate_prologue(const void* q_raw, const void* k_raw, const void* g_raw, 
                        const void* w_raw, void* q, void* k, void* g, void* beta, void* w,
                        float* inv_norm_q, float* inv_norm_k,
                        int64_t batch, int64_t time, int64_t heads, int dtype, int g_dtype, void* stream);
+
+/*
+ * Forward entry points with the prologue fused in: the kernels activate the raw tensors as they load
+ * them (gate flags) and scale by the reciprocal row norms they compute on the way (normalisation
+ * flag), so an inference call never materialises the activated tensors.  `prologue` is a
+ * combination of GDN2_PROLOGUE_NORMALIZE_QK and GDN2_PROLOGUE_ACTIVATE_GATES (0 = exactly the
+ * plain entry point).  Forward only -- a training call activates with gdn2_gate_prologue, whose
+ * outputs backward needs anyway -- hence no checkpoint arguments.  Otherwise as
+ * gdn2_token_forward / gdn2_token_forward_t1_zero / gdn2_chunk_forward.  Same counterpart in the
+ * official API as gdn2_gate_prologue (use_qk_l2norm_in_kernel / use_gate_in_kernel).
+ */
+int gdn2_token_forward_fused(const void* q, const void* k, const void* v, const void* g,
+                             const void* beta, const void* w, const float* initial_state,
+                             void* out, float* final_state,
+                             int64_t batch, int64_t time, int64_t heads,
+                             int64_t t_begin, int64_t t_end,
+                             int dtype, int g_dtype, float scale, int prologue, void* stream);
+int gdn2_token_forward_t1_zero_fused(const void* q, const void* k, const void* v, const void* w,
+                                     void* out, float* final_state, int64_t batch, int64_t heads,
+                                     int dtype, float scale, int prologue, void* stream);
+int gdn2_chunk_forward_fused(const void* q, const void* k, const void* v, const void* g,
+                             const void* beta, const void* w, const float* initial_state,
+                             void* out, float* final_state, void* workspace, void* scratch,
+                             int64_t batch, int64_t time, int64_t heads, int64_t full_tokens,
+                             int dtype, int g_dtype, float scale, int prologue, void* stream);
 
 /*
  * VJP of gdn2_gate_prologue: from the raw inputs, the stored reciprocal norms and the cotangents of

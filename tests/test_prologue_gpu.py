@@ -83,15 +83,75 @@ def test_fused_flags_forward_and_backward_against_oracle(time, normalize_qk, act
         assert err < limit, f"{name}: {err:.3e}"
 
 
+def _exact_reference(cpu, normalize_qk, activate_gates, scale=None):
+    """Recurrence on the exactly activated (un-rounded, float64) tensors: what the in-kernel prologue of
+    the forward kernels approximates in fp32."""
+
+    q, k, v, g, beta, w, s0 = cpu
+    qa, ka, ga, ba, wa = oracle.gate_prologue(q, k, g, beta, w, normalize_qk=normalize_qk,
+                                              activate_gates=activate_gates)
+    return oracle.recurrence(qa, ka, v.double(), ga, ba, wa, None if s0 is None else s0.double(), scale=scale)
+
+
+@pytest.mark.parametrize("time", [1, 19, 64, 200])
+@pytest.mark.parametrize("normalize_qk,activate_gates", [(True, True), (True, False), (False, True)])
+def test_inference_applies_the_prologue_inside_the_forward_kernels(time, normalize_qk, activate_gates):
+    """Without gradients no activated tensor is materialised: the prep kernel (full chunks), the token
+    kernel (short sequences and the ragged tail) apply the flags as they load the raw inputs."""
+
+    raw = list(oracle.make_raw_inputs(2, time, 3, seed=300 + time))
+    if not normalize_qk:
+        act = oracle.gate_prologue(*[raw[i] for i in (0, 1, 3, 4, 5)], activate_gates=False)
+        raw[0], raw[1] = act[0].to(torch.bfloat16), act[1].to(torch.bfloat16)
+    if not activate_gates:
+        act = oracle.gate_prologue(*[raw[i] for i in (0, 1, 3, 4, 5)], normalize_qk=False)
+        raw[3], raw[4], raw[5] = act[2].float(), act[3].to(torch.bfloat16), act[4].to(torch.bfloat16)
+    ref_out, ref_fin = _exact_reference(raw, normalize_qk, activate_gates)
+    args = [t.to(DEV) for t in raw]
+    from gdn2_sm120_b200 import _lib
+    _lib.KERNEL_EVENTS = {}
+    try:
+        with torch.no_grad():
+            out, fin = chunk_gdn2(*args[:6], args[6], output_final_state=True,
+                                  use_qk_l2norm_in_kernel=normalize_qk, use_gate_in_kernel=activate_gates)
+        called = set(_lib.KERNEL_EVENTS)
+    finally:
+        _lib.KERNEL_EVENTS = None
+    assert "gdn2_gate_prologue" not in called and any(name.endswith("_fused") for name in called)
+    torch.testing.assert_close(out.float().cpu(), ref_out.float(), rtol=2e-2, atol=1e-2)
+    assert oracle.rel_l2(fin, ref_fin) < (1e-3 if time >= 64 else 1e-5)
+
+
+@pytest.mark.parametrize("with_state", [True, False])
+def test_decode_kernels_apply_the_prologue(with_state):
+    """T = 1 with 288 heads: the persistent decode kernel (with a state) and the closed form (without)."""
+
+    raw = list(oracle.make_raw_inputs(9, 1, 32, seed=91))
+    if not with_state:
+        raw[6] = None
+    ref_out, ref_fin = _exact_reference(raw, True, True, scale=0.2)
+    args = [None if t is None else t.to(DEV) for t in raw]
+    out, fin = recurrent_gdn2(*args[:6], args[6], scale=0.2, use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True)
+    torch.testing.assert_close(out.float().cpu(), ref_out.float(), rtol=2e-3, atol=2e-3)
+    assert oracle.rel_l2(fin, ref_fin) < 1e-5
+    # the flags off: bit-identical to the plain entry points (the fused kernels are the same kernels)
+    plain = [t.to(DEV) for t in oracle.make_inputs(9, 1, 32, seed=92)]
+    a = recurrent_gdn2(*plain[:6], plain[6] if with_state else None)
+    from gdn2_sm120_b200.recurrent import token_forward
+    b = token_forward(*plain[:6], plain[6] if with_state else None, prologue=0)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
 def test_recurrent_api_accepts_the_flags():
     cpu = oracle.make_raw_inputs(2, 1, 3, seed=77)
-    q, k, v, g, beta, w, s0 = cpu
-    act, ref_out, ref_fin, _ = _reference(cpu, None, None, True, True)
+    ref_out, ref_fin = _exact_reference(cpu, True, True)
     args = [t.to(DEV) for t in cpu]
     out, fin = recurrent_gdn2(*args[:6], args[6], use_qk_l2norm_in_kernel=True, use_gate_in_kernel=True)
     torch.testing.assert_close(out.float().cpu(), ref_out.to(out.dtype).float(), rtol=2e-3, atol=2e-3)
     assert oracle.rel_l2(fin, ref_fin) < 1e-5
-    # identical to calling the prologue by hand
+    # the materialising route (prologue kernel, then the plain operator) agrees within the rounding of
+    # the activated tensors to the sequence dtype
     qa, ka, ga, ba, wa = gate_prologue(args[0], args[1], args[3], args[4], args[5])
     out2, fin2 = recurrent_gdn2(qa, ka, args[2], ga, ba, wa, args[6])
-    assert torch.equal(out, out2) and torch.equal(fin, fin2)
+    torch.testing.assert_close(out.float(), out2.float(), rtol=2e-2, atol=1e-2)
+    assert oracle.rel_l2(fin, fin2) < 5e-3
