@@ -74,7 +74,9 @@ struct PrepParams {
 __device__ __forceinline__ int gram_b_offset(int I) { return kRsN * ((I == 0) ? 0 : (I == 1) ? 2 : (I == 2) ? 6 : 12); }
 __device__ __forceinline__ int gram_col(int I) { return (I == 0) ? 0 : (I == 1) ? 16 : (I == 2) ? 48 : 96; }
 
-template <typename T, typename G>
+// kPro: the instantiation that can apply the layer prologue to raw inputs (p.prologue says which parts);
+// the plain instantiation carries none of that code.
+template <typename T, typename G, bool kPro = false>
 __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   PrepSmem& sm = *reinterpret_cast<PrepSmem*>(smem_raw);
@@ -124,7 +126,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
       rv[e] = load4_raw<T>(p.v, idx);
       rw[e] = load4_raw<T>(p.w, idx);
     }
-    const bool pro_norm = (p.prologue & kPrologueNorm) != 0, pro_gate = (p.prologue & kPrologueGate) != 0;
+    const bool pro_norm = kPro && (p.prologue & kPrologueNorm) != 0;
+    const bool pro_gate = kPro && (p.prologue & kPrologueGate) != 0;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       float gv[4];
@@ -872,7 +875,7 @@ int launch_chunk_forward(const void* q, const void* k, const void* v, const void
   profile_mark(0, stream);
   PrepParams pp{q, k, v, g, beta, w, workspace, scratch, T, H, n_chunks, n_ch, scale, training, prologue};
   GDN2_DISPATCH_TYPES(dtype, g_dtype, {
-    auto kernel = chunk_prep_kernel<T, G>;
+    auto kernel = prologue != 0 ? chunk_prep_kernel<T, G, true> : chunk_prep_kernel<T, G, false>;
     const int smem = int(sizeof(PrepSmem));
     err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }

@@ -59,7 +59,9 @@ __device__ __forceinline__ float4 ld_red4(const float (*red)[kTokVT], int col) {
   return s;
 }
 
-template <typename T, typename G>
+// kPro (here and in the two decode kernels below): the instantiation that can apply the layer prologue
+// to raw inputs; the plain instantiation carries none of that code.
+template <typename T, typename G, bool kPro = false>
 __global__ void __launch_bounds__(kTokThreads) token_forward_kernel(const TokenFwdParams p) {
   __shared__ float s_a[2][kDim], s_e[2][kDim], s_k[2][kDim], s_q[2][kDim];
   __shared__ float s_z[2][kTokVT];
@@ -72,7 +74,8 @@ __global__ void __launch_bounds__(kTokThreads) token_forward_kernel(const TokenF
   const int64_t bh = blockIdx.x / kTokTiles;
   const int64_t b = bh / p.H, h = bh % p.H;
   const int col0 = vt * kTokVT + cg * 4;
-  const bool pro_norm = (p.prologue & kPrologueNorm) != 0, pro_gate = (p.prologue & kPrologueGate) != 0;
+  const bool pro_norm = kPro && (p.prologue & kPrologueNorm) != 0;
+  const bool pro_gate = kPro && (p.prologue & kPrologueGate) != 0;
 
   auto stage = [&](int64_t t, int buf) {
     const int64_t idx = ((b * p.T + t) * p.H + h) * kDim;
@@ -138,7 +141,7 @@ __global__ void __launch_bounds__(kTokThreads) token_forward_kernel(const TokenF
     float r[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < kRowsPerThread; ++i) {
-      const float a = s_a[buf][rg + 16 * i], e = s_e[buf][rg + 16 * i] * ik;
+      const float a = s_a[buf][rg + 16 * i], e = kPro ? s_e[buf][rg + 16 * i] * ik : s_e[buf][rg + 16 * i];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         S[i][c] *= a;
@@ -163,7 +166,8 @@ __global__ void __launch_bounds__(kTokThreads) token_forward_kernel(const TokenF
     float o[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < kRowsPerThread; ++i) {
-      const float kv = s_k[buf][rg + 16 * i] * ik, qv = s_q[buf][rg + 16 * i] * iq;
+      const float kv = kPro ? s_k[buf][rg + 16 * i] * ik : s_k[buf][rg + 16 * i];
+      const float qv = kPro ? s_q[buf][rg + 16 * i] * iq : s_q[buf][rg + 16 * i];
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         S[i][c] = fmaf(kv, u[c], S[i][c]);
@@ -223,7 +227,7 @@ struct DecodeParams {
   int prologue;     // kPrologueNorm | kPrologueGate
 };
 
-template <typename T, typename G>
+template <typename T, typename G, bool kPro = false>
 __global__ void __launch_bounds__(kDecThreads, 1) token_decode_ring_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) unsigned char dec_smem_raw[];
   DecodeSmem& sm = *reinterpret_cast<DecodeSmem*>(dec_smem_raw);
@@ -255,7 +259,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) token_decode_ring_kernel(const
       va = ldf<T>(p.w, idx); vb = ldf<T>(p.v, idx);
     }
   };
-  const bool pro_norm = (p.prologue & kPrologueNorm) != 0, pro_gate = (p.prologue & kPrologueGate) != 0;
+  const bool pro_norm = kPro && (p.prologue & kPrologueNorm) != 0;
+  const bool pro_gate = kPro && (p.prologue & kPrologueGate) != 0;
   auto stage_vectors = [&](int buf) {
     if (kh == 0) {
       if (pro_gate) { va = prologue_log_decay(va); vb = prologue_sigmoid(vb); }
@@ -324,7 +329,9 @@ __global__ void __launch_bounds__(kDecThreads, 1) token_decode_ring_kernel(const
       iq = rsqrtf(sm.nrm[buf][0][0] + sm.nrm[buf][1][0] + sm.nrm[buf][2][0] + sm.nrm[buf][3][0] + kPrologueEps);
       ik = rsqrtf(sm.nrm[buf][0][1] + sm.nrm[buf][1][1] + sm.nrm[buf][2][1] + sm.nrm[buf][3][1] + kPrologueEps);
     }
-    const float u = (sm.z[buf][col] - ik * (sm.red[buf][0][col] + sm.red[buf][1][col])) * ik;  // u * ik: S += (k ik) u
+    const float r_sum = sm.red[buf][0][col] + sm.red[buf][1][col];
+    const float u = kPro ? (sm.z[buf][col] - ik * r_sum) * ik  // u * ik: S += (k ik) u
+                         : sm.z[buf][col] - r_sum;
     // pass 2: S <- a S + k u^T ; o[v] = sum_k S[k][v] (scale q[k])
     float o = 0.f;
 #pragma unroll 4
@@ -351,7 +358,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) token_decode_ring_kernel(const
       tc::bulk_commit();
     }
     if (kh == 0) {
-      float ov = iq * (sm.redo[buf][0][col] + sm.redo[buf][1][col]);
+      float ov = sm.redo[buf][0][col] + sm.redo[buf][1][col];
+      if (kPro) ov *= iq;
       if (dead) ov = __int_as_float(0x7fc00000);  // a bulk copy never arrived: make the failure visible
       stf<T>(p.out, bh * kDim + col, ov);
     }
@@ -369,7 +377,7 @@ struct T1ZeroParams {
   int prologue;
 };
 
-template <typename T>
+template <typename T, bool kPro = false>
 __global__ void __launch_bounds__(kTokThreads) token_t1_zero_kernel(const T1ZeroParams p) {
   __shared__ float s_k[kDim];
   __shared__ float s_z[kTokVT];
@@ -381,7 +389,8 @@ __global__ void __launch_bounds__(kTokThreads) token_t1_zero_kernel(const T1Zero
   const int64_t bh = blockIdx.x / kTokTiles;
   const int64_t idx = bh * kDim;  // T == 1: [B, 1, H, 128]
 
-  const bool pro_norm = (p.prologue & kPrologueNorm) != 0, pro_gate = (p.prologue & kPrologueGate) != 0;
+  const bool pro_norm = kPro && (p.prologue & kPrologueNorm) != 0;
+  const bool pro_gate = kPro && (p.prologue & kPrologueGate) != 0;
   const float kv = ldf<T>(p.k, idx + tid);
   const float qv = ldf<T>(p.q, idx + tid);
   float qk = p.scale * qv * kv;
@@ -743,7 +752,7 @@ int launch_token_forward(const void* q, const void* k, const void* v, const void
     const int smem = int(sizeof(DecodeSmem));
     const unsigned grid = unsigned(B * H < sms ? B * H : sms);
     GDN2_DISPATCH_TYPES(dtype, g_dtype, {
-      auto kernel = token_decode_ring_kernel<T, G>;
+      auto kernel = prologue != 0 ? token_decode_ring_kernel<T, G, true> : token_decode_ring_kernel<T, G, false>;
       err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
       if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
       kernel<<<grid, kDecThreads, smem, stream>>>(dp);
@@ -752,8 +761,10 @@ int launch_token_forward(const void* q, const void* k, const void* v, const void
   }
   TokenFwdParams p{q, k, v, g, beta, w, s_in, out, s_out, bnd,
                    T, H, t_begin, t_end, slots_for(t_begin, t_end), scale, prologue};
-  GDN2_DISPATCH_TYPES(dtype, g_dtype,
-                      (token_forward_kernel<T, G><<<unsigned(blocks), kTokThreads, 0, stream>>>(p)));
+  GDN2_DISPATCH_TYPES(dtype, g_dtype, {
+    if (prologue != 0) token_forward_kernel<T, G, true><<<unsigned(blocks), kTokThreads, 0, stream>>>(p);
+    else token_forward_kernel<T, G, false><<<unsigned(blocks), kTokThreads, 0, stream>>>(p);
+  });
   return check_launch();
 }
 
@@ -764,9 +775,11 @@ int launch_token_t1_zero(const void* q, const void* k, const void* v, const void
   if (!grid_fits(blocks)) return GDN2_ERR_TOO_LARGE;
   T1ZeroParams p{q, k, v, w, out, s_out, H, scale, prologue};
   if (dtype == GDN2_BF16) {
-    token_t1_zero_kernel<__nv_bfloat16><<<unsigned(blocks), kTokThreads, 0, stream>>>(p);
+    if (prologue != 0) token_t1_zero_kernel<__nv_bfloat16, true><<<unsigned(blocks), kTokThreads, 0, stream>>>(p);
+    else token_t1_zero_kernel<__nv_bfloat16, false><<<unsigned(blocks), kTokThreads, 0, stream>>>(p);
   } else {
-    token_t1_zero_kernel<__half><<<unsigned(blocks), kTokThreads, 0, stream>>>(p);
+    if (prologue != 0) token_t1_zero_kernel<__half, true><<<unsigned(blocks), kTokThreads, 0, stream>>>(p);
+    else token_t1_zero_kernel<__half, false><<<unsigned(blocks), kTokThreads, 0, stream>>>(p);
   }
   return check_launch();
 }

@@ -43,11 +43,12 @@ def _use_compact_wy_backward(batch: int, time: int, heads: int) -> bool:
     return time >= _PARALLEL_BACKWARD_MIN_TOKENS
 
 
-def _forward_with_aux(seq, state, scale: float, prepare_backward: bool):
+def _forward_with_aux(seq, state, scale: float, prepare_backward: bool, prologue: int = 0):
     """Forward of one (detached) problem on the shape-dispatched kernels.
 
     Returns ``(output, final_state, aux)``; ``aux`` (the checkpoints backward consumes) is ``None``
-    unless ``prepare_backward`` and the sequence is not empty."""
+    unless ``prepare_backward`` and the sequence is not empty.  ``prologue`` (inference only) makes
+    the forward kernels apply the layer prologue to raw inputs."""
 
     q = seq[0]
     batch, time, heads = q.shape[0], q.shape[1], q.shape[2]
@@ -66,11 +67,11 @@ def _forward_with_aux(seq, state, scale: float, prepare_backward: bool):
                                   heads, 0, time, _validate.float32_scale(scale))
             aux = ChunkForwardAux(None, boundaries, 0)
         else:
-            output, final_state = token_forward(*seq, state, scale=scale)
+            output, final_state = token_forward(*seq, state, scale=scale, prologue=prologue)
     elif prepare_backward:
         output, final_state, aux = chunk_forward(*seq, state, scale=scale, return_aux=True)
     else:
-        output, final_state = chunk_forward(*seq, state, scale=scale)
+        output, final_state = chunk_forward(*seq, state, scale=scale, prologue=prologue)
     return output, final_state, aux
 
 

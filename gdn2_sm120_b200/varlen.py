@@ -29,7 +29,7 @@ import torch
 
 from . import _validate
 from .backward import backward_from_aux
-from .ops import _aux_from_tensors, _aux_tensors, _forward_with_aux
+from .ops import _aux_from_tensors, _aux_tensors, _forward_with_aux, _prologue_flags
 from .prologue import gate_prologue
 
 _DIM = 128
@@ -49,7 +49,7 @@ def _bounds(cu_seqlens, total: int) -> tuple[int, ...]:
     return tuple(values)
 
 
-def _packed_forward(seq, state, bounds, scale: float, prepare_backward: bool):
+def _packed_forward(seq, state, bounds, scale: float, prepare_backward: bool, prologue: int = 0):
     """Forward over every packed sequence; returns output, final states and the saved checkpoints."""
 
     q = seq[0]
@@ -67,7 +67,7 @@ def _packed_forward(seq, state, bounds, scale: float, prepare_backward: bool):
             layouts.append((0, 0, 0, 0))
             continue
         piece = tuple(t[:, start:stop] for t in seq)
-        out_i, final_i, aux = _forward_with_aux(piece, state_i, scale, prepare_backward)
+        out_i, final_i, aux = _forward_with_aux(piece, state_i, scale, prepare_backward, prologue)
         output[:, start:stop].copy_(out_i)
         final_state[i:i + 1].copy_(final_i)
         tensors, layout = _aux_tensors(aux)
@@ -151,9 +151,6 @@ def chunk_gdn2_varlen(
     output_scale = float(scale) if scale is not None else 1.0 / math.sqrt(_DIM)
     if not math.isfinite(output_scale):
         raise ValueError("scale must be finite")
-    if use_qk_l2norm_in_kernel or use_gate_in_kernel:
-        q, k, g, beta, w = gate_prologue(q, k, g, beta, w, normalize_qk=use_qk_l2norm_in_kernel,
-                                         activate_gates=use_gate_in_kernel)
     _validate.sequence_inputs(q, k, v, g, beta, w, need_alignment=True)
     n_seq, heads = len(bounds) - 1, q.shape[2]
     if initial_state is not None:
@@ -162,11 +159,16 @@ def chunk_gdn2_varlen(
         isinstance(t, torch.Tensor) and t.requires_grad for t in (q, k, v, g, beta, w, initial_state)
     )
     if wants_grad:
+        # training: materialise the activated tensors once for the whole packed batch
+        if use_qk_l2norm_in_kernel or use_gate_in_kernel:
+            q, k, g, beta, w = gate_prologue(q, k, g, beta, w, normalize_qk=use_qk_l2norm_in_kernel,
+                                             activate_gates=use_gate_in_kernel)
         output, final_state = _ChunkGDN2Varlen.apply(q, k, v, g, beta, w, initial_state, bounds, output_scale)
     else:
         seq = tuple(_validate.detached(x) for x in (q, k, v, g, beta, w))
-        output, final_state, _, _ = _packed_forward(seq, _validate.detached(initial_state), bounds,
-                                                    output_scale, False)
+        output, final_state, _, _ = _packed_forward(
+            seq, _validate.detached(initial_state), bounds, output_scale, False,
+            _prologue_flags(use_qk_l2norm_in_kernel, use_gate_in_kernel))
     return output, final_state if output_final_state else None
 
 
