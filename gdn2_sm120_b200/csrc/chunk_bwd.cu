@@ -851,23 +851,6 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
 // A [n_slots][128 k][128 v] fp32 array of states seen as a 5-D tensor (v % 4, k % 8, v / 4, k / 8, slot):
 // a box (4, 8, box_v4, 16, 1) lands in shared memory as the blocked K-major tile X[r = k][c = v] of
 // 4 * box_v4 value columns (8 rows x 16 bytes core matrices, CS = 128, RS = 128 * box_v4).
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult query;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &query) != cudaSuccess ||
-        query != cudaDriverEntryPointSuccess) {
-      return EncodeTiledFn(nullptr);
-    }
-    return reinterpret_cast<EncodeTiledFn>(ptr);
-  }();
-  return fn;
-}
-
 static bool encode_state_map(CUtensorMap* tm, const float* base, int64_t n_slots, int box_v4) {
   EncodeTiledFn encode = encode_tiled_fn();
   if (encode == nullptr) return false;

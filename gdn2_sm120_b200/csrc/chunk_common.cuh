@@ -31,6 +31,8 @@
 // Arrays are stored one after another (struct of arrays), each n_ch entries long.
 #pragma once
 
+#include <cuda.h>
+
 #include "common.cuh"
 #include "tc05.cuh"
 
@@ -153,6 +155,44 @@ __device__ __forceinline__ void unpack4<__half>(uint2 raw, float (&out)[4]) {
 template <>
 __device__ __forceinline__ void unpack4<float>(float4 raw, float (&out)[4]) {
   out[0] = raw.x; out[1] = raw.y; out[2] = raw.z; out[3] = raw.w;
+}
+
+// ---- tensor maps (host) -------------------------------------------------------------------------
+// cuTensorMapEncodeTiled through the runtime's driver entry point query: the library does not link
+// against the driver API for this one call.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &query) != cudaSuccess ||
+        query != cudaDriverEntryPointSuccess) {
+      return EncodeTiledFn(nullptr);
+    }
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// A contiguous [B, T, H, 128] sequence tensor seen as (channel, head, b * T + t): a box
+// (128, 1, 64) is one head's 64-token chunk, landing in shared memory as dense [64][128] rows.
+inline bool encode_sequence_map(CUtensorMap* tm, const void* base, int64_t rows, int64_t heads, int dtype) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return false;
+  const cuuint64_t es = (dtype == GDN2_FP32) ? 4 : 2;
+  const CUtensorMapDataType type = (dtype == GDN2_FP32)   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                   : (dtype == GDN2_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                          : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const cuuint64_t dims[3] = {cuuint64_t(kDim), cuuint64_t(heads), cuuint64_t(rows)};
+  const cuuint64_t strides[2] = {cuuint64_t(kDim) * es, cuuint64_t(heads) * kDim * es};  // bytes, dimensions 1..2
+  const cuuint32_t box[3] = {cuuint32_t(kDim), 1, cuuint32_t(kChunk)};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  return encode(tm, type, 3, const_cast<void*>(base), dims, strides, box, elem_strides,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {

@@ -1,7 +1,11 @@
 // Tensor-core chunk forward (64-token chunks, compact-WY form), two kernels:
 //
-//   chunk_prep_kernel   one CTA per (batch, chunk, head), all chunks in parallel.  Builds the WY
-//                       factors of the chunk and writes them as operand-ready blobs:
+//   chunk_prep_kernel   persistent, one CTA per SM walking over the (batch, chunk, head) units, all
+//                       chunks independent.  The raw inputs of the next unit arrive by tiled TMA
+//                       loads under the tail of the current one (a CTA that starts a unit with
+//                       per-thread loads spends a quarter of its time issuing them: the load/store
+//                       unit's queue, not HBM, is the limit).  Builds the WY factors of the chunk
+//                       and writes them as operand-ready blobs:
 //                       cumulative log-decay, block-anchored Gram products on tf32 tcgen05 MMAs,
 //                       blocked inverse of the unit lower-triangular system on CUDA cores (fp32),
 //                       Y = T E and U^T = Z^T T^T on tf32 tcgen05 MMAs.
@@ -57,9 +61,17 @@ struct PrepSmem {
   float part[16][kDim];                // per 4-token group partial sums -> exclusive prefixes
   float gend[kDim];
   float nrm[16][2][4][2];              // fused prologue: per (warp, token group, token) sums of q^2, k^2 over 64 channels
-  alignas(8) uint64_t bar[2];
+  alignas(8) uint64_t bar[2];          // MMA commits
+  alignas(8) uint64_t bar_ld[2];       // raw inputs of the next unit: {g, k, q} and {beta, v, w}
   uint32_t tmem_base;
 };
+// landing zones of the raw [64][128] input tiles of the next unit, in regions that are dead by then:
+// g, k, q over the fp32 scratch in region 1 (free once T is written), beta, v, w over E^T / Z^T in
+// region 2 (free once the last MMAs have read them)
+constexpr int kStageK = 32768, kStageQ = 49152;                     // region 1: g at 0 (16 or 32 KiB)
+constexpr int kStageBeta = 0, kStageV = 16384, kStageW = 32768;     // region 2
+constexpr uint32_t kStageTile16 = kChunk * kDim * 2;                // a 16-bit input tile
+static_assert(kStageQ + kStageTile16 <= 16 * kRsN && kStageW + kStageTile16 <= 20 * kRsN, "staging exceeds its region");
 
 struct PrepParams {
   const void *q, *k, *v, *g, *beta, *w;
@@ -77,7 +89,11 @@ __device__ __forceinline__ int gram_col(int I) { return (I == 0) ? 0 : (I == 1) 
 // kPro: the instantiation that can apply the layer prologue to raw inputs (p.prologue says which parts);
 // the plain instantiation carries none of that code.
 template <typename T, typename G, bool kPro = false>
-__global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepParams p) {
+__global__ void __launch_bounds__(kPrepThreads, 1)
+chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
+                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_q,
+                  const __grid_constant__ CUtensorMap tm_beta, const __grid_constant__ CUtensorMap tm_v,
+                  const __grid_constant__ CUtensorMap tm_w) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   PrepSmem& sm = *reinterpret_cast<PrepSmem*>(smem_raw);
   const WsLayout ws{p.n_ch, p.training != 0};
@@ -95,6 +111,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
   if (tid == 0) {
     mbar_init(&sm.bar[0], 1);
     mbar_init(&sm.bar[1], 1);
+    mbar_init(&sm.bar_ld[0], 1);
+    mbar_init(&sm.bar_ld[1], 1);
     fence_mbar_init();
   }
 
@@ -104,27 +122,54 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
   const int kc0 = 4 * c4;
   const int q4 = warp & 3, part = warp >> 2;  // TMEM lane quadrant of this warp, and its share of the columns
 
-  const int64_t ch = blockIdx.x;
-  auto seq_index = [&](int64_t ch_, int e) {
-    const int64_t h_ = ch_ % p.H, c_ = (ch_ / p.H) % p.n_chunks, b_ = ch_ / (p.H * p.n_chunks);
-    return ((b_ * p.T + c_ * kChunk + 4 * tg + e) * p.H + h_) * kDim + kc0;
+  // unit -> TMA coordinates (channel 0, head, first row of the chunk in the [B * T] row space)
+  const int heads = int(p.H), chunks = int(p.n_chunks), n_ch = int(p.n_ch);
+  constexpr uint32_t kStageTileG = kChunk * kDim * sizeof(G);
+  auto issue_gkq = [&](int ch_) {
+    const int h_ = ch_ % heads, bc = ch_ / heads, row = (bc / chunks) * int(p.T) + (bc % chunks) * kChunk;
+    mbar_arrive_expect_tx(&sm.bar_ld[0], kStageTileG + 2 * kStageTile16);
+    tma_load_3d(sm.gram_a, &tm_g, 0, h_, row, &sm.bar_ld[0]);
+    tma_load_3d(sm.gram_a + kStageK, &tm_k, 0, h_, row, &sm.bar_ld[0]);
+    tma_load_3d(sm.gram_a + kStageQ, &tm_q, 0, h_, row, &sm.bar_ld[0]);
   };
-  // ---- every global load of the chunk is issued up front, the log-decay first: the prefix sums below
-  // wait for it alone while the other five tensors are still streaming in -----------------------------
+  auto issue_bvw = [&](int ch_) {
+    const int h_ = ch_ % heads, bc = ch_ / heads, row = (bc / chunks) * int(p.T) + (bc % chunks) * kChunk;
+    mbar_arrive_expect_tx(&sm.bar_ld[1], 3 * kStageTile16);
+    tma_load_3d(sm.gram_b + kStageBeta, &tm_beta, 0, h_, row, &sm.bar_ld[1]);
+    tma_load_3d(sm.gram_b + kStageV, &tm_v, 0, h_, row, &sm.bar_ld[1]);
+    tma_load_3d(sm.gram_b + kStageW, &tm_w, 0, h_, row, &sm.bar_ld[1]);
+  };
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (tid == 0 && int(blockIdx.x) < n_ch) {
+    issue_gkq(int(blockIdx.x));
+    issue_bvw(int(blockIdx.x));
+  }
+  const uint32_t tb = sm.tmem_base;
+  // this thread's 8- or 16-byte piece of row 4 tg + e of a staged [64][128] tile
+  auto staged = [&](const uint8_t* tile, int e, int elem_bytes) {
+    return tile + ((4 * tg + e) * kDim + kc0) * elem_bytes;
+  };
+
+  uint32_t par = 0;
+  for (int ch = int(blockIdx.x); ch < n_ch; ch += int(gridDim.x), par ^= 1u) {
+  const int ch_next = ch + int(gridDim.x);
+  // ---- the raw inputs were brought in while the previous unit was finishing; the log-decay is
+  // consumed first: the prefix sums below need it alone ------------------------------------------------
   float Gc[4][4], kk[4][4], qq[4][4], bb[4][4], zz[4][4];
   {
-    typename Raw4<G>::type rg[4];
-    typename Raw4<T>::type rk[4], rq[4], rb[4], rv[4], rw[4];
+    using RawG = typename Raw4<G>::type;
+    using RawT = typename Raw4<T>::type;
+    RawG rg[4];
+    RawT rk[4], rq[4];
+    waiter.wait(&sm.bar_ld[0], par);
 #pragma unroll
-    for (int e = 0; e < 4; ++e) rg[e] = load4_raw<G>(p.g, seq_index(ch, e));
+    for (int e = 0; e < 4; ++e) rg[e] = *reinterpret_cast<const RawG*>(staged(sm.gram_a, e, sizeof(G)));
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const int64_t idx = seq_index(ch, e);
-      rk[e] = load4_raw<T>(p.k, idx);
-      rq[e] = load4_raw<T>(p.q, idx);
-      rb[e] = load4_raw<T>(p.beta, idx);
-      rv[e] = load4_raw<T>(p.v, idx);
-      rw[e] = load4_raw<T>(p.w, idx);
+      rk[e] = *reinterpret_cast<const RawT*>(staged(sm.gram_a + kStageK, e, 2));
+      rq[e] = *reinterpret_cast<const RawT*>(staged(sm.gram_a + kStageQ, e, 2));
     }
     const bool pro_norm = kPro && (p.prologue & kPrologueNorm) != 0;
     const bool pro_gate = kPro && (p.prologue & kPrologueGate) != 0;
@@ -162,6 +207,14 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
         }
       }
     }
+    waiter.wait(&sm.bar_ld[1], par);
+    RawT rb[4], rv[4], rw[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      rb[e] = *reinterpret_cast<const RawT*>(staged(sm.gram_b + kStageBeta, e, 2));
+      rv[e] = *reinterpret_cast<const RawT*>(staged(sm.gram_b + kStageV, e, 2));
+      rw[e] = *reinterpret_cast<const RawT*>(staged(sm.gram_b + kStageW, e, 2));
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -187,7 +240,6 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
       for (int f = 0; f < 4; ++f) zz[e][f] = to_tf32(vv[f] * ww[f]);
     }
   }
-  const uint32_t tb = sm.tmem_base;
   if (tid < kDim) {
     float run = 0.f;
 #pragma unroll
@@ -216,9 +268,9 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     t_far[1][f] = (mb + 3 < 4) ? __expf(sm.part[4 * (mb + 3)][kc] - a_nx[f]) : 0.f;
   }
 
-  uint8_t* blob_q = p.sc + sc.off_q() + ch * kBlobQ;
-  uint8_t* blob_kt = p.sc + sc.off_kt() + ch * kBlobKt;
-  uint8_t* blob_kn = p.ws + ws.off_kn() + ch * kBlobKn;
+  uint8_t* blob_q = p.sc + sc.off_q() + int64_t(ch) * kBlobQ;
+  uint8_t* blob_kt = p.sc + sc.off_kt() + int64_t(ch) * kBlobKt;
+  uint8_t* blob_kn = p.ws + ws.off_kn() + int64_t(ch) * kBlobKn;
   float ebar[4][4], ktail[4][4], qgam[4][4];
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
@@ -281,13 +333,13 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     store_global_32b(blob_kt + off, make_float4(ktail[0][f], ktail[1][f], ktail[2][f], ktail[3][f]),
                      make_float4(ktail[0][f + 1], ktail[1][f + 1], ktail[2][f + 1], ktail[3][f + 1]));
     if (training) {
-      store_global_32b(p.ws + ws.off_qt() + ch * kBlobQt + off,
+      store_global_32b(p.ws + ws.off_qt() + int64_t(ch) * kBlobQt + off,
                        make_float4(qgam[0][f], qgam[1][f], qgam[2][f], qgam[3][f]),
                        make_float4(qgam[0][f + 1], qgam[1][f + 1], qgam[2][f + 1], qgam[3][f + 1]));
     }
   }
   if (tid < kDim) {
-    reinterpret_cast<float*>(p.ws + ws.off_d() + ch * kBlobD)[tid] = __expf(sm.gend[tid]);
+    reinterpret_cast<float*>(p.ws + ws.off_d() + int64_t(ch) * kBlobD)[tid] = __expf(sm.gend[tid]);
   }
   fence_async_smem();
   tc_fence_before();
@@ -307,7 +359,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     }
     mma_commit(&sm.bar[0]);
   }
-  waiter.wait(&sm.bar[0], 0);
+  waiter.wait(&sm.bar[0], par);
   tc_fence_after();
 
   // the Gram operands are dead: region 1 becomes fp32 scratch, region 2 receives E^T and Z^T
@@ -333,7 +385,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     const int I_lo = (q4 & 1) * 2;
     const int my_I = I_lo + (lane >> 4);
     const int c0 = 16 * part;
-    uint8_t* blob_a = p.sc + sc.off_a() + ch * kBlobA;
+    uint8_t* blob_a = p.sc + sc.off_a() + int64_t(ch) * kBlobA;
     uint32_t lo[16], hi[16];
     const bool need_lo = c0 < 16 * (I_lo + 1), need_hi = c0 < 16 * (I_lo + 2);
     if (need_lo) tmem_ld16(tmem_addr(tb, 32 * q4, gram_col(I_lo) + c0), lo);
@@ -484,9 +536,9 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
         // transposed tiles X[r = j][c = i]: here `i` plays the role of the row j, 4*c4t.. of the column i
         const int j = i;
         const float4 tc = ld4(Tc + j * kLd + 4 * c4t);
-        *reinterpret_cast<float4*>(p.ws + ws.off_tt() + ch * kBlobTt + off) =
+        *reinterpret_cast<float4*>(p.ws + ws.off_tt() + int64_t(ch) * kBlobTt + off) =
             make_float4(to_tf32(tc.x), to_tf32(tc.y), to_tf32(tc.z), to_tf32(tc.w));
-        *reinterpret_cast<float4*>(p.ws + ws.off_at() + ch * kBlobAt + off) =
+        *reinterpret_cast<float4*>(p.ws + ws.off_at() + int64_t(ch) * kBlobAt + off) =
             make_float4(An[(4 * c4t) * kLd + j], An[(4 * c4t + 1) * kLd + j], An[(4 * c4t + 2) * kLd + j],
                         An[(4 * c4t + 3) * kLd + j]);
       }
@@ -499,6 +551,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
   // ---- Y = T E (rows 0..63 of an M = 128 product), U^T = Z^T T^T, and Y^T = E^T T^T when training ----
   if (tid == 0) {
     tc_fence_after();
+    // region 1 (fp32 scratch) is dead: g, k, q of the next unit land there under the MMAs and the epilogue
+    if (ch_next < n_ch) issue_gkq(ch_next);
     const uint32_t t0a = smem_u32(sm.tmat), e0 = smem_u32(et_tile), z0 = smem_u32(zt_tile);
     const uint32_t id_y = idesc(128, 128, kFmtTF32, kMajorK, kMajorK);
     const uint32_t id_u = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
@@ -521,8 +575,10 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     }
     mma_commit(&sm.bar[1]);
   }
-  waiter.wait(&sm.bar[1], 0);
+  waiter.wait(&sm.bar[1], par);
   tc_fence_after();
+  // the MMAs have read E^T and Z^T: beta, v, w of the next unit land in region 2 under the epilogue
+  if (tid == 0 && ch_next < n_ch) issue_bvw(ch_next);
   {
     auto rn4 = [](const uint32_t* r) {
       return make_float4(to_tf32(__uint_as_float(r[0])), to_tf32(__uint_as_float(r[1])),
@@ -531,7 +587,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     // Y: lanes 0..63 hold rows i; the four warps of quadrants 0 and 1 take 32 key columns each
     if (q4 < 2) {
       const int i = 32 * q4 + lane;
-      uint8_t* blob_y = p.sc + sc.off_y() + ch * kBlobY;
+      uint8_t* blob_y = p.sc + sc.off_y() + int64_t(ch) * kBlobY;
 #pragma unroll
       for (int c0 = 32 * part; c0 < 32 * part + 32; c0 += 16) {
         uint32_t r[16];
@@ -547,7 +603,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
     {
       const int row = 32 * q4 + lane;
       const int c0 = 16 * part;
-      uint8_t* blob_ut = p.sc + sc.off_ut() + ch * kBlobUt;
+      uint8_t* blob_ut = p.sc + sc.off_ut() + int64_t(ch) * kBlobUt;
       uint32_t r[16];
       tmem_ld16(tmem_addr(tb, 32 * q4, 128 + c0), r);
       tmem_wait_ld();
@@ -557,7 +613,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
             make_uint4(r[4 * j4], r[4 * j4 + 1], r[4 * j4 + 2], r[4 * j4 + 3]);
       }
       if (training) {
-        uint8_t* blob_yt = p.ws + ws.off_yt() + ch * kBlobYt;
+        uint8_t* blob_yt = p.ws + ws.off_yt() + int64_t(ch) * kBlobYt;
         tmem_ld16(tmem_addr(tb, 32 * q4, 192 + c0), r);
         tmem_wait_ld();
 #pragma unroll
@@ -567,6 +623,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) chunk_prep_kernel(const PrepP
       }
     }
   }
+  }  // units of this CTA
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tb, 256);
@@ -872,6 +929,22 @@ int launch_chunk_forward(const void* q, const void* k, const void* v, const void
   cudaError_t err = cudaMemsetAsync(status, 0, kStatusBytes, stream);
   if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
 
+  // the prep kernel addresses its inputs through tensor maps: rows b * T + t in 31 bits, 16-byte aligned bases
+  if (B * T > int64_t(0x7fffffff)) return GDN2_ERR_TOO_LARGE;
+  const void* seq[6] = {g, k, q, beta, v, w};
+  CUtensorMap tm[6];
+  for (int i = 0; i < 6; ++i) {
+    if ((reinterpret_cast<uintptr_t>(seq[i]) & 15u) != 0 ||
+        !encode_sequence_map(&tm[i], seq[i], B * T, H, i == 0 ? g_dtype : dtype)) {
+      return GDN2_ERR_LAUNCH;
+    }
+  }
+  int device = 0, sm_count = 0;
+  err = cudaGetDevice(&device);
+  if (err == cudaSuccess) err = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+  if (err != cudaSuccess || sm_count <= 0) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
+  const unsigned prep_grid = unsigned(n_ch < int64_t(sm_count) ? n_ch : int64_t(sm_count));
+
   profile_mark(0, stream);
   PrepParams pp{q, k, v, g, beta, w, workspace, scratch, T, H, n_chunks, n_ch, scale, training, prologue};
   GDN2_DISPATCH_TYPES(dtype, g_dtype, {
@@ -879,7 +952,7 @@ int launch_chunk_forward(const void* q, const void* k, const void* v, const void
     const int smem = int(sizeof(PrepSmem));
     err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
-    kernel<<<unsigned(n_ch), kPrepThreads, smem, stream>>>(pp);
+    kernel<<<prep_grid, kPrepThreads, smem, stream>>>(pp, tm[0], tm[1], tm[2], tm[3], tm[4], tm[5]);
   });
   int st = check_launch();
   if (st != GDN2_OK) return st;
