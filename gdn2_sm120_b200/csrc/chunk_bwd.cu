@@ -310,6 +310,13 @@ constexpr int kKItBytes = 16 * (528 + 1040 + 1552 + 2064);  // 82944
 constexpr int kOffEat = kOffKIt + kKItBytes;      // C: E_a^T X[r = k][c = i], RS kRsT           33024
 constexpr int kOffQat = kOffEat + 16 * kRsT;      // C: Q_a^T                                    33024
 constexpr int kEndC = kOffQat + 16 * kRsT;        // 218624
+// final chain: k and q of the unit as 16-bit [64][128] tiles over the dO rows of the stack (dk and dq
+// replace them in place and leave by tiled TMA stores), the log-decay prefix G as an fp32 tile over
+// the dS_1 buffer.  The next unit's prefetch keeps clear of both until the chain is over.
+constexpr int kOffTileK = kOffStack + 8 * kRsN;   // 36864
+constexpr int kOffTileQ = kOffTileK + 16384;
+constexpr int kOffTileG = kOffDs1;
+static_assert(kOffTileQ + 16384 <= kOffRn, "chain tiles exceed the dO rows of the stack");
 constexpr int kOffMisc = (kEndB > kEndC ? kEndB : kEndC);
 struct VjpMisc {
   float part[16][kDim];   // exclusive prefixes of the log-decay per 4-token group
@@ -398,7 +405,8 @@ __device__ __forceinline__ void tmem_ld8f(uint32_t taddr, float (&x)[8]) {
 template <typename T, typename G, bool kF32Grads = false>
 __global__ void __launch_bounds__(kVjpThreads, 1)
 chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s0,
-                     const __grid_constant__ CUtensorMap tm_ds) {
+                     const __grid_constant__ CUtensorMap tm_ds, const __grid_constant__ CUtensorMap tm_dq,
+                     const __grid_constant__ CUtensorMap tm_dk) {
   using O = typename std::conditional<kF32Grads, float, T>::type;  // element type of dq, dk, dv, dbeta, dw
   extern __shared__ __align__(128) uint8_t smem[];
   VjpMisc& ms = *reinterpret_cast<VjpMisc*>(smem + kOffMisc);
@@ -437,17 +445,26 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
   // tensor cores read the fp32 containers as tf32).  No register staging.  The kernel is persistent:
   // one SM takes in bytes at a limited rate, so the copies for the CTA's next chunk-head are issued as
   // soon as the last MMA of the current one has read shared memory, and land during its final chain.
-  auto issue_loads = [&](int64_t ch_) {
+  // The chain keeps the dO rows of the stack and the dS_1 buffer for its own tiles, so the copies come in
+  // two parts: S_0, R and dZ before the chain, the dS_1 half after it (bar_s expects both from the start).
+  auto s0_slot_of = [&](int64_t ch_) {
     const int64_t h_ = ch_ % p.H, c_ = (ch_ / p.H) % p.n_chunks, b_ = ch_ / (p.H * p.n_chunks);
-    const int s0_slot_ = int((b_ * (p.n_chunks + 1) + c_) * p.H + h_);
+    return int((b_ * (p.n_chunks + 1) + c_) * p.H + h_);
+  };
+  auto issue_loads = [&](int64_t ch_) {
     mbar_arrive_expect_tx(&ms.bar_s, uint32_t(65536 + 32768));
-    tma_load_5d(smem + kOffDs1, &tm_ds, 0, 0, 0, 0, s0_slot_ + int(p.H), &ms.bar_s);
-    tma_load_5d(smem + kOffS0, &tm_s0, 0, 0, 0, 0, s0_slot_, &ms.bar_s);
+    tma_load_5d(smem + kOffS0, &tm_s0, 0, 0, 0, 0, s0_slot_of(ch_), &ms.bar_s);
     mbar_arrive_expect_tx(&ms.bar_a, uint32_t(kBlobDZ + kBlobRn));
     bulk_g2s(smem + kOffRn, p.ws + ws.off_rn() + ch_ * kBlobRn, uint32_t(kBlobRn), &ms.bar_a);
     bulk_g2s(smem + kOffStack, p.sc + sc.off_dz() + ch_ * kBlobDZ, uint32_t(kBlobDZ), &ms.bar_a);
   };
-  if (tid == 0 && int64_t(blockIdx.x) < p.n_ch) issue_loads(blockIdx.x);
+  auto issue_ds1 = [&](int64_t ch_) {
+    tma_load_5d(smem + kOffDs1, &tm_ds, 0, 0, 0, 0, s0_slot_of(ch_) + int(p.H), &ms.bar_s);
+  };
+  if (tid == 0 && int64_t(blockIdx.x) < p.n_ch) {
+    issue_loads(blockIdx.x);
+    issue_ds1(blockIdx.x);
+  }
 
   uint32_t iter = 0;
   for (int64_t ch = blockIdx.x; ch < p.n_ch; ch += gridDim.x, ++iter) {
@@ -489,6 +506,11 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     for (int e = 0; e < 4; ++e) {
       load4v<T>(p.d_out, seq_idx(4 * tg + e) + kc0, dv4[e]);
       load4v<G>(p.g, seq_idx(4 * tg + e) + kc0, Gc[e]);
+    }
+    if (!kF32Grads) {
+      // the dk / dq tiles of the previous unit lie where the dO rows go: their stores must have read them
+      if (tid == 0) bulk_wait_read_all();
+      __syncthreads();
     }
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -721,6 +743,18 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
   tc_fence_after();
   // shared memory (all but the small arrays of VjpMisc) is dead from here on: fetch the next chunk-head
   if (tid == 0 && ch + gridDim.x < p.n_ch) issue_loads(ch + gridDim.x);
+  // hand k, q and the log-decay prefix to the chain, which walks the tokens of one channel: these threads
+  // hold them as 4 x 4 patches (the same values, and for G the same summation order, as the tiles above)
+  {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int off = (4 * tg + e) * kDim + kc0;
+      store4v<T>(smem + kOffTileK, off, kk[e][0], kk[e][1], kk[e][2], kk[e][3]);
+      store4v<T>(smem + kOffTileQ, off, qq[e][0], qq[e][1], qq[e][2], qq[e][3]);
+      store4v<float>(smem + kOffTileG, off, Gc[e][0], Gc[e][1], Gc[e][2], Gc[e][3]);
+    }
+    __syncthreads();
+  }
 
   // ================================ per-channel chain ==============================================
   // One thread = one key channel over one 16-token block.  The log-decay G and the anchored operands
@@ -747,15 +781,13 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     for (int sb = 0; sb < 2; ++sb) {
       const int i0 = 16 * blk + 8 * sb;
       float Gb[8], kv[8], bv[8], sq[8], P3[8], P2[8], dG[8], x[8], y[8];
-      float loc = 0.f;
 #pragma unroll
       for (int t = 0; t < 8; ++t) {
-        const int64_t idx = seq_idx(i0 + t) + kc;
-        loc = ((t & 3) ? loc : 0.f) + ldf<G>(p.g, idx);
-        Gb[t] = loc + ms.part[(i0 + t) >> 2][kc];
-        kv[t] = ldf<T>(p.k, idx);
-        bv[t] = ldf<T>(p.beta, idx);
-        sq[t] = p.scale * ldf<T>(p.q, idx);  // loaded here: no global load may follow a global store
+        const int off = (i0 + t) * kDim + kc;
+        Gb[t] = ldf<float>(smem + kOffTileG, off);
+        kv[t] = ldf<T>(smem + kOffTileK, off);
+        sq[t] = p.scale * ldf<T>(smem + kOffTileQ, off);
+        bv[t] = ldf<T>(p.beta, seq_idx(i0 + t) + kc);  // loaded here: no global load may follow a global store
       }
       // row blocks I = blk + d that contain these tokens as columns, nearest first: the own block uses
       // exp(a_me - G), the others exp(a_next - G) (times the block-to-block factor from d = 2 on)
@@ -810,8 +842,16 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
         const float ea = Gb[t], eg = ea * e_ame;
         const float P1 = failed ? poison_nan() : fmaf(x[t], eg, y[t] * ea);
         const float dGt = fmaf(to_tf32(sq[t] * ea), y[t], fmaf(sq[t] * eg, x[t], dG[t]));
-        stf<O>(p.dq, idx, p.scale * P1);
-        stf<O>(p.dk, idx, failed ? poison_nan() : fmaf(bv[t], P2[t], P3[t]));
+        const float dk_t = failed ? poison_nan() : fmaf(bv[t], P2[t], P3[t]);
+        if (kF32Grads) {
+          stf<O>(p.dq, idx, p.scale * P1);
+          stf<O>(p.dk, idx, dk_t);
+        } else {
+          // in place over q and k (this thread's own slots, already read): the tiles leave by TMA stores
+          const int off = (i0 + t) * kDim + kc;
+          stf<T>(smem + kOffTileQ, off, p.scale * P1);
+          stf<T>(smem + kOffTileK, off, dk_t);
+        }
         stf<O>(p.dbeta, idx, failed ? poison_nan() : kv[t] * P2[t]);
         dGv[8 * sb + t] = dGt;
         tot += dGt;
@@ -838,10 +878,22 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     }
   }
   // the next chunk-head reuses the arrays of VjpMisc and the TMEM columns
+  fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (tid == 0) {
+    if (!kF32Grads) {
+      const int row = int(b * p.T + t0);
+      tma_store_3d(&tm_dq, 0, int(h), row, smem + kOffTileQ);
+      tma_store_3d(&tm_dk, 0, int(h), row, smem + kOffTileK);
+      bulk_commit();
+    }
+    // the G tile is dead: the dS_1 half of the next chunk-head may land on it
+    if (ch + gridDim.x < p.n_ch) issue_ds1(ch + gridDim.x);
+  }
   }  // chunk-head loop
+  if (tid == 0) bulk_wait_all();  // the last dq / dk tiles are in global memory before the CTA retires
   if (warp == 0) tmem_dealloc(tb, 512);
 }
 
@@ -907,6 +959,14 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
       !encode_state_map(&tm_s0, bnd, n_slots, 32) || !encode_state_map(&tm_ds, d_bnd, n_slots, 16)) {
     return GDN2_ERR_LAUNCH;
   }
+  // dq and dk leave the VJP kernel as [64][128] tiles through tiled TMA stores (rows b * T + t in 31 bits)
+  CUtensorMap tm_dq, tm_dk;
+  if (B * T > int64_t(0x7fffffff)) return GDN2_ERR_TOO_LARGE;
+  if ((reinterpret_cast<uintptr_t>(dq) & 15u) != 0 || (reinterpret_cast<uintptr_t>(dk) & 15u) != 0 ||
+      !encode_sequence_map(&tm_dq, dq, B * T, H, grads_f32 ? GDN2_FP32 : dtype) ||
+      !encode_sequence_map(&tm_dk, dk, B * T, H, grads_f32 ? GDN2_FP32 : dtype)) {
+    return GDN2_ERR_LAUNCH;
+  }
   VjpParams vp{q, k, v, g, beta, w, d_out, workspace, scratch, bnd, d_bnd, dq, dk, dv, dg, dbeta, dw,
                status, T, H, n_chunks, n_ch, scale};
   const unsigned vjp_grid = unsigned(n_ch < int64_t(sm_count) ? n_ch : int64_t(sm_count));
@@ -914,13 +974,13 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
     auto kernel = chunk_bwd_vjp_kernel<__nv_bfloat16, float, true>;
     err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kVjpSmemBytes);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
-    kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds);
+    kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds, tm_dq, tm_dk);
   } else {
     GDN2_DISPATCH_TYPES(dtype, g_dtype, {
       auto kernel = chunk_bwd_vjp_kernel<T, G>;
       err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kVjpSmemBytes);
       if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
-      kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds);
+      kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds, tm_dq, tm_dk);
     });
   }
   st = check_launch();

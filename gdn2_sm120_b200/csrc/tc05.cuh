@@ -86,6 +86,12 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, in
       ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
       : "memory");
 }
+// 3-D tiled TMA store shared -> global (bulk async-group completion); same alignment rules.
+__device__ __forceinline__ void tma_store_3d(const void* tmap, int c0, int c1, int c2, const void* smem_src) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(tmap),
+               "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(smem_src))
+               : "memory");
+}
 
 __device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst),
