@@ -46,8 +46,13 @@ def workspace_bytes(batch: int, full_tokens: int, heads: int, training: bool = F
     return int(size)
 
 
-def scratch_bytes(batch: int, full_tokens: int, heads: int, backward: bool = False) -> int:
-    size = _lib.lib().gdn2_chunk_scratch_bytes(batch, full_tokens, heads, int(backward))
+def scratch_bytes(batch: int, full_tokens: int, heads: int, backward: bool = False, *,
+                  training: bool = False) -> int:
+    """Per-call scratch: of a backward pass, or of the forward of an inference / a training call (a
+    training forward keeps the tiles both scans read in its workspace, so its scratch is smaller)."""
+
+    kind = 1 if backward else (2 if training else 0)
+    size = _lib.lib().gdn2_chunk_scratch_bytes(batch, full_tokens, heads, kind)
     if size <= 0:
         raise RuntimeError(f"gdn2_chunk_scratch_bytes failed with status {size}")
     return int(size)
@@ -59,13 +64,13 @@ def _backward_wave_bytes(batch: int, full_tokens: int, heads: int) -> int:
     return scratch_bytes(batch, full_tokens, heads, True) + batch * (full_tokens // _CHUNK + 1) * heads * _STATE_BYTES
 
 
-def plan_waves(batch: int, full_tokens: int, heads: int, *, backward: bool = False,
+def plan_waves(batch: int, full_tokens: int, heads: int, *, backward: bool = False, training: bool = False,
                budget: int | None = None) -> list[tuple[int, int]]:
     """Batch ranges ``[(b0, b1), ...]`` of the waves of one pass."""
 
     budget = SCRATCH_BUDGET_BYTES if budget is None else budget
     per_row = (_backward_wave_bytes(1, full_tokens, heads) if backward
-               else scratch_bytes(1, full_tokens, heads, False))
+               else scratch_bytes(1, full_tokens, heads, False, training=training))
     rows = max(1, min(batch, budget // per_row))
     # equal-sized waves (the last one may be smaller by at most one row per wave)
     n_waves = -(-batch // rows)
@@ -103,12 +108,12 @@ def forward(q, k, v, g, beta, w, initial_state, output, final_state, chunk_bound
     training = chunk_boundaries is not None
     if prologue and training:
         raise ValueError("the fused prologue is forward-only")
-    waves = plan_waves(batch, full_tokens, heads)
+    waves = plan_waves(batch, full_tokens, heads, training=training)
     rows = waves[0][1] - waves[0][0]
-    needed = scratch_bytes(rows, full_tokens, heads, False) + sum(
-        workspace_bytes(b1 - b0, full_tokens, heads, training) for b0, b1 in waves)
+    scratch_size = scratch_bytes(rows, full_tokens, heads, False, training=training)
+    needed = scratch_size + sum(workspace_bytes(b1 - b0, full_tokens, heads, training) for b0, b1 in waves)
     check_memory(needed, q.device, "chunk forward")
-    scratch = torch.empty(scratch_bytes(rows, full_tokens, heads, False), device=q.device, dtype=torch.uint8)
+    scratch = torch.empty(scratch_size, device=q.device, dtype=torch.uint8)
     dtype, g_dtype = _lib.dtype_code(q.dtype), _lib.dtype_code(g.dtype)
     stream = _lib.stream_ptr(q.device)
     workspaces = []
@@ -144,7 +149,10 @@ def read_status(workspace, batch: int, full_tokens: int, heads: int) -> int:
             return int(_lib.lib().gdn2_chunk_read_status(
                 workspace.data_ptr(), batch, full_tokens, heads, _lib.stream_ptr(workspace.device)))
     worst = 0
-    for (b0, b1), ws in zip(plan_waves(batch, full_tokens, heads), workspace):
+    waves = plan_waves(batch, full_tokens, heads)
+    if len(waves) != len(workspace):  # the workspaces of a training call
+        waves = plan_waves(batch, full_tokens, heads, training=True)
+    for (b0, b1), ws in zip(waves, workspace):
         worst = max(worst, read_status(ws, b1 - b0, full_tokens, heads))
     return worst
 
@@ -159,7 +167,7 @@ def backward(q, k, v, g, beta, w, workspaces, chunk_boundaries, d_out, d_final_s
     the backward scratch of the (single) wave for inspection by tests."""
 
     dq, dk, dv, dg, dbeta, dw = grads
-    forward_waves = plan_waves(batch, full_tokens, heads)
+    forward_waves = plan_waves(batch, full_tokens, heads, training=True)
     if len(forward_waves) != len(workspaces):
         raise ValueError("workspaces do not match the wave plan of this shape")
     n_slots = full_tokens // _CHUNK + 1

@@ -1,5 +1,7 @@
 // Tensor-core chunk backward (64-token chunks), two kernels that consume the WY tiles and
-// residuals saved by the forward and the fp32 chunk-start states:
+// residuals saved by the forward and the fp32 chunk-start states.  The reverse scan reads the very
+// tiles the forward scan read, through tiled TMA loads in the other swizzle: what the forward
+// contracted over columns it contracts over rows (K-major <-> MN-major operands, tc05.cuh).
 //
 //   chunk_bwd_scan_kernel  one CTA per (batch, head), chunks in reverse order.  The state
 //                          cotangent lives transposed (dS^T: value rows x key columns) in TMEM:
@@ -40,12 +42,13 @@ constexpr int kRsDot = 2064;   // dO^T tile: padded row-group stride (16-byte ch
 constexpr int kCsZ = 144, kRsZ = 32 * kCsZ;  // dZ tile: the padded strides of the VJP kernel's [dZ ; dO] stack
 
 struct BScanSmem {
-  alignas(128) uint8_t dot[16 * kRsDot];  // dO^T tile X[r = v][c = i], tf32 (built from dO)
-  alignas(128) uint8_t kn[32768];    // K_tail   X[r = j][c = k]
-  alignas(128) uint8_t qt[32768];    // Qg^T     X[r = k][c = i]
-  alignas(128) uint8_t yt[32768];    // Y^T      X[r = k][c = j]
-  alignas(128) uint8_t at[16384];    // Aqk^T    X[r = j][c = i]
-  alignas(128) uint8_t tt[16384];    // T^T      X[r = j][c = i]
+  // swizzled operand tiles, slabs of 32 columns (tc05.cuh): Q is read MN-major, the others K-major
+  alignas(1024) uint8_t kn[32768];   // Kn[j][k]: 4 slabs of 64 lines
+  alignas(1024) uint8_t q[32768];    // Q[i][k]:  4 slabs of 64 lines
+  alignas(1024) uint8_t yt[32768];   // Yt[k][j]: 2 slabs of 128 lines
+  alignas(1024) uint8_t at[16384];   // At[j][i]: 2 slabs of 64 lines
+  alignas(1024) uint8_t tt[16384];   // Tt[j][i]: 2 slabs of 64 lines
+  alignas(128) uint8_t dot[16 * kRsDot];  // dO^T tile X[r = v][c = i], tf32, blocked (built from dO)
   alignas(128) uint8_t dz[kBlobDZ];  // dZ staging, natural tile X[r = j][c = v] with the padded strides
   alignas(16) float d[kDim];
   alignas(8) uint64_t bar_ak, bar_qy, bar_mma1, bar_mma2;
@@ -53,7 +56,7 @@ struct BScanSmem {
 };
 
 struct BScanParams {
-  const uint8_t* ws;        // workspace of the training forward (Kn, Qt, Yt, At, Tt, D)
+  const uint8_t* ws;        // workspace of the training forward (D; the tiles come through tensor maps)
   uint8_t* sc;              // scratch: receives dZ
   const void* d_out;        // [B,T,H,128]
   const float* ds_final;    // [B,H,128,128] or null
@@ -64,8 +67,11 @@ struct BScanParams {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const BScanParams p) {
-  extern __shared__ __align__(128) uint8_t smem_raw[];
+__global__ void __launch_bounds__(kBScanThreads, 1)
+chunk_bwd_scan_kernel(const BScanParams p, const __grid_constant__ CUtensorMap tm_at,
+                      const __grid_constant__ CUtensorMap tm_tt, const __grid_constant__ CUtensorMap tm_kn,
+                      const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_yt) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   BScanSmem& sm = *reinterpret_cast<BScanSmem*>(smem_raw);
   const WsLayout ws{p.n_ch, true};
   const ScratchLayout sc{p.n_ch};
@@ -103,17 +109,22 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
 
   auto ch_of = [&](int64_t c) { return (b * p.n_chunks + c) * p.H + h; };
   auto load_ak = [&](int64_t c) {
-    const int64_t ch = ch_of(c);
-    mbar_arrive_expect_tx(&sm.bar_ak, uint32_t(kBlobAt + kBlobKn + kBlobTt));
-    bulk_g2s(sm.at, p.ws + ws.off_at() + ch * kBlobAt, uint32_t(kBlobAt), &sm.bar_ak);
-    bulk_g2s(sm.tt, p.ws + ws.off_tt() + ch * kBlobTt, uint32_t(kBlobTt), &sm.bar_ak);
-    bulk_g2s(sm.kn, p.ws + ws.off_kn() + ch * kBlobKn, uint32_t(kBlobKn), &sm.bar_ak);
+    const int ch = int(ch_of(c));
+    mbar_arrive_expect_tx(&sm.bar_ak, uint32_t(kTileAt + kTileKn + kTileTt));
+#pragma unroll
+    for (int s = 0; s < 2; ++s) tma_load_3d(sm.at + s * 8192, &tm_at, 32 * s, 0, ch, &sm.bar_ak);
+#pragma unroll
+    for (int s = 0; s < 4; ++s) tma_load_3d(sm.kn + s * 8192, &tm_kn, 32 * s, 0, ch, &sm.bar_ak);
+#pragma unroll
+    for (int s = 0; s < 2; ++s) tma_load_3d(sm.tt + s * 8192, &tm_tt, 32 * s, 0, ch, &sm.bar_ak);
   };
   auto load_qy = [&](int64_t c) {
     const int64_t ch = ch_of(c);
-    mbar_arrive_expect_tx(&sm.bar_qy, uint32_t(kBlobQt + kBlobYt + kBlobD));
-    bulk_g2s(sm.qt, p.ws + ws.off_qt() + ch * kBlobQt, uint32_t(kBlobQt), &sm.bar_qy);
-    bulk_g2s(sm.yt, p.ws + ws.off_yt() + ch * kBlobYt, uint32_t(kBlobYt), &sm.bar_qy);
+    mbar_arrive_expect_tx(&sm.bar_qy, uint32_t(kTileQ + kTileYt + kBlobD));
+#pragma unroll
+    for (int s = 0; s < 4; ++s) tma_load_3d(sm.q + s * 8192, &tm_q, 32 * s, 0, int(ch), &sm.bar_qy);
+#pragma unroll
+    for (int s = 0; s < 2; ++s) tma_load_3d(sm.yt + s * 16384, &tm_yt, 32 * s, 0, int(ch), &sm.bar_qy);
     bulk_g2s(sm.d, p.ws + ws.off_d() + ch * kBlobD, uint32_t(kBlobD), &sm.bar_qy);
   };
   // dO of one chunk: 4 tokens x 4 channels per thread, still packed
@@ -184,22 +195,22 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
       tc_fence_after();
       const uint32_t d0 = smem_u32(sm.dot), a0 = smem_u32(sm.at), kn0 = smem_u32(sm.kn);
       const uint32_t id64 = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
-      // dR^T = dO^T Aqk   (A: dO^T [v x i], B: Aqk^T tile X[r = j][c = i])
+      // dR^T = dO^T Aqk   (A: dO^T [v x i], B: At[j][i] read K-major)
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        mma_tf32_ss(tb + kColR, smem_desc(d0 + ks * 256, 128, kRsDot), smem_desc(a0 + ks * 256, 128, 2048), id64,
+        mma_tf32_ss(tb + kColR, smem_desc(d0 + ks * 256, 128, kRsDot), smem_desc_sw128_k(a0, 8192, ks), id64,
                     ks > 0 ? 1u : 0u);
       }
-      // dR^T += dS^T Kt^T (A: cotangent columns, K = 128 keys; B: K_tail tile X[r = j][c = k])
+      // dR^T += dS^T Kt^T (A: cotangent columns, K = 128 keys; B: Kn[j][k] read K-major)
 #pragma unroll
       for (int ks = 0; ks < 16; ++ks) {
-        mma_tf32_ts(tb + kColR, tb + kColS + ks * 8, smem_desc(kn0 + ks * 256, 128, 4096), id64, 1u);
+        mma_tf32_ts(tb + kColR, tb + kColS + ks * 8, smem_desc_sw128_k(kn0, 8192, ks), id64, 1u);
       }
-      // dZ^T = dR^T T     (A: the accumulator just produced, K = 64 tokens; B: T^T tile X[r = j][c = i])
+      // dZ^T = dR^T T     (A: the accumulator just produced, K = 64 tokens; B: Tt[j][i] read K-major)
       const uint32_t tt0 = smem_u32(sm.tt);
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        mma_tf32_ts(tb + kColZ, tb + kColR + ks * 8, smem_desc(tt0 + ks * 256, 128, 2048), id64, ks > 0 ? 1u : 0u);
+        mma_tf32_ts(tb + kColZ, tb + kColR + ks * 8, smem_desc_sw128_k(tt0, 8192, ks), id64, ks > 0 ? 1u : 0u);
       }
       mma_commit(&sm.bar_mma1);
     }
@@ -240,18 +251,18 @@ __global__ void __launch_bounds__(kBScanThreads, 1) chunk_bwd_scan_kernel(const 
       tc_fence_after();
       bulk_s2g(p.sc + sc.off_dz() + ch_of(c) * kBlobDZ, sm.dz, uint32_t(kBlobDZ));
       bulk_commit();
-      const uint32_t d0 = smem_u32(sm.dot), q0 = smem_u32(sm.qt), y0 = smem_u32(sm.yt);
-      const uint32_t id_pos = idesc(128, 128, kFmtTF32, kMajorK, kMajorK);
+      const uint32_t d0 = smem_u32(sm.dot), q0 = smem_u32(sm.q), y0 = smem_u32(sm.yt);
+      const uint32_t id_pos = idesc(128, 128, kFmtTF32, kMajorK, kMajorMN);
       const uint32_t id_neg = idesc(128, 128, kFmtTF32, kMajorK, kMajorK, 1, 0);
-      // dS^T += dO^T Qg   (B: Qg^T tile X[r = k][c = i])
+      // dS^T += dO^T Qg   (K = 64 tokens; B: Q[i][k] read MN-major)
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        mma_tf32_ss(tb + kColS, smem_desc(d0 + ks * 256, 128, kRsDot), smem_desc(q0 + ks * 256, 128, 2048), id_pos, 1u);
+        mma_tf32_ss(tb + kColS, smem_desc(d0 + ks * 256, 128, kRsDot), smem_desc_sw128_mn(q0, 8192, ks), id_pos, 1u);
       }
-      // dS^T -= dR^T Y    (A: dR^T columns, K = 64 tokens; B: Y^T tile X[r = k][c = j])
+      // dS^T -= dR^T Y    (A: dR^T columns, K = 64 tokens; B: Yt[k][j] read K-major)
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        mma_tf32_ts(tb + kColS, tb + kColR + ks * 8, smem_desc(y0 + ks * 256, 128, 2048), id_neg, 1u);
+        mma_tf32_ts(tb + kColS, tb + kColR + ks * 8, smem_desc_sw128_k(y0, 16384, ks), id_neg, 1u);
       }
       mma_commit(&sm.bar_mma2);
     }
@@ -932,18 +943,27 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
   cudaError_t err;
 
   profile_mark(3, stream);
+  // the reverse scan's operands: the forward's tiles, each in the swizzle of the role backward reads it in
+  CUtensorMap tm_at, tm_tt, tm_kn, tm_q, tm_yt;
+  if (!encode_tile_map(&tm_at, workspace + ws.off_at(), n_ch, kChunk, kChunk, false) ||
+      !encode_tile_map(&tm_tt, workspace + ws.off_tt(), n_ch, kChunk, kChunk, false) ||
+      !encode_tile_map(&tm_kn, workspace + ws.off_kn(), n_ch, kChunk, kDim, false) ||
+      !encode_tile_map(&tm_q, workspace + ws.off_q(), n_ch, kChunk, kDim, true) ||
+      !encode_tile_map(&tm_yt, workspace + ws.off_yt(), n_ch, kDim, kChunk, false)) {
+    return GDN2_ERR_LAUNCH;
+  }
   BScanParams sp{workspace, scratch, d_out, ds_final, d_bnd, ds_init, status, T, H, n_chunks, n_ch};
   const int scan_smem = int(sizeof(BScanSmem));
   if (dtype == GDN2_BF16) {
     auto kernel = chunk_bwd_scan_kernel<__nv_bfloat16>;
     err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), scan_smem);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
-    kernel<<<unsigned(B * H), kBScanThreads, scan_smem, stream>>>(sp);
+    kernel<<<unsigned(B * H), kBScanThreads, scan_smem, stream>>>(sp, tm_at, tm_tt, tm_kn, tm_q, tm_yt);
   } else {
     auto kernel = chunk_bwd_scan_kernel<__half>;
     err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), scan_smem);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
-    kernel<<<unsigned(B * H), kBScanThreads, scan_smem, stream>>>(sp);
+    kernel<<<unsigned(B * H), kBScanThreads, scan_smem, stream>>>(sp, tm_at, tm_tt, tm_kn, tm_q, tm_yt);
   }
   int st = check_launch();
   if (st != GDN2_OK) return st;

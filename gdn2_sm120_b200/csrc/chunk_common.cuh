@@ -1,34 +1,35 @@
 // Shared definitions of the 64-token tensor-core chunk path.
 //
-// For every chunk-head ch = (b * n_chunks + c) * H + h the prep kernel writes operand-ready
-// tiles ("WY blobs") that the scan kernels pull into shared memory with 1-D bulk copies.  All
-// tiles are "blocked" (see tc05.cuh), CS = 128, tf32 values in fp32 containers.  They live in two
-// caller-provided buffers:
+// For every unit ch = (b * n_chunks + c) * H + h (one 64-token chunk of one head) the prep kernel
+// writes the WY factors as plain row-major fp32 matrices holding tf32 values ("tiles"), ONE copy of
+// each.  The forward scan and the reverse scan both consume them: the forward contracts over one index
+// of a tile and the backward over the other, so one kernel reads a tile as a K-major operand and the
+// other as an MN-major operand.  Tiled TMA loads put the same global bytes into shared memory in the
+// layout each role needs (K-major: 128-byte swizzle; MN-major tf32: 128-byte swizzle with 32-byte
+// atoms, the only MN-major form the tensor cores accept for 32-bit operands).  The orientation of a
+// tile in global memory is the one its producer can store with full 128-byte lines: token-major for
+// tiles made from registers, transposed for tiles read out of tensor memory (lane = row).
 //
-// scratch (dead when the call returns; one buffer can serve any number of calls on a stream)
-//   forward:
-//   Y    X[r = token i (64)][c = key k (128)]   RS = 4096   32 KiB   Y = (I+L)^-1 E
-//   Ut   X[r = value v (128)][c = token i (64)] RS = 2048   32 KiB   U^T, U = (I+L)^-1 (w*v)
-//   Q    X[r = token i (64)][c = key k (128)]   RS = 4096   32 KiB   scale * gamma * q
-//   Kt   X[r = key k (128)][c = token j (64)]   RS = 2048   32 KiB   (k * gamma_end / gamma)^T
-//   A    X[r = token i (64)][c = token j (64)]  RS = 2048   16 KiB   tril(Q_gamma Kbar^T)
-//   backward:
-//   dZ   X[r = token j (64)][c = value v (128)] RS = 4608, CS = 144   36 KiB   dZ = T^T dR (reverse
-//        scan -> VJP kernel; the padded strides are those of the shared-memory tile it is copied into)
+//   Q    [token i (64)][key k (128)]     32 KiB   scale * gamma * q            fwd K-major,  bwd MN-major
+//   Kn   [token j (64)][key k (128)]     32 KiB   k * gamma_end / gamma        fwd MN-major, bwd K-major
+//   Yt   [key k (128)][token i (64)]     32 KiB   Y^T, Y = (I+L)^-1 E          fwd MN-major, bwd K-major
+//   At   [token j (64)][token i (64)]    16 KiB   tril(Q_gamma Kbar^T)^T       fwd MN-major, bwd K-major
+//   Tt   [token j (64)][token i (64)]    16 KiB   ((I+L)^-1)^T                 bwd K-major (training only)
+//   U    [token j (64)][value v (128)]   32 KiB   U = (I+L)^-1 (w*v)           forward only: copied into
+//                                                                               tensor memory by threads
+//   D    float[128]                      512 B    gamma_end
 //
-// workspace (a training call's workspace is what backward consumes; an inference call's holds
-// only D and the status block)
-//   D    float[128]                                         512 B    gamma_end
-//   status block, 256 B
-//   and, for training calls only (backward contracts over the other index of each tile):
-//   Yt   X[r = key k (128)][c = token i (64)]   RS = 2048   32 KiB   Y^T
-//   Qt   X[r = key k (128)][c = token i (64)]   RS = 2048   32 KiB   Q_gamma^T
-//   Kn   X[r = token j (64)][c = key k (128)]   RS = 4096   32 KiB   K_tail
-//   At   X[r = token j (64)][c = token i (64)]  RS = 2048   16 KiB   A_qk^T
-//   Tt   X[r = token j (64)][c = token i (64)]  RS = 2048   16 KiB   ((I+L)^-1)^T
-//   Rn   X[r = token j (64)][c = value v (128)] RS = 4096   32 KiB   R = U - Y S_0 (forward scan)
+// Two more per-unit arrays are "blocked" tiles (see tc05.cuh) that bulk copies move as they are:
+//   Rn   X[r = token j (64)][c = value v (128)] RS = 4096, CS = 128   32 KiB   R = U - Y S_0
+//        (forward scan -> VJP kernel)
+//   dZ   X[r = token j (64)][c = value v (128)] RS = 4608, CS = 144   36 KiB   dZ = T^T dR
+//        (reverse scan -> VJP kernel; the padded strides are those of the tile it is copied into)
 //
-// Arrays are stored one after another (struct of arrays), each n_ch entries long.
+// Buffers (caller-provided, struct of arrays, each array n_ch entries long):
+//   workspace  D, a 256-byte status block, and for a training call what backward consumes:
+//              Rn, Q, Kn, Yt, At, Tt
+//   scratch    dead when the call returns: forward U (and Q, Kn, Yt, At for an inference call);
+//              backward dZ
 #pragma once
 
 #include <cuda.h>
@@ -40,12 +41,11 @@ namespace gdn2 {
 
 constexpr int kChunk = GDN2_CHUNK;  // 64
 
-constexpr int64_t kBlobY = 32768, kBlobUt = 32768, kBlobQ = 32768, kBlobKt = 32768;
-constexpr int64_t kBlobA = 16384, kBlobD = 512;
-constexpr int64_t kBlobFwdScratch = kBlobY + kBlobUt + kBlobQ + kBlobKt + kBlobA;
-constexpr int64_t kBlobYt = 32768, kBlobQt = 32768, kBlobKn = 32768, kBlobAt = 16384, kBlobTt = 16384;
+constexpr int64_t kTileQ = 32768, kTileKn = 32768, kTileYt = 32768, kTileU = 32768;
+constexpr int64_t kTileAt = 16384, kTileTt = 16384, kBlobD = 512;
 constexpr int64_t kBlobRn = 32768, kBlobDZ = 8 * 4608;
 constexpr int64_t kStatusBytes = 256;
+constexpr int64_t kFwdTilesBytes = kTileQ + kTileKn + kTileYt + kTileAt;  // the tiles both scans read
 
 // workspace: what a training forward leaves for backward (inference: D and the status block only)
 struct WsLayout {
@@ -54,27 +54,49 @@ struct WsLayout {
   __host__ __device__ int64_t off_d() const { return 0; }
   __host__ __device__ int64_t off_status() const { return n_ch * kBlobD; }
   // training-only arrays follow the status block
-  __host__ __device__ int64_t off_yt() const { return off_status() + kStatusBytes; }
-  __host__ __device__ int64_t off_qt() const { return off_yt() + n_ch * kBlobYt; }
-  __host__ __device__ int64_t off_kn() const { return off_qt() + n_ch * kBlobQt; }
-  __host__ __device__ int64_t off_at() const { return off_kn() + n_ch * kBlobKn; }
-  __host__ __device__ int64_t off_tt() const { return off_at() + n_ch * kBlobAt; }
-  __host__ __device__ int64_t off_rn() const { return off_tt() + n_ch * kBlobTt; }
-  __host__ __device__ int64_t total() const { return training ? off_rn() + n_ch * kBlobRn : off_yt(); }
+  __host__ __device__ int64_t off_rn() const { return off_status() + kStatusBytes; }
+  __host__ __device__ int64_t off_q() const { return off_rn() + n_ch * kBlobRn; }
+  __host__ __device__ int64_t off_kn() const { return off_q() + n_ch * kTileQ; }
+  __host__ __device__ int64_t off_yt() const { return off_kn() + n_ch * kTileKn; }
+  __host__ __device__ int64_t off_at() const { return off_yt() + n_ch * kTileYt; }
+  __host__ __device__ int64_t off_tt() const { return off_at() + n_ch * kTileAt; }
+  __host__ __device__ int64_t total() const { return training ? off_tt() + n_ch * kTileTt : off_rn(); }
 };
 
 // scratch of one call
 struct ScratchLayout {
   int64_t n_ch;
-  __host__ __device__ int64_t off_y() const { return 0; }
-  __host__ __device__ int64_t off_ut() const { return n_ch * kBlobY; }
-  __host__ __device__ int64_t off_q() const { return n_ch * (kBlobY + kBlobUt); }
-  __host__ __device__ int64_t off_kt() const { return n_ch * (kBlobY + kBlobUt + kBlobQ); }
-  __host__ __device__ int64_t off_a() const { return n_ch * (kBlobY + kBlobUt + kBlobQ + kBlobKt); }
-  __host__ __device__ int64_t total_forward() const { return n_ch * kBlobFwdScratch; }
+  __host__ __device__ int64_t off_u() const { return 0; }
+  // inference calls only (a training call keeps these in its workspace)
+  __host__ __device__ int64_t off_q() const { return n_ch * kTileU; }
+  __host__ __device__ int64_t off_kn() const { return off_q() + n_ch * kTileQ; }
+  __host__ __device__ int64_t off_yt() const { return off_kn() + n_ch * kTileKn; }
+  __host__ __device__ int64_t off_at() const { return off_yt() + n_ch * kTileYt; }
+  __host__ __device__ int64_t total_forward(bool training) const {
+    return training ? n_ch * kTileU : n_ch * (kTileU + kFwdTilesBytes);
+  }
   __host__ __device__ int64_t off_dz() const { return 0; }
   __host__ __device__ int64_t total_backward() const { return n_ch * kBlobDZ; }
 };
+
+// where the forward tile arrays of a call live
+struct ForwardTiles {
+  uint8_t *q, *kn, *yt, *at, *tt, *u;
+};
+inline ForwardTiles forward_tiles(uint8_t* workspace, uint8_t* scratch, int64_t n_ch, bool training) {
+  const WsLayout ws{n_ch, training};
+  const ScratchLayout sc{n_ch};
+  ForwardTiles t;
+  t.u = scratch + sc.off_u();
+  if (training) {
+    t.q = workspace + ws.off_q(); t.kn = workspace + ws.off_kn(); t.yt = workspace + ws.off_yt();
+    t.at = workspace + ws.off_at(); t.tt = workspace + ws.off_tt();
+  } else {
+    t.q = scratch + sc.off_q(); t.kn = scratch + sc.off_kn(); t.yt = scratch + sc.off_yt();
+    t.at = scratch + sc.off_at(); t.tt = nullptr;
+  }
+  return t;
+}
 
 // device status codes written to the workspace status word (0 = ok)
 enum : int { kStatusOk = 0, kStatusBarrierTimeout = 1 };
@@ -191,6 +213,35 @@ inline bool encode_sequence_map(CUtensorMap* tm, const void* base, int64_t rows,
   const cuuint32_t box[3] = {cuuint32_t(kDim), 1, cuuint32_t(kChunk)};
   const cuuint32_t elem_strides[3] = {1, 1, 1};
   return encode(tm, type, 3, const_cast<void*>(base), dims, strides, box, elem_strides,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// An array of n_ch row-major fp32 tiles [rows][cols] seen as (col, row, unit): a box (32, rows, 1) is a
+// slab of 32 columns of one tile, `rows` lines of 128 bytes in shared memory.  kMnMajor chooses the
+// swizzle: 128-byte with 32-byte atoms (the tile is read as an MN-major operand, contraction over its
+// rows) or plain 128-byte (K-major operand, contraction over its columns).
+inline bool encode_tile_map(CUtensorMap* tm, const uint8_t* base, int64_t n_ch, int rows, int cols, bool mn_major) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[3] = {cuuint64_t(cols), cuuint64_t(rows), cuuint64_t(n_ch)};
+  const cuuint64_t strides[2] = {cuuint64_t(cols) * 4, cuuint64_t(rows) * cols * 4};
+  const cuuint32_t box[3] = {32, cuuint32_t(rows), 1};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  return encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<uint8_t*>(base), dims, strides, box, elem_strides,
+                CU_TENSOR_MAP_INTERLEAVE_NONE,
+                mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+// The same array, whole tiles without swizzle (box (cols, rows, 1); cols <= 256): for tiles that threads read.
+inline bool encode_plain_tile_map(CUtensorMap* tm, const uint8_t* base, int64_t n_ch, int rows, int cols) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[3] = {cuuint64_t(cols), cuuint64_t(rows), cuuint64_t(n_ch)};
+  const cuuint64_t strides[2] = {cuuint64_t(cols) * 4, cuuint64_t(rows) * cols * 4};
+  const cuuint32_t box[3] = {cuuint32_t(cols), cuuint32_t(rows), 1};
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  return encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<uint8_t*>(base), dims, strides, box, elem_strides,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }

@@ -15,7 +15,8 @@
 //                           R^T  = U^T - S^T Y^T
 //                           O^T  = S^T Qg^T + R^T Aqk^T
 //                           S^T <- S^T diag(d) + R^T Kt
-//                       Operand blobs arrive by 1-D bulk copies on mbarriers.
+//                       The B operands are the prep kernel's row-major tiles, brought in by tiled
+//                       TMA loads in the swizzled layout of their role (chunk_common.cuh).
 //
 // Math per chunk (reference: src/gdn2_sm120/reference.py:149-172, chunk.py:188-331, with the
 // chunk length re-chosen as 64 and the decay normalisation anchored per 16-token block so that
@@ -75,11 +76,11 @@ static_assert(kStageQ + kStageTile16 <= 16 * kRsN && kStageW + kStageTile16 <= 2
 
 struct PrepParams {
   const void *q, *k, *v, *g, *beta, *w;
-  uint8_t* ws;   // workspace (D, status; training: the tiles backward consumes)
-  uint8_t* sc;   // scratch (the tiles the forward scan consumes)
+  uint8_t* ws;   // workspace (D, status)
+  ForwardTiles tiles;  // the tile arrays (in the workspace for a training call, else in the scratch)
   int64_t T, H, n_chunks, n_ch;
   float scale;
-  int training;  // also write the transposed tiles that backward consumes
+  int training;  // also write T^T, which only backward consumes
   int prologue;  // kPrologueNorm | kPrologueGate: the inputs are raw projections / gate pre-activations
 };
 
@@ -94,10 +95,9 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
                   const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_q,
                   const __grid_constant__ CUtensorMap tm_beta, const __grid_constant__ CUtensorMap tm_v,
                   const __grid_constant__ CUtensorMap tm_w) {
-  extern __shared__ __align__(128) uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   PrepSmem& sm = *reinterpret_cast<PrepSmem*>(smem_raw);
   const WsLayout ws{p.n_ch, p.training != 0};
-  const ScratchLayout sc{p.n_ch};
   int* status = reinterpret_cast<int*>(p.ws + ws.off_status());
   BoundedWaiter waiter(status);
   const bool training = p.training != 0;
@@ -268,14 +268,13 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
     t_far[1][f] = (mb + 3 < 4) ? __expf(sm.part[4 * (mb + 3)][kc] - a_nx[f]) : 0.f;
   }
 
-  uint8_t* blob_q = p.sc + sc.off_q() + int64_t(ch) * kBlobQ;
-  uint8_t* blob_kt = p.sc + sc.off_kt() + int64_t(ch) * kBlobKt;
-  uint8_t* blob_kn = p.ws + ws.off_kn() + int64_t(ch) * kBlobKn;
-  float ebar[4][4], ktail[4][4], qgam[4][4];
+  float* tile_q = reinterpret_cast<float*>(p.tiles.q + int64_t(ch) * kTileQ);
+  float* tile_kn = reinterpret_cast<float*>(p.tiles.kn + int64_t(ch) * kTileKn);
+  float ebar[4][4];
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
     const int i = 4 * tg + e;
-    float ea[4], qa[4], kown[4], knb[4];
+    float ea[4], qa[4], kown[4], knb[4], qgam[4], ktail[4];
 #pragma unroll
     for (int f = 0; f < 4; ++f) {
       const float Gi = Gc[e][f] + sm.part[tg][kc0 + f];
@@ -287,10 +286,10 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
       ea[f] = to_tf32(bk * anchored);
       qa[f] = to_tf32(sq * anchored);
       ebar[e][f] = to_tf32(bk * anchored * e_amb[f]);
-      qgam[e][f] = to_tf32(sq * anchored * e_amb[f]);
+      qgam[f] = to_tf32(sq * anchored * e_amb[f]);
       kown[f] = to_tf32(kk[e][f] * own);
       knb[f] = kk[e][f] * nb;
-      ktail[e][f] = to_tf32(knb[f] * t_end[f]);
+      ktail[f] = to_tf32(knb[f] * t_end[f]);
     }
     // Gram A operand rows i (erase) and 64 + i (query), tf32, K-major, padded chunk stride
     *reinterpret_cast<float4*>(sm.gram_a + (i >> 3) * kRsN + c4 * kCsN + (i & 7) * 16) =
@@ -313,30 +312,9 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
                         to_tf32(knb[2] * t_far[far][2]), to_tf32(knb[3] * t_far[far][3]));
       }
     }
-    // natural workspace tiles X[r = i][c = k]: Q_gamma always, K_tail when training.  The chunks of
-    // tokens i - 1 and i (i odd) are neighbours in a blocked tile: one 32-byte store for the pair.
-    if (e & 1) {
-      const uint32_t off = blk_off<4>(i - 1, kc0, 4096, 128);
-      store_global_32b(blob_q + off, make_float4(qgam[e - 1][0], qgam[e - 1][1], qgam[e - 1][2], qgam[e - 1][3]),
-                       make_float4(qgam[e][0], qgam[e][1], qgam[e][2], qgam[e][3]));
-      if (training) {
-        store_global_32b(blob_kn + off, make_float4(ktail[e - 1][0], ktail[e - 1][1], ktail[e - 1][2], ktail[e - 1][3]),
-                         make_float4(ktail[e][0], ktail[e][1], ktail[e][2], ktail[e][3]));
-      }
-    }
-  }
-  // transposed workspace tiles X[r = channel][c = token]: one 16-byte chunk (4 tokens) per channel, the
-  // chunks of channels f and f + 1 next to each other
-#pragma unroll
-  for (int f = 0; f < 4; f += 2) {
-    const uint32_t off = blk_off<4>(kc0 + f, 4 * tg, 2048, 128);
-    store_global_32b(blob_kt + off, make_float4(ktail[0][f], ktail[1][f], ktail[2][f], ktail[3][f]),
-                     make_float4(ktail[0][f + 1], ktail[1][f + 1], ktail[2][f + 1], ktail[3][f + 1]));
-    if (training) {
-      store_global_32b(p.ws + ws.off_qt() + int64_t(ch) * kBlobQt + off,
-                       make_float4(qgam[0][f], qgam[1][f], qgam[2][f], qgam[3][f]),
-                       make_float4(qgam[0][f + 1], qgam[1][f + 1], qgam[2][f + 1], qgam[3][f + 1]));
-    }
+    // token-major tiles Q[i][k] and Kn[i][k]: the 16 lanes of a token write 256 consecutive bytes
+    *reinterpret_cast<float4*>(tile_q + i * kDim + kc0) = make_float4(qgam[0], qgam[1], qgam[2], qgam[3]);
+    *reinterpret_cast<float4*>(tile_kn + i * kDim + kc0) = make_float4(ktail[0], ktail[1], ktail[2], ktail[3]);
   }
   if (tid < kDim) {
     reinterpret_cast<float*>(p.ws + ws.off_d() + int64_t(ch) * kBlobD)[tid] = __expf(sm.gend[tid]);
@@ -365,10 +343,9 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
   // the Gram operands are dead: region 1 becomes fp32 scratch, region 2 receives E^T and Z^T
   float* Ln = reinterpret_cast<float*>(sm.gram_a);           // [64][kLd]   L
   float* Tn = Ln + 64 * kLd;                                  // [64][kLd]   T
-  float* An = Tn + 64 * kLd;                                  // [64][kLd]   A_qk, natural (training)
-  float* Tc = An + 64 * kLd;                                  // [64][kLd]   T transposed: Tc[j][i] = T[i][j]
+  float* Tc = Tn + 64 * kLd;                                  // [64][kLd]   T transposed: Tc[j][i] = T[i][j]
   float* Wt = Tc + 64 * kLd;                                  // [3][16][kLdW] block products, transposed
-  static_assert((4 * 64 * kLd + 3 * 16 * kLdW) * 4 <= 16 * kRsN, "fp32 scratch exceeds the Gram A region");
+  static_assert((3 * 64 * kLd + 3 * 16 * kLdW) * 4 <= 16 * kRsN, "fp32 scratch exceeds the Gram A region");
   uint8_t* et_tile = sm.gram_b;                               // E^T  X[r = k][c = j], tf32, RS kRsT
   uint8_t* zt_tile = sm.gram_b + kTileT;                      // Z^T  X[r = v][c = j], tf32, RS kRsT
 #pragma unroll
@@ -385,7 +362,7 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
     const int I_lo = (q4 & 1) * 2;
     const int my_I = I_lo + (lane >> 4);
     const int c0 = 16 * part;
-    uint8_t* blob_a = p.sc + sc.off_a() + int64_t(ch) * kBlobA;
+    float* tile_at = reinterpret_cast<float*>(p.tiles.at + int64_t(ch) * kTileAt);
     uint32_t lo[16], hi[16];
     const bool need_lo = c0 < 16 * (I_lo + 1), need_hi = c0 < 16 * (I_lo + 2);
     if (need_lo) tmem_ld16(tmem_addr(tb, 32 * q4, gram_col(I_lo) + c0), lo);
@@ -403,15 +380,9 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
 #pragma unroll
       for (int j = 0; j < 16; ++j) Ln[i * kLd + c0 + j] = vals[j];
     } else {
+      // A_qk leaves transposed, At[j][i]: the 32 lanes of a warp (rows i) fill one 128-byte line per column j
 #pragma unroll
-      for (int j4 = 0; j4 < 4; ++j4) {
-        *reinterpret_cast<float4*>(blob_a + blk_off<4>(i, c0 + 4 * j4, 2048, 128)) =
-            make_float4(vals[4 * j4], vals[4 * j4 + 1], vals[4 * j4 + 2], vals[4 * j4 + 3]);
-      }
-      if (training) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) An[i * kLd + c0 + j] = vals[j];
-      }
+      for (int j = 0; j < 16; ++j) tile_at[(c0 + j) * kChunk + i] = vals[j];
     }
   }
   for (int e = tid; e < 64 * kLd / 4; e += kPrepThreads) {
@@ -524,23 +495,21 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
     Tc[cc * kLd + 32 + r] = -s;
   }
   __syncthreads();
-  // T as tf32 tile X[r = i][c = j] in shared memory (MMA operand); its transpose goes to the workspace when training
+  // T as tf32 tile X[r = i][c = j] in shared memory (MMA operand); T^T[j][i] goes to the workspace when training
   {
     for (int e = tid; e < 64 * 16; e += kPrepThreads) {
       const int i = e & 63, c4t = e >> 6;  // consecutive threads -> consecutive rows -> contiguous 16-byte chunks
       const float4 tn = ld4(Tn + i * kLd + 4 * c4t);
-      const float4 val = make_float4(to_tf32(tn.x), to_tf32(tn.y), to_tf32(tn.z), to_tf32(tn.w));
-      const uint32_t off = blk_off<4>(i, 4 * c4t, 2048, 128);
-      *reinterpret_cast<float4*>(sm.tmat + off) = val;
-      if (training) {
-        // transposed tiles X[r = j][c = i]: here `i` plays the role of the row j, 4*c4t.. of the column i
-        const int j = i;
+      *reinterpret_cast<float4*>(sm.tmat + blk_off<4>(i, 4 * c4t, 2048, 128)) =
+          make_float4(to_tf32(tn.x), to_tf32(tn.y), to_tf32(tn.z), to_tf32(tn.w));
+    }
+    if (training) {
+      float* tile_tt = reinterpret_cast<float*>(p.tiles.tt + int64_t(ch) * kTileTt);
+      for (int e = tid; e < 64 * 16; e += kPrepThreads) {
+        const int j = e >> 4, c4t = e & 15;  // consecutive threads -> consecutive 16-byte pieces of a row
         const float4 tc = ld4(Tc + j * kLd + 4 * c4t);
-        *reinterpret_cast<float4*>(p.ws + ws.off_tt() + int64_t(ch) * kBlobTt + off) =
+        *reinterpret_cast<float4*>(tile_tt + j * kChunk + 4 * c4t) =
             make_float4(to_tf32(tc.x), to_tf32(tc.y), to_tf32(tc.z), to_tf32(tc.w));
-        *reinterpret_cast<float4*>(p.ws + ws.off_at() + int64_t(ch) * kBlobAt + off) =
-            make_float4(An[(4 * c4t) * kLd + j], An[(4 * c4t + 1) * kLd + j], An[(4 * c4t + 2) * kLd + j],
-                        An[(4 * c4t + 3) * kLd + j]);
       }
     }
   }
@@ -548,7 +517,7 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
   tc_fence_before();
   __syncthreads();
 
-  // ---- Y = T E (rows 0..63 of an M = 128 product), U^T = Z^T T^T, and Y^T = E^T T^T when training ----
+  // ---- Y = T E (rows 0..63 of an M = 128 product) and U^T = Z^T T^T ----------------------------------
   if (tid == 0) {
     tc_fence_after();
     // region 1 (fp32 scratch) is dead: g, k, q of the next unit land there under the MMAs and the epilogue
@@ -566,13 +535,6 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
       mma_tf32_ss(tb + 128, smem_desc(z0 + ks * 256, 128, kRsT), smem_desc(t0a + ks * 256, 128, 2048), id_u,
                   ks > 0 ? 1u : 0u);
     }
-    if (training) {
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        mma_tf32_ss(tb + 192, smem_desc(e0 + ks * 256, 128, kRsT), smem_desc(t0a + ks * 256, 128, 2048), id_u,
-                    ks > 0 ? 1u : 0u);
-      }
-    }
     mma_commit(&sm.bar[1]);
   }
   waiter.wait(&sm.bar[1], par);
@@ -580,47 +542,31 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
   // the MMAs have read E^T and Z^T: beta, v, w of the next unit land in region 2 under the epilogue
   if (tid == 0 && ch_next < n_ch) issue_bvw(ch_next);
   {
-    auto rn4 = [](const uint32_t* r) {
-      return make_float4(to_tf32(__uint_as_float(r[0])), to_tf32(__uint_as_float(r[1])),
-                         to_tf32(__uint_as_float(r[2])), to_tf32(__uint_as_float(r[3])));
-    };
-    // Y: lanes 0..63 hold rows i; the four warps of quadrants 0 and 1 take 32 key columns each
+    // Both accumulators leave transposed: a register holds one column, the 32 lanes of a warp hold 32
+    // consecutive rows of it, which are 128 consecutive bytes of the row-major tile.
+    // Y (lanes 0..63 = tokens i): Yt[k][i]; the four warps of quadrants 0 and 1 take 32 key columns each
     if (q4 < 2) {
       const int i = 32 * q4 + lane;
-      uint8_t* blob_y = p.sc + sc.off_y() + int64_t(ch) * kBlobY;
+      float* tile_yt = reinterpret_cast<float*>(p.tiles.yt + int64_t(ch) * kTileYt) + i;
 #pragma unroll
       for (int c0 = 32 * part; c0 < 32 * part + 32; c0 += 16) {
         uint32_t r[16];
         tmem_ld16(tmem_addr(tb, 32 * q4, c0), r);
         tmem_wait_ld();
 #pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          *reinterpret_cast<float4*>(blob_y + blk_off<4>(i, c0 + 4 * j4, 4096, 128)) = rn4(r + 4 * j4);
-        }
+        for (int j = 0; j < 16; ++j) tile_yt[(c0 + j) * kChunk] = to_tf32(__uint_as_float(r[j]));
       }
     }
-    // U^T (kept in full fp32) and Y^T: lane = value / key row; each warp of a quadrant takes 16 tokens
+    // U^T (lanes = values v; kept in full fp32): U[j][v]; each warp of a quadrant takes 16 tokens
     {
       const int row = 32 * q4 + lane;
       const int c0 = 16 * part;
-      uint8_t* blob_ut = p.sc + sc.off_ut() + int64_t(ch) * kBlobUt;
+      float* tile_u = reinterpret_cast<float*>(p.tiles.u + int64_t(ch) * kTileU) + row;
       uint32_t r[16];
       tmem_ld16(tmem_addr(tb, 32 * q4, 128 + c0), r);
       tmem_wait_ld();
 #pragma unroll
-      for (int j4 = 0; j4 < 4; ++j4) {
-        *reinterpret_cast<uint4*>(blob_ut + blk_off<4>(row, c0 + 4 * j4, 2048, 128)) =
-            make_uint4(r[4 * j4], r[4 * j4 + 1], r[4 * j4 + 2], r[4 * j4 + 3]);
-      }
-      if (training) {
-        uint8_t* blob_yt = p.ws + ws.off_yt() + int64_t(ch) * kBlobYt;
-        tmem_ld16(tmem_addr(tb, 32 * q4, 192 + c0), r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          *reinterpret_cast<float4*>(blob_yt + blk_off<4>(row, c0 + 4 * j4, 2048, 128)) = rn4(r + 4 * j4);
-        }
-      }
+      for (int j = 0; j < 16; ++j) tile_u[(c0 + j) * kDim] = __uint_as_float(r[j]);
     }
   }
   }  // units of this CTA
@@ -635,11 +581,12 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
 constexpr int kScanThreads = 512;
 
 struct ScanSmem {
-  alignas(128) uint8_t y[32768];
-  alignas(128) uint8_t ut[32768];
-  alignas(128) uint8_t q[32768];
-  alignas(128) uint8_t kt[32768];
-  alignas(128) uint8_t a[16384];
+  // swizzled operand tiles, slabs of 32 columns (tc05.cuh): Yt and At and Kn are read MN-major, Q K-major
+  alignas(1024) uint8_t yt[32768];   // Yt[k][i]: 2 slabs of 128 lines
+  alignas(1024) uint8_t q[32768];    // Q[i][k]:  4 slabs of 64 lines
+  alignas(1024) uint8_t kn[32768];   // Kn[j][k]: 4 slabs of 64 lines
+  alignas(1024) uint8_t at[16384];   // At[j][i]: 2 slabs of 64 lines
+  alignas(1024) float u[kChunk * kDim];  // U[j][v], plain rows: threads copy it into tensor memory
   alignas(16) float d[kDim];
   alignas(8) uint64_t bar_yqa, bar_ut, bar_kt, bar_mma1, bar_mma2;
   uint32_t tmem_base;
@@ -647,7 +594,6 @@ struct ScanSmem {
 
 struct ScanParams {
   const uint8_t* ws;   // workspace (D)
-  const uint8_t* sc;   // scratch (Y, Ut, Q, Kt, A)
   const float* s_in;   // [B,H,128,128] or null
   void* out;           // [B,T,H,128]
   float* s_out;        // [B,H,128,128] or null
@@ -659,11 +605,13 @@ struct ScanParams {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanParams p) {
-  extern __shared__ __align__(128) uint8_t smem_raw[];
+__global__ void __launch_bounds__(kScanThreads, 1)
+chunk_scan_kernel(const ScanParams p, const __grid_constant__ CUtensorMap tm_yt,
+                  const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kn,
+                  const __grid_constant__ CUtensorMap tm_at, const __grid_constant__ CUtensorMap tm_u) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   ScanSmem& sm = *reinterpret_cast<ScanSmem*>(smem_raw);
   const WsLayout ws{p.n_ch, p.training != 0};
-  const ScratchLayout sc{p.n_ch};
   BoundedWaiter waiter(p.status);
   // a wait that ran out in the prep kernel left garbage tiles: results become NaN from the start
   const bool upstream_failed = *static_cast<volatile const int*>(p.status) != kStatusOk;
@@ -699,20 +647,24 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
 
   auto ch_of = [&](int64_t c) { return (b * p.n_chunks + c) * p.H + h; };
   auto load_yqa = [&](int64_t c) {
-    const int64_t ch = ch_of(c);
-    mbar_arrive_expect_tx(&sm.bar_yqa, uint32_t(kBlobY + kBlobQ + kBlobA));
-    bulk_g2s(sm.y, p.sc + sc.off_y() + ch * kBlobY, uint32_t(kBlobY), &sm.bar_yqa);
-    bulk_g2s(sm.q, p.sc + sc.off_q() + ch * kBlobQ, uint32_t(kBlobQ), &sm.bar_yqa);
-    bulk_g2s(sm.a, p.sc + sc.off_a() + ch * kBlobA, uint32_t(kBlobA), &sm.bar_yqa);
+    const int ch = int(ch_of(c));
+    mbar_arrive_expect_tx(&sm.bar_yqa, uint32_t(kTileYt + kTileQ + kTileAt));
+#pragma unroll
+    for (int s = 0; s < 2; ++s) tma_load_3d(sm.yt + s * 16384, &tm_yt, 32 * s, 0, ch, &sm.bar_yqa);
+#pragma unroll
+    for (int s = 0; s < 4; ++s) tma_load_3d(sm.q + s * 8192, &tm_q, 32 * s, 0, ch, &sm.bar_yqa);
+#pragma unroll
+    for (int s = 0; s < 2; ++s) tma_load_3d(sm.at + s * 8192, &tm_at, 32 * s, 0, ch, &sm.bar_yqa);
   };
   auto load_ut = [&](int64_t c) {
-    mbar_arrive_expect_tx(&sm.bar_ut, uint32_t(kBlobUt));
-    bulk_g2s(sm.ut, p.sc + sc.off_ut() + ch_of(c) * kBlobUt, uint32_t(kBlobUt), &sm.bar_ut);
+    mbar_arrive_expect_tx(&sm.bar_ut, uint32_t(kTileU));
+    tma_load_3d(sm.u, &tm_u, 0, 0, int(ch_of(c)), &sm.bar_ut);
   };
   auto load_kt = [&](int64_t c) {
     const int64_t ch = ch_of(c);
-    mbar_arrive_expect_tx(&sm.bar_kt, uint32_t(kBlobKt + kBlobD));
-    bulk_g2s(sm.kt, p.sc + sc.off_kt() + ch * kBlobKt, uint32_t(kBlobKt), &sm.bar_kt);
+    mbar_arrive_expect_tx(&sm.bar_kt, uint32_t(kTileKn + kBlobD));
+#pragma unroll
+    for (int s = 0; s < 4; ++s) tma_load_3d(sm.kn + s * 8192, &tm_kn, 32 * s, 0, int(ch), &sm.bar_kt);
     bulk_g2s(sm.d, p.ws + ws.off_d() + ch * kBlobD, uint32_t(kBlobD), &sm.bar_kt);
   };
 
@@ -744,13 +696,9 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
     // ---- R^T <- U^T (16 token columns of row v of the U^T tile into TMEM) ---------------------------
     waiter.wait(&sm.bar_ut, par);
     {
-      const uint8_t* row = sm.ut + (vrow >> 3) * 2048 + (vrow & 7) * 16 + (i0 / 4) * 128;
       uint32_t r[16];
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        const uint4 x = *reinterpret_cast<const uint4*>(row + c4 * 128);
-        r[4 * c4] = x.x; r[4 * c4 + 1] = x.y; r[4 * c4 + 2] = x.z; r[4 * c4 + 3] = x.w;
-      }
+      for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(sm.u[(i0 + j) * kDim + vrow]);
       tmem_st16(tmem_addr(tb, lane_base, kColR + i0), r);
       tmem_wait_st();
     }
@@ -760,23 +708,24 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
     if (tid == 0) {
       tc_fence_after();
       if (c + 1 < p.n_chunks) load_ut(c + 1);  // every thread has consumed the U^T tile
-      const uint32_t y0 = smem_u32(sm.y), q0 = smem_u32(sm.q), a0 = smem_u32(sm.a);
-      const uint32_t id_neg = idesc(128, 64, kFmtTF32, kMajorK, kMajorK, 1, 0);
-      const uint32_t id_pos = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
-      // R^T -= S^T Y^T   (A = state columns, K = 128 keys)
+      const uint32_t y0 = smem_u32(sm.yt), q0 = smem_u32(sm.q), a0 = smem_u32(sm.at);
+      const uint32_t id_neg_mn = idesc(128, 64, kFmtTF32, kMajorK, kMajorMN, 1, 0);
+      const uint32_t id_pos_k = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
+      const uint32_t id_pos_mn = idesc(128, 64, kFmtTF32, kMajorK, kMajorMN);
+      // R^T -= S^T Y^T   (A = state columns, K = 128 keys; B = Yt[k][i] read MN-major)
 #pragma unroll
       for (int ks = 0; ks < 16; ++ks) {
-        mma_tf32_ts(tb + kColR, tb + kColS + ks * 8, smem_desc(y0 + ks * 256, 128, 4096), id_neg, 1u);
+        mma_tf32_ts(tb + kColR, tb + kColS + ks * 8, smem_desc_sw128_mn(y0, 16384, ks), id_neg_mn, 1u);
       }
-      // O^T = S^T Qg^T
+      // O^T = S^T Qg^T   (B = Q[i][k] read K-major)
 #pragma unroll
       for (int ks = 0; ks < 16; ++ks) {
-        mma_tf32_ts(tb + kColO, tb + kColS + ks * 8, smem_desc(q0 + ks * 256, 128, 4096), id_pos, ks > 0 ? 1u : 0u);
+        mma_tf32_ts(tb + kColO, tb + kColS + ks * 8, smem_desc_sw128_k(q0, 8192, ks), id_pos_k, ks > 0 ? 1u : 0u);
       }
-      // O^T += R^T Aqk^T  (A = residual columns, K = 64 tokens)
+      // O^T += R^T Aqk^T  (A = residual columns, K = 64 tokens; B = At[j][i] read MN-major)
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        mma_tf32_ts(tb + kColO, tb + kColR + ks * 8, smem_desc(a0 + ks * 256, 128, 2048), id_pos, 1u);
+        mma_tf32_ts(tb + kColO, tb + kColR + ks * 8, smem_desc_sw128_mn(a0, 8192, ks), id_pos_mn, 1u);
       }
       mma_commit(&sm.bar_mma1);
     }
@@ -829,12 +778,12 @@ __global__ void __launch_bounds__(kScanThreads, 1) chunk_scan_kernel(const ScanP
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
-      const uint32_t kt0 = smem_u32(sm.kt);
-      const uint32_t id_s = idesc(128, 128, kFmtTF32, kMajorK, kMajorK);
-      // S^T += R^T Kt   (B tile X[r = key][c = token])
+      const uint32_t kn0 = smem_u32(sm.kn);
+      const uint32_t id_s = idesc(128, 128, kFmtTF32, kMajorK, kMajorMN);
+      // S^T += R^T Kt   (K = 64 tokens; B = Kn[j][k] read MN-major)
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        mma_tf32_ts(tb + kColS, tb + kColR + ks * 8, smem_desc(kt0 + ks * 256, 128, 2048), id_s, 1u);
+        mma_tf32_ts(tb + kColS, tb + kColR + ks * 8, smem_desc_sw128_mn(kn0, 8192, ks), id_s, 1u);
       }
       mma_commit(&sm.bar_mma2);
     }
@@ -906,9 +855,10 @@ int64_t chunk_workspace_bytes(int64_t batch, int64_t full_tokens, int64_t heads,
   return ws.total();
 }
 
-int64_t chunk_scratch_bytes(int64_t batch, int64_t full_tokens, int64_t heads, int backward) {
+// kind: 0 = forward of an inference call, 1 = backward, 2 = forward of a training call
+int64_t chunk_scratch_bytes(int64_t batch, int64_t full_tokens, int64_t heads, int kind) {
   const ScratchLayout sc{batch * (full_tokens / kChunk) * heads};
-  return backward ? sc.total_backward() : sc.total_forward();
+  return kind == 1 ? sc.total_backward() : sc.total_forward(kind == 2);
 }
 
 int64_t chunk_status_offset(int64_t batch, int64_t full_tokens, int64_t heads) {
@@ -946,7 +896,8 @@ int launch_chunk_forward(const void* q, const void* k, const void* v, const void
   const unsigned prep_grid = unsigned(n_ch < int64_t(sm_count) ? n_ch : int64_t(sm_count));
 
   profile_mark(0, stream);
-  PrepParams pp{q, k, v, g, beta, w, workspace, scratch, T, H, n_chunks, n_ch, scale, training, prologue};
+  const ForwardTiles tiles = forward_tiles(workspace, scratch, n_ch, training != 0);
+  PrepParams pp{q, k, v, g, beta, w, workspace, tiles, T, H, n_chunks, n_ch, scale, training, prologue};
   GDN2_DISPATCH_TYPES(dtype, g_dtype, {
     auto kernel = prologue != 0 ? chunk_prep_kernel<T, G, true> : chunk_prep_kernel<T, G, false>;
     const int smem = int(sizeof(PrepSmem));
@@ -958,18 +909,27 @@ int launch_chunk_forward(const void* q, const void* k, const void* v, const void
   if (st != GDN2_OK) return st;
   profile_mark(1, stream);
 
-  ScanParams sp{workspace, scratch, s_in, out, s_out, bnd, status, T, H, n_chunks, n_ch, workspace, training};
+  // the scan's operands: the same tiles, in the swizzle of the role the forward reads them in
+  CUtensorMap tm_yt, tm_q, tm_kn, tm_at, tm_u;
+  if (!encode_tile_map(&tm_yt, tiles.yt, n_ch, kDim, kChunk, true) ||
+      !encode_tile_map(&tm_q, tiles.q, n_ch, kChunk, kDim, false) ||
+      !encode_tile_map(&tm_kn, tiles.kn, n_ch, kChunk, kDim, true) ||
+      !encode_tile_map(&tm_at, tiles.at, n_ch, kChunk, kChunk, true) ||
+      !encode_plain_tile_map(&tm_u, tiles.u, n_ch, kChunk, kDim)) {
+    return GDN2_ERR_LAUNCH;
+  }
+  ScanParams sp{workspace, s_in, out, s_out, bnd, status, T, H, n_chunks, n_ch, workspace, training};
   const int smem = int(sizeof(ScanSmem));
   if (dtype == GDN2_BF16) {
     auto kernel = chunk_scan_kernel<__nv_bfloat16>;
     err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
-    kernel<<<unsigned(B * H), kScanThreads, smem, stream>>>(sp);
+    kernel<<<unsigned(B * H), kScanThreads, smem, stream>>>(sp, tm_yt, tm_q, tm_kn, tm_at, tm_u);
   } else {
     auto kernel = chunk_scan_kernel<__half>;
     err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), smem);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
-    kernel<<<unsigned(B * H), kScanThreads, smem, stream>>>(sp);
+    kernel<<<unsigned(B * H), kScanThreads, smem, stream>>>(sp, tm_yt, tm_q, tm_kn, tm_at, tm_u);
   }
   st = check_launch();
   profile_mark(2, stream);

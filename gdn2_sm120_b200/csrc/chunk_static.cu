@@ -34,7 +34,7 @@ namespace {
 constexpr int64_t kStaticMaxChunkHeads = GDN2_STATIC_MAX_CHUNK_HEADS;
 // inference workspace (chunk-end decays + status block) followed by the forward scratch tiles
 constexpr int64_t kStaticWorkspaceBytes = kStaticMaxChunkHeads * kBlobD + kStatusBytes;
-constexpr int64_t kStaticBytes = kStaticWorkspaceBytes + kStaticMaxChunkHeads * kBlobFwdScratch;
+constexpr int64_t kStaticBytes = kStaticWorkspaceBytes + kStaticMaxChunkHeads * (kTileU + kFwdTilesBytes);
 static_assert(kStaticWorkspaceBytes % 256 == 0, "the scratch part must keep the array's alignment");
 
 // Device-resident scratch.  In host code this name is only a handle for cudaGetSymbolAddress, never

@@ -158,6 +158,35 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
   return d;
 }
 
+// Swizzled operands, fetched by tiled TMA loads from a row-major fp32 matrix X[rows][cols] in slabs of
+// 32 columns: a slab is `rows` lines of 128 bytes, slab s of a tile starts s * rows * 128 bytes after
+// the tile (which is 1024-byte aligned).
+//   K-major operand (MN index = row, K index = column), TMA swizzle 128B: 8-line atoms, SBO = 1024;
+//     the K step of 8 tf32 values is 32 bytes inside the line, then the next slab.
+__device__ __forceinline__ uint64_t smem_desc_sw128_k(uint32_t tile, uint32_t slab_bytes, int kstep) {
+  const uint32_t saddr = tile + uint32_t(kstep >> 2) * slab_bytes + uint32_t(kstep & 3) * 32u;
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024u >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;  // 128-byte swizzle
+  return d;
+}
+//   MN-major operand (K index = row, MN index = column), TMA swizzle 128B with 32-byte atoms: 4-line
+//     atoms, SBO = 512 (next 4 rows of K), LBO = slab stride (next 32 columns of MN); the K step of 8
+//     rows is 1024 bytes.  32-bit operands have no other MN-major form.
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t tile, uint32_t slab_bytes, int kstep) {
+  const uint32_t saddr = tile + uint32_t(kstep) * 1024u;
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((slab_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>(512u >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(1) << 61;  // 128-byte swizzle, 32-byte atoms
+  return d;
+}
+
 enum : uint32_t { kFmtF16 = 0, kFmtBF16 = 1, kFmtTF32 = 2 };
 enum : uint32_t { kMajorK = 0, kMajorMN = 1 };
 
