@@ -58,7 +58,9 @@ struct PrepSmem {
   // region 2: tf32 Gram B operands K^I X[r = j < 16 (I + 1)][c = k]: 2 (I + 1) row groups each;
   //           after the Gram products: E^T at +0 and Z^T at +kTileT, tiles X[r = channel][c = j]
   alignas(128) uint8_t gram_b[20 * kRsN];               // 92160
-  alignas(128) uint8_t tmat[32768];    // T tile X[r = i][c = j], tf32, RS 2048 (rows 64..127 unused filler)
+  alignas(128) uint8_t tmat[32768];    // T tile X[r = i][c = j], tf32, RS 2048 (rows 64..127: filler of the M = 128
+                                       // product, whose output rows nobody reads; v of the next unit is staged there)
+  alignas(128) uint8_t stage_w[16384]; // w of the next unit
   float part[16][kDim];                // per 4-token group partial sums -> exclusive prefixes
   float gend[kDim];
   float nrm[16][2][4][2];              // fused prologue: per (warp, token group, token) sums of q^2, k^2 over 64 channels
@@ -66,13 +68,16 @@ struct PrepSmem {
   alignas(8) uint64_t bar_ld[2];       // raw inputs of the next unit: {g, k, q} and {beta, v, w}
   uint32_t tmem_base;
 };
-// landing zones of the raw [64][128] input tiles of the next unit, in regions that are dead by then:
-// g, k, q over the fp32 scratch in region 1 (free once T is written), beta, v, w over E^T / Z^T in
-// region 2 (free once the last MMAs have read them)
+// landing zones of the raw [64][128] input tiles of the next unit, in places that are dead by then:
+// g, k, q over the fp32 scratch in region 1 (free once T is written, just before the last MMAs);
+// beta behind E^T / Z^T in region 2, v in the filler rows of the T tile, w in its own buffer (free as
+// soon as the Gram products are done, half a unit earlier)
 constexpr int kStageK = 32768, kStageQ = 49152;                     // region 1: g at 0 (16 or 32 KiB)
-constexpr int kStageBeta = 0, kStageV = 16384, kStageW = 32768;     // region 2
+constexpr int kStageBeta = 2 * kTileT;                              // region 2, behind the two transposed tiles
+constexpr int kStageV = 16384;                                      // T tile, rows 64..127
 constexpr uint32_t kStageTile16 = kChunk * kDim * 2;                // a 16-bit input tile
-static_assert(kStageQ + kStageTile16 <= 16 * kRsN && kStageW + kStageTile16 <= 20 * kRsN, "staging exceeds its region");
+static_assert(kStageQ + kStageTile16 <= 16 * kRsN && kStageBeta + kStageTile16 <= 20 * kRsN, "staging exceeds its region");
+static_assert(kStageBeta % 128 == 0, "TMA destinations are 128-byte aligned");
 
 struct PrepParams {
   const void *q, *k, *v, *g, *beta, *w;
@@ -136,8 +141,8 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
     const int h_ = ch_ % heads, bc = ch_ / heads, row = (bc / chunks) * int(p.T) + (bc % chunks) * kChunk;
     mbar_arrive_expect_tx(&sm.bar_ld[1], 3 * kStageTile16);
     tma_load_3d(sm.gram_b + kStageBeta, &tm_beta, 0, h_, row, &sm.bar_ld[1]);
-    tma_load_3d(sm.gram_b + kStageV, &tm_v, 0, h_, row, &sm.bar_ld[1]);
-    tma_load_3d(sm.gram_b + kStageW, &tm_w, 0, h_, row, &sm.bar_ld[1]);
+    tma_load_3d(sm.tmat + kStageV, &tm_v, 0, h_, row, &sm.bar_ld[1]);
+    tma_load_3d(sm.stage_w, &tm_w, 0, h_, row, &sm.bar_ld[1]);
   };
   tc_fence_before();
   __syncthreads();
@@ -212,8 +217,8 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       rb[e] = *reinterpret_cast<const RawT*>(staged(sm.gram_b + kStageBeta, e, 2));
-      rv[e] = *reinterpret_cast<const RawT*>(staged(sm.gram_b + kStageV, e, 2));
-      rw[e] = *reinterpret_cast<const RawT*>(staged(sm.gram_b + kStageW, e, 2));
+      rv[e] = *reinterpret_cast<const RawT*>(staged(sm.tmat + kStageV, e, 2));
+      rw[e] = *reinterpret_cast<const RawT*>(staged(sm.stage_w, e, 2));
     }
     tc_fence_before();
     __syncthreads();
@@ -339,6 +344,8 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
   }
   waiter.wait(&sm.bar[0], par);
   tc_fence_after();
+  // the Gram operands are dead: beta, v, w of the next unit start to arrive
+  if (tid == 0 && ch_next < n_ch) issue_bvw(ch_next);
 
   // the Gram operands are dead: region 1 becomes fp32 scratch, region 2 receives E^T and Z^T
   float* Ln = reinterpret_cast<float*>(sm.gram_a);           // [64][kLd]   L
@@ -539,8 +546,6 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
   }
   waiter.wait(&sm.bar[1], par);
   tc_fence_after();
-  // the MMAs have read E^T and Z^T: beta, v, w of the next unit land in region 2 under the epilogue
-  if (tid == 0 && ch_next < n_ch) issue_bvw(ch_next);
   {
     // Both accumulators leave transposed: a register holds one column, the 32 lanes of a warp hold 32
     // consecutive rows of it, which are 128 consecutive bytes of the row-major tile.
