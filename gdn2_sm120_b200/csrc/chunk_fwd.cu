@@ -385,7 +385,10 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
     }
     if (r < 64) {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) Ln[i * kLd + c0 + j] = vals[j];
+      for (int j4 = 0; j4 < 4; ++j4) {
+        *reinterpret_cast<float4*>(Ln + i * kLd + c0 + 4 * j4) =
+            make_float4(vals[4 * j4], vals[4 * j4 + 1], vals[4 * j4 + 2], vals[4 * j4 + 3]);
+      }
     } else {
       // A_qk leaves transposed, At[j][i]: the 32 lanes of a warp (rows i) fill one 128-byte line per column j
 #pragma unroll
@@ -467,39 +470,49 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
   }
   __syncthreads();
   // level 2, W2 = L[32.., ..32) P, stored transposed over the (now dead) first 32 rows of L
+  // A thread forms two entries of a column (rows r and r + 16): the column of the right factor is the
+  // expensive read (a different 16-byte piece per lane, four shared-memory wavefronts), the row of the
+  // left factor is a broadcast; the column is read once for both.
   float* W2t = Ln;  // W2t[c][r] = W2[r][c], leading dimension kLd
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int e = tid + kPrepThreads * half, r = e >> 5, cc = e & 31;
+  {
+    const int r = tid >> 5, cc = tid & 31;
     const float* lrow = Ln + (32 + r) * kLd;
     const float* pcol = Tc + cc * kLd;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 acc0 = make_float4(0.f, 0.f, 0.f, 0.f), acc1 = acc0;
 #pragma unroll
     for (int m4 = 0; m4 < 8; ++m4) {
-      const float4 a = ld4(lrow + 4 * m4), b = ld4(pcol + 4 * m4);
-      acc.x = fmaf(a.x, b.x, acc.x); acc.y = fmaf(a.y, b.y, acc.y);
-      acc.z = fmaf(a.z, b.z, acc.z); acc.w = fmaf(a.w, b.w, acc.w);
+      const float4 b = ld4(pcol + 4 * m4);
+      const float4 a0 = ld4(lrow + 4 * m4), a1 = ld4(lrow + 16 * kLd + 4 * m4);
+      acc0.x = fmaf(a0.x, b.x, acc0.x); acc0.y = fmaf(a0.y, b.y, acc0.y);
+      acc0.z = fmaf(a0.z, b.z, acc0.z); acc0.w = fmaf(a0.w, b.w, acc0.w);
+      acc1.x = fmaf(a1.x, b.x, acc1.x); acc1.y = fmaf(a1.y, b.y, acc1.y);
+      acc1.z = fmaf(a1.z, b.z, acc1.z); acc1.w = fmaf(a1.w, b.w, acc1.w);
     }
     // rows 32.. of L are read above by other threads; W2t lives in rows 0..31, which nobody reads any more
-    W2t[cc * kLd + r] = (acc.x + acc.y) + (acc.z + acc.w);
+    W2t[cc * kLd + r] = (acc0.x + acc0.y) + (acc0.z + acc0.w);
+    W2t[cc * kLd + r + 16] = (acc1.x + acc1.y) + (acc1.z + acc1.w);
   }
   __syncthreads();
   // level 2, T[32 + r][c] = -sum_m Q[r][m] W2[m][c]
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int e = tid + kPrepThreads * half, r = e >> 5, cc = e & 31;
+  {
+    const int r = tid >> 5, cc = tid & 31;
     const float* qrow = Tn + (32 + r) * kLd + 32;
     const float* wcol = W2t + cc * kLd;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 acc0 = make_float4(0.f, 0.f, 0.f, 0.f), acc1 = acc0;
 #pragma unroll
     for (int m4 = 0; m4 < 8; ++m4) {
-      const float4 a = ld4(qrow + 4 * m4), b = ld4(wcol + 4 * m4);
-      acc.x = fmaf(a.x, b.x, acc.x); acc.y = fmaf(a.y, b.y, acc.y);
-      acc.z = fmaf(a.z, b.z, acc.z); acc.w = fmaf(a.w, b.w, acc.w);
+      const float4 b = ld4(wcol + 4 * m4);
+      const float4 a0 = ld4(qrow + 4 * m4), a1 = ld4(qrow + 16 * kLd + 4 * m4);
+      acc0.x = fmaf(a0.x, b.x, acc0.x); acc0.y = fmaf(a0.y, b.y, acc0.y);
+      acc0.z = fmaf(a0.z, b.z, acc0.z); acc0.w = fmaf(a0.w, b.w, acc0.w);
+      acc1.x = fmaf(a1.x, b.x, acc1.x); acc1.y = fmaf(a1.y, b.y, acc1.y);
+      acc1.z = fmaf(a1.z, b.z, acc1.z); acc1.w = fmaf(a1.w, b.w, acc1.w);
     }
-    const float s = (acc.x + acc.y) + (acc.z + acc.w);
-    Tn[(32 + r) * kLd + cc] = -s;
-    Tc[cc * kLd + 32 + r] = -s;
+    const float s0 = (acc0.x + acc0.y) + (acc0.z + acc0.w), s1 = (acc1.x + acc1.y) + (acc1.z + acc1.w);
+    Tn[(32 + r) * kLd + cc] = -s0;
+    Tc[cc * kLd + 32 + r] = -s0;
+    Tn[(48 + r) * kLd + cc] = -s1;
+    Tc[cc * kLd + 48 + r] = -s1;
   }
   __syncthreads();
   // T as tf32 tile X[r = i][c = j] in shared memory (MMA operand); T^T[j][i] goes to the workspace when training
