@@ -310,8 +310,9 @@ constexpr int kRsS = 16 * kCsS;        // 2304
 // dynamic shared memory map (bytes).  Phase B = products with the states, phase C = Gram VJP.
 constexpr int kOffStack = 0;                      // B: [dZ ; dO] X[r = 128][c = v], RS kRsN     73728 (dZ rows: bulk copy)
 constexpr int kOffRn = kOffStack + 16 * kRsN;     // B: R X[r = j][c = v], RS 4096 (bulk copy)   32768
-constexpr int kOffS0 = kOffRn + 32768;            // B: S_0 X[r = k][c = v], RS 4096             65536
-constexpr int kOffDs1 = kOffS0 + 65536;           // B: dS_1 half X[r = k][c = 64 v], RS 2048    32768
+constexpr int kOffS0 = kOffRn + 32768;            // B: S_0[k][v], 4 swizzled slabs of 128 lines  65536
+constexpr int kOffDs1 = kOffS0 + 65536;           // B: dS_1[k][64 v] half, 2 swizzled slabs      32768
+static_assert(kOffS0 % 1024 == 0 && kOffDs1 % 1024 == 0, "swizzled tiles are 1024-byte aligned");
 constexpr int kEndB = kOffDs1 + 32768;            // 204800
 constexpr int kOffStack2 = 0;                     // C: [dL_I ; dA_I] for I = 0..3, X[r = 128][c = j], RS 2048   32768
 constexpr int kOffDLt = 32768;                    // C: dL^T X[r = j][c = i], RS kRsS            18432
@@ -419,7 +420,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
                      const __grid_constant__ CUtensorMap tm_ds, const __grid_constant__ CUtensorMap tm_dq,
                      const __grid_constant__ CUtensorMap tm_dk) {
   using O = typename std::conditional<kF32Grads, float, T>::type;  // element type of dq, dk, dv, dbeta, dw
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ __align__(1024) uint8_t smem[];
   VjpMisc& ms = *reinterpret_cast<VjpMisc*>(smem + kOffMisc);
   const WsLayout ws{p.n_ch, true};
   const ScratchLayout sc{p.n_ch};
@@ -451,11 +452,12 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
   constexpr uint32_t kColD2 = 64, kColD3 = 128, kColD4 = 256, kColD5 = 320;
 
   // Everything the first MMA batch of a chunk-head reads arrives asynchronously: the dZ rows of the
-  // stack and the residual R as 1-D bulk copies, S_0 and the first 64 value columns of dS_1 as 5-D tiled
-  // TMA loads that turn the row-major fp32 checkpoints into blocked K-major tiles on the way (the
-  // tensor cores read the fp32 containers as tf32).  No register staging.  The kernel is persistent:
-  // one SM takes in bytes at a limited rate, so the copies for the CTA's next chunk-head are issued as
-  // soon as the last MMA of the current one has read shared memory, and land during its final chain.
+  // stack and the residual R as 1-D bulk copies, S_0 and the first 64 value columns of dS_1 as tiled TMA
+  // loads (128-byte swizzle) that put the row-major fp32 checkpoints into shared memory as K-major
+  // operands, 32 value columns per slab (the tensor cores read the fp32 containers as tf32).  No
+  // register staging.  The kernel is persistent: one SM takes in bytes at a limited rate, so the copies
+  // for the CTA's next chunk-head are issued as soon as the last MMA of the current one has read shared
+  // memory, and land during its final chain.
   // The chain keeps the dO rows of the stack and the dS_1 buffer for its own tiles, so the copies come in
   // two parts: S_0, R and dZ before the chain, the dS_1 half after it (bar_s expects both from the start).
   auto s0_slot_of = [&](int64_t ch_) {
@@ -464,13 +466,17 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
   };
   auto issue_loads = [&](int64_t ch_) {
     mbar_arrive_expect_tx(&ms.bar_s, uint32_t(65536 + 32768));
-    tma_load_5d(smem + kOffS0, &tm_s0, 0, 0, 0, 0, s0_slot_of(ch_), &ms.bar_s);
+#pragma unroll
+    for (int sl = 0; sl < 4; ++sl) tma_load_3d(smem + kOffS0 + sl * 16384, &tm_s0, 32 * sl, 0, s0_slot_of(ch_), &ms.bar_s);
     mbar_arrive_expect_tx(&ms.bar_a, uint32_t(kBlobDZ + kBlobRn));
     bulk_g2s(smem + kOffRn, p.ws + ws.off_rn() + ch_ * kBlobRn, uint32_t(kBlobRn), &ms.bar_a);
     bulk_g2s(smem + kOffStack, p.sc + sc.off_dz() + ch_ * kBlobDZ, uint32_t(kBlobDZ), &ms.bar_a);
   };
   auto issue_ds1 = [&](int64_t ch_) {
-    tma_load_5d(smem + kOffDs1, &tm_ds, 0, 0, 0, 0, s0_slot_of(ch_) + int(p.H), &ms.bar_s);
+#pragma unroll
+    for (int sl = 0; sl < 2; ++sl) {
+      tma_load_3d(smem + kOffDs1 + sl * 16384, &tm_ds, 32 * sl, 0, s0_slot_of(ch_) + int(p.H), &ms.bar_s);
+    }
   };
   if (tid == 0 && int64_t(blockIdx.x) < p.n_ch) {
     issue_loads(blockIdx.x);
@@ -487,24 +493,24 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
   auto seq_idx = [&](int tok) { return ((b * p.T + t0 + tok) * p.H + h) * int64_t(kDim); };
   const int ds1_slot = int((b * (p.n_chunks + 1) + c + 1) * p.H + h);
   // dd[k] += sum over the 64 value columns of half `hf` of dS_1[k][v] S_0[k][v], both read from their
-  // shared-memory tiles.  chunk id qd = tid + 512 x: key row = (qd & 7) + 8 (qd >> 7), 4-value chunk = (qd >> 3) & 15
+  // shared-memory tiles.  The two tiles are swizzled alike (a line = 32 values of one key row, its
+  // 16-byte pieces permuted by the row), so equal positions hold equal (k, v) and the order inside a
+  // line does not matter for the sum.  Piece qd = tid + 512 x: line (qd >> 3) = slab * 128 + k, piece qd & 7.
   auto dd_half = [&](int hf) {
 #pragma unroll
     for (int x = 0; x < 4; ++x) {
       const int qd = tid + 512 * x;
-      const int v4 = (qd >> 3) & 15;
-      const float4 ds = *reinterpret_cast<const float4*>(smem + kOffDs1 + (qd >> 7) * 2048 + v4 * 128 + (qd & 7) * 16);
-      const float4 s0 = *reinterpret_cast<const float4*>(smem + kOffS0 + (qd >> 7) * 4096 + (v4 + 16 * hf) * 128 + (qd & 7) * 16);
+      const int line = qd >> 3, slab = line >> 7, kr = line & 127;
+      const float4 ds = *reinterpret_cast<const float4*>(smem + kOffDs1 + slab * 16384 + kr * 128 + (qd & 7) * 16);
+      const float4 s0 = *reinterpret_cast<const float4*>(smem + kOffS0 + (2 * hf + slab) * 16384 + kr * 128 + (qd & 7) * 16);
       float acc = ds.x * s0.x + ds.y * s0.y + ds.z * s0.z + ds.w * s0.w;
-      // lanes that differ in bits 3, 4 hold other value chunks of the same key row
-      acc += __shfl_xor_sync(0xffffffffu, acc, 8);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 16);
-      // one owner per (warp & 3, key row): partial sums in a fixed order, no atomics, so that the
-      // result does not depend on the timing of the warps (xt is free until the end of the chain)
-      if ((lane >> 3) == 0) {
-        float* slot = &ms.xt[warp & 3][(qd & 7) + 8 * (qd >> 7)];
-        *slot = (hf == 0) ? acc : *slot + acc;
-      }
+      // the 8 lanes of a line
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      // one owner per (half, slab, key row): partial sums in fixed slots, no atomics, so that the result
+      // does not depend on the timing of the warps (xt is free until the end of the chain)
+      if ((lane & 7) == 0) ms.xt[2 * hf + slab][kr] = acc;
     }
   };
 
@@ -552,7 +558,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     const uint32_t id128 = idesc(128, 128, kFmtTF32, kMajorK, kMajorK);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
-      mma_tf32_ss(tb + kColD4, smem_desc(d1 + ks * 256, 128, 2048), smem_desc(rn + ks * 256, 128, 4096), id64,
+      mma_tf32_ss(tb + kColD4, smem_desc_sw128_k(d1, 16384, ks), smem_desc(rn + ks * 256, 128, 4096), id64,
                   ks > 0 ? 1u : 0u);
     }
     mma_commit(&ms.bar_r);  // the dS_1 buffer may be refilled once these have run
@@ -563,14 +569,15 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     }
 #pragma unroll
     for (int ks = 0; ks < 16; ++ks) {
-      mma_tf32_ss(tb + kColD3, smem_desc(s0 + ks * 256, 128, 4096), smem_desc(st + ks * 2 * kCsN, kCsN, kRsN), id128,
+      mma_tf32_ss(tb + kColD3, smem_desc_sw128_k(s0, 16384, ks), smem_desc(st + ks * 2 * kCsN, kCsN, kRsN), id128,
                   ks > 0 ? 1u : 0u);
     }
     mma_commit(&ms.bar_m);
     // the second 64 value columns of dS_1 replace the first as soon as their product has run
     waiter.wait(&ms.bar_r, 0);
     mbar_arrive_expect_tx(&ms.bar_d, 32768u);
-    tma_load_5d(smem + kOffDs1, &tm_ds, 0, 0, 16, 0, ds1_slot, &ms.bar_d);
+#pragma unroll
+    for (int sl = 0; sl < 2; ++sl) tma_load_3d(smem + kOffDs1 + sl * 16384, &tm_ds, 64 + 32 * sl, 0, ds1_slot, &ms.bar_d);
   }
   // ---- under the tensor cores: log-decay prefixes, dv = dZ w, dw = dZ v, and the raw inputs of the
   // Gram operands.  Every load is issued before the first store: the outputs may alias the inputs as
@@ -622,7 +629,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     const uint32_t id64 = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
-      mma_tf32_ss(tb + kColD4, smem_desc(d1 + ks * 256, 128, 2048), smem_desc(rn + (8 + ks) * 256, 128, 4096), id64, 1u);
+      mma_tf32_ss(tb + kColD4, smem_desc_sw128_k(d1, 16384, ks), smem_desc(rn + (8 + ks) * 256, 128, 4096), id64, 1u);
     }
     mma_commit(&ms.bar_r);
   }
@@ -910,22 +917,6 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
 
 }  // namespace
 
-// ---- tensor maps ------------------------------------------------------------------------------------
-// A [n_slots][128 k][128 v] fp32 array of states seen as a 5-D tensor (v % 4, k % 8, v / 4, k / 8, slot):
-// a box (4, 8, box_v4, 16, 1) lands in shared memory as the blocked K-major tile X[r = k][c = v] of
-// 4 * box_v4 value columns (8 rows x 16 bytes core matrices, CS = 128, RS = 128 * box_v4).
-static bool encode_state_map(CUtensorMap* tm, const float* base, int64_t n_slots, int box_v4) {
-  EncodeTiledFn encode = encode_tiled_fn();
-  if (encode == nullptr) return false;
-  const cuuint64_t dims[5] = {4, 8, 32, 16, cuuint64_t(n_slots)};
-  const cuuint64_t strides[4] = {512, 16, 4096, 65536};  // bytes, dimensions 1..4
-  const cuuint32_t box[5] = {4, 8, cuuint32_t(box_v4), 16, 1};
-  const cuuint32_t elem_strides[5] = {1, 1, 1, 1, 1};
-  return encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, const_cast<float*>(base), dims, strides, box, elem_strides,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 // ---- launcher ---------------------------------------------------------------------------------------
 int launch_chunk_backward(const void* q, const void* k, const void* v, const void* g, const void* beta,
                           const void* w, const void* d_out, const float* ds_final, const float* bnd,
@@ -976,7 +967,8 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
   CUtensorMap tm_s0, tm_ds;
   const int64_t n_slots = B * (n_chunks + 1) * H;
   if ((reinterpret_cast<uintptr_t>(bnd) & 15u) != 0 || (reinterpret_cast<uintptr_t>(d_bnd) & 15u) != 0 ||
-      !encode_state_map(&tm_s0, bnd, n_slots, 32) || !encode_state_map(&tm_ds, d_bnd, n_slots, 16)) {
+      !encode_tile_map(&tm_s0, reinterpret_cast<const uint8_t*>(bnd), n_slots, kDim, kDim, false) ||
+      !encode_tile_map(&tm_ds, reinterpret_cast<const uint8_t*>(d_bnd), n_slots, kDim, kDim, false)) {
     return GDN2_ERR_LAUNCH;
   }
   // dq and dk leave the VJP kernel as [64][128] tiles through tiled TMA stores (rows b * T + t in 31 bits)

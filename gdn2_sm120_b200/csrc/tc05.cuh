@@ -69,17 +69,8 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
       "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
-// 1-D bulk copy shared -> global (bulk async-group completion).
-// 5-D tiled TMA load global -> shared; completion (bytes) on an mbarrier.  `tmap` points at a
+// 3-D tiled TMA load global -> shared; completion (bytes) on an mbarrier.  `tmap` points at a
 // CUtensorMap in kernel-parameter space.  c0 must keep c0 * element size a multiple of 16 bytes.
-__device__ __forceinline__ void tma_load_5d(void* smem_dst, const void* tmap, int c0, int c1, int c2, int c3, int c4,
-                                            uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
-      ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4), "r"(smem_u32(bar))
-      : "memory");
-}
-// 3-D tiled TMA load global -> shared; same rules.
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, int c0, int c1, int c2, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
@@ -93,6 +84,7 @@ __device__ __forceinline__ void tma_store_3d(const void* tmap, int c0, int c1, i
                : "memory");
 }
 
+// 1-D bulk copy shared -> global (bulk async-group completion).
 __device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst),
                "r"(smem_u32(smem_src)), "r"(bytes)
