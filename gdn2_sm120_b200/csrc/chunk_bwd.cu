@@ -309,7 +309,7 @@ constexpr int kRsS = 16 * kCsS;        // 2304
 
 // dynamic shared memory map (bytes).  Phase B = products with the states, phase C = Gram VJP.
 constexpr int kOffStack = 0;                      // B: [dZ ; dO] X[r = 128][c = v], RS kRsN     73728 (dZ rows: bulk copy)
-constexpr int kOffRn = kOffStack + 16 * kRsN;     // B: R X[r = j][c = v], RS 4096 (bulk copy)   32768
+constexpr int kOffRn = kOffStack + 16 * kRsN;     // B: R[j][v], 4 swizzled slabs of 64 lines    32768
 constexpr int kOffS0 = kOffRn + 32768;            // B: S_0[k][v], 4 swizzled slabs of 128 lines  65536
 constexpr int kOffDs1 = kOffS0 + 65536;           // B: dS_1[k][64 v] half, 2 swizzled slabs      32768
 static_assert(kOffS0 % 1024 == 0 && kOffDs1 % 1024 == 0, "swizzled tiles are 1024-byte aligned");
@@ -417,8 +417,8 @@ __device__ __forceinline__ void tmem_ld8f(uint32_t taddr, float (&x)[8]) {
 template <typename T, typename G, bool kF32Grads = false>
 __global__ void __launch_bounds__(kVjpThreads, 1)
 chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s0,
-                     const __grid_constant__ CUtensorMap tm_ds, const __grid_constant__ CUtensorMap tm_dq,
-                     const __grid_constant__ CUtensorMap tm_dk) {
+                     const __grid_constant__ CUtensorMap tm_ds, const __grid_constant__ CUtensorMap tm_rn,
+                     const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_dk) {
   using O = typename std::conditional<kF32Grads, float, T>::type;  // element type of dq, dk, dv, dbeta, dw
   extern __shared__ __align__(1024) uint8_t smem[];
   VjpMisc& ms = *reinterpret_cast<VjpMisc*>(smem + kOffMisc);
@@ -469,7 +469,8 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
 #pragma unroll
     for (int sl = 0; sl < 4; ++sl) tma_load_3d(smem + kOffS0 + sl * 16384, &tm_s0, 32 * sl, 0, s0_slot_of(ch_), &ms.bar_s);
     mbar_arrive_expect_tx(&ms.bar_a, uint32_t(kBlobDZ + kBlobRn));
-    bulk_g2s(smem + kOffRn, p.ws + ws.off_rn() + ch_ * kBlobRn, uint32_t(kBlobRn), &ms.bar_a);
+#pragma unroll
+    for (int sl = 0; sl < 4; ++sl) tma_load_3d(smem + kOffRn + sl * 8192, &tm_rn, 32 * sl, 0, int(ch_), &ms.bar_a);
     bulk_g2s(smem + kOffStack, p.sc + sc.off_dz() + ch_ * kBlobDZ, uint32_t(kBlobDZ), &ms.bar_a);
   };
   auto issue_ds1 = [&](int64_t ch_) {
@@ -558,13 +559,13 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     const uint32_t id128 = idesc(128, 128, kFmtTF32, kMajorK, kMajorK);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
-      mma_tf32_ss(tb + kColD4, smem_desc_sw128_k(d1, 16384, ks), smem_desc(rn + ks * 256, 128, 4096), id64,
+      mma_tf32_ss(tb + kColD4, smem_desc_sw128_k(d1, 16384, ks), smem_desc_sw128_k(rn, 8192, ks), id64,
                   ks > 0 ? 1u : 0u);
     }
     mma_commit(&ms.bar_r);  // the dS_1 buffer may be refilled once these have run
 #pragma unroll
     for (int ks = 0; ks < 16; ++ks) {
-      mma_tf32_ss(tb + kColD2, smem_desc(st + ks * 2 * kCsN, kCsN, kRsN), smem_desc(rn + ks * 256, 128, 4096), id64,
+      mma_tf32_ss(tb + kColD2, smem_desc(st + ks * 2 * kCsN, kCsN, kRsN), smem_desc_sw128_k(rn, 8192, ks), id64,
                   ks > 0 ? 1u : 0u);
     }
 #pragma unroll
@@ -629,7 +630,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     const uint32_t id64 = idesc(128, 64, kFmtTF32, kMajorK, kMajorK);
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
-      mma_tf32_ss(tb + kColD4, smem_desc_sw128_k(d1, 16384, ks), smem_desc(rn + (8 + ks) * 256, 128, 4096), id64, 1u);
+      mma_tf32_ss(tb + kColD4, smem_desc_sw128_k(d1, 16384, ks), smem_desc_sw128_k(rn, 8192, 8 + ks), id64, 1u);
     }
     mma_commit(&ms.bar_r);
   }
@@ -979,6 +980,8 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
       !encode_sequence_map(&tm_dk, dk, B * T, H, grads_f32 ? GDN2_FP32 : dtype)) {
     return GDN2_ERR_LAUNCH;
   }
+  CUtensorMap tm_rn;
+  if (!encode_tile_map(&tm_rn, workspace + ws.off_rn(), n_ch, kChunk, kDim, false)) return GDN2_ERR_LAUNCH;
   VjpParams vp{q, k, v, g, beta, w, d_out, workspace, scratch, bnd, d_bnd, dq, dk, dv, dg, dbeta, dw,
                status, T, H, n_chunks, n_ch, scale};
   const unsigned vjp_grid = unsigned(n_ch < int64_t(sm_count) ? n_ch : int64_t(sm_count));
@@ -986,13 +989,13 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
     auto kernel = chunk_bwd_vjp_kernel<__nv_bfloat16, float, true>;
     err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kVjpSmemBytes);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
-    kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds, tm_dq, tm_dk);
+    kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds, tm_rn, tm_dq, tm_dk);
   } else {
     GDN2_DISPATCH_TYPES(dtype, g_dtype, {
       auto kernel = chunk_bwd_vjp_kernel<T, G>;
       err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kVjpSmemBytes);
       if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
-      kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds, tm_dq, tm_dk);
+      kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds, tm_rn, tm_dq, tm_dk);
     });
   }
   st = check_launch();

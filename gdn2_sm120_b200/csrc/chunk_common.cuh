@@ -19,9 +19,9 @@
 //                                                                               tensor memory by threads
 //   D    float[128]                      512 B    gamma_end
 //
-// Two more per-unit arrays are "blocked" tiles (see tc05.cuh) that bulk copies move as they are:
-//   Rn   X[r = token j (64)][c = value v (128)] RS = 4096, CS = 128   32 KiB   R = U - Y S_0
-//        (forward scan -> VJP kernel)
+//   Rn   [token j (64)][value v (128)]   32 KiB   R = U - Y S_0   forward scan -> VJP kernel (K-major)
+//
+// One more per-unit array is a "blocked" tile (see tc05.cuh) that a bulk copy moves as it is:
 //   dZ   X[r = token j (64)][c = value v (128)] RS = 4608, CS = 144   36 KiB   dZ = T^T dR
 //        (reverse scan -> VJP kernel; the padded strides are those of the tile it is copied into)
 //

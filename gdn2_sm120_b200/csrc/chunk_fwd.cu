@@ -605,6 +605,8 @@ struct ScanSmem {
   alignas(1024) uint8_t kn[32768];   // Kn[j][k]: 4 slabs of 64 lines
   alignas(1024) uint8_t at[16384];   // At[j][i]: 2 slabs of 64 lines
   alignas(1024) float u[kChunk * kDim];  // U[j][v], plain rows: threads copy it into tensor memory
+  alignas(128) float ck[kDim * kDim];    // training: the chunk-start state [k][v] on its way out (one bulk
+                                         // store per chunk: 64 KiB of per-thread stores would hold up the chain)
   alignas(16) float d[kDim];
   alignas(8) uint64_t bar_yqa, bar_ut, bar_kt, bar_mma1, bar_mma2;
   uint32_t tmem_base;
@@ -721,6 +723,7 @@ chunk_scan_kernel(const ScanParams p, const __grid_constant__ CUtensorMap tm_yt,
       tmem_wait_st();
     }
     waiter.wait(&sm.bar_yqa, par);
+    if (tid == 0) bulk_wait_read_all();  // the previous checkpoint has left its staging buffer
     tc_fence_before();
     __syncthreads();
     if (tid == 0) {
@@ -751,19 +754,17 @@ chunk_scan_kernel(const ScanParams p, const __grid_constant__ CUtensorMap tm_yt,
     tc_fence_after();
     if (tid == 0 && c + 1 < p.n_chunks) load_yqa(c + 1);  // the three MMAs no longer read Y, Q, A
 
-    // ---- training: keep the residual R = U - Y S_0 (natural tile X[r = j][c = v]) for backward ------
+    // ---- training: keep the residual R = U - Y S_0 for backward -------------------------------------
     {
       uint32_t rr[16], ro[16];
       if (p.training) tmem_ld16(tmem_addr(tb, lane_base, kColR + i0), rr);
       tmem_ld16(tmem_addr(tb, lane_base, kColO + i0), ro);
       tmem_wait_ld();
       if (p.training) {
-        uint8_t* blob_rn = p.ws_out + ws.off_rn() + ch_of(c) * kBlobRn + (vrow >> 2) * 128 + (vrow & 3) * 4;
+        // row-major R[j][v]: the 32 lanes of a warp fill one 128-byte line per token
+        float* rn = reinterpret_cast<float*>(p.ws_out + ws.off_rn() + ch_of(c) * kBlobRn) + vrow;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int tok = i0 + j;
-          *reinterpret_cast<float*>(blob_rn + (tok >> 3) * 4096 + (tok & 7) * 16) = to_tf32(__uint_as_float(rr[j]));
-        }
+        for (int j = 0; j < 16; ++j) rn[(i0 + j) * kDim] = to_tf32(__uint_as_float(rr[j]));
       }
       // ---- output rows of this chunk: o[t0 + i][v] ---------------------------------------------------
       T* out = static_cast<T*>(p.out);
@@ -777,15 +778,13 @@ chunk_scan_kernel(const ScanParams p, const __grid_constant__ CUtensorMap tm_yt,
     // ---- checkpoint the chunk-start state, then decay the accumulator: S^T <- S^T diag(d) ----------
     waiter.wait(&sm.bar_kt, par);
     {
-      float* ck = (p.bnd != nullptr)
-                      ? p.bnd + ((b * (p.n_chunks + 1) + c) * p.H + h) * int64_t(kDim) * kDim + vrow
-                      : nullptr;
       uint32_t r[32];
       tmem_ld32(tmem_addr(tb, lane_base, kColS + k0), r);
       tmem_wait_ld();
-      if (ck != nullptr) {
+      if (p.bnd != nullptr) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) ck[(k0 + j) * kDim] = __uint_as_float(r[j]);
+        for (int j = 0; j < 32; ++j) sm.ck[(k0 + j) * kDim + vrow] = __uint_as_float(r[j]);
+        fence_async_smem();
       }
 #pragma unroll
       for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * sm.d[k0 + j]);
@@ -796,6 +795,11 @@ chunk_scan_kernel(const ScanParams p, const __grid_constant__ CUtensorMap tm_yt,
     __syncthreads();
     if (tid == 0) {
       tc_fence_after();
+      if (p.bnd != nullptr) {
+        bulk_s2g(p.bnd + ((b * (p.n_chunks + 1) + c) * p.H + h) * int64_t(kDim) * kDim, sm.ck,
+                 uint32_t(kDim * kDim * sizeof(float)));
+        bulk_commit();
+      }
       const uint32_t kn0 = smem_u32(sm.kn);
       const uint32_t id_s = idesc(128, 128, kFmtTF32, kMajorK, kMajorMN);
       // S^T += R^T Kt   (K = 64 tokens; B = Kn[j][k] read MN-major)
@@ -828,6 +832,7 @@ chunk_scan_kernel(const ScanParams p, const __grid_constant__ CUtensorMap tm_yt,
       if (ck != nullptr) ck[(k0 + j) * kDim] = x;
     }
   }
+  if (tid == 0) bulk_wait_all();  // the last staged checkpoint is in global memory before the CTA retires
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tb, 256);
