@@ -34,6 +34,8 @@
 
 #include <cuda.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "tc05.cuh"
 
@@ -199,11 +201,52 @@ inline EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// Encoding a tensor map costs the host some 20 microseconds and a call needs a dozen of them; the
+// maps depend only on addresses and shapes, which repeat from call to call (allocators hand the same
+// blocks out again), so the last few hundred are kept.  Direct-mapped, one mutex.
+struct TensorMapKey {
+  uintptr_t base;
+  cuuint64_t dims[3], strides[2];
+  cuuint32_t box[3];
+  int type, swizzle;
+  bool operator==(const TensorMapKey& o) const {
+    return base == o.base && dims[0] == o.dims[0] && dims[1] == o.dims[1] && dims[2] == o.dims[2] &&
+           strides[0] == o.strides[0] && strides[1] == o.strides[1] && box[0] == o.box[0] && box[1] == o.box[1] &&
+           box[2] == o.box[2] && type == o.type && swizzle == o.swizzle;
+  }
+};
+
+inline bool encode_3d_cached(CUtensorMap* tm, CUtensorMapDataType type, const void* base, const cuuint64_t (&dims)[3],
+                             const cuuint64_t (&strides)[2], const cuuint32_t (&box)[3], CUtensorMapSwizzle swizzle) {
+  constexpr int kSlots = 512;
+  struct Slot { bool used = false; TensorMapKey key; CUtensorMap map; };
+  static Slot slots[kSlots];
+  static std::mutex mutex;
+  TensorMapKey key{reinterpret_cast<uintptr_t>(base), {dims[0], dims[1], dims[2]}, {strides[0], strides[1]},
+                   {box[0], box[1], box[2]}, int(type), int(swizzle)};
+  uint64_t h = key.base * 0x9E3779B97F4A7C15ull;
+  h ^= (key.dims[2] + 0x632BE59BD9B4E019ull * key.strides[1]) + (uint64_t(key.box[1]) << 7) + uint64_t(key.swizzle) * 31 + uint64_t(key.type);
+  h ^= h >> 29;
+  Slot& slot = slots[h % kSlots];
+  {
+    std::lock_guard<std::mutex> lock(mutex);
+    if (slot.used && slot.key == key) { *tm = slot.map; return true; }
+  }
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return false;
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  if (encode(tm, type, 3, const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+    return false;
+  }
+  std::lock_guard<std::mutex> lock(mutex);
+  slot.used = true; slot.key = key; slot.map = *tm;
+  return true;
+}
+
 // A contiguous [B, T, H, 128] sequence tensor seen as (channel, head, b * T + t): a box
 // (128, 1, 64) is one head's 64-token chunk, landing in shared memory as dense [64][128] rows.
 inline bool encode_sequence_map(CUtensorMap* tm, const void* base, int64_t rows, int64_t heads, int dtype) {
-  EncodeTiledFn encode = encode_tiled_fn();
-  if (encode == nullptr) return false;
   const cuuint64_t es = (dtype == GDN2_FP32) ? 4 : 2;
   const CUtensorMapDataType type = (dtype == GDN2_FP32)   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                    : (dtype == GDN2_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -211,39 +254,26 @@ inline bool encode_sequence_map(CUtensorMap* tm, const void* base, int64_t rows,
   const cuuint64_t dims[3] = {cuuint64_t(kDim), cuuint64_t(heads), cuuint64_t(rows)};
   const cuuint64_t strides[2] = {cuuint64_t(kDim) * es, cuuint64_t(heads) * kDim * es};  // bytes, dimensions 1..2
   const cuuint32_t box[3] = {cuuint32_t(kDim), 1, cuuint32_t(kChunk)};
-  const cuuint32_t elem_strides[3] = {1, 1, 1};
-  return encode(tm, type, 3, const_cast<void*>(base), dims, strides, box, elem_strides,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return encode_3d_cached(tm, type, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 // An array of n_ch row-major fp32 tiles [rows][cols] seen as (col, row, unit): a box (32, rows, 1) is a
-// slab of 32 columns of one tile, `rows` lines of 128 bytes in shared memory.  kMnMajor chooses the
+// slab of 32 columns of one tile, `rows` lines of 128 bytes in shared memory.  mn_major chooses the
 // swizzle: 128-byte with 32-byte atoms (the tile is read as an MN-major operand, contraction over its
 // rows) or plain 128-byte (K-major operand, contraction over its columns).
 inline bool encode_tile_map(CUtensorMap* tm, const uint8_t* base, int64_t n_ch, int rows, int cols, bool mn_major) {
-  EncodeTiledFn encode = encode_tiled_fn();
-  if (encode == nullptr) return false;
   const cuuint64_t dims[3] = {cuuint64_t(cols), cuuint64_t(rows), cuuint64_t(n_ch)};
   const cuuint64_t strides[2] = {cuuint64_t(cols) * 4, cuuint64_t(rows) * cols * 4};
   const cuuint32_t box[3] = {32, cuuint32_t(rows), 1};
-  const cuuint32_t elem_strides[3] = {1, 1, 1};
-  return encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<uint8_t*>(base), dims, strides, box, elem_strides,
-                CU_TENSOR_MAP_INTERLEAVE_NONE,
-                mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return encode_3d_cached(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, dims, strides, box,
+                          mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B);
 }
 // The same array, whole tiles without swizzle (box (cols, rows, 1); cols <= 256): for tiles that threads read.
 inline bool encode_plain_tile_map(CUtensorMap* tm, const uint8_t* base, int64_t n_ch, int rows, int cols) {
-  EncodeTiledFn encode = encode_tiled_fn();
-  if (encode == nullptr) return false;
   const cuuint64_t dims[3] = {cuuint64_t(cols), cuuint64_t(rows), cuuint64_t(n_ch)};
   const cuuint64_t strides[2] = {cuuint64_t(cols) * 4, cuuint64_t(rows) * cols * 4};
   const cuuint32_t box[3] = {cuuint32_t(cols), cuuint32_t(rows), 1};
-  const cuuint32_t elem_strides[3] = {1, 1, 1};
-  return encode(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<uint8_t*>(base), dims, strides, box, elem_strides,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return encode_3d_cached(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
