@@ -294,10 +294,11 @@ int64_t gdn2_chunk_workspace_bytes(int64_t batch, int64_t full_tokens, int64_t h
   return chunk_workspace_bytes(batch, full_tokens, heads, training);
 }
 
-int64_t gdn2_chunk_scratch_bytes(int64_t batch, int64_t full_tokens, int64_t heads, int backward) {
+int64_t gdn2_chunk_scratch_bytes(int64_t batch, int64_t full_tokens, int64_t heads, int kind) {
   if (batch <= 0 || heads <= 0 || full_tokens <= 0 || full_tokens % GDN2_CHUNK != 0) return GDN2_ERR_BAD_SHAPE;
+  if (kind < 0 || kind > 2) return GDN2_ERR_BAD_SHAPE;
   if (check_shape(batch, full_tokens, heads) != GDN2_OK) return GDN2_ERR_TOO_LARGE;
-  return chunk_scratch_bytes(batch, full_tokens, heads, backward);
+  return chunk_scratch_bytes(batch, full_tokens, heads, kind);
 }
 
 namespace {

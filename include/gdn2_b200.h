@@ -152,21 +152,27 @@ int gdn2_token_chunk_vjp(const void* q, const void* k, const void* v, const void
  * of GDN2_CHUNK) of a [batch, T, heads, 128] problem:
  *
  *   workspace  gdn2_chunk_workspace_bytes(batch, full_tokens, heads, training).  Holds the
- *              chunk-end decays and a device status word; with `training` != 0 also the tiles
- *              and residuals gdn2_chunk_backward consumes (Y^T, Q_gamma^T, K_tail, A_qk^T,
- *              ((I+L)^-1)^T, R: 160 KiB per 64-token chunk and head), and must then stay alive
- *              and unmodified until that call has run.
- *   scratch    gdn2_chunk_scratch_bytes(batch, full_tokens, heads, backward).  Tiles that only
- *              live inside one call (forward: Y, U^T, Q_gamma, K_tail^T, A_qk, 144 KiB per
- *              chunk-head; backward: dZ, 36 KiB per chunk-head).  Dead when the call's kernels
- *              have run, so one scratch buffer serves every call on a stream; a large batch can
- *              be processed as several calls over batch slices that share it.
+ *              chunk-end decays and a device status word; with `training` != 0 also what
+ *              gdn2_chunk_backward consumes: the residual R and the WY tiles Q_gamma, K_tail, Y^T,
+ *              A_qk^T, ((I+L)^-1)^T, one copy of each (the forward scan and the reverse scan read the
+ *              same tiles): 160 KiB per 64-token chunk and head.  It must then stay alive and
+ *              unmodified until that call has run.
+ *   scratch    gdn2_chunk_scratch_bytes(batch, full_tokens, heads, kind).  Tiles that only live
+ *              inside one call.  kind 0: forward of an inference call (U and the WY tiles, 144 KiB
+ *              per chunk-head); kind 2: forward of a training call (U alone, 32 KiB per chunk-head:
+ *              the other tiles are in its workspace); kind 1: backward (dZ, 36 KiB per chunk-head).
+ *              Dead when the call's kernels have run, so one scratch buffer serves every call on a
+ *              stream; a large batch can be processed as several calls over batch slices that share it.
+ * The kernels address tiles, sequence tensors and state checkpoints through tensor maps, which the
+ * entry points encode on the host (no device memory involved; recent maps are cached by address and
+ * shape).  Buffers, sequence tensors and states must be 16-byte aligned, and batch * time must be
+ * below 2^31.
  * Together they replace the intermediate allocations of chunk_forward
  * (src/gdn2_sm120/chunk.py:1317-1362) and of the backward launchers
  * (src/gdn2_sm120/backward_wy.py:1669-1984).
  */
 int64_t gdn2_chunk_workspace_bytes(int64_t batch, int64_t full_tokens, int64_t heads, int training);
-int64_t gdn2_chunk_scratch_bytes(int64_t batch, int64_t full_tokens, int64_t heads, int backward);
+int64_t gdn2_chunk_scratch_bytes(int64_t batch, int64_t full_tokens, int64_t heads, int kind);
 
 /*
  * Chunkwise forward over tokens [0, full_tokens).  Replaces _prepare_wy_kernel and
@@ -177,7 +183,7 @@ int64_t gdn2_chunk_scratch_bytes(int64_t batch, int64_t full_tokens, int64_t hea
  *   final_state    fp32 state after token full_tokens-1 (may alias initial_state exactly); or NULL
  *   chunk_boundaries  NULL, or fp32 [B, full_tokens/64 + 1, H,128,128]: state before every
  *                  chunk and after the last one (the activation checkpoints of backward)
- *   workspace, scratch  see above (forward scratch)
+ *   workspace, scratch  see above (forward scratch: kind 2 when `training`, else kind 0)
  *   training       non-zero: workspace was sized with training = 1, chunk_boundaries is
  *                  required, and everything backward needs is saved
  * All sequence pointers, states, the workspace and the scratch must be 16-byte aligned.
