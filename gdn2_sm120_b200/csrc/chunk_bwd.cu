@@ -328,7 +328,13 @@ constexpr int kEndC = kOffQat + 16 * kRsT;        // 218624
 constexpr int kOffTileK = kOffStack + 8 * kRsN;   // 36864
 constexpr int kOffTileQ = kOffTileK + 16384;
 constexpr int kOffTileG = kOffDs1;
-static_assert(kOffTileQ + 16384 <= kOffRn, "chain tiles exceed the dO rows of the stack");
+// beta (dbeta in place) has no 16 KiB hole left: its 16-token blocks 0..2 sit behind the dS_1 buffer,
+// block 3 in the last 4 KiB of the dO rows; a chain thread works on one block, so it sees one base
+constexpr int kOffTileB012 = kEndB;               // 204800, 12 KiB
+constexpr int kOffTileB3 = kOffTileQ + 16384;     // 69632, 4 KiB
+static_assert(kOffTileB3 + 4096 <= kOffRn, "chain tiles exceed the dO rows of the stack");
+static_assert(kOffTileB012 + 12288 <= kEndC, "beta tile exceeds the free space behind the dS_1 buffer");
+__device__ __forceinline__ int beta_tile_offset(int blk) { return blk < 3 ? kOffTileB012 + blk * 4096 : kOffTileB3; }
 constexpr int kOffMisc = (kEndB > kEndC ? kEndB : kEndC);
 struct VjpMisc {
   float part[16][kDim];   // exclusive prefixes of the log-decay per 4-token group
@@ -418,7 +424,8 @@ template <typename T, typename G, bool kF32Grads = false>
 __global__ void __launch_bounds__(kVjpThreads, 1)
 chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s0,
                      const __grid_constant__ CUtensorMap tm_ds, const __grid_constant__ CUtensorMap tm_rn,
-                     const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_dk) {
+                     const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_dk,
+                     const __grid_constant__ CUtensorMap tm_dbeta) {
   using O = typename std::conditional<kF32Grads, float, T>::type;  // element type of dq, dk, dv, dbeta, dw
   extern __shared__ __align__(1024) uint8_t smem[];
   VjpMisc& ms = *reinterpret_cast<VjpMisc*>(smem + kOffMisc);
@@ -770,6 +777,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
       const int off = (4 * tg + e) * kDim + kc0;
       store4v<T>(smem + kOffTileK, off, kk[e][0], kk[e][1], kk[e][2], kk[e][3]);
       store4v<T>(smem + kOffTileQ, off, qq[e][0], qq[e][1], qq[e][2], qq[e][3]);
+      store4v<T>(smem + beta_tile_offset(mb), (4 * (tg & 3) + e) * kDim + kc0, bb[e][0], bb[e][1], bb[e][2], bb[e][3]);
       store4v<float>(smem + kOffTileG, off, Gc[e][0], Gc[e][1], Gc[e][2], Gc[e][3]);
     }
     __syncthreads();
@@ -806,7 +814,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
         Gb[t] = ldf<float>(smem + kOffTileG, off);
         kv[t] = ldf<T>(smem + kOffTileK, off);
         sq[t] = p.scale * ldf<T>(smem + kOffTileQ, off);
-        bv[t] = ldf<T>(p.beta, seq_idx(i0 + t) + kc);  // loaded here: no global load may follow a global store
+        bv[t] = ldf<T>(smem + beta_tile_offset(blk), (8 * sb + t) * kDim + kc);
       }
       // row blocks I = blk + d that contain these tokens as columns, nearest first: the own block uses
       // exp(a_me - G), the others exp(a_next - G) (times the block-to-block factor from d = 2 on)
@@ -870,8 +878,9 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
           const int off = (i0 + t) * kDim + kc;
           stf<T>(smem + kOffTileQ, off, p.scale * P1);
           stf<T>(smem + kOffTileK, off, dk_t);
+          stf<T>(smem + beta_tile_offset(blk), (8 * sb + t) * kDim + kc, failed ? poison_nan() : kv[t] * P2[t]);
         }
-        stf<O>(p.dbeta, idx, failed ? poison_nan() : kv[t] * P2[t]);
+        if (kF32Grads) stf<O>(p.dbeta, idx, failed ? poison_nan() : kv[t] * P2[t]);
         dGv[8 * sb + t] = dGt;
         tot += dGt;
       }
@@ -906,6 +915,8 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
       const int row = int(b * p.T + t0);
       tma_store_3d(&tm_dq, 0, int(h), row, smem + kOffTileQ);
       tma_store_3d(&tm_dk, 0, int(h), row, smem + kOffTileK);
+#pragma unroll
+      for (int bq = 0; bq < 4; ++bq) tma_store_3d(&tm_dbeta, 0, int(h), row + 16 * bq, smem + beta_tile_offset(bq));
       bulk_commit();
     }
     // the G tile is dead: the dS_1 half of the next chunk-head may land on it
@@ -980,6 +991,11 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
       !encode_sequence_map(&tm_dk, dk, B * T, H, grads_f32 ? GDN2_FP32 : dtype)) {
     return GDN2_ERR_LAUNCH;
   }
+  CUtensorMap tm_dbeta;
+  if ((reinterpret_cast<uintptr_t>(dbeta) & 15u) != 0 ||
+      !encode_sequence_map(&tm_dbeta, dbeta, B * T, H, grads_f32 ? GDN2_FP32 : dtype, 16)) {
+    return GDN2_ERR_LAUNCH;
+  }
   CUtensorMap tm_rn;
   if (!encode_tile_map(&tm_rn, workspace + ws.off_rn(), n_ch, kChunk, kDim, false)) return GDN2_ERR_LAUNCH;
   VjpParams vp{q, k, v, g, beta, w, d_out, workspace, scratch, bnd, d_bnd, dq, dk, dv, dg, dbeta, dw,
@@ -989,13 +1005,13 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
     auto kernel = chunk_bwd_vjp_kernel<__nv_bfloat16, float, true>;
     err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kVjpSmemBytes);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
-    kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds, tm_rn, tm_dq, tm_dk);
+    kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds, tm_rn, tm_dq, tm_dk, tm_dbeta);
   } else {
     GDN2_DISPATCH_TYPES(dtype, g_dtype, {
       auto kernel = chunk_bwd_vjp_kernel<T, G>;
       err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kVjpSmemBytes);
       if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
-      kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds, tm_rn, tm_dq, tm_dk);
+      kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds, tm_rn, tm_dq, tm_dk, tm_dbeta);
     });
   }
   st = check_launch();

@@ -245,15 +245,17 @@ inline bool encode_3d_cached(CUtensorMap* tm, CUtensorMapDataType type, const vo
 }
 
 // A contiguous [B, T, H, 128] sequence tensor seen as (channel, head, b * T + t): a box
-// (128, 1, 64) is one head's 64-token chunk, landing in shared memory as dense [64][128] rows.
-inline bool encode_sequence_map(CUtensorMap* tm, const void* base, int64_t rows, int64_t heads, int dtype) {
+// (128, 1, 64) is one head's 64-token chunk, landing in shared memory as dense [64][128] rows
+// (`box_rows` tokens instead of 64 when given).
+inline bool encode_sequence_map(CUtensorMap* tm, const void* base, int64_t rows, int64_t heads, int dtype,
+                                int box_rows = kChunk) {
   const cuuint64_t es = (dtype == GDN2_FP32) ? 4 : 2;
   const CUtensorMapDataType type = (dtype == GDN2_FP32)   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                    : (dtype == GDN2_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const cuuint64_t dims[3] = {cuuint64_t(kDim), cuuint64_t(heads), cuuint64_t(rows)};
   const cuuint64_t strides[2] = {cuuint64_t(kDim) * es, cuuint64_t(heads) * kDim * es};  // bytes, dimensions 1..2
-  const cuuint32_t box[3] = {cuuint32_t(kDim), 1, cuuint32_t(kChunk)};
+  const cuuint32_t box[3] = {cuuint32_t(kDim), 1, cuuint32_t(box_rows)};
   return encode_3d_cached(tm, type, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
