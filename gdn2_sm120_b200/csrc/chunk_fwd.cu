@@ -162,7 +162,7 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
   const int ch_next = ch + int(gridDim.x);
   // ---- the raw inputs were brought in while the previous unit was finishing; the log-decay is
   // consumed first: the prefix sums below need it alone ------------------------------------------------
-  float Gc[4][4], kk[4][4], qq[4][4], bb[4][4], zz[4][4];
+  float Gc[4][4], kk[4][4], qq[4][4], bb[4][4];
   {
     using RawG = typename Raw4<G>::type;
     using RawT = typename Raw4<T>::type;
@@ -213,24 +213,19 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
       }
     }
     waiter.wait(&sm.bar_ld[1], par);
-    RawT rb[4], rv[4], rw[4];
+    // v and w stay where they landed until Z is built, after the Gram products: nothing overwrites their
+    // landing zones before the next unit's copies, which are issued after that
+    RawT rb[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      rb[e] = *reinterpret_cast<const RawT*>(staged(sm.gram_b + kStageBeta, e, 2));
-      rv[e] = *reinterpret_cast<const RawT*>(staged(sm.tmat + kStageV, e, 2));
-      rw[e] = *reinterpret_cast<const RawT*>(staged(sm.stage_w, e, 2));
-    }
+    for (int e = 0; e < 4; ++e) rb[e] = *reinterpret_cast<const RawT*>(staged(sm.gram_b + kStageBeta, e, 2));
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      float vv[4], ww[4];
       unpack4<T>(rk[e], kk[e]);
       unpack4<T>(rq[e], qq[e]);
       unpack4<T>(rb[e], bb[e]);
-      unpack4<T>(rv[e], vv);
-      unpack4<T>(rw[e], ww);
       if (pro_norm) {
         const float inv_q = rsqrtf(sm.nrm[warp][lane >> 4][e][0] + sm.nrm[warp ^ 1][lane >> 4][e][0] + kPrologueEps);
         const float inv_k = rsqrtf(sm.nrm[warp][lane >> 4][e][1] + sm.nrm[warp ^ 1][lane >> 4][e][1] + kPrologueEps);
@@ -239,10 +234,8 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
       }
       if (pro_gate) {
 #pragma unroll
-        for (int f = 0; f < 4; ++f) { bb[e][f] = prologue_sigmoid(bb[e][f]); ww[f] = prologue_sigmoid(ww[f]); }
+        for (int f = 0; f < 4; ++f) bb[e][f] = prologue_sigmoid(bb[e][f]);
       }
-#pragma unroll
-      for (int f = 0; f < 4; ++f) zz[e][f] = to_tf32(vv[f] * ww[f]);
     }
   }
   if (tid < kDim) {
@@ -344,9 +337,6 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
   }
   waiter.wait(&sm.bar[0], par);
   tc_fence_after();
-  // the Gram operands are dead: beta, v, w of the next unit start to arrive
-  if (tid == 0 && ch_next < n_ch) issue_bvw(ch_next);
-
   // the Gram operands are dead: region 1 becomes fp32 scratch, region 2 receives E^T and Z^T
   float* Ln = reinterpret_cast<float*>(sm.gram_a);           // [64][kLd]   L
   float* Tn = Ln + 64 * kLd;                                  // [64][kLd]   T
@@ -355,11 +345,27 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
   static_assert((3 * 64 * kLd + 3 * 16 * kLdW) * 4 <= 16 * kRsN, "fp32 scratch exceeds the Gram A region");
   uint8_t* et_tile = sm.gram_b;                               // E^T  X[r = k][c = j], tf32, RS kRsT
   uint8_t* zt_tile = sm.gram_b + kTileT;                      // Z^T  X[r = v][c = j], tf32, RS kRsT
+  {
+    // Z = w * v from the staged inputs (kept out of registers until now)
+    float zz[4][4];
+    const bool pro_gate = kPro && (p.prologue & kPrologueGate) != 0;
 #pragma unroll
-  for (int f = 0; f < 4; ++f) {
-    const uint32_t off = blk_off<4>(kc0 + f, 4 * tg, kRsT, 128);
-    *reinterpret_cast<float4*>(et_tile + off) = make_float4(ebar[0][f], ebar[1][f], ebar[2][f], ebar[3][f]);
-    *reinterpret_cast<float4*>(zt_tile + off) = make_float4(zz[0][f], zz[1][f], zz[2][f], zz[3][f]);
+    for (int e = 0; e < 4; ++e) {
+      float vv[4], ww[4];
+      unpack4<T>(*reinterpret_cast<const typename Raw4<T>::type*>(staged(sm.tmat + kStageV, e, 2)), vv);
+      unpack4<T>(*reinterpret_cast<const typename Raw4<T>::type*>(staged(sm.stage_w, e, 2)), ww);
+#pragma unroll
+      for (int f = 0; f < 4; ++f) {
+        if (pro_gate) ww[f] = prologue_sigmoid(ww[f]);
+        zz[e][f] = to_tf32(vv[f] * ww[f]);
+      }
+    }
+#pragma unroll
+    for (int f = 0; f < 4; ++f) {
+      const uint32_t off = blk_off<4>(kc0 + f, 4 * tg, kRsT, 128);
+      *reinterpret_cast<float4*>(et_tile + off) = make_float4(ebar[0][f], ebar[1][f], ebar[2][f], ebar[3][f]);
+      *reinterpret_cast<float4*>(zt_tile + off) = make_float4(zz[0][f], zz[1][f], zz[2][f], zz[3][f]);
+    }
   }
   {
     // pull L (rows 0..63) into fp32 scratch and A_qk (rows 64..127) into the workspace;
@@ -401,6 +407,9 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
   }
   tc_fence_before();
   __syncthreads();
+  // every thread has read v and w of this unit, the Gram operands are dead: beta, v, w of the next unit
+  // start to arrive
+  if (tid == 0 && ch_next < n_ch) issue_bvw(ch_next);
 
   // ---- T = (I + L)^-1, blocked: 16x16 diagonal blocks by substitution, the rest by block products.
   // T is kept in both orientations (Tn row-major, Tc column-major) and the block products W transposed,
