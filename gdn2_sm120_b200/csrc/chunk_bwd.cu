@@ -110,13 +110,16 @@ chunk_bwd_scan_kernel(const BScanParams p, const __grid_constant__ CUtensorMap t
   auto ch_of = [&](int64_t c) { return (b * p.n_chunks + c) * p.H + h; };
   auto load_ak = [&](int64_t c) {
     const int ch = int(ch_of(c));
-    mbar_arrive_expect_tx(&sm.bar_ak, uint32_t(kTileAt + kTileKn + kTileTt));
-#pragma unroll
-    for (int s = 0; s < 2; ++s) tma_load_3d(sm.at + s * 8192, &tm_at, 32 * s, 0, ch, &sm.bar_ak);
+    mbar_arrive_expect_tx(&sm.bar_ak, uint32_t(kTileAt + kTileKn + kTileTt - 2 * 4096));
+    // At and Tt are zero for j >= 32, i < 32: three 32-row boxes each, the fourth quadrant stays zero
+    tma_load_3d(sm.at, &tm_at, 0, 0, ch, &sm.bar_ak);
+    tma_load_3d(sm.at + 8192, &tm_at, 32, 0, ch, &sm.bar_ak);
+    tma_load_3d(sm.at + 8192 + 4096, &tm_at, 32, 32, ch, &sm.bar_ak);
 #pragma unroll
     for (int s = 0; s < 4; ++s) tma_load_3d(sm.kn + s * 8192, &tm_kn, 32 * s, 0, ch, &sm.bar_ak);
-#pragma unroll
-    for (int s = 0; s < 2; ++s) tma_load_3d(sm.tt + s * 8192, &tm_tt, 32 * s, 0, ch, &sm.bar_ak);
+    tma_load_3d(sm.tt, &tm_tt, 0, 0, ch, &sm.bar_ak);
+    tma_load_3d(sm.tt + 8192, &tm_tt, 32, 0, ch, &sm.bar_ak);
+    tma_load_3d(sm.tt + 8192 + 4096, &tm_tt, 32, 32, ch, &sm.bar_ak);
   };
   auto load_qy = [&](int64_t c) {
     const int64_t ch = ch_of(c);
@@ -135,6 +138,12 @@ chunk_bwd_scan_kernel(const BScanParams p, const __grid_constant__ CUtensorMap t
     }
   };
 
+  // lines 32..63 of the first slab of At and Tt (j >= 32, i < 32) are never loaded: zero, once
+  for (int e = tid; e < 4096 / 16; e += kBScanThreads) {
+    reinterpret_cast<float4*>(sm.at + 4096)[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+    reinterpret_cast<float4*>(sm.tt + 4096)[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  fence_async_smem();
   typename Raw4<T>::type do_raw[4] = {};
   if (p.n_chunks > 0) {
     if (tid == 0) {
@@ -948,8 +957,8 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
   profile_mark(3, stream);
   // the reverse scan's operands: the forward's tiles, each in the swizzle of the role backward reads it in
   CUtensorMap tm_at, tm_tt, tm_kn, tm_q, tm_yt;
-  if (!encode_tile_map(&tm_at, workspace + ws.off_at(), n_ch, kChunk, kChunk, false) ||
-      !encode_tile_map(&tm_tt, workspace + ws.off_tt(), n_ch, kChunk, kChunk, false) ||
+  if (!encode_tile_map(&tm_at, workspace + ws.off_at(), n_ch, kChunk, kChunk, false, 32) ||
+      !encode_tile_map(&tm_tt, workspace + ws.off_tt(), n_ch, kChunk, kChunk, false, 32) ||
       !encode_tile_map(&tm_kn, workspace + ws.off_kn(), n_ch, kChunk, kDim, false) ||
       !encode_tile_map(&tm_q, workspace + ws.off_q(), n_ch, kChunk, kDim, true) ||
       !encode_tile_map(&tm_yt, workspace + ws.off_yt(), n_ch, kDim, kChunk, false)) {

@@ -15,6 +15,8 @@
 //   Yt   [key k (128)][token i (64)]     32 KiB   Y^T, Y = (I+L)^-1 E          fwd MN-major, bwd K-major
 //   At   [token j (64)][token i (64)]    16 KiB   tril(Q_gamma Kbar^T)^T       fwd MN-major, bwd K-major
 //   Tt   [token j (64)][token i (64)]    16 KiB   ((I+L)^-1)^T                 bwd K-major (training only)
+//        (both are zero where j > i: the quadrant j >= 32, i < 32 is neither written nor read, the
+//        consumers keep those lines of their shared-memory tile at zero; 12 KiB move)
 //   U    [token j (64)][value v (128)]   32 KiB   U = (I+L)^-1 (w*v)           forward only: copied into
 //                                                                               tensor memory by threads
 //   D    float[128]                      512 B    gamma_end
@@ -263,10 +265,12 @@ inline bool encode_sequence_map(CUtensorMap* tm, const void* base, int64_t rows,
 // slab of 32 columns of one tile, `rows` lines of 128 bytes in shared memory.  mn_major chooses the
 // swizzle: 128-byte with 32-byte atoms (the tile is read as an MN-major operand, contraction over its
 // rows) or plain 128-byte (K-major operand, contraction over its columns).
-inline bool encode_tile_map(CUtensorMap* tm, const uint8_t* base, int64_t n_ch, int rows, int cols, bool mn_major) {
+// (`box_rows` < rows: boxes of that many rows, for tiles whose zero quadrant is never moved.)
+inline bool encode_tile_map(CUtensorMap* tm, const uint8_t* base, int64_t n_ch, int rows, int cols, bool mn_major,
+                            int box_rows = 0) {
   const cuuint64_t dims[3] = {cuuint64_t(cols), cuuint64_t(rows), cuuint64_t(n_ch)};
   const cuuint64_t strides[2] = {cuuint64_t(cols) * 4, cuuint64_t(rows) * cols * 4};
-  const cuuint32_t box[3] = {32, cuuint32_t(rows), 1};
+  const cuuint32_t box[3] = {32, cuuint32_t(box_rows > 0 ? box_rows : rows), 1};
   return encode_3d_cached(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, dims, strides, box,
                           mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B);
 }

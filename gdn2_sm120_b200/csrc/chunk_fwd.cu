@@ -396,9 +396,12 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
             make_float4(vals[4 * j4], vals[4 * j4 + 1], vals[4 * j4 + 2], vals[4 * j4 + 3]);
       }
     } else {
-      // A_qk leaves transposed, At[j][i]: the 32 lanes of a warp (rows i) fill one 128-byte line per column j
+      // A_qk leaves transposed, At[j][i]: the 32 lanes of a warp (rows i) fill one 128-byte line per column j;
+      // the quadrant j >= 32, i < 32 is zero and stays unwritten (nobody reads it)
+      if (!(c0 >= 32 && i < 32)) {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) tile_at[(c0 + j) * kChunk + i] = vals[j];
+        for (int j = 0; j < 16; ++j) tile_at[(c0 + j) * kChunk + i] = vals[j];
+      }
     }
   }
   for (int e = tid; e < 64 * kLd / 4; e += kPrepThreads) {
@@ -536,6 +539,7 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
       float* tile_tt = reinterpret_cast<float*>(p.tiles.tt + int64_t(ch) * kTileTt);
       for (int e = tid; e < 64 * 16; e += kPrepThreads) {
         const int j = e >> 4, c4t = e & 15;  // consecutive threads -> consecutive 16-byte pieces of a row
+        if (j >= 32 && c4t < 8) continue;    // the zero quadrant j >= 32, i < 32 stays unwritten
         const float4 tc = ld4(Tc + j * kLd + 4 * c4t);
         *reinterpret_cast<float4*>(tile_tt + j * kChunk + 4 * c4t) =
             make_float4(to_tf32(tc.x), to_tf32(tc.y), to_tf32(tc.z), to_tf32(tc.w));
@@ -677,13 +681,15 @@ chunk_scan_kernel(const ScanParams p, const __grid_constant__ CUtensorMap tm_yt,
   auto ch_of = [&](int64_t c) { return (b * p.n_chunks + c) * p.H + h; };
   auto load_yqa = [&](int64_t c) {
     const int ch = int(ch_of(c));
-    mbar_arrive_expect_tx(&sm.bar_yqa, uint32_t(kTileYt + kTileQ + kTileAt));
+    mbar_arrive_expect_tx(&sm.bar_yqa, uint32_t(kTileYt + kTileQ + kTileAt - 4096));
 #pragma unroll
     for (int s = 0; s < 2; ++s) tma_load_3d(sm.yt + s * 16384, &tm_yt, 32 * s, 0, ch, &sm.bar_yqa);
 #pragma unroll
     for (int s = 0; s < 4; ++s) tma_load_3d(sm.q + s * 8192, &tm_q, 32 * s, 0, ch, &sm.bar_yqa);
-#pragma unroll
-    for (int s = 0; s < 2; ++s) tma_load_3d(sm.at + s * 8192, &tm_at, 32 * s, 0, ch, &sm.bar_yqa);
+    // At is zero for j >= 32, i < 32: three 32-row boxes, the fourth quadrant of the tile stays zero
+    tma_load_3d(sm.at, &tm_at, 0, 0, ch, &sm.bar_yqa);
+    tma_load_3d(sm.at + 8192, &tm_at, 32, 0, ch, &sm.bar_yqa);
+    tma_load_3d(sm.at + 8192 + 4096, &tm_at, 32, 32, ch, &sm.bar_yqa);
   };
   auto load_ut = [&](int64_t c) {
     mbar_arrive_expect_tx(&sm.bar_ut, uint32_t(kTileU));
@@ -697,6 +703,11 @@ chunk_scan_kernel(const ScanParams p, const __grid_constant__ CUtensorMap tm_yt,
     bulk_g2s(sm.d, p.ws + ws.off_d() + ch * kBlobD, uint32_t(kBlobD), &sm.bar_kt);
   };
 
+  // lines 32..63 of the first slab of At (j >= 32, i < 32) are never loaded: zero, once
+  for (int e = tid; e < 4096 / 16; e += kScanThreads) {
+    reinterpret_cast<float4*>(sm.at + 4096)[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  fence_async_smem();
   if (tid == 0) {
     load_ut(0);
     load_yqa(0);
@@ -946,7 +957,7 @@ int launch_chunk_forward(const void* q, const void* k, const void* v, const void
   if (!encode_tile_map(&tm_yt, tiles.yt, n_ch, kDim, kChunk, true) ||
       !encode_tile_map(&tm_q, tiles.q, n_ch, kChunk, kDim, false) ||
       !encode_tile_map(&tm_kn, tiles.kn, n_ch, kChunk, kDim, true) ||
-      !encode_tile_map(&tm_at, tiles.at, n_ch, kChunk, kChunk, true) ||
+      !encode_tile_map(&tm_at, tiles.at, n_ch, kChunk, kChunk, true, 32) ||
       !encode_plain_tile_map(&tm_u, tiles.u, n_ch, kChunk, kDim)) {
     return GDN2_ERR_LAUNCH;
   }
