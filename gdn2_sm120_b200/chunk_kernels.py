@@ -69,8 +69,15 @@ def plan_waves(batch: int, full_tokens: int, heads: int, *, backward: bool = Fal
     """Batch ranges ``[(b0, b1), ...]`` of the waves of one pass."""
 
     budget = SCRATCH_BUDGET_BYTES if budget is None else budget
-    per_row = (_backward_wave_bytes(1, full_tokens, heads) if backward
-               else scratch_bytes(1, full_tokens, heads, False, training=training))
+    if backward:
+        per_row = _backward_wave_bytes(1, full_tokens, heads)
+    elif training:
+        # backward runs over the same waves (a workspace belongs to one wave): the larger of the two
+        # transients, the backward one (dZ tiles and cotangent checkpoints), sets the wave size
+        per_row = max(scratch_bytes(1, full_tokens, heads, False, training=True),
+                      _backward_wave_bytes(1, full_tokens, heads))
+    else:
+        per_row = scratch_bytes(1, full_tokens, heads, False)
     rows = max(1, min(batch, budget // per_row))
     # equal-sized waves (the last one may be smaller by at most one row per wave)
     n_waves = -(-batch // rows)
@@ -171,7 +178,8 @@ def backward(q, k, v, g, beta, w, workspaces, chunk_boundaries, d_out, d_final_s
     if len(forward_waves) != len(workspaces):
         raise ValueError("workspaces do not match the wave plan of this shape")
     n_slots = full_tokens // _CHUNK + 1
-    # backward waves subdivide the forward's (a workspace belongs to one forward wave)
+    # backward runs over the forward's waves (a workspace belongs to one wave; plan_waves sized them
+    # for the backward transients)
     dtype, g_dtype = _lib.dtype_code(q.dtype), _lib.dtype_code(g.dtype)
     stream = _lib.stream_ptr(q.device)
     rows = max(b1 - b0 for b0, b1 in forward_waves)

@@ -235,3 +235,28 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setenv("GDN2_B200_LIB", str(tmp_path / "nope.so"))
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         _lib.lib()
+
+
+def test_wave_plan_sizes_training_waves_for_the_backward_transients():
+    """The workspace of a wave is what backward consumes, so backward runs over the forward's waves: a
+    training plan must keep the backward scratch of a wave (dZ tiles + cotangent checkpoints) inside the
+    budget, not only the smaller forward scratch.  B=32, T=16384, H=32 is the one-GPU point of the
+    8-GPU configuration."""
+
+    from gdn2_sm120_b200 import chunk_kernels
+
+    batch, tokens, heads = 32, 16384, 32
+    waves = chunk_kernels.plan_waves(batch, tokens, heads, training=True)
+    assert waves[0][0] == 0 and waves[-1][1] == batch
+    assert all(a[1] == b[0] for a, b in zip(waves, waves[1:]))
+    rows = max(b1 - b0 for b0, b1 in waves)
+    assert chunk_kernels._backward_wave_bytes(rows, tokens, heads) <= chunk_kernels.SCRATCH_BUDGET_BYTES
+    assert len(waves) >= 3
+    # scratch sizes by kind: a training forward keeps the tiles both scans read in its workspace
+    units = batch * (tokens // 64) * heads
+    assert chunk_kernels.scratch_bytes(batch, tokens, heads, False) == units * 144 * 1024
+    assert chunk_kernels.scratch_bytes(batch, tokens, heads, False, training=True) == units * 32 * 1024
+    assert chunk_kernels.scratch_bytes(batch, tokens, heads, True) == units * 36 * 1024
+    assert chunk_kernels.workspace_bytes(batch, tokens, heads, True) == units * (160 * 1024 + 512) + 256
+    # an inference plan is sized by its own scratch alone
+    assert len(chunk_kernels.plan_waves(batch, tokens, heads)) == 4
