@@ -1,17 +1,19 @@
 // Inline-PTX wrappers for the sm_100a tensor-core path: tcgen05 MMA with TMEM accumulators,
 // shared-memory matrix descriptors, mbarriers and bulk asynchronous copies.
 //
-// Operand storage convention used by every kernel of this library ("blocked" tiles, no
-// swizzle): a matrix X[r][c] of 4-byte (or 2-byte) elements is stored as 8-row x 16-byte
-// core matrices,
+// Two operand storage conventions are in use.
+//
+// "Blocked" tiles, no swizzle (tiles that threads build in shared memory, and dZ): a matrix X[r][c] of
+// 4-byte (or 2-byte) elements is stored as 8-row x 16-byte core matrices,
 //
 //     offset(r, c) = (r / 8) * RS + (c / CH) * CS + (r % 8) * 16 + (c % CH) * ES,   CH = 16 / ES,
 //
-// RS = byte stride between 8-row groups, CS = byte stride between 16-byte column chunks.
-// The same tile serves two MMA roles:
-//   K-major  operand (MN index = r, K index = c):  SBO = RS, LBO = CS, next K step = +2*CS
-//   MN-major operand (K index = r, MN index = c):  SBO = CS, LBO = RS, next K step = +RS
-// (SBO is always the block stride along the M/N direction, LBO along K.)
+// RS = byte stride between 8-row groups, CS = byte stride between 16-byte column chunks.  Read as a
+// K-major operand (MN index = r, K index = c): SBO = RS, LBO = CS, next K step = +2*CS.  (The same
+// tile read MN-major works for 16-bit operands only; 32-bit operands have one MN-major form, below.)
+//
+// Swizzled slabs (tiles that arrive by tiled TMA loads from row-major global matrices): see
+// smem_desc_sw128_k / smem_desc_sw128_mn.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -95,21 +97,6 @@ __device__ __forceinline__ void bulk_wait_read_all() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
-// 16-byte asynchronous copy global -> shared by the calling thread (generic proxy; follow the wait
-// with fence_async_smem() before an MMA reads the data).
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
-}
-// 8- or 16-byte asynchronous copy global -> shared by the calling thread
-template <int kBytes>
-__device__ __forceinline__ void cp_async(void* smem_dst, const void* gsrc) {
-  static_assert(kBytes == 8 || kBytes == 16, "cp.async copies 4, 8 or 16 bytes");
-  asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "n"(kBytes)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // ---- TMEM management ---------------------------------------------------------------------
 // One full warp executes alloc / dealloc; ncols is a power of two in [32, 512].
@@ -203,22 +190,6 @@ __device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, ui
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(b_desc), "r"(id), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t id,
-                                           uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(id), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t id,
-                                           uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
       "r"(a_tmem), "l"(b_desc), "r"(id), "r"(accumulate)
       : "memory");
 }
