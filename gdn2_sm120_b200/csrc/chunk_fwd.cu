@@ -5,7 +5,7 @@
 //                       loads under the tail of the current one (a CTA that starts a unit with
 //                       per-thread loads spends a quarter of its time issuing them: the load/store
 //                       unit's queue, not HBM, is the limit).  Builds the WY factors of the chunk
-//                       and writes them as operand-ready blobs:
+//                       and writes them as row-major tiles:
 //                       cumulative log-decay, block-anchored Gram products on tf32 tcgen05 MMAs,
 //                       blocked inverse of the unit lower-triangular system on CUDA cores (fp32),
 //                       Y = T E and U^T = Z^T T^T on tf32 tcgen05 MMAs.
@@ -633,7 +633,7 @@ struct ScanParams {
   float* bnd;          // [B, n_chunks+1, H,128,128] or null
   int* status;
   int64_t T, H, n_chunks, n_ch;
-  uint8_t* ws_out;     // same workspace, writable (training: residual blobs)
+  uint8_t* ws_out;     // same workspace, writable (training: residual tiles)
   int training;
 };
 
