@@ -46,6 +46,16 @@ def test_chunk_forward_grids(batch, heads):
     check(out, state, ref_out, ref_state)
 
 
+def test_chunk_forward_more_units_than_sms():
+    """An inference call whose units (batch x chunks x heads = 256) outnumber the SMs: the persistent prep
+    kernel walks over several units per CTA with the next unit's inputs arriving under the current one."""
+
+    cpu = oracle.make_inputs(2, 2048, 4, seed=4096)
+    ref_out, ref_state = oracle.recurrence(*cpu)
+    out, state = chunk_gdn2(*dev(*cpu), output_final_state=True)
+    check(out, state, ref_out, ref_state)
+
+
 @pytest.mark.parametrize("dtype,g_dtype", [(torch.float16, torch.float32), (torch.float16, torch.float16),
                                            (torch.bfloat16, torch.bfloat16)])
 def test_chunk_forward_dtypes(dtype, g_dtype):
