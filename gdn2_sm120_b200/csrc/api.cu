@@ -155,7 +155,7 @@ using namespace gdn2;
 
 extern "C" {
 
-int gdn2_version(void) { return 100; /* 0.1.0 */ }
+int gdn2_version(void) { return 200; /* 0.2.0: row-major WY tiles, scratch kinds */ }
 
 const char* gdn2_status_string(int status) {
   switch (status) {
