@@ -463,7 +463,7 @@ def run_gpu_arm(args):
     roofline = None
     if dominant is not None:
         per_ch = traffic_per_chunk_head()
-        chunk_heads = token_heads // 64
+        chunk_heads = B * -(-T // 64) * H  # a ragged length is rounded up to whole chunks
 
         def kernel_entry(name):
             seconds = kernel_ms[name] * 1e-3
@@ -574,8 +574,8 @@ def run_gpu_arm(args):
             "config4_per_gpu_share": time_training_config(pkg, shard, device, 4, 16384, 32, seed=16384 + rank,
                                                           steps=min(args.steps, 5)),
         }
-        extra["train_T8200"]["what"] = (f"fwd+bwd B={B} T=8200 H={H} per GPU: 128 full chunks on the chunk "
-                                        "kernels, the 8-token tail on the token kernels")
+        extra["train_T8200"]["what"] = (f"fwd+bwd B={B} T=8200 H={H} per GPU: 129 chunks on the chunk kernels, "
+                                        "the last one with 8 of its 64 tokens")
         extra["config4_per_gpu_share"]["what"] = (
             "fwd+bwd B=4 T=16384 H=32 per GPU = the 8-GPU configuration (global B=32) at N=8; with fewer "
             "GPUs this is weak scaling of the same per-GPU share, device-timed, slowest rank")

@@ -5,10 +5,11 @@ Mirrors ``chunk_forward`` / ``ChunkForwardAux`` of the reference
 ``final_state_out`` rules (``final_state_out`` may alias ``initial_state`` exactly,
 never partially) and the ``return_aux`` contract used by the autograd wrapper.
 
-A sequence is split into ``full_tokens = 64 * (T // 64)`` tokens that the tensor-core
-chunk kernels process and a ragged tail of ``T - full_tokens < 64`` tokens that the
-exact fp32 token kernels process on the same buffers (the reference does the same with
-its scalar tail scan, chunk.py:1021-1053).
+From 64 tokens on the tensor-core chunk kernels process the whole sequence:
+``full_tokens = 64 * ceil(T / 64)``, the last chunk of a ragged length being partial (the
+kernels read its missing tokens as zeros, the identity step of the recurrence; the reference
+runs a scalar tail scan instead, chunk.py:1021-1053).  Shorter sequences
+(``full_tokens = 0``) go to the exact fp32 token kernels as one tail.
 
 Activation checkpoints for backward are the fp32 states at chunk / span starts plus,
 for the chunk kernels, the workspaces of per-chunk WY factors that the forward prep kernel
@@ -37,8 +38,8 @@ class ChunkForwardAux:
                           64-token chunk and after the last one, or ``None``.
     ``tail_boundaries``   fp32 ``[B, ceil(tail/16) + 1, H, 128, 128]``: state before every
                           16-token span of the tail ``[full_tokens, T)`` and after it, or
-                          ``None`` when there is no tail.
-    ``full_tokens``       number of leading tokens covered by ``chunk_boundaries``.
+                          ``None`` when there is no tail (any sequence of 64 tokens or more).
+    ``full_tokens``       tokens covered by ``chunk_boundaries`` (``T`` rounded up to whole chunks).
     ``workspace``         the chunk kernels' per-chunk WY factors (operand-ready tiles written
                           by the forward prep kernel and reused by backward), a tuple with one
                           tensor per wave of batch rows, or ``None``.
@@ -55,9 +56,13 @@ def _token_slots(tokens: int) -> int:
 
 
 def _chunk_kernel_tokens(time: int) -> int:
-    """Leading tokens handed to the tensor-core chunk kernels: every full 64-token chunk."""
+    """Tokens handed to the tensor-core chunk kernels, a multiple of 64: none below 64 tokens, else the
+    whole sequence rounded up (the kernels treat the missing tokens of a partial last chunk as identity
+    steps, so a ragged length costs one more chunk instead of a pass through the token kernels)."""
 
-    return (time // _CHUNK) * _CHUNK
+    if time < _CHUNK:
+        return 0
+    return -(-time // _CHUNK) * _CHUNK
 
 
 def chunk_forward(
@@ -125,7 +130,7 @@ def chunk_forward(
                 )
 
     full_tokens = _chunk_kernel_tokens(time)
-    tail = time - full_tokens
+    tail = max(0, time - full_tokens)  # only sequences shorter than one chunk have one
     chunk_boundaries = tail_boundaries = None
     if return_aux:
         if full_tokens:

@@ -33,10 +33,10 @@ CHECK_MEMORY_MIN_BYTES = 16 << 30
 
 
 def supported_tokens(time: int, *, training: bool = False) -> int:
-    """Leading tokens the chunk kernels process (a multiple of 64, possibly 0)."""
+    """Tokens the chunk kernels process (a multiple of 64: 0 below 64 tokens, else ``time`` rounded up)."""
 
     del training
-    return (time // _CHUNK) * _CHUNK
+    return 0 if time < _CHUNK else -(-time // _CHUNK) * _CHUNK
 
 
 def workspace_bytes(batch: int, full_tokens: int, heads: int, training: bool = False) -> int:

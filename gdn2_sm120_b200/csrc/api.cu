@@ -311,7 +311,8 @@ int chunk_forward_checked(const void* q, const void* k, const void* v, const voi
   if (training && !chunk_boundaries) return GDN2_ERR_NULL_POINTER;
   int st = check_shape(batch, time, heads);
   if (st != GDN2_OK) return st;
-  if (full_tokens <= 0 || full_tokens > time || full_tokens % GDN2_CHUNK != 0) return GDN2_ERR_BAD_RANGE;
+  // whole chunks only, or rounded up over a partial last chunk (its missing tokens are identity steps)
+  if (full_tokens <= 0 || full_tokens % GDN2_CHUNK != 0 || full_tokens >= time + GDN2_CHUNK) return GDN2_ERR_BAD_RANGE;
   if ((st = check_types(dtype, g_dtype)) != GDN2_OK) return st;
   // the fused prologue is a forward-only feature: backward differentiates the activated tensors
   if (!valid_prologue(prologue) || (prologue != 0 && training)) return GDN2_ERR_UNSUPPORTED;
@@ -359,7 +360,8 @@ int chunk_backward_checked(const void* q, const void* k, const void* v, const vo
     return GDN2_ERR_NULL_POINTER;
   int st = check_shape(batch, time, heads);
   if (st != GDN2_OK) return st;
-  if (full_tokens <= 0 || full_tokens > time || full_tokens % GDN2_CHUNK != 0) return GDN2_ERR_BAD_RANGE;
+  // whole chunks only, or rounded up over a partial last chunk (its missing tokens are identity steps)
+  if (full_tokens <= 0 || full_tokens % GDN2_CHUNK != 0 || full_tokens >= time + GDN2_CHUNK) return GDN2_ERR_BAD_RANGE;
   if ((st = check_types(dtype, g_dtype)) != GDN2_OK) return st;
   const void* need16[] = {q, k, v, g, beta, w, d_out, d_final_state, chunk_boundaries, d_boundaries, workspace,
                           scratch, dq, dk, dv, dg, dbeta, dw, d_initial_state};

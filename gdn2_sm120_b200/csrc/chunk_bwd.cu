@@ -134,7 +134,12 @@ chunk_bwd_scan_kernel(const BScanParams p, const __grid_constant__ CUtensorMap t
   auto load_do = [&](int64_t c, typename Raw4<T>::type (&raw)[4]) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      raw[e] = load4_raw<T>(p.d_out, ((b * p.T + c * kChunk + 4 * tg + e) * p.H + h) * kDim + 4 * lane);
+      // past the end of a ragged sequence there is no cotangent: read the chunk's first token instead
+      // (always there) and drop the value, so that no branch separates the loads
+      const int64_t t = c * kChunk + 4 * tg + e;
+      const typename Raw4<T>::type x =
+          load4_raw<T>(p.d_out, ((b * p.T + (t < p.T ? t : c * kChunk)) * p.H + h) * kDim + 4 * lane);
+      raw[e] = (t < p.T) ? x : typename Raw4<T>::type{};
     }
   };
 
@@ -429,7 +434,9 @@ __device__ __forceinline__ void tmem_ld8f(uint32_t taddr, float (&x)[8]) {
 
 // kF32Grads: dq, dk, dv, dbeta, dw leave as fp32 instead of the sequence dtype (the values before
 // their final rounding; used by tests to judge the arithmetic apart from the 16-bit cast).
-template <typename T, typename G, bool kF32Grads = false>
+// kRagged: the sequence length is not a multiple of 64 and the last chunk of every (batch, head) is
+// partial; only this instantiation carries the guards (they cost the others 6 %).
+template <typename T, typename G, bool kF32Grads = false, bool kRagged = false>
 __global__ void __launch_bounds__(kVjpThreads, 1)
 chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s0,
                      const __grid_constant__ CUtensorMap tm_ds, const __grid_constant__ CUtensorMap tm_rn,
@@ -508,6 +515,11 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
   const int64_t b = ch / (p.H * p.n_chunks);
   const int64_t t0 = c * kChunk;
   auto seq_idx = [&](int tok) { return ((b * p.T + t0 + tok) * p.H + h) * int64_t(kDim); };
+  // tokens of this chunk that exist: 64 except in the last chunk of a ragged sequence, whose missing
+  // tokens read as zeros (the identity step) and whose gradients are not stored
+  const int n_valid = kRagged ? int(min(int64_t(kChunk), p.T - t0)) : kChunk;
+  auto there = [&](int tok) { return !kRagged || tok < n_valid; };            // does token `tok` of the chunk exist
+  auto clamped = [&](int tok) { return kRagged ? min(tok, n_valid - 1) : tok; };  // a token that does
   const int ds1_slot = int((b * (p.n_chunks + 1) + c + 1) * p.H + h);
   // dd[k] += sum over the 64 value columns of half `hf` of dS_1[k][v] S_0[k][v], both read from their
   // shared-memory tiles.  The two tiles are swizzled alike (a line = 32 values of one key row, its
@@ -538,8 +550,20 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     float dv4[4][4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      load4v<T>(p.d_out, seq_idx(4 * tg + e) + kc0, dv4[e]);
-      load4v<G>(p.g, seq_idx(4 * tg + e) + kc0, Gc[e]);
+      // a token past the end of a ragged sequence: the last real token is read instead (no branch around
+      // the loads, they are all issued back to back) and its value dropped below
+      const int64_t idx = seq_idx(clamped(4 * tg + e)) + kc0;
+      load4v<T>(p.d_out, idx, dv4[e]);
+      load4v<G>(p.g, idx, Gc[e]);
+    }
+    if (kRagged && n_valid < kChunk) {  // CTA-uniform; false for every chunk but the last one of a sequence
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (!there(4 * tg + e)) {
+#pragma unroll
+          for (int f = 0; f < 4; ++f) dv4[e][f] = Gc[e][f] = 0.f;
+        }
+      }
     }
     if (!kF32Grads) {
       // the dk / dq tiles of the previous unit lie where the dO rows go: their stores must have read them
@@ -615,12 +639,21 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     typename Raw4<T>::type wr[4], vr[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const int64_t idx = seq_idx(4 * tg + e) + kc0;
+      const int64_t idx = seq_idx(clamped(4 * tg + e)) + kc0;  // see phase A
       wr[e] = load4_raw<T>(p.w, idx);
       vr[e] = load4_raw<T>(p.v, idx);
       load4v<T>(p.k, idx, kk[e]);
       load4v<T>(p.q, idx, qq[e]);
       load4v<T>(p.beta, idx, bb[e]);
+    }
+    if (kRagged && n_valid < kChunk) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (!there(4 * tg + e)) {
+#pragma unroll
+          for (int f = 0; f < 4; ++f) kk[e][f] = qq[e][f] = bb[e][f] = 0.f;
+        }
+      }
     }
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -631,8 +664,10 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
       float wv[4], vv[4];
       unpack4<T>(wr[e], wv);
       unpack4<T>(vr[e], vv);
-      store4v<O>(p.dv, idx, dz.x * wv[0], dz.y * wv[1], dz.z * wv[2], dz.w * wv[3]);
-      store4v<O>(p.dw, idx, dz.x * vv[0], dz.y * vv[1], dz.z * vv[2], dz.w * vv[3]);
+      if (there(j)) {
+        store4v<O>(p.dv, idx, dz.x * wv[0], dz.y * wv[1], dz.z * wv[2], dz.w * wv[3]);
+        store4v<O>(p.dw, idx, dz.x * vv[0], dz.y * vv[1], dz.z * vv[2], dz.w * vv[3]);
+      }
     }
   }
   // ---- M4 (second half) once the second half of dS_1 has landed -----------------------------------------
@@ -880,8 +915,10 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
         const float dGt = fmaf(to_tf32(sq[t] * ea), y[t], fmaf(sq[t] * eg, x[t], dG[t]));
         const float dk_t = failed ? poison_nan() : fmaf(bv[t], P2[t], P3[t]);
         if (kF32Grads) {
-          stf<O>(p.dq, idx, p.scale * P1);
-          stf<O>(p.dk, idx, dk_t);
+          if (there(i0 + t)) {
+            stf<O>(p.dq, idx, p.scale * P1);
+            stf<O>(p.dk, idx, dk_t);
+          }
         } else {
           // in place over q and k (this thread's own slots, already read): the tiles leave by TMA stores
           const int off = (i0 + t) * kDim + kc;
@@ -889,7 +926,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
           stf<T>(smem + kOffTileK, off, dk_t);
           stf<T>(smem + beta_tile_offset(blk), (8 * sb + t) * kDim + kc, failed ? poison_nan() : kv[t] * P2[t]);
         }
-        if (kF32Grads) stf<O>(p.dbeta, idx, failed ? poison_nan() : kv[t] * P2[t]);
+        if (kF32Grads && there(i0 + t)) stf<O>(p.dbeta, idx, failed ? poison_nan() : kv[t] * P2[t]);
         dGv[8 * sb + t] = dGt;
         tot += dGt;
       }
@@ -911,7 +948,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
 #pragma unroll
     for (int t = 15; t >= 0; --t) {
       run += dGv[t];
-      stf<G>(p.dg, seq_idx(16 * blk + t) + kc, failed ? poison_nan() : run);
+      if (there(16 * blk + t)) stf<G>(p.dg, seq_idx(16 * blk + t) + kc, failed ? poison_nan() : run);
     }
   }
   // the next chunk-head reuses the arrays of VjpMisc and the TMEM columns
@@ -921,11 +958,13 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
   tc_fence_after();
   if (tid == 0) {
     if (!kF32Grads) {
-      const int row = int(b * p.T + t0);
-      tma_store_3d(&tm_dq, 0, int(h), row, smem + kOffTileQ);
-      tma_store_3d(&tm_dk, 0, int(h), row, smem + kOffTileK);
+      // (the boxes are clipped at token T - 1: rows of a partial last chunk that do not exist are dropped)
+      tma_store_4d(&tm_dq, 0, int(h), int(t0), int(b), smem + kOffTileQ);
+      tma_store_4d(&tm_dk, 0, int(h), int(t0), int(b), smem + kOffTileK);
 #pragma unroll
-      for (int bq = 0; bq < 4; ++bq) tma_store_3d(&tm_dbeta, 0, int(h), row + 16 * bq, smem + beta_tile_offset(bq));
+      for (int bq = 0; bq < 4; ++bq) {  // (a box that starts past token T - 1 is dropped whole)
+        tma_store_4d(&tm_dbeta, 0, int(h), int(t0) + 16 * bq, int(b), smem + beta_tile_offset(bq));
+      }
       bulk_commit();
     }
     // the G tile is dead: the dS_1 half of the next chunk-head may land on it
@@ -996,13 +1035,13 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
   CUtensorMap tm_dq, tm_dk;
   if (B * T > int64_t(0x7fffffff)) return GDN2_ERR_TOO_LARGE;
   if ((reinterpret_cast<uintptr_t>(dq) & 15u) != 0 || (reinterpret_cast<uintptr_t>(dk) & 15u) != 0 ||
-      !encode_sequence_map(&tm_dq, dq, B * T, H, grads_f32 ? GDN2_FP32 : dtype) ||
-      !encode_sequence_map(&tm_dk, dk, B * T, H, grads_f32 ? GDN2_FP32 : dtype)) {
+      !encode_sequence_map(&tm_dq, dq, B, T, H, grads_f32 ? GDN2_FP32 : dtype) ||
+      !encode_sequence_map(&tm_dk, dk, B, T, H, grads_f32 ? GDN2_FP32 : dtype)) {
     return GDN2_ERR_LAUNCH;
   }
   CUtensorMap tm_dbeta;
   if ((reinterpret_cast<uintptr_t>(dbeta) & 15u) != 0 ||
-      !encode_sequence_map(&tm_dbeta, dbeta, B * T, H, grads_f32 ? GDN2_FP32 : dtype, 16)) {
+      !encode_sequence_map(&tm_dbeta, dbeta, B, T, H, grads_f32 ? GDN2_FP32 : dtype, 16)) {
     return GDN2_ERR_LAUNCH;
   }
   CUtensorMap tm_rn;
@@ -1010,14 +1049,16 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
   VjpParams vp{q, k, v, g, beta, w, d_out, workspace, scratch, bnd, d_bnd, dq, dk, dv, dg, dbeta, dw,
                status, T, H, n_chunks, n_ch, scale};
   const unsigned vjp_grid = unsigned(n_ch < int64_t(sm_count) ? n_ch : int64_t(sm_count));
+  const bool ragged = full_tokens > T;  // the last chunk of every (batch, head) is partial
   if (grads_f32) {
-    auto kernel = chunk_bwd_vjp_kernel<__nv_bfloat16, float, true>;
+    auto kernel = ragged ? chunk_bwd_vjp_kernel<__nv_bfloat16, float, true, true>
+                         : chunk_bwd_vjp_kernel<__nv_bfloat16, float, true, false>;
     err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kVjpSmemBytes);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
     kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds, tm_rn, tm_dq, tm_dk, tm_dbeta);
   } else {
     GDN2_DISPATCH_TYPES(dtype, g_dtype, {
-      auto kernel = chunk_bwd_vjp_kernel<T, G>;
+      auto kernel = ragged ? chunk_bwd_vjp_kernel<T, G, false, true> : chunk_bwd_vjp_kernel<T, G, false, false>;
       err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kVjpSmemBytes);
       if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
       kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds, tm_rn, tm_dq, tm_dk, tm_dbeta);

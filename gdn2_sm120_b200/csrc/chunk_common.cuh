@@ -208,26 +208,31 @@ inline EncodeTiledFn encode_tiled_fn() {
 // blocks out again), so the last few hundred are kept.  Direct-mapped, one mutex.
 struct TensorMapKey {
   uintptr_t base;
-  cuuint64_t dims[3], strides[2];
-  cuuint32_t box[3];
-  int type, swizzle;
+  cuuint64_t dims[4], strides[3];
+  cuuint32_t box[4];
+  int rank, type, swizzle;
   bool operator==(const TensorMapKey& o) const {
-    return base == o.base && dims[0] == o.dims[0] && dims[1] == o.dims[1] && dims[2] == o.dims[2] &&
-           strides[0] == o.strides[0] && strides[1] == o.strides[1] && box[0] == o.box[0] && box[1] == o.box[1] &&
-           box[2] == o.box[2] && type == o.type && swizzle == o.swizzle;
+    bool same = base == o.base && rank == o.rank && type == o.type && swizzle == o.swizzle;
+    for (int i = 0; i < 4; ++i) same = same && dims[i] == o.dims[i] && box[i] == o.box[i];
+    for (int i = 0; i < 3; ++i) same = same && strides[i] == o.strides[i];
+    return same;
   }
 };
 
-inline bool encode_3d_cached(CUtensorMap* tm, CUtensorMapDataType type, const void* base, const cuuint64_t (&dims)[3],
-                             const cuuint64_t (&strides)[2], const cuuint32_t (&box)[3], CUtensorMapSwizzle swizzle) {
+// rank 3 or 4; unused trailing entries of dims / strides / box are 1 / 0 / 1
+inline bool encode_cached(CUtensorMap* tm, int rank, CUtensorMapDataType type, const void* base,
+                          const cuuint64_t (&dims)[4], const cuuint64_t (&strides)[3], const cuuint32_t (&box)[4],
+                          CUtensorMapSwizzle swizzle) {
   constexpr int kSlots = 512;
   struct Slot { bool used = false; TensorMapKey key; CUtensorMap map; };
   static Slot slots[kSlots];
   static std::mutex mutex;
-  TensorMapKey key{reinterpret_cast<uintptr_t>(base), {dims[0], dims[1], dims[2]}, {strides[0], strides[1]},
-                   {box[0], box[1], box[2]}, int(type), int(swizzle)};
+  TensorMapKey key{reinterpret_cast<uintptr_t>(base), {dims[0], dims[1], dims[2], dims[3]},
+                   {strides[0], strides[1], strides[2]}, {box[0], box[1], box[2], box[3]}, rank, int(type),
+                   int(swizzle)};
   uint64_t h = key.base * 0x9E3779B97F4A7C15ull;
-  h ^= (key.dims[2] + 0x632BE59BD9B4E019ull * key.strides[1]) + (uint64_t(key.box[1]) << 7) + uint64_t(key.swizzle) * 31 + uint64_t(key.type);
+  h ^= (key.dims[2] + 0x632BE59BD9B4E019ull * key.strides[1]) + (uint64_t(key.box[1]) << 7) + (uint64_t(key.box[2]) << 17) +
+       uint64_t(key.swizzle) * 31 + uint64_t(key.type) + uint64_t(rank) * 131 + key.dims[3] * 0x2545F4914F6CDD1Dull;
   h ^= h >> 29;
   Slot& slot = slots[h % kSlots];
   {
@@ -236,9 +241,11 @@ inline bool encode_3d_cached(CUtensorMap* tm, CUtensorMapDataType type, const vo
   }
   EncodeTiledFn encode = encode_tiled_fn();
   if (encode == nullptr) return false;
-  const cuuint32_t elem_strides[3] = {1, 1, 1};
-  if (encode(tm, type, 3, const_cast<void*>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+  const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+  // OOB_FILL_NONE: the part of a load box outside the tensor reads as zero
+  if (encode(tm, type, cuuint32_t(rank), const_cast<void*>(base), dims, strides, box, elem_strides,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
     return false;
   }
   std::lock_guard<std::mutex> lock(mutex);
@@ -246,19 +253,21 @@ inline bool encode_3d_cached(CUtensorMap* tm, CUtensorMapDataType type, const vo
   return true;
 }
 
-// A contiguous [B, T, H, 128] sequence tensor seen as (channel, head, b * T + t): a box
-// (128, 1, 64) is one head's 64-token chunk, landing in shared memory as dense [64][128] rows
-// (`box_rows` tokens instead of 64 when given).
-inline bool encode_sequence_map(CUtensorMap* tm, const void* base, int64_t rows, int64_t heads, int dtype,
-                                int box_rows = kChunk) {
+// A contiguous [B, T, H, 128] sequence tensor seen as (channel, head, token, batch): a box
+// (128, 1, 64, 1) is one head's 64-token chunk, landing in shared memory as dense [64][128] rows
+// (`box_rows` tokens instead of 64 when given).  Tokens are a dimension of their own so that the last,
+// partial chunk of a ragged sequence reads zeros beyond token T - 1 (and a store is clipped there).
+inline bool encode_sequence_map(CUtensorMap* tm, const void* base, int64_t batch, int64_t time, int64_t heads,
+                                int dtype, int box_rows = kChunk) {
   const cuuint64_t es = (dtype == GDN2_FP32) ? 4 : 2;
   const CUtensorMapDataType type = (dtype == GDN2_FP32)   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                    : (dtype == GDN2_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                           : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  const cuuint64_t dims[3] = {cuuint64_t(kDim), cuuint64_t(heads), cuuint64_t(rows)};
-  const cuuint64_t strides[2] = {cuuint64_t(kDim) * es, cuuint64_t(heads) * kDim * es};  // bytes, dimensions 1..2
-  const cuuint32_t box[3] = {cuuint32_t(kDim), 1, cuuint32_t(box_rows)};
-  return encode_3d_cached(tm, type, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+  const cuuint64_t dims[4] = {cuuint64_t(kDim), cuuint64_t(heads), cuuint64_t(time), cuuint64_t(batch)};
+  const cuuint64_t strides[3] = {cuuint64_t(kDim) * es, cuuint64_t(heads) * kDim * es,
+                                 cuuint64_t(time) * heads * kDim * es};  // bytes, dimensions 1..3
+  const cuuint32_t box[4] = {cuuint32_t(kDim), 1, cuuint32_t(box_rows), 1};
+  return encode_cached(tm, 4, type, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 // An array of n_ch row-major fp32 tiles [rows][cols] seen as (col, row, unit): a box (32, rows, 1) is a
@@ -268,18 +277,18 @@ inline bool encode_sequence_map(CUtensorMap* tm, const void* base, int64_t rows,
 // (`box_rows` < rows: boxes of that many rows, for tiles whose zero quadrant is never moved.)
 inline bool encode_tile_map(CUtensorMap* tm, const uint8_t* base, int64_t n_ch, int rows, int cols, bool mn_major,
                             int box_rows = 0) {
-  const cuuint64_t dims[3] = {cuuint64_t(cols), cuuint64_t(rows), cuuint64_t(n_ch)};
-  const cuuint64_t strides[2] = {cuuint64_t(cols) * 4, cuuint64_t(rows) * cols * 4};
-  const cuuint32_t box[3] = {32, cuuint32_t(box_rows > 0 ? box_rows : rows), 1};
-  return encode_3d_cached(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, dims, strides, box,
-                          mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B);
+  const cuuint64_t dims[4] = {cuuint64_t(cols), cuuint64_t(rows), cuuint64_t(n_ch), 1};
+  const cuuint64_t strides[3] = {cuuint64_t(cols) * 4, cuuint64_t(rows) * cols * 4, 0};
+  const cuuint32_t box[4] = {32, cuuint32_t(box_rows > 0 ? box_rows : rows), 1, 1};
+  return encode_cached(tm, 3, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, dims, strides, box,
+                       mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B);
 }
 // The same array, whole tiles without swizzle (box (cols, rows, 1); cols <= 256): for tiles that threads read.
 inline bool encode_plain_tile_map(CUtensorMap* tm, const uint8_t* base, int64_t n_ch, int rows, int cols) {
-  const cuuint64_t dims[3] = {cuuint64_t(cols), cuuint64_t(rows), cuuint64_t(n_ch)};
-  const cuuint64_t strides[2] = {cuuint64_t(cols) * 4, cuuint64_t(rows) * cols * 4};
-  const cuuint32_t box[3] = {cuuint32_t(cols), cuuint32_t(rows), 1};
-  return encode_3d_cached(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+  const cuuint64_t dims[4] = {cuuint64_t(cols), cuuint64_t(rows), cuuint64_t(n_ch), 1};
+  const cuuint64_t strides[3] = {cuuint64_t(cols) * 4, cuuint64_t(rows) * cols * 4, 0};
+  const cuuint32_t box[4] = {cuuint32_t(cols), cuuint32_t(rows), 1, 1};
+  return encode_cached(tm, 3, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {

@@ -127,22 +127,24 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
   const int kc0 = 4 * c4;
   const int q4 = warp & 3, part = warp >> 2;  // TMEM lane quadrant of this warp, and its share of the columns
 
-  // unit -> TMA coordinates (channel 0, head, first row of the chunk in the [B * T] row space)
+  // unit -> TMA coordinates (channel 0, head, first token of the chunk, batch row).  The last chunk of a
+  // ragged sequence reaches past token T - 1: the loads fill those rows with zeros, which is the identity
+  // step of the recurrence (no decay, no key, no query, no value).
   const int heads = int(p.H), chunks = int(p.n_chunks), n_ch = int(p.n_ch);
   constexpr uint32_t kStageTileG = kChunk * kDim * sizeof(G);
   auto issue_gkq = [&](int ch_) {
-    const int h_ = ch_ % heads, bc = ch_ / heads, row = (bc / chunks) * int(p.T) + (bc % chunks) * kChunk;
+    const int h_ = ch_ % heads, bc = ch_ / heads, b_ = bc / chunks, t_ = (bc % chunks) * kChunk;
     mbar_arrive_expect_tx(&sm.bar_ld[0], kStageTileG + 2 * kStageTile16);
-    tma_load_3d(sm.gram_a, &tm_g, 0, h_, row, &sm.bar_ld[0]);
-    tma_load_3d(sm.gram_a + kStageK, &tm_k, 0, h_, row, &sm.bar_ld[0]);
-    tma_load_3d(sm.gram_a + kStageQ, &tm_q, 0, h_, row, &sm.bar_ld[0]);
+    tma_load_4d(sm.gram_a, &tm_g, 0, h_, t_, b_, &sm.bar_ld[0]);
+    tma_load_4d(sm.gram_a + kStageK, &tm_k, 0, h_, t_, b_, &sm.bar_ld[0]);
+    tma_load_4d(sm.gram_a + kStageQ, &tm_q, 0, h_, t_, b_, &sm.bar_ld[0]);
   };
   auto issue_bvw = [&](int ch_) {
-    const int h_ = ch_ % heads, bc = ch_ / heads, row = (bc / chunks) * int(p.T) + (bc % chunks) * kChunk;
+    const int h_ = ch_ % heads, bc = ch_ / heads, b_ = bc / chunks, t_ = (bc % chunks) * kChunk;
     mbar_arrive_expect_tx(&sm.bar_ld[1], 3 * kStageTile16);
-    tma_load_3d(sm.gram_b + kStageBeta, &tm_beta, 0, h_, row, &sm.bar_ld[1]);
-    tma_load_3d(sm.tmat + kStageV, &tm_v, 0, h_, row, &sm.bar_ld[1]);
-    tma_load_3d(sm.stage_w, &tm_w, 0, h_, row, &sm.bar_ld[1]);
+    tma_load_4d(sm.gram_b + kStageBeta, &tm_beta, 0, h_, t_, b_, &sm.bar_ld[1]);
+    tma_load_4d(sm.tmat + kStageV, &tm_v, 0, h_, t_, b_, &sm.bar_ld[1]);
+    tma_load_4d(sm.stage_w, &tm_w, 0, h_, t_, b_, &sm.bar_ld[1]);
   };
   tc_fence_before();
   __syncthreads();
@@ -160,6 +162,9 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
   uint32_t par = 0;
   for (int ch = int(blockIdx.x); ch < n_ch; ch += int(gridDim.x), par ^= 1u) {
   const int ch_next = ch + int(gridDim.x);
+  // tokens of this chunk that exist (64 except in the last chunk of a ragged sequence); only the fused
+  // prologue needs to know: its activations do not map the zero fill to the identity step
+  const int n_valid = kPro ? min(kChunk, int(p.T) - ((ch / heads) % chunks) * kChunk) : kChunk;
   // ---- the raw inputs were brought in while the previous unit was finishing; the log-decay is
   // consumed first: the prefix sums below need it alone ------------------------------------------------
   float Gc[4][4], kk[4][4], qq[4][4], bb[4][4];
@@ -184,7 +189,7 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
       unpack4<G>(rg[e], gv);
 #pragma unroll
       for (int f = 0; f < 4; ++f) {
-        if (pro_gate) gv[f] = prologue_log_decay(gv[f]);
+        if (pro_gate) gv[f] = (4 * tg + e < n_valid) ? prologue_log_decay(gv[f]) : 0.f;
         Gc[e][f] = (e ? Gc[e - 1][f] : 0.f) + gv[f];
       }
     }
@@ -234,7 +239,7 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
       }
       if (pro_gate) {
 #pragma unroll
-        for (int f = 0; f < 4; ++f) bb[e][f] = prologue_sigmoid(bb[e][f]);
+        for (int f = 0; f < 4; ++f) bb[e][f] = (4 * tg + e < n_valid) ? prologue_sigmoid(bb[e][f]) : 0.f;
       }
     }
   }
@@ -356,7 +361,7 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
       unpack4<T>(*reinterpret_cast<const typename Raw4<T>::type*>(staged(sm.stage_w, e, 2)), ww);
 #pragma unroll
       for (int f = 0; f < 4; ++f) {
-        if (pro_gate) ww[f] = prologue_sigmoid(ww[f]);
+        if (pro_gate) ww[f] = (4 * tg + e < n_valid) ? prologue_sigmoid(ww[f]) : 0.f;
         zz[e][f] = to_tf32(vv[f] * ww[f]);
       }
     }
@@ -791,8 +796,10 @@ chunk_scan_kernel(const ScanParams p, const __grid_constant__ CUtensorMap tm_yt,
       const bool failed = upstream_failed || waiter.dead;
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
-        out[((b * p.T + t0 + i0 + j) * p.H + h) * kDim + vrow] =
-            from_float<T>(failed ? poison_nan() : __uint_as_float(ro[j]));
+        if (t0 + i0 + j < p.T) {  // the last chunk of a ragged sequence has fewer than 64 tokens
+          out[((b * p.T + t0 + i0 + j) * p.H + h) * kDim + vrow] =
+              from_float<T>(failed ? poison_nan() : __uint_as_float(ro[j]));
+        }
       }
     }
     // ---- checkpoint the chunk-start state, then decay the accumulator: S^T <- S^T diag(d) ----------
@@ -922,13 +929,13 @@ int launch_chunk_forward(const void* q, const void* k, const void* v, const void
   cudaError_t err = cudaMemsetAsync(status, 0, kStatusBytes, stream);
   if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
 
-  // the prep kernel addresses its inputs through tensor maps: rows b * T + t in 31 bits, 16-byte aligned bases
+  // the prep kernel addresses its inputs through tensor maps: 16-byte aligned bases
   if (B * T > int64_t(0x7fffffff)) return GDN2_ERR_TOO_LARGE;
   const void* seq[6] = {g, k, q, beta, v, w};
   CUtensorMap tm[6];
   for (int i = 0; i < 6; ++i) {
     if ((reinterpret_cast<uintptr_t>(seq[i]) & 15u) != 0 ||
-        !encode_sequence_map(&tm[i], seq[i], B * T, H, i == 0 ? g_dtype : dtype)) {
+        !encode_sequence_map(&tm[i], seq[i], B, T, H, i == 0 ? g_dtype : dtype)) {
       return GDN2_ERR_LAUNCH;
     }
   }

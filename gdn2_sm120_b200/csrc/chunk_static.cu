@@ -77,7 +77,8 @@ extern "C" int gdn2_chunk_forward_static(const void* q, const void* k, const voi
   using namespace gdn2;
   if (!q || !k || !v || !g || !beta || !w || !out) return GDN2_ERR_NULL_POINTER;
   if (batch <= 0 || heads <= 0 || time <= 0) return GDN2_ERR_BAD_SHAPE;
-  if (full_tokens <= 0 || full_tokens > time || full_tokens % GDN2_CHUNK != 0) return GDN2_ERR_BAD_RANGE;
+  // whole chunks only, or rounded up over a partial last chunk (its missing tokens are identity steps)
+  if (full_tokens <= 0 || full_tokens % GDN2_CHUNK != 0 || full_tokens >= time + GDN2_CHUNK) return GDN2_ERR_BAD_RANGE;
   if (!valid_seq_dtype(dtype) || !valid_gate_dtype(g_dtype, dtype)) return GDN2_ERR_BAD_DTYPE;
   // reject anything that does not fit the fixed array (checked without overflow)
   const int64_t n_chunks = full_tokens / GDN2_CHUNK;

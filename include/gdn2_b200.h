@@ -148,8 +148,13 @@ int gdn2_token_chunk_vjp(const void* q, const void* k, const void* v, const void
 /*
  * ---- tensor-core chunk path (64-token chunks) ---------------------------------------
  *
- * The chunk kernels use two caller-owned buffers for `full_tokens` leading tokens (a multiple
- * of GDN2_CHUNK) of a [batch, T, heads, 128] problem:
+ * The chunk kernels process the tokens [0, full_tokens) of a [batch, T, heads, 128] problem, where
+ * full_tokens is a multiple of GDN2_CHUNK: either 64 * floor(T / 64), the caller sending the ragged
+ * tail through the token entry points (forward after the chunks, backward before them), or
+ * 64 * ceil(T / 64), in which case the last chunk is partial: the kernels read its missing tokens as
+ * zeros, which is the identity step of the recurrence, write no output row and no gradient for them,
+ * and the state after the last chunk is the state after token T - 1.  Sizes below are asked with the
+ * same full_tokens.  Two caller-owned buffers:
  *
  *   workspace  gdn2_chunk_workspace_bytes(batch, full_tokens, heads, training).  Holds the
  *              chunk-end decays and a device status word; with `training` != 0 also what
