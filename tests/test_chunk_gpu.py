@@ -46,6 +46,30 @@ def test_chunk_forward_grids(batch, heads):
     check(out, state, ref_out, ref_state)
 
 
+def test_both_ways_of_handling_a_ragged_length_agree():
+    """The C ABI takes a ragged length either way: whole chunks on the chunk kernels plus the tail on the
+    token kernels (full_tokens = 64 * floor(T / 64)), or everything on the chunk kernels with a partial
+    last chunk (64 * ceil(T / 64), what chunk_gdn2 does).  Same inputs, both against the oracle."""
+
+    from gdn2_sm120_b200 import chunk_kernels
+    from gdn2_sm120_b200.recurrent import _launch_token_forward
+
+    batch, time, heads = 2, 150, 3
+    cpu = oracle.make_inputs(batch, time, heads, seed=150)
+    ref_out, ref_state = oracle.recurrence(*cpu)
+    q, k, v, g, beta, w, s0 = dev(*cpu)
+    out_pad, fin_pad = chunk_gdn2(q, k, v, g, beta, w, s0, output_final_state=True)
+    check(out_pad, fin_pad, ref_out, ref_state)
+    out_split, fin_split = torch.empty_like(v), torch.empty_like(s0)
+    scale = 128 ** -0.5
+    chunk_kernels.forward(q, k, v, g, beta, w, s0, out_split, fin_split, None, batch, time, heads, 128, scale)
+    _launch_token_forward(q, k, v, g, beta, w, fin_split, out_split, fin_split, None, batch, time, heads, 128,
+                          time, scale)
+    check(out_split, fin_split, ref_out, ref_state)
+    # the first two chunks are the same computation either way
+    assert torch.equal(out_split[:, :128], out_pad[:, :128])
+
+
 def test_chunk_forward_more_units_than_sms():
     """An inference call whose units (batch x chunks x heads = 256) outnumber the SMs: the persistent prep
     kernel walks over several units per CTA with the next unit's inputs arriving under the current one."""
