@@ -8,14 +8,16 @@
 //                              dR^T  = dO^T Aqk + dS^T Kt^T        dZ^T = dR^T T
 //                              dS^T <- dS^T diag(d) + dO^T Qg - dR^T Y
 //                          It writes dZ = T^T dR per chunk and the cotangent at every chunk start.
-//   chunk_bwd_vjp_kernel   one CTA per (batch, chunk, head), all chunks in parallel.  With
-//                          R = T (Z - E S_0) as the parametrisation (no Y / U needed):
+//   chunk_bwd_vjp_kernel   persistent, one CTA per SM walking over the (batch, chunk, head) units,
+//                          all chunks independent.  With R = T (Z - E S_0) as the parametrisation
+//                          (no Y / U needed):
 //                              dv = dZ w, dw = dZ v             (dZ = T^T dR comes from the scan)
 //                              [-dE ; dQg] = [dZ ; dO] S_0^T    dKt = R dS_1^T
 //                              [-dL ; dA]  = [dZ ; dO] R^T      (strictly lower / lower part)
 //                          then the Gram products' VJP with the same 16-token block anchors as the
 //                          forward, and a per-channel chain (one thread = one key channel) that
 //                          forms dq, dk, dbeta and the reverse cumulative sum for dg.
+// A ragged length ends in a partial chunk: tokens past T - 1 carry no cotangent and get no gradient.
 //
 // Reference counterparts: boundary scan  src/gdn2_sm120/backward_parallel.py:721-1049,
 // compact-WY VJP  src/gdn2_sm120/backward_wy.py:226-1168 (a 10-12 launch graph there).
