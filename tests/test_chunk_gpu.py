@@ -70,6 +70,21 @@ def test_both_ways_of_handling_a_ragged_length_agree():
     assert torch.equal(out_split[:, :128], out_pad[:, :128])
 
 
+def test_a_sequence_shorter_than_one_chunk_runs_as_one_partial_chunk():
+    """The Python API sends fewer than 64 tokens to the token kernels, but the C ABI takes them as one
+    partial chunk too (full_tokens = 64 > T): 40 real tokens, 24 identity steps."""
+
+    from gdn2_sm120_b200 import chunk_kernels
+
+    batch, time, heads = 2, 40, 2
+    cpu = oracle.make_inputs(batch, time, heads, seed=40)
+    ref_out, ref_state = oracle.recurrence(*cpu)
+    q, k, v, g, beta, w, s0 = dev(*cpu)
+    out, fin = torch.empty_like(v), torch.empty_like(s0)
+    chunk_kernels.forward(q, k, v, g, beta, w, s0, out, fin, None, batch, time, heads, 64, 128 ** -0.5)
+    check(out, fin, ref_out, ref_state)
+
+
 def test_chunk_forward_more_units_than_sms():
     """An inference call whose units (batch x chunks x heads = 256) outnumber the SMs: the persistent prep
     kernel walks over several units per CTA with the next unit's inputs arriving under the current one."""
