@@ -657,20 +657,27 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
         }
       }
     }
+    // a warp's four tokens exist all (every warp of a full chunk: the plain sequence of stores) or only
+    // some (one warp of the last chunk of a ragged sequence at most): warp-uniform choice, no predicate
+    // on the common path
+    auto store_dv_dw = [&](auto guarded) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int j = 4 * tg + e;
-      float4 dz = *reinterpret_cast<const float4*>(smem + kOffStack + (j >> 3) * kRsN + c4 * kCsN + (j & 7) * 16);
-      if (upstream_failed || waiter.dead) dz = make_float4(poison_nan(), poison_nan(), poison_nan(), poison_nan());
-      const int64_t idx = seq_idx(j) + kc0;
-      float wv[4], vv[4];
-      unpack4<T>(wr[e], wv);
-      unpack4<T>(vr[e], vv);
-      if (there(j)) {
-        store4v<O>(p.dv, idx, dz.x * wv[0], dz.y * wv[1], dz.z * wv[2], dz.w * wv[3]);
-        store4v<O>(p.dw, idx, dz.x * vv[0], dz.y * vv[1], dz.z * vv[2], dz.w * vv[3]);
+      for (int e = 0; e < 4; ++e) {
+        const int j = 4 * tg + e;
+        float4 dz = *reinterpret_cast<const float4*>(smem + kOffStack + (j >> 3) * kRsN + c4 * kCsN + (j & 7) * 16);
+        if (upstream_failed || waiter.dead) dz = make_float4(poison_nan(), poison_nan(), poison_nan(), poison_nan());
+        const int64_t idx = seq_idx(j) + kc0;
+        float wv[4], vv[4];
+        unpack4<T>(wr[e], wv);
+        unpack4<T>(vr[e], vv);
+        if (!decltype(guarded)::value || j < n_valid) {
+          store4v<O>(p.dv, idx, dz.x * wv[0], dz.y * wv[1], dz.z * wv[2], dz.w * wv[3]);
+          store4v<O>(p.dw, idx, dz.x * vv[0], dz.y * vv[1], dz.z * vv[2], dz.w * vv[3]);
+        }
       }
-    }
+    };
+    if (!kRagged || 4 * tg + 4 <= n_valid) store_dv_dw(std::false_type{});
+    else store_dv_dw(std::true_type{});
   }
   // ---- M4 (second half) once the second half of dS_1 has landed -----------------------------------------
   waiter.wait(&ms.bar_d, par);
@@ -947,10 +954,18 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     for (int bq = 3; bq > 0; --bq) {
       if (bq > blk) run += ms.xt[bq][kc];
     }
+    if (!kRagged || 16 * blk + 16 <= n_valid) {  // the whole 16-token block exists (warp-uniform)
 #pragma unroll
-    for (int t = 15; t >= 0; --t) {
-      run += dGv[t];
-      if (there(16 * blk + t)) stf<G>(p.dg, seq_idx(16 * blk + t) + kc, failed ? poison_nan() : run);
+      for (int t = 15; t >= 0; --t) {
+        run += dGv[t];
+        stf<G>(p.dg, seq_idx(16 * blk + t) + kc, failed ? poison_nan() : run);
+      }
+    } else {
+#pragma unroll
+      for (int t = 15; t >= 0; --t) {
+        run += dGv[t];
+        if (16 * blk + t < n_valid) stf<G>(p.dg, seq_idx(16 * blk + t) + kc, failed ? poison_nan() : run);
+      }
     }
   }
   // the next chunk-head reuses the arrays of VjpMisc and the TMEM columns
