@@ -380,6 +380,10 @@ struct VjpParams {
   int64_t T, H, n_chunks, n_ch;
   float scale;
 };
+// tensor maps of the seven sequence tensors the VJP kernel reads (for L2 prefetches only)
+struct VjpInputMaps {
+  CUtensorMap q, k, v, g, beta, w, d_out;
+};
 
 template <typename T>
 __device__ __forceinline__ void load4v(const void* base, int64_t idx, float (&out)[4]);
@@ -443,7 +447,7 @@ __global__ void __launch_bounds__(kVjpThreads, 1)
 chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s0,
                      const __grid_constant__ CUtensorMap tm_ds, const __grid_constant__ CUtensorMap tm_rn,
                      const __grid_constant__ CUtensorMap tm_dq, const __grid_constant__ CUtensorMap tm_dk,
-                     const __grid_constant__ CUtensorMap tm_dbeta) {
+                     const __grid_constant__ CUtensorMap tm_dbeta, const __grid_constant__ VjpInputMaps tm_in) {
   using O = typename std::conditional<kF32Grads, float, T>::type;  // element type of dq, dk, dv, dbeta, dw
   extern __shared__ __align__(1024) uint8_t smem[];
   VjpMisc& ms = *reinterpret_cast<VjpMisc*>(smem + kOffMisc);
@@ -822,6 +826,19 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
   tc_fence_after();
   // shared memory (all but the small arrays of VjpMisc) is dead from here on: fetch the next chunk-head
   if (tid == 0 && ch + gridDim.x < p.n_ch) issue_loads(ch + gridDim.x);
+  // The sequence tensors of the next chunk-head are read with per-thread loads, whose rate is set by the
+  // bytes in flight over the latency: have its seven [64][128] tiles brought into L2 while the chain runs.
+  if (tid == 64 && ch + gridDim.x < p.n_ch) {
+    const int64_t ch_ = ch + gridDim.x;
+    const int h_ = int(ch_ % p.H), t_ = int((ch_ / p.H) % p.n_chunks) * kChunk, b_ = int(ch_ / (p.H * p.n_chunks));
+    tma_prefetch_l2_4d(&tm_in.d_out, 0, h_, t_, b_);
+    tma_prefetch_l2_4d(&tm_in.g, 0, h_, t_, b_);
+    tma_prefetch_l2_4d(&tm_in.w, 0, h_, t_, b_);
+    tma_prefetch_l2_4d(&tm_in.v, 0, h_, t_, b_);
+    tma_prefetch_l2_4d(&tm_in.k, 0, h_, t_, b_);
+    tma_prefetch_l2_4d(&tm_in.q, 0, h_, t_, b_);
+    tma_prefetch_l2_4d(&tm_in.beta, 0, h_, t_, b_);
+  }
   // hand k, q and the log-decay prefix to the chain, which walks the tokens of one channel: these threads
   // hold them as 4 x 4 patches (the same values, and for G the same summation order, as the tiles above)
   {
@@ -1063,6 +1080,17 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
   }
   CUtensorMap tm_rn;
   if (!encode_tile_map(&tm_rn, workspace + ws.off_rn(), n_ch, kChunk, kDim, false)) return GDN2_ERR_LAUNCH;
+  VjpInputMaps tm_in;
+  {
+    const void* bases[7] = {q, k, v, g, beta, w, d_out};
+    CUtensorMap* maps[7] = {&tm_in.q, &tm_in.k, &tm_in.v, &tm_in.g, &tm_in.beta, &tm_in.w, &tm_in.d_out};
+    for (int i = 0; i < 7; ++i) {
+      if ((reinterpret_cast<uintptr_t>(bases[i]) & 15u) != 0 ||
+          !encode_sequence_map(maps[i], bases[i], B, T, H, i == 3 ? g_dtype : dtype)) {
+        return GDN2_ERR_LAUNCH;
+      }
+    }
+  }
   VjpParams vp{q, k, v, g, beta, w, d_out, workspace, scratch, bnd, d_bnd, dq, dk, dv, dg, dbeta, dw,
                status, T, H, n_chunks, n_ch, scale};
   const unsigned vjp_grid = unsigned(n_ch < int64_t(sm_count) ? n_ch : int64_t(sm_count));
@@ -1072,13 +1100,13 @@ int launch_chunk_backward(const void* q, const void* k, const void* v, const voi
                          : chunk_bwd_vjp_kernel<__nv_bfloat16, float, true, false>;
     err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kVjpSmemBytes);
     if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
-    kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds, tm_rn, tm_dq, tm_dk, tm_dbeta);
+    kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds, tm_rn, tm_dq, tm_dk, tm_dbeta, tm_in);
   } else {
     GDN2_DISPATCH_TYPES(dtype, g_dtype, {
       auto kernel = ragged ? chunk_bwd_vjp_kernel<T, G, false, true> : chunk_bwd_vjp_kernel<T, G, false, false>;
       err = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kVjpSmemBytes);
       if (err != cudaSuccess) { record_cuda_error(err); return GDN2_ERR_LAUNCH; }
-      kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds, tm_rn, tm_dq, tm_dk, tm_dbeta);
+      kernel<<<vjp_grid, kVjpThreads, kVjpSmemBytes, stream>>>(vp, tm_s0, tm_ds, tm_rn, tm_dq, tm_dk, tm_dbeta, tm_in);
     });
   }
   st = check_launch();

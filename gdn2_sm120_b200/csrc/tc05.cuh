@@ -71,6 +71,13 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
       "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
+// Ask for a 4-D box of a tensor map to be brought into L2 (no destination, no completion to wait for).
+// Coordinates as for a load.
+__device__ __forceinline__ void tma_prefetch_l2_4d(const void* tmap, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(tmap), "r"(c0),
+               "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
 // 3-D tiled TMA load global -> shared; completion (bytes) on an mbarrier.  `tmap` points at a
 // CUtensorMap in kernel-parameter space.  c0 must keep c0 * element size a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, int c0, int c1, int c2, uint64_t* bar) {
