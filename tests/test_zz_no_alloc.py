@@ -41,18 +41,19 @@ def _call_ordinary(q, k, v, g, beta, w, s0, batch, time, heads, full, scale):
     return out, fin
 
 
-@pytest.mark.parametrize("shapes", [[(1, 256, 4, 501, True), (2, 128, 3, 502, False)]])
+@pytest.mark.parametrize("shapes", [[(1, 256, 4, 501, True), (2, 128, 3, 502, False), (1, 200, 3, 503, True)]])
 def test_static_workspace_entry_matches_ordinary_entry_twice(shapes):
     scale = 128 ** -0.5
     for batch, time, heads, seed, with_state in shapes:
         cpu = oracle.make_inputs(batch, time, heads, seed=seed, with_state=with_state)
         q, k, v, g, beta, w = (t.to(DEV) for t in cpu[:6])
         s0 = cpu[6].to(DEV) if with_state else None
-        status, out_s, fin_s = _call_static(q, k, v, g, beta, w, s0, batch, time, heads, time, scale)
+        full = -(-time // 64) * 64  # 200 tokens: four chunks, the last one with 8 of its 64 tokens
+        status, out_s, fin_s = _call_static(q, k, v, g, beta, w, s0, batch, time, heads, full, scale)
         assert status == 0, _lib.lib().gdn2_status_string(status)
         # no bounded wait ran out inside the kernels (status word of the fixed array)
         assert _lib.lib().gdn2_chunk_static_read_status(torch.cuda.current_stream().cuda_stream) == 0
-        out_o, fin_o = _call_ordinary(q, k, v, g, beta, w, s0, batch, time, heads, time, scale)
+        out_o, fin_o = _call_ordinary(q, k, v, g, beta, w, s0, batch, time, heads, full, scale)
         torch.cuda.synchronize()
         torch.testing.assert_close(out_s.float(), out_o.float(), rtol=2e-2, atol=1e-2)
         assert oracle.rel_l2(fin_s, fin_o) < 1e-3
