@@ -872,9 +872,12 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     const float t_end = __expf(gend - a_nx);     // exp(G_end - G) = exp(a_next - G) t_end
     const float far2 = (blk + 2 < 4) ? __expf(ms.part[4 * (blk + 2)][kc] - a_nx) : 1.f;  // row block blk + 2
     const float far3 = (blk + 3 < 4) ? __expf(ms.part[4 * (blk + 3)][kc] - a_nx) : 1.f;  // row block blk + 3
-    float dGv[16];
+    // dG of a token goes back into the slot of the G tile this thread read its log-decay from (nobody else
+    // touches it), and the two halves of the block run as a loop: the kernel is a long stretch of
+    // straight-line code that every warp walks once per unit, and what it does not need to hold twice
+    // saves instruction fetches
     float e_part = 0.f, tot = 0.f;
-#pragma unroll
+#pragma unroll 1
     for (int sb = 0; sb < 2; ++sb) {
       const int i0 = 16 * blk + 8 * sb;
       float Gb[8], kv[8], bv[8], sq[8], P3[8], P2[8], dG[8], x[8], y[8];
@@ -953,7 +956,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
           stf<T>(smem + beta_tile_offset(blk), (8 * sb + t) * kDim + kc, failed ? poison_nan() : kv[t] * P2[t]);
         }
         if (kF32Grads && there(i0 + t)) stf<O>(p.dbeta, idx, failed ? poison_nan() : kv[t] * P2[t]);
-        dGv[8 * sb + t] = dGt;
+        stf<float>(smem + kOffTileG, (i0 + t) * kDim + kc, dGt);
         tot += dGt;
       }
     }
@@ -961,7 +964,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     __syncthreads();
     if (blk == 3) {
       const float end_term = ms.xe[0][kc] + ms.xe[1][kc] + ms.xe[2][kc] + ms.xe[3][kc] + __expf(gend) * dd_k;
-      dGv[15] += end_term;
+      *reinterpret_cast<float*>(smem + kOffTileG + (63 * kDim + kc) * 4) += end_term;
       tot += end_term;
     }
     ms.xt[blk][kc] = tot;
@@ -974,13 +977,13 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     if (!kRagged || 16 * blk + 16 <= n_valid) {  // the whole 16-token block exists (warp-uniform)
 #pragma unroll
       for (int t = 15; t >= 0; --t) {
-        run += dGv[t];
+        run += ldf<float>(smem + kOffTileG, (16 * blk + t) * kDim + kc);
         stf<G>(p.dg, seq_idx(16 * blk + t) + kc, failed ? poison_nan() : run);
       }
     } else {
 #pragma unroll
       for (int t = 15; t >= 0; --t) {
-        run += dGv[t];
+        run += ldf<float>(smem + kOffTileG, (16 * blk + t) * kDim + kc);
         if (16 * blk + t < n_valid) stf<G>(p.dg, seq_idx(16 * blk + t) + kc, failed ? poison_nan() : run);
       }
     }
