@@ -68,9 +68,24 @@ constexpr int kPrologueNorm = GDN2_PROLOGUE_NORMALIZE_QK;   // q, k are raw proj
 constexpr int kPrologueGate = GDN2_PROLOGUE_ACTIVATE_GATES; // beta, w, g are pre-activations
 constexpr float kPrologueEps = 1e-6f;
 
-__device__ __forceinline__ float prologue_sigmoid(float x) { return 1.f / (1.f + expf(-x)); }
-// log-decay g = -softplus(x); softplus(x) equals x to fp32 precision beyond 20
-__device__ __forceinline__ float prologue_log_decay(float x) { return x > 20.f ? -x : -log1pf(expf(x)); }
+// The activations inside the forward kernels run on the special-function unit (ex2 / lg2 / rcp
+// approximations, about 1e-6 relative, far below the 16-bit inputs' own rounding): the library routines
+// (expf, log1pf, a full division) made the prologue half of the prep kernel's code and two thirds again
+// of its time.  (The stand-alone activation kernel of a training step is memory-bound and keeps them.)
+__device__ __forceinline__ float prologue_sigmoid(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + __expf(-x)));
+  return r;
+}
+// log-decay g = -softplus(x) = -log(1 + e^x).  Small e^x: the series e - e^2/2 + e^3/3 (its first
+// dropped term is below 2^-26 of the sum there; lg2 of a number next to 1 would lose the digits);
+// softplus(x) equals x to fp32 precision beyond 20.
+__device__ __forceinline__ float prologue_log_decay(float x) {
+  const float e = __expf(fminf(x, 20.f));
+  const float series = e * (1.f - e * (0.5f - e * 0.33333334f));
+  const float direct = __logf(1.f + e);
+  return x > 20.f ? -x : -(e < 0.00390625f ? series : direct);
+}
 
 // ---- host-side status helpers ---------------------------------------------------
 void record_cuda_error(cudaError_t err);  // defined in api.cu
