@@ -516,9 +516,11 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
   uint32_t iter = 0;
   for (int64_t ch = blockIdx.x; ch < p.n_ch; ch += gridDim.x, ++iter) {
   const uint32_t par = iter & 1u;
-  const int64_t h = ch % p.H;
-  const int64_t c = (ch / p.H) % p.n_chunks;
-  const int64_t b = ch / (p.H * p.n_chunks);
+  // (unit numbers fit 31 bits, the launcher checks: 32-bit divisions, a fraction of the 64-bit routine)
+  const uint32_t bc32 = uint32_t(ch) / uint32_t(p.H);
+  const int64_t h = uint32_t(ch) - bc32 * uint32_t(p.H);
+  const int64_t b = bc32 / uint32_t(p.n_chunks);
+  const int64_t c = bc32 - uint32_t(b) * uint32_t(p.n_chunks);
   const int64_t t0 = c * kChunk;
   auto seq_idx = [&](int tok) { return ((b * p.T + t0 + tok) * p.H + h) * int64_t(kDim); };
   // tokens of this chunk that exist: 64 except in the last chunk of a ragged sequence, whose missing
