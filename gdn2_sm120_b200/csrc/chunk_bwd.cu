@@ -663,9 +663,9 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
         }
       }
     }
-    // a warp's four tokens exist all (every warp of a full chunk: the plain sequence of stores) or only
-    // some (one warp of the last chunk of a ragged sequence at most): warp-uniform choice, no predicate
-    // on the common path
+    // (the ragged instantiation has the one, predicated copy of these stores: a second, unpredicated copy
+    // for the warps whose tokens all exist made it slower, that kernel is close to the size of the
+    // instruction cache)
     auto store_dv_dw = [&](auto guarded) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -682,7 +682,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
         }
       }
     };
-    if (!kRagged || 4 * tg + 4 <= n_valid) store_dv_dw(std::false_type{});
+    if (!kRagged) store_dv_dw(std::false_type{});
     else store_dv_dw(std::true_type{});
   }
   // ---- M4 (second half) once the second half of dS_1 has landed -----------------------------------------
@@ -976,7 +976,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     for (int bq = 3; bq > 0; --bq) {
       if (bq > blk) run += ms.xt[bq][kc];
     }
-    if (!kRagged || 16 * blk + 16 <= n_valid) {  // the whole 16-token block exists (warp-uniform)
+    if (!kRagged) {
 #pragma unroll
       for (int t = 15; t >= 0; --t) {
         run += ldf<float>(smem + kOffTileG, (16 * blk + t) * kDim + kc);
