@@ -429,6 +429,10 @@ __device__ __forceinline__ void store4v<__half>(void* base, int64_t idx, float a
 __device__ __forceinline__ float anchored_k(float k, float decay, float far, bool use_far) {
   return to_tf32(k * (use_far ? decay * far : decay));
 }
+// the same product for the tile itself, which only the tensor cores read (they drop the low bits themselves)
+__device__ __forceinline__ float anchored_k_operand(float k, float decay, float far, bool use_far) {
+  return to_tf32_operand(k * (use_far ? decay * far : decay));
+}
 
 __device__ __forceinline__ void tmem_ld8f(uint32_t taddr, float (&x)[8]) {
   uint32_t r[8];
@@ -724,7 +728,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
     for (int j = 0; j < 16; ++j) {
       const int col = c0 + j;
       const float x = __uint_as_float(raw[j]);
-      vals[j] = to_tf32((r < 64) ? ((col < i) ? -x : 0.f) : ((col <= i) ? x : 0.f));
+      vals[j] = to_tf32_operand((r < 64) ? ((col < i) ? -x : 0.f) : ((col <= i) ? x : 0.f));
       *reinterpret_cast<float*>(tr_base + (col >> 3) * kRsS + (i >> 2) * kCsS + (col & 7) * 16 + (i & 3) * 4) = vals[j];
     }
 #pragma unroll
@@ -747,8 +751,8 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
         const float Gi = Gc[e][f] + ms.part[tg][kc];
         Gc[e][f] = Gi;
         const float anchored = __expf(Gi - ms.part[4 * mb][kc]);
-        eat[e][f] = to_tf32(bb[e][f] * kk[e][f] * anchored);
-        qat[e][f] = to_tf32(p.scale * qq[e][f] * anchored);
+        eat[e][f] = to_tf32_operand(bb[e][f] * kk[e][f] * anchored);
+        qat[e][f] = to_tf32_operand(p.scale * qq[e][f] * anchored);
       }
     }
 #pragma unroll
@@ -780,7 +784,7 @@ chunk_bwd_vjp_kernel(const VjpParams p, const __grid_constant__ CUtensorMap tm_s
           const float far = (I > mb + 1) ? __expf(ms.part[4 * I][kc] - a_nx) : 1.f;
           float val[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) val[e] = anchored_k(kk[e][f], (I == mb) ? own[e] : nb[e], far, I > mb + 1);
+          for (int e = 0; e < 4; ++e) val[e] = anchored_k_operand(kk[e][f], (I == mb) ? own[e] : nb[e], far, I > mb + 1);
           *reinterpret_cast<float4*>(smem + kit_offset(I) + blk_off<4>(kc, 4 * tg, kit_rs(I), 128)) =
               make_float4(val[0], val[1], val[2], val[3]);
         }

@@ -286,13 +286,13 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
       const float nb = own * c_nx[f];                // exp(a_nx - G_i) <= 1: decay from token i to the next block start
       const float bk = bb[e][f] * kk[e][f];
       const float sq = p.scale * qq[e][f];
-      ea[f] = to_tf32(bk * anchored);
-      qa[f] = to_tf32(sq * anchored);
-      ebar[e][f] = to_tf32(bk * anchored * e_amb[f]);
-      qgam[f] = to_tf32(sq * anchored * e_amb[f]);
-      kown[f] = to_tf32(kk[e][f] * own);
+      ea[f] = to_tf32_operand(bk * anchored);
+      qa[f] = to_tf32_operand(sq * anchored);
+      ebar[e][f] = to_tf32_operand(bk * anchored * e_amb[f]);
+      qgam[f] = to_tf32_operand(sq * anchored * e_amb[f]);
+      kown[f] = to_tf32_operand(kk[e][f] * own);
       knb[f] = kk[e][f] * nb;
-      ktail[f] = to_tf32(knb[f] * t_end[f]);
+      ktail[f] = to_tf32_operand(knb[f] * t_end[f]);
     }
     // Gram A operand rows i (erase) and 64 + i (query), tf32, K-major, padded chunk stride
     *reinterpret_cast<float4*>(sm.gram_a + (i >> 3) * kRsN + c4 * kCsN + (i & 7) * 16) =
@@ -305,14 +305,14 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
         make_float4(kown[0], kown[1], kown[2], kown[3]);
     if (mb + 1 < 4) {
       *reinterpret_cast<float4*>(sm.gram_b + gram_b_offset(mb + 1) + row_off) =
-          make_float4(to_tf32(knb[0]), to_tf32(knb[1]), to_tf32(knb[2]), to_tf32(knb[3]));
+          make_float4(to_tf32_operand(knb[0]), to_tf32_operand(knb[1]), to_tf32_operand(knb[2]), to_tf32_operand(knb[3]));
     }
 #pragma unroll
     for (int far = 0; far < 2; ++far) {
       if (mb + 2 + far < 4) {
         *reinterpret_cast<float4*>(sm.gram_b + gram_b_offset(mb + 2 + far) + row_off) =
-            make_float4(to_tf32(knb[0] * t_far[far][0]), to_tf32(knb[1] * t_far[far][1]),
-                        to_tf32(knb[2] * t_far[far][2]), to_tf32(knb[3] * t_far[far][3]));
+            make_float4(to_tf32_operand(knb[0] * t_far[far][0]), to_tf32_operand(knb[1] * t_far[far][1]),
+                        to_tf32_operand(knb[2] * t_far[far][2]), to_tf32_operand(knb[3] * t_far[far][3]));
       }
     }
     // token-major tiles Q[i][k] and Kn[i][k]: the 16 lanes of a token write 256 consecutive bytes
@@ -362,7 +362,7 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
 #pragma unroll
       for (int f = 0; f < 4; ++f) {
         if (pro_gate) ww[f] = (4 * tg + e < n_valid) ? prologue_sigmoid(ww[f]) : 0.f;
-        zz[e][f] = to_tf32(vv[f] * ww[f]);
+        zz[e][f] = to_tf32_operand(vv[f] * ww[f]);
       }
     }
 #pragma unroll
@@ -392,7 +392,7 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
       const bool mine_lo = (my_I == I_lo);
       const float x = mine_lo ? (need_lo ? __uint_as_float(lo[j]) : 0.f) : (need_hi ? __uint_as_float(hi[j]) : 0.f);
       const int col = c0 + j;
-      vals[j] = (r < 64) ? ((col < i) ? x : 0.f) : ((col <= i) ? to_tf32(x) : 0.f);
+      vals[j] = (r < 64) ? ((col < i) ? x : 0.f) : ((col <= i) ? to_tf32_operand(x) : 0.f);
     }
     if (r < 64) {
 #pragma unroll
@@ -538,7 +538,7 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
       const int i = e & 63, c4t = e >> 6;  // consecutive threads -> consecutive rows -> contiguous 16-byte chunks
       const float4 tn = ld4(Tn + i * kLd + 4 * c4t);
       *reinterpret_cast<float4*>(sm.tmat + blk_off<4>(i, 4 * c4t, 2048, 128)) =
-          make_float4(to_tf32(tn.x), to_tf32(tn.y), to_tf32(tn.z), to_tf32(tn.w));
+          make_float4(to_tf32_operand(tn.x), to_tf32_operand(tn.y), to_tf32_operand(tn.z), to_tf32_operand(tn.w));
     }
     if (training) {
       float* tile_tt = reinterpret_cast<float*>(p.tiles.tt + int64_t(ch) * kTileTt);
@@ -547,7 +547,7 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
         if (j >= 32 && c4t < 8) continue;    // the zero quadrant j >= 32, i < 32 stays unwritten
         const float4 tc = ld4(Tc + j * kLd + 4 * c4t);
         *reinterpret_cast<float4*>(tile_tt + j * kChunk + 4 * c4t) =
-            make_float4(to_tf32(tc.x), to_tf32(tc.y), to_tf32(tc.z), to_tf32(tc.w));
+            make_float4(to_tf32_operand(tc.x), to_tf32_operand(tc.y), to_tf32_operand(tc.z), to_tf32_operand(tc.w));
       }
     }
   }
@@ -590,7 +590,7 @@ chunk_prep_kernel(const PrepParams p, const __grid_constant__ CUtensorMap tm_g,
         tmem_ld16(tmem_addr(tb, 32 * q4, c0), r);
         tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) tile_yt[(c0 + j) * kChunk] = to_tf32(__uint_as_float(r[j]));
+        for (int j = 0; j < 16; ++j) tile_yt[(c0 + j) * kChunk] = to_tf32_operand(__uint_as_float(r[j]));
       }
     }
     // U^T (lanes = values v; kept in full fp32): U[j][v]; each warp of a quadrant takes 16 tokens

@@ -287,6 +287,10 @@ __device__ __forceinline__ void store_global_32b(void* ptr, float4 lo, float4 hi
 __device__ __forceinline__ float to_tf32(float x) {
   return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
 }
+// The same rounding for a value that only the tensor cores will read (an operand tile in shared memory, a
+// tile in the workspace): they ignore the 13 low bits of the container, so adding half a unit is all it
+// takes and the mask can stay away.  Anything the CUDA cores multiply by as well needs to_tf32.
+__device__ __forceinline__ float to_tf32_operand(float x) { return __uint_as_float(__float_as_uint(x) + 0x1000u); }
 
 }  // namespace tc
 }  // namespace gdn2
