@@ -285,7 +285,9 @@ int gdn2_gate_prologue(const void* q_raw, const void* k_raw, const void* g_raw, 
 /*
  * Forward entry points with the prologue fused in: the kernels activate the raw tensors as they load
  * them (gate flags) and scale by the reciprocal row norms they compute on the way (normalisation
- * flag), so an inference call never materialises the activated tensors.  `prologue` is a
+ * flag), so an inference call never materialises the activated tensors (the activations use the
+ * hardware's exp2 / log2 / reciprocal approximations, about 1e-6 relative, where gdn2_gate_prologue
+ * uses the library routines).  `prologue` is a
  * combination of GDN2_PROLOGUE_NORMALIZE_QK and GDN2_PROLOGUE_ACTIVATE_GATES (0 = exactly the
  * plain entry point).  Forward only -- a training call activates with gdn2_gate_prologue, whose
  * outputs backward needs anyway -- hence no checkpoint arguments.  Otherwise as
